@@ -1,0 +1,135 @@
+/* r3d_b200.h -- the C ABI of libr3d_b200.so, a B200 (sm_100a) drop-in for libr3d's
+ * quantised-matmul bands. Two layers, both extern "C", plain pointers and sizes only:
+ *
+ *  (1) The radiance kernel-plugin surface, exactly what the engine's loader binds in
+ *      libr3d (rad_abi.h declares rad_plugin_abi_version / rad_plugin_info /
+ *      rad_kernel_schema_* / rad_kernel_*), plus the row entry symbols below, which the
+ *      reference's dlopen harnesses also bind by name.
+ *  (2) A thin launch layer under the entries (r3d_b200_*): one call per kernel family,
+ *      operands already validated. The entries are host C++; this layer is the only
+ *      place host code crosses into CUDA.
+ *
+ * Every launch is asynchronous on the caller's stream and returns RAD_OK once enqueued.
+ * Citations name the libr3d interface each symbol replaces (path within that project).
+ */
+#ifndef R3D_B200_H
+#define R3D_B200_H
+
+#include "rad_abi.h"
+#ifndef __cplusplus
+#include <stdbool.h>
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ (1) row entries */
+
+/* gemm_nt_q @ fp8a8, any M. Replaces r3d_rad_gemm_nt_q_fp8
+ * (src/r3d_gemm_fp8a8.hip:1055-1085). */
+int r3d_rad_gemm_nt_q_fp8(const RadArgs* a, RadStream s);
+/* gemm_nt_q @ fp8a8, decode band M <= 8. Replaces r3d_rad_gemm_nt_q_fp8_decode
+ * (src/r3d_gemm_fp8a8.hip:1098-1130). */
+int r3d_rad_gemm_nt_q_fp8_decode(const RadArgs* a, RadStream s);
+/* gemm_nt_q @ mxfp4a8, any M. Replaces r3d_rad_gemm_nt_q
+ * (src/r3d_gemm_mxfp4.hip:1587-1691). */
+int r3d_rad_gemm_nt_q(const RadArgs* a, RadStream s);
+/* gemm_nt_q @ mxfp4a8, decode band M <= 8, fp32 walk. Replaces
+ * r3d_rad_gemm_nt_q_mxfp4_decode (src/r3d_gemm_mxfp4.hip:1715-1716). */
+int r3d_rad_gemm_nt_q_mxfp4_decode(const RadArgs* a, RadStream s);
+/* gemm_nt_q @ mxfp4a8, decode band, int8-per-32 activation arm. Replaces
+ * r3d_rad_gemm_nt_q_mxfp4_decode_q8x (src/r3d_gemm_mxfp4.hip:1717-1718). */
+int r3d_rad_gemm_nt_q_mxfp4_decode_q8x(const RadArgs* a, RadStream s);
+/* The q8x OFF lever (R3D_MXFP4_Q8X=0). Replaces r3d_mxfp4_q8x_off
+ * (src/r3d_gemm_mxfp4.hip:1724-1730). */
+bool r3d_mxfp4_q8x_off(void);
+/* logits_gemm over the joined e4m3 + block-scale head, f32 logits. Replaces
+ * r3d_rad_logits_gemm_e4m3 (src/r3d_gemm_logits.hip:145-226). */
+int r3d_rad_logits_gemm_e4m3(const RadArgs* a, RadStream s);
+/* Layout hooks of that row. Replace r3d_layout_head / r3d_relayout_head /
+ * r3d_unrelayout_head (src/r3d_gemm_logits.hip:233-272). */
+int r3d_layout_head(const RadParam* p, int n_p, int operand, const RadEncoding* enc,
+                    const int* sel, const RadTensor* planes, int n, RadLayout* out);
+int r3d_relayout_head(const RadParam* p, int n_p, int operand, const RadEncoding* enc,
+                      const int* sel, const RadTensor* planes, int n, void* dst,
+                      int64_t dst_bytes);
+int r3d_unrelayout_head(const RadParam* p, int n_p, int operand, const RadEncoding* enc,
+                        const int* sel, const void* src, int64_t src_bytes,
+                        const RadTensor* planes, int n);
+
+/* ------------------------------------------------------------------ (2) launch layer */
+
+/* Which kernel serves a call. AUTO picks by shape and alignment the way the entries do. */
+enum {
+    R3D_ARM_AUTO   = 0,
+    R3D_ARM_EXACT  = 1,   /* oracle-order walk: bit-identical to the CPU restatement */
+    R3D_ARM_STREAM = 2,   /* weight-streaming tensor-core walk, M <= 64 */
+    R3D_ARM_TILE   = 3    /* tcgen05 tile, prefill M */
+};
+
+/* Operands of one gemm_nt_q call. Pitches are in elements of the tensor they belong to,
+ * except b_pitch of a packed e2m1 weight, which is in bytes (K/2). */
+typedef struct R3dGemmQ {
+    const void*  a;         /* e4m3 codes [M, K] */
+    const float* a_scale;   /* f32 [M, as_cols] */
+    const void*  b;         /* e4m3 codes [N, K]   |  e2m1 nibbles [N, K/2 bytes] */
+    const void*  b_scale;   /* bf16|f32 [N/rblk, bs_cols]  |  E8M0 bytes [N, K/32] */
+    void*        y;         /* bf16 [M, N] */
+    int32_t      m, n, k;
+    int32_t      as_cols, bs_cols;
+    int32_t      rblk;      /* fp8a8: weight rows one scale row covers (1 or 128) */
+    int32_t      bs_dtype;  /* fp8a8: RAD_BF16 or RAD_F32 */
+    int64_t      a_pitch, b_pitch, y_pitch, as_pitch, bs_pitch;
+    int32_t      arm;
+    int32_t      reserved;
+} R3dGemmQ;
+
+/* Replaces the kernel dispatch inside f8_launch_tile (src/r3d_gemm_fp8a8.hip:926-1050). */
+int r3d_b200_gemm_fp8a8(const R3dGemmQ* q, void* stream);
+/* Replaces the kernel dispatch of r3d_gemm_nt_q_impl and the fp32 decode walk
+ * (src/r3d_gemm_mxfp4.hip:1613-1690, :2125-2169). */
+int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream);
+/* The int8-per-32 arm: requantise the activation into x8/sg (caller-owned scratch,
+ * x8 >= m*k bytes, sg >= m*k/32 floats), then the dot. walk 0 = per-256 tree, 1 = lane
+ * map. Replaces m4_act_i8_kernel + gemm_nt_mxfp4_gemv_q8x[_lm]_kernel
+ * (src/r3d_gemm_mxfp4.hip:1150-1166, :1217-1458); needs no repacked weight plane. */
+int r3d_b200_gemm_mxfp4a8_q8x(const R3dGemmQ* q, int8_t* x8, float* sg, int walk,
+                              void* stream);
+
+typedef struct R3dLogits {
+    const void* x;          /* bf16 [M, K] */
+    const void* codes;      /* e4m3 [N, K] dense   |  e2m1 nibbles (head_fmt 1) */
+    const void* scale;      /* bf16|f16|f32 [ceil(N/br), ceil(K/128)]  |  E8M0 [N, K/32] */
+    void*       y;          /* f32 [M, N] (y_dtype RAD_F32) or bf16 (RAD_BF16) */
+    int32_t     m, n, k;
+    int32_t     br;         /* weight rows per scale row: 1 or 128 */
+    int32_t     scale_dtype;
+    int32_t     y_dtype;
+    int32_t     head_fmt;   /* 0 = e4m3 + block scale (the reference head), 1 = mxfp4 */
+    int32_t     arm;
+    int64_t     x_pitch, code_pitch, y_pitch, scale_pitch;
+} R3dLogits;
+
+/* Replaces the launch of logits_e4m3_kernel (src/r3d_gemm_logits.hip:196-221). */
+int r3d_b200_logits(const R3dLogits* l, void* stream);
+
+/* Activation producer: per (row, group) amax/448 scale and RTNE-saturating e4m3 codes.
+ * x_dtype RAD_BF16 or RAD_F32. Replaces quant_act_fp8_kernel (src/r3d_band.hip:119-153). */
+int r3d_b200_quant_act_fp8(const void* x, int32_t x_dtype, int64_t x_pitch, void* q,
+                           int64_t q_pitch, float* scale, int64_t s_pitch, int32_t rows,
+                           int32_t n, int32_t group, void* stream);
+
+/* Which arm AUTO would pick for this call (no launch): for tests and debug prints, the
+ * role R3D_DEBUG_GEMM's "which arm launched" lines play in the reference
+ * (src/r3d_gemm_fp8a8.hip:976-983). */
+int r3d_b200_pick_arm_fp8a8(const R3dGemmQ* q);
+int r3d_b200_pick_arm_mxfp4a8(const R3dGemmQ* q);
+
+/* Kernels this library launched since load (all arms): bench bookkeeping. */
+long long r3d_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* R3D_B200_H */

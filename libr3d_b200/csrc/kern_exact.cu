@@ -1,0 +1,326 @@
+/* kern_exact.cu -- the oracle-order arm of every band.
+ *
+ * These kernels perform the float operations of libr3d's stated arithmetic in exactly the
+ * stated order, so their output is bit-identical to a scalar CPU walk of the same rule:
+ *   fp8a8    src/r3d_gemm_fp8a8.hip:9-15   per 128-of-K group: ascending f32 sum of exact
+ *            products, then acc += (sub * sa) * sb
+ *   mxfp4a8  src/r3d_gemm_mxfp4.hip:14-15  per 32-of-K group: ascending f32 sum, then
+ *            acc += (sub * sa[g/4]) * 2^(x-127)
+ *   logits   src/r3d_gemm_logits.hip:5-9   w = code * scale rounded once, one fma chain
+ *            per output over ascending k
+ * They accept any alignment and any legal shape, which makes them the arm every other
+ * kernel is cross-checked against on the device and the fallback for geometries the
+ * streaming arms cannot take. Speed is secondary: a lane owns whole scale groups so the
+ * group sum needs no cross-lane step, and the 32 group terms of one sweep are then added
+ * in group order through shuffles (each lane performs the same additions).
+ *
+ * Build with -fmad=false: a contracted mul+add would be a different rounding.
+ */
+#include "r3d_kernels.h"
+#include "r3d_numerics.cuh"
+
+namespace r3d {
+
+__device__ __forceinline__ float ld_scale_any(const void* base, int64_t idx, int dt) {
+    if (dt == RAD_F32) return ((const float*)base)[idx];
+    if (dt == RAD_F16) return f16_to_f32(((const uint16_t*)base)[idx]);
+    return bf16_to_f32(((const uint16_t*)base)[idx]);
+}
+
+/* column of a scale grid with `cols` columns that covers 128-of-K chunk c of nchunk */
+__device__ __forceinline__ int scale_col(int c, int cols, int nchunk) {
+    return cols == nchunk ? c : (cols == 1 ? 0 : (int)((int64_t)c * cols / nchunk));
+}
+
+/* Add the 32 lane terms of one sweep to acc in lane order; lanes >= nlive hold no term. */
+__device__ __forceinline__ float ordered_add(float acc, float term, int nlive) {
+#pragma unroll 8
+    for (int j = 0; j < 32; ++j) {
+        const float t = __shfl_sync(0xffffffffu, term, j);
+        if (j < nlive) acc = __fadd_rn(acc, t);
+    }
+    return acc;
+}
+
+/* ------------------------------------------------------------------ fp8a8 */
+template <int MT>
+__global__ __launch_bounds__(128) void k_fp8a8_exact(const R3dGemmQ p, const int m0) {
+    __shared__ float lut[256];
+    for (int i = threadIdx.x; i < 256; i += 128) lut[i] = e4m3_to_f32((uint8_t)i);
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (r >= p.n) return;
+    const int live = min(MT, p.m - m0);
+    const int ngrp = p.k >> 7;
+    const uint8_t* A = (const uint8_t*)p.a;
+    const uint8_t* brow = (const uint8_t*)p.b + (int64_t)r * p.b_pitch;
+    const int64_t srow = p.rblk > 1 ? r / p.rblk : r;
+
+    float acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = 0.0f;
+
+    for (int g0 = 0; g0 < ngrp; g0 += 32) {
+        const int g = g0 + lane;
+        float term[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) term[m] = 0.0f;
+        if (g < ngrp) {
+            float part[MT];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) part[m] = 0.0f;
+            const uint8_t* bw = brow + ((int64_t)g << 7);
+            for (int s = 0; s < 128; ++s) {
+                const float b = lut[bw[s]];
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+                    if (m < live) {
+                        const float a = lut[A[(int64_t)(m0 + m) * p.a_pitch + ((int64_t)g << 7) + s]];
+                        part[m] = __fadd_rn(part[m], __fmul_rn(a, b));
+                    }
+            }
+            const float sb = ld_scale_any(p.b_scale,
+                                          srow * p.bs_pitch + scale_col(g, p.bs_cols, ngrp),
+                                          p.bs_dtype);
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+                if (m < live) {
+                    const float sa = p.a_scale[(int64_t)(m0 + m) * p.as_pitch +
+                                               scale_col(g, p.as_cols, ngrp)];
+                    term[m] = __fmul_rn(__fmul_rn(part[m], sa), sb);
+                }
+        }
+        const int nlive = min(32, ngrp - g0);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[m] = ordered_add(acc[m], term[m], nlive);
+    }
+    if (lane == 0) {
+        uint16_t* Y = (uint16_t*)p.y;
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+            if (m < live) Y[(int64_t)(m0 + m) * p.y_pitch + r] = f32_to_bf16(acc[m]);
+    }
+}
+
+/* ------------------------------------------------------------------ mxfp4a8 */
+template <int MT>
+__global__ __launch_bounds__(128) void k_mxfp4a8_exact(const R3dGemmQ p, const int m0) {
+    __shared__ float lut[256];
+    for (int i = threadIdx.x; i < 256; i += 128) lut[i] = e4m3_to_f32((uint8_t)i);
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (r >= p.n) return;
+    const int live = min(MT, p.m - m0);
+    const int ngrp = (p.k + 31) >> 5;
+    const int n128 = (p.k + 127) >> 7;
+    const uint8_t* A = (const uint8_t*)p.a;
+    const uint8_t* brow = (const uint8_t*)p.b + (int64_t)r * p.b_pitch;
+    const uint8_t* srow = (const uint8_t*)p.b_scale + (int64_t)r * p.bs_pitch;
+
+    float acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = 0.0f;
+
+    for (int g0 = 0; g0 < ngrp; g0 += 32) {
+        const int g = g0 + lane;
+        float term[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) term[m] = 0.0f;
+        if (g < ngrp) {
+            float part[MT];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) part[m] = 0.0f;
+            const int k0 = g << 5;
+            const int kn = min(32, p.k - k0);
+            for (int j = 0; j < kn; ++j) {
+                const uint8_t byte = brow[(k0 + j) >> 1];
+                const float w = e2m1_to_f32((j & 1) ? (uint8_t)(byte >> 4) : (uint8_t)(byte & 15));
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+                    if (m < live) {
+                        const float a = lut[A[(int64_t)(m0 + m) * p.a_pitch + k0 + j]];
+                        part[m] = __fadd_rn(part[m], __fmul_rn(a, w));
+                    }
+            }
+            const float sc = e8m0_to_f32(srow[g]);
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+                if (m < live) {
+                    const float sa = p.a_scale[(int64_t)(m0 + m) * p.as_pitch +
+                                               scale_col(g >> 2, p.as_cols, n128)];
+                    term[m] = __fmul_rn(__fmul_rn(part[m], sa), sc);
+                }
+        }
+        const int nlive = min(32, ngrp - g0);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[m] = ordered_add(acc[m], term[m], nlive);
+    }
+    if (lane == 0) {
+        uint16_t* Y = (uint16_t*)p.y;
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+            if (m < live) Y[(int64_t)(m0 + m) * p.y_pitch + r] = f32_to_bf16(acc[m]);
+    }
+}
+
+/* ------------------------------------------------------------------ logits
+ * One thread per head row: the oracle's single fma chain cannot be split and stay
+ * bit-identical. */
+template <int MT>
+__global__ __launch_bounds__(128) void k_logits_exact(const R3dLogits p, const int m0) {
+    __shared__ float lut[256];
+    for (int i = threadIdx.x; i < 256; i += 128) lut[i] = e4m3_to_f32((uint8_t)i);
+    __syncthreads();
+    const int n = blockIdx.x * 128 + threadIdx.x;
+    if (n >= p.n) return;
+    const int live = min(MT, p.m - m0);
+    const uint16_t* X = (const uint16_t*)p.x;
+    const uint8_t* crow = (const uint8_t*)p.codes + (int64_t)n * p.code_pitch;
+    float acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = 0.0f;
+
+    if (p.head_fmt == 0) {
+        const int64_t sbase = (int64_t)(n / p.br) * p.scale_pitch;
+        for (int k = 0; k < p.k; ++k) {
+            const float sv = ld_scale_any(p.scale, sbase + (k >> 7), p.scale_dtype);
+            const float w = __fmul_rn(lut[crow[k]], sv);
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+                if (m < live)
+                    acc[m] = __fmaf_rn(bf16_to_f32(X[(int64_t)(m0 + m) * p.x_pitch + k]), w, acc[m]);
+        }
+    } else {
+        const uint8_t* srow = (const uint8_t*)p.scale + (int64_t)n * p.scale_pitch;
+        for (int k = 0; k < p.k; ++k) {
+            const uint8_t byte = crow[k >> 1];
+            const float w = __fmul_rn(
+                e2m1_to_f32((k & 1) ? (uint8_t)(byte >> 4) : (uint8_t)(byte & 15)),
+                e8m0_to_f32(srow[k >> 5]));
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+                if (m < live)
+                    acc[m] = __fmaf_rn(bf16_to_f32(X[(int64_t)(m0 + m) * p.x_pitch + k]), w, acc[m]);
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+        if (m < live) {
+            if (p.y_dtype == RAD_F32)
+                ((float*)p.y)[(int64_t)(m0 + m) * p.y_pitch + n] = acc[m];
+            else
+                ((uint16_t*)p.y)[(int64_t)(m0 + m) * p.y_pitch + n] = f32_to_bf16(acc[m]);
+        }
+}
+
+/* ------------------------------------------------------------------ quant_act_fp8
+ * src/r3d_band.hip:119-153. One block per (row, group). */
+__global__ __launch_bounds__(128) void k_quant_act_fp8(
+    const void* __restrict__ x, const int x_dtype, const int64_t x_pitch,
+    uint8_t* __restrict__ q, const int64_t q_pitch, float* __restrict__ scale,
+    const int64_t s_pitch, const int n, const int group, const int ngrp) {
+    __shared__ float red[4];
+    __shared__ float s_sc;
+    const int row = blockIdx.x / ngrp, gi = blockIdx.x - row * ngrp;
+    const int k0 = gi * group, k1 = min(k0 + group, n);
+    auto ld = [&](int k) -> float {
+        return x_dtype == RAD_F32 ? ((const float*)x)[(int64_t)row * x_pitch + k]
+                                  : bf16_to_f32(((const uint16_t*)x)[(int64_t)row * x_pitch + k]);
+    };
+    float amax = 0.0f;
+    for (int k = k0 + threadIdx.x; k < k1; k += 128) {
+        const float m = fabsf(ld(k));
+        if (m > amax) amax = m;                 /* strict >: NaN never wins */
+    }
+    for (int off = 16; off; off >>= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, amax, off);
+        if (o > amax) amax = o;
+    }
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float r = red[0];
+        for (int w = 1; w < 4; ++w) if (red[w] > r) r = red[w];
+        const float sc = r > 0.0f ? __fmul_rn(r, 1.0f / 448.0f) : 1.0f;
+        s_sc = sc;
+        scale[(int64_t)row * s_pitch + gi] = sc;
+    }
+    __syncthreads();
+    const float inv = __fdiv_rn(1.0f, s_sc);
+    for (int k = k0 + threadIdx.x; k < k1; k += 128) {
+        float c = __fmul_rn(ld(k), inv);
+        if (c > 448.0f) c = 448.0f;
+        if (c < -448.0f) c = -448.0f;
+        q[(int64_t)row * q_pitch + k] = f32_to_e4m3(c);
+    }
+}
+
+/* ------------------------------------------------------------------ launchers */
+
+template <typename P, typename F>
+static int launch_mt(F launch, const P& p) {
+    /* rows in tiles of 8 tokens; a tile of fewer rides the smallest bucket that holds it
+     * (the ladder rounds UP: src/r3d_gemm_fp8a8.hip:992-997) */
+    for (int m0 = 0; m0 < p.m; m0 += 8) {
+        const int left = p.m - m0;
+        launch(left <= 1 ? 1 : left <= 2 ? 2 : left <= 4 ? 4 : 8, m0);
+    }
+    return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+}
+
+int exact_fp8a8(const R3dGemmQ& p, cudaStream_t st) {
+    const dim3 grid((unsigned)((p.n + 3) / 4));
+    return launch_mt(
+        [&](int mt, int m0) {
+            count_launch();
+            switch (mt) {
+                case 1: k_fp8a8_exact<1><<<grid, 128, 0, st>>>(p, m0); break;
+                case 2: k_fp8a8_exact<2><<<grid, 128, 0, st>>>(p, m0); break;
+                case 4: k_fp8a8_exact<4><<<grid, 128, 0, st>>>(p, m0); break;
+                default: k_fp8a8_exact<8><<<grid, 128, 0, st>>>(p, m0); break;
+            }
+        }, p);
+}
+
+int exact_mxfp4a8(const R3dGemmQ& p, cudaStream_t st) {
+    const dim3 grid((unsigned)((p.n + 3) / 4));
+    return launch_mt(
+        [&](int mt, int m0) {
+            count_launch();
+            switch (mt) {
+                case 1: k_mxfp4a8_exact<1><<<grid, 128, 0, st>>>(p, m0); break;
+                case 2: k_mxfp4a8_exact<2><<<grid, 128, 0, st>>>(p, m0); break;
+                case 4: k_mxfp4a8_exact<4><<<grid, 128, 0, st>>>(p, m0); break;
+                default: k_mxfp4a8_exact<8><<<grid, 128, 0, st>>>(p, m0); break;
+            }
+        }, p);
+}
+
+int exact_logits(const R3dLogits& p, cudaStream_t st) {
+    const dim3 grid((unsigned)((p.n + 127) / 128));
+    return launch_mt(
+        [&](int mt, int m0) {
+            count_launch();
+            switch (mt) {
+                case 1: k_logits_exact<1><<<grid, 128, 0, st>>>(p, m0); break;
+                case 2: k_logits_exact<2><<<grid, 128, 0, st>>>(p, m0); break;
+                case 4: k_logits_exact<4><<<grid, 128, 0, st>>>(p, m0); break;
+                default: k_logits_exact<8><<<grid, 128, 0, st>>>(p, m0); break;
+            }
+        }, p);
+}
+
+int launch_quant_act_fp8(const void* x, int x_dtype, int64_t x_pitch, void* q, int64_t q_pitch,
+                         float* scale, int64_t s_pitch, int rows, int n, int group,
+                         cudaStream_t st) {
+    if (group <= 0 || group > n) group = n;
+    const int ngrp = (n + group - 1) / group;
+    count_launch();
+    k_quant_act_fp8<<<(unsigned)(rows * ngrp), 128, 0, st>>>(
+        x, x_dtype, x_pitch, (uint8_t*)q, q_pitch, scale, s_pitch, n, group, ngrp);
+    return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+}
+
+} /* namespace r3d */

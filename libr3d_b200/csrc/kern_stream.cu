@@ -1,0 +1,530 @@
+/* kern_stream.cu -- the weight-streaming arm of the decode / verify bands (M <= 64).
+ *
+ * At these M every band is bound by how fast the weight plane leaves HBM, so the kernel is
+ * built around the stream and the arithmetic is made free:
+ *
+ *   producer warp   cp.async.bulk (the TMA unit's untiled copy) pulls one row segment per
+ *                   instruction from HBM into a ring of shared-memory stages, completion
+ *                   counted on an mbarrier per stage; rows land at a padded pitch so the
+ *                   consumers' fragment reads are bank-conflict free.
+ *   consumer warps  each owns 16 weight rows. Weight rows sit on the M axis of
+ *                   mma.sync.m16n8k32 (e4m3) / m16n8k16 (bf16), the <= 8 tokens of an n-tile
+ *                   on the N axis, so one instruction retires 512 weight elements whatever
+ *                   M is. K positions inside an MMA are permuted so that a lane's fragment
+ *                   registers are the contiguous bytes it loaded (the same permutation is
+ *                   applied to the activation fragment, so the dot product is unchanged).
+ *   formats         fp8a8: codes feed the MMA untouched.
+ *                   mxfp4a8: an e2m1 code c maps to the e4m3 byte (c&7)<<2 | (c&8)<<4,
+ *                   which is exactly e2m1(c) * 2^-6 (subnormals included); the 2^6 is
+ *                   folded into the activation scale. One MMA spans exactly one 32-of-K
+ *                   scale group.
+ *                   logits: an e4m3 code b maps to the bf16 pattern (b&0x7f)<<4 | sign,
+ *                   exactly e4m3(b) * 2^-120; bf16 x feeds the MMA untouched.
+ *   flush           scale groups are applied to the f32 MMA result in registers:
+ *                   acc += (sub * sa) * sb per 128 of K (fp8a8, the reference's order);
+ *                   t += sub32 * 2^(x-127) per 32 of K then acc += t * sa per 128
+ *                   (mxfp4a8: (sub*sa)*2^d == (sub*2^d)*sa up to one rounding,
+ *                   src/r3d_gemm_mxfp4.hip:24-27); acc += (sub * 2^120) * s (logits).
+ *
+ * Rounding class: products are exact; sums inside a group are associated by the tensor
+ * core rather than ascending, so results are graded by tolerance against the oracle-order
+ * arm (<= 2 bf16 ulp), not bit for bit -- the class libr3d's own WMMA arms are in
+ * (src/r3d_gemm_fp8a8.hip:346-349).
+ *
+ * Every wait on an mbarrier is bounded; on expiry the kernel records a status word that
+ * r3d_b200_stream_status() reads and leaves without storing.
+ */
+#include "r3d_kernels.h"
+#include "r3d_numerics.cuh"
+#include <cstdio>
+
+namespace r3d {
+
+__device__ int g_stream_status = 0;   /* 0 ok; nonzero = a bounded wait expired */
+
+namespace {
+
+constexpr int kConsumers   = 4;                 /* consumer warps per CTA */
+constexpr int kThreads     = (kConsumers + 1) * 32;
+constexpr int kWarpBytes   = 256;               /* weight bytes per row per warp per stage */
+constexpr int kStages      = 4;
+constexpr long long kSpinCycles = 2000000000LL; /* ~1 s: bound of every barrier wait */
+
+enum { FMT_FP8 = 0, FMT_MXFP4 = 1, FMT_LOGITS = 2 };
+
+struct StreamParams {
+    const uint8_t* w;      int64_t w_pitch;     /* weight plane, bytes per row */
+    const uint8_t* ws;     int64_t ws_pitch;    /* weight scales (format-specific) */
+    const uint8_t* act;    int64_t act_pitch;   /* activation rows, bytes per row */
+    const float*   as;     int64_t as_pitch;    /* activation scales f32 */
+    void*          y;      int64_t y_pitch;
+    int m, n, k;
+    int as_cols, ws_cols, rblk, ws_dtype, y_dtype;
+    int row_bytes;                               /* weight bytes per row that hold K */
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
+                 ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+/* Bounded wait. False = gave up (status word set). */
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try(bar, parity)) {
+        if (clock64() - t0 > kSpinCycles) { atomicExch(&g_stream_status, code); return false; }
+    }
+    return true;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes,
+                                         uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+/* same, accumulating from zero: d = a * b */
+__device__ __forceinline__ void mma_e4m3_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                           uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+/* four e2m1 codes in the low (even k) / high (odd k) nibbles of the bytes of w -> four
+ * e4m3 bytes holding e2m1 * 2^-6 */
+__device__ __forceinline__ uint32_t e2m1_even_to_e4m3(uint32_t w) {
+    return ((w << 2) & 0x1C1C1C1Cu) | ((w << 4) & 0x80808080u);
+}
+__device__ __forceinline__ uint32_t e2m1_odd_to_e4m3(uint32_t w) {
+    return ((w >> 2) & 0x1C1C1C1Cu) | (w & 0x80808080u);
+}
+/* two e4m3 bytes (selected by `sel` into byte lanes 1 and 3) -> two bf16 patterns holding
+ * e4m3 * 2^-120. The NaN code maps to a bf16 NaN. */
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t w, uint32_t sel) {
+    const uint32_t v = prmt(w, 0u, sel);                    /* b1 << 24 | b0 << 8 */
+    uint32_t h = (v & 0x80008000u) | ((v >> 4) & 0x07F007F0u);
+    if (((v & 0x7F007F00u) + 0x01000100u) & 0x80008000u) {  /* a byte is 0x7f: NaN code */
+        if ((v & 0x00007F00u) == 0x00007F00u) h |= 0x00007FC0u;
+        if ((v & 0x7F000000u) == 0x7F000000u) h |= 0x7FC00000u;
+    }
+    return h;
+}
+
+__device__ __forceinline__ float ld_scale(const uint8_t* base, int64_t idx, int dt) {
+    if (dt == RAD_F32) return __ldg((const float*)base + idx);
+    if (dt == RAD_F16) return f16_to_f32(__ldg((const uint16_t*)base + idx));
+    return bf16_to_f32(__ldg((const uint16_t*)base + idx));
+}
+__device__ __forceinline__ int scale_col(int c, int cols, int nchunk) {
+    return cols == nchunk ? c : (cols == 1 ? 0 : (int)((int64_t)c * cols / nchunk));
+}
+
+template <int FMT> struct Geo {
+    /* smem row pitch pad: fragment reads are LDS.128 by (row, quad) for fp8/logits and
+     * LDS.32 by (row, quad) for mxfp4; these pads make a warp's reads conflict free */
+    static constexpr int pad = (FMT == FMT_MXFP4) ? 16 : 64;
+};
+
+/* NT = n-tiles of 8 tokens; KS = warps that split K inside a CTA (1, 2 or 4), the other
+ * 4/KS warps split rows. */
+template <int FMT, int NT, int KS>
+__global__ void __launch_bounds__(kThreads)
+k_stream(const StreamParams P) {
+    constexpr int RW   = kConsumers / KS;          /* row-warps */
+    constexpr int RT   = 16 * RW;                  /* rows per CTA */
+    constexpr int SKB  = kWarpBytes * KS;          /* weight bytes per row per stage */
+    constexpr int PITCH = SKB + Geo<FMT>::pad;
+    constexpr int SCP  = SKB / 16;                 /* mxfp4: scale bytes per row per stage */
+    constexpr int W_BYTES = RT * PITCH;
+    constexpr int S_BYTES = (FMT == FMT_MXFP4) ? RT * SCP : 0;
+    constexpr int STAGE = W_BYTES + S_BYTES;
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full  = (uint64_t*)(smem + kStages * STAGE);
+    uint64_t* empty = full + kStages;
+    float* lut = (float*)(empty + kStages);                 /* mxfp4: E8M0 -> f32 */
+    float* red = lut + 256;                                 /* KS > 1: partial sums */
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r0 = blockIdx.x * RT;
+    const int nks = (P.row_bytes + SKB - 1) / SKB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kConsumers); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (FMT == FMT_MXFP4)
+        for (int i = threadIdx.x; i < 256; i += kThreads) lut[i] = e8m0_to_f32((uint8_t)i);
+    __syncthreads();
+
+    if (warp == kConsumers) {
+        /* ---------------- producer ---------------- */
+        for (int it = 0; it < nks; ++it) {
+            const int s = it % kStages;
+            if (!mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1, 1)) break;
+            const int nb = min(SKB, P.row_bytes - it * SKB);
+            uint8_t* st = smem + s * STAGE;
+            if (lane == 0)
+                mbar_expect_tx(&full[s], (uint32_t)(RT * nb + (FMT == FMT_MXFP4 ? RT * (nb >> 4) : 0)));
+            __syncwarp();
+            for (int row = lane; row < RT; row += 32) {
+                const int64_t gr = min(r0 + row, P.n - 1);       /* ragged N: reload a live row */
+                bulk_g2s(st + row * PITCH, P.w + gr * P.w_pitch + (int64_t)it * SKB,
+                         (uint32_t)nb, &full[s]);
+                if (FMT == FMT_MXFP4)
+                    bulk_g2s(st + W_BYTES + row * SCP,
+                             P.ws + gr * P.ws_pitch + (int64_t)it * SCP,
+                             (uint32_t)(nb >> 4), &full[s]);
+            }
+        }
+        return;
+    }
+
+    /* ---------------- consumers ---------------- */
+    const int wr = warp / KS, wk = warp % KS;
+    const int g = lane >> 2, q = lane & 3;
+    const int rowA = min(r0 + wr * 16 + g, P.n - 1);
+    const int rowB = min(r0 + wr * 16 + g + 8, P.n - 1);
+    const int n128 = (P.k + 127) >> 7;
+
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
+
+    /* activation row pointers of this lane's B fragment (token j*8+g), clamped to a live row */
+    const uint8_t* arow[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) arow[j] = P.act + (int64_t)min(j * 8 + g, P.m - 1) * P.act_pitch;
+    /* tokens of this lane's accumulator columns */
+    int tokc[NT][2];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        tokc[j][0] = min(j * 8 + 2 * q, P.m - 1);
+        tokc[j][1] = min(j * 8 + 2 * q + 1, P.m - 1);
+    }
+
+    bool alive = true;
+    for (int it = 0; it < nks && alive; ++it) {
+        const int s = it % kStages;
+        if (!mbar_wait(&full[s], (it / kStages) & 1, 2)) { alive = false; break; }
+        const int nb = min(SKB, P.row_bytes - it * SKB);
+        const int lo = wk * kWarpBytes;                       /* this warp's slice of the stage */
+        const int nbytes = max(0, min(kWarpBytes, nb - lo));
+        const uint8_t* st = smem + s * STAGE;
+        const uint8_t* pa = st + (wr * 16 + g) * PITCH + lo;
+        const uint8_t* pb = pa + 8 * PITCH;
+        const int kb0 = it * SKB + lo;                        /* weight byte offset in the row */
+
+        if (FMT == FMT_FP8) {
+            for (int gb = 0; gb < nbytes; gb += 128) {
+                float c[NT][4];
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) c[j][i] = 0.0f;
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    const int off = gb + ch * 64 + q * 16;
+                    const uint4 wa = *(const uint4*)(pa + off);
+                    const uint4 wb = *(const uint4*)(pb + off);
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        const uint4 x = __ldg((const uint4*)(arow[j] + kb0 + off));
+                        mma_e4m3(c[j], wa.x, wb.x, wa.y, wb.y, x.x, x.y);
+                        mma_e4m3(c[j], wa.z, wb.z, wa.w, wb.w, x.z, x.w);
+                    }
+                }
+                const int grp = (kb0 + gb) >> 7;
+                const int cb = scale_col(grp, P.ws_cols, n128), ca = scale_col(grp, P.as_cols, n128);
+                const float sb0 = ld_scale(P.ws, (int64_t)(P.rblk > 1 ? rowA / P.rblk : rowA) * P.ws_pitch + cb, P.ws_dtype);
+                const float sb1 = ld_scale(P.ws, (int64_t)(P.rblk > 1 ? rowB / P.rblk : rowB) * P.ws_pitch + cb, P.ws_dtype);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const float sa0 = __ldg(P.as + (int64_t)tokc[j][0] * P.as_pitch + ca);
+                    const float sa1 = __ldg(P.as + (int64_t)tokc[j][1] * P.as_pitch + ca);
+                    acc[j][0] += (c[j][0] * sa0) * sb0;
+                    acc[j][1] += (c[j][1] * sa1) * sb0;
+                    acc[j][2] += (c[j][2] * sa0) * sb1;
+                    acc[j][3] += (c[j][3] * sa1) * sb1;
+                }
+            }
+        } else if (FMT == FMT_MXFP4) {
+            const uint8_t* sa_ = st + W_BYTES + (wr * 16 + g) * SCP + (lo >> 4);
+            const uint8_t* sb_ = sa_ + 8 * SCP;
+            for (int blk = 0; blk < (nbytes >> 6); ++blk) {     /* 128 of K = 64 nibble bytes */
+                float t[NT][4];
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) t[j][i] = 0.0f;
+                const uint32_t sw0 = *(const uint32_t*)(sa_ + blk * 4);
+                const uint32_t sw1 = *(const uint32_t*)(sb_ + blk * 4);
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {                /* one 32-of-K scale group */
+                    const uint32_t w0 = *(const uint32_t*)(pa + blk * 64 + jj * 16 + q * 4);
+                    const uint32_t w1 = *(const uint32_t*)(pb + blk * 64 + jj * 16 + q * 4);
+                    const uint32_t a0 = e2m1_even_to_e4m3(w0), a2 = e2m1_odd_to_e4m3(w0);
+                    const uint32_t a1 = e2m1_even_to_e4m3(w1), a3 = e2m1_odd_to_e4m3(w1);
+                    const float s0 = lut[(sw0 >> (8 * jj)) & 0xffu];
+                    const float s1 = lut[(sw1 >> (8 * jj)) & 0xffu];
+                    const int ka = (kb0 + blk * 64 + jj * 16) * 2 + q * 8;   /* activation byte */
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        const uint2 x = __ldg((const uint2*)(arow[j] + ka));
+                        const uint32_t b0 = prmt(x.x, x.y, 0x6420u);   /* even k */
+                        const uint32_t b1 = prmt(x.x, x.y, 0x7531u);   /* odd k  */
+                        float c[4];
+                        mma_e4m3_z(c, a0, a1, a2, a3, b0, b1);
+                        t[j][0] = fmaf(c[0], s0, t[j][0]);
+                        t[j][1] = fmaf(c[1], s0, t[j][1]);
+                        t[j][2] = fmaf(c[2], s1, t[j][2]);
+                        t[j][3] = fmaf(c[3], s1, t[j][3]);
+                    }
+                }
+                const int ca = scale_col(((kb0 + blk * 64) * 2) >> 7, P.as_cols, n128);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    /* the e4m3 image of an e2m1 code is 2^-6 too small: give it back here */
+                    const float sa0 = __ldg(P.as + (int64_t)tokc[j][0] * P.as_pitch + ca) * 64.0f;
+                    const float sa1 = __ldg(P.as + (int64_t)tokc[j][1] * P.as_pitch + ca) * 64.0f;
+                    acc[j][0] += t[j][0] * sa0;
+                    acc[j][1] += t[j][1] * sa1;
+                    acc[j][2] += t[j][2] * sa0;
+                    acc[j][3] += t[j][3] * sa1;
+                }
+            }
+        } else {  /* FMT_LOGITS: e4m3 codes x bf16 activations */
+            for (int gb = 0; gb < nbytes; gb += 128) {
+                float c[NT][4];
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) c[j][i] = 0.0f;
+                const int kvalid = min(128, P.k - (kb0 + gb));   /* ragged K tail (multiple of 64 here) */
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    if (ch * 64 >= kvalid) break;
+                    const int off = gb + ch * 64 + q * 16;
+                    const uint4 wa = *(const uint4*)(pa + off);
+                    const uint4 wb = *(const uint4*)(pb + off);
+                    const uint32_t ua[4] = {wa.x, wa.y, wa.z, wa.w};
+                    const uint32_t ub[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {              /* 4 codes per row per MMA */
+                        const uint32_t a0 = e4m3x2_to_bf16x2(ua[i], 0x1404u);
+                        const uint32_t a2 = e4m3x2_to_bf16x2(ua[i], 0x3424u);
+                        const uint32_t a1 = e4m3x2_to_bf16x2(ub[i], 0x1404u);
+                        const uint32_t a3 = e4m3x2_to_bf16x2(ub[i], 0x3424u);
+#pragma unroll
+                        for (int j = 0; j < NT; ++j) {
+                            const uint2 x = __ldg((const uint2*)(arow[j] + (int64_t)(kb0 + off + i * 4) * 2));
+                            mma_bf16(c[j], a0, a1, a2, a3, x.x, x.y);
+                        }
+                    }
+                }
+                const int grp = (kb0 + gb) >> 7;
+                const float sb0 = ld_scale(P.ws, (int64_t)(rowA / P.rblk) * P.ws_pitch + grp, P.ws_dtype);
+                const float sb1 = ld_scale(P.ws, (int64_t)(rowB / P.rblk) * P.ws_pitch + grp, P.ws_dtype);
+                const float up = 1.329227995784916e36f;          /* 2^120 */
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    acc[j][0] += (c[j][0] * up) * sb0;
+                    acc[j][1] += (c[j][1] * up) * sb0;
+                    acc[j][2] += (c[j][2] * up) * sb1;
+                    acc[j][3] += (c[j][3] * up) * sb1;
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+
+    /* ---------------- epilogue ---------------- */
+    if (KS > 1) {
+        /* warps that split K add their partial sums through shared memory, in wk order */
+        float* mine = red + (size_t)warp * (NT * 4 * 32);
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mine[(j * 4 + i) * 32 + lane] = acc[j][i];
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32));
+        if (wk != 0) return;
+#pragma unroll
+        for (int o = 1; o < KS; ++o) {
+            const float* other = red + (size_t)(warp + o) * (NT * 4 * 32);
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[j][i] += other[(j * 4 + i) * 32 + lane];
+        }
+    }
+    if (!alive) return;
+    const int ra = r0 + wr * 16 + g, rb = ra + 8;
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int tok = j * 8 + 2 * q + (i & 1);
+            const int row = (i & 2) ? rb : ra;
+            if (tok < P.m && row < P.n) {
+                if (P.y_dtype == RAD_F32) ((float*)P.y)[(int64_t)tok * P.y_pitch + row] = acc[j][i];
+                else ((uint16_t*)P.y)[(int64_t)tok * P.y_pitch + row] = f32_to_bf16(acc[j][i]);
+            }
+        }
+}
+
+template <int FMT, int NT, int KS>
+size_t smem_bytes() {
+    constexpr int RT = 16 * (kConsumers / KS);
+    constexpr int SKB = kWarpBytes * KS;
+    constexpr int STAGE = RT * (SKB + Geo<FMT>::pad) + (FMT == FMT_MXFP4 ? RT * (SKB / 16) : 0);
+    return (size_t)kStages * STAGE + 2 * kStages * sizeof(uint64_t) + 256 * sizeof(float) +
+           (KS > 1 ? (size_t)kConsumers * NT * 4 * 32 * sizeof(float) : 0);
+}
+
+template <int FMT, int NT, int KS>
+int launch_one(const StreamParams& P, cudaStream_t st) {
+    constexpr int RT = 16 * (kConsumers / KS);
+    const size_t smem = smem_bytes<FMT, NT, KS>();
+    static bool attr_set = false;     /* one opt-in per instantiation */
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(k_stream<FMT, NT, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess) return RAD_E_DEVICE;
+        attr_set = true;
+    }
+    const unsigned grid = (unsigned)((P.n + RT - 1) / RT);
+    count_launch();
+    k_stream<FMT, NT, KS><<<grid, kThreads, smem, st>>>(P);
+    return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+}
+
+/* Rows per CTA: whole 64-row tiles when there are enough of them to fill the machine,
+ * otherwise split K across the warps of a CTA so more CTAs exist. */
+int pick_ks(int n) {
+    const int t64 = (n + 63) / 64;
+    if (t64 >= 296) return 1;
+    if ((n + 31) / 32 >= 296) return 2;
+    return 4;
+}
+
+template <int FMT>
+int launch_fmt(const StreamParams& P, cudaStream_t st) {
+    const int nt = (P.m + 7) / 8;
+    const int ks = pick_ks(P.n);
+#define R3D_KS(NT_)                                                         \
+    (ks == 1 ? launch_one<FMT, NT_, 1>(P, st)                               \
+             : ks == 2 ? launch_one<FMT, NT_, 2>(P, st) : launch_one<FMT, NT_, 4>(P, st))
+    if (nt <= 1) return R3D_KS(1);
+    if (nt <= 2) return R3D_KS(2);
+    if (nt <= 4) return R3D_KS(4);
+    return R3D_KS(8);
+#undef R3D_KS
+}
+
+bool al16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
+
+} /* anonymous namespace */
+
+bool stream_fp8a8_ok(const R3dGemmQ& p) {
+    return p.m >= 1 && p.m <= 64 && (p.k % 128) == 0 && al16(p.b) && (p.b_pitch % 16) == 0 &&
+           al16(p.a) && (p.a_pitch % 16) == 0;
+}
+bool stream_mxfp4a8_ok(const R3dGemmQ& p) {
+    /* whole stages of scale bytes: a row's K/32 scale bytes must split into 16-byte copies */
+    return p.m >= 1 && p.m <= 64 && (p.k % 512) == 0 && al16(p.b) && (p.b_pitch % 16) == 0 &&
+           al16(p.b_scale) && (p.bs_pitch % 16) == 0 && al16(p.a) && (p.a_pitch % 16) == 0;
+}
+bool stream_logits_ok(const R3dLogits& p) {
+    return p.head_fmt == 0 && p.m >= 1 && p.m <= 64 && (p.k % 64) == 0 && al16(p.codes) &&
+           (p.code_pitch % 16) == 0 && (((uintptr_t)p.x) & 7) == 0 && (p.x_pitch % 4) == 0;
+}
+
+int stream_fp8a8(const R3dGemmQ& p, cudaStream_t st) {
+    StreamParams P{};
+    P.w = (const uint8_t*)p.b; P.w_pitch = p.b_pitch;
+    P.ws = (const uint8_t*)p.b_scale; P.ws_pitch = p.bs_pitch;
+    P.act = (const uint8_t*)p.a; P.act_pitch = p.a_pitch;
+    P.as = p.a_scale; P.as_pitch = p.as_pitch;
+    P.y = p.y; P.y_pitch = p.y_pitch;
+    P.m = p.m; P.n = p.n; P.k = p.k;
+    P.as_cols = p.as_cols; P.ws_cols = p.bs_cols; P.rblk = p.rblk; P.ws_dtype = p.bs_dtype;
+    P.y_dtype = RAD_BF16; P.row_bytes = p.k;
+    return launch_fmt<FMT_FP8>(P, st);
+}
+
+int stream_mxfp4a8(const R3dGemmQ& p, cudaStream_t st) {
+    StreamParams P{};
+    P.w = (const uint8_t*)p.b; P.w_pitch = p.b_pitch;
+    P.ws = (const uint8_t*)p.b_scale; P.ws_pitch = p.bs_pitch;
+    P.act = (const uint8_t*)p.a; P.act_pitch = p.a_pitch;
+    P.as = p.a_scale; P.as_pitch = p.as_pitch;
+    P.y = p.y; P.y_pitch = p.y_pitch;
+    P.m = p.m; P.n = p.n; P.k = p.k;
+    P.as_cols = p.as_cols; P.ws_cols = p.bs_cols; P.rblk = 1; P.ws_dtype = RAD_E8M0;
+    P.y_dtype = RAD_BF16; P.row_bytes = p.k / 2;
+    return launch_fmt<FMT_MXFP4>(P, st);
+}
+
+int stream_logits(const R3dLogits& p, cudaStream_t st) {
+    StreamParams P{};
+    P.w = (const uint8_t*)p.codes; P.w_pitch = p.code_pitch;
+    P.ws = (const uint8_t*)p.scale; P.ws_pitch = p.scale_pitch;
+    P.act = (const uint8_t*)p.x; P.act_pitch = p.x_pitch * 2;
+    P.as = nullptr; P.as_pitch = 0;
+    P.y = p.y; P.y_pitch = p.y_pitch;
+    P.m = p.m; P.n = p.n; P.k = p.k;
+    P.as_cols = 0; P.ws_cols = (p.k + 127) / 128; P.rblk = p.br; P.ws_dtype = p.scale_dtype;
+    P.y_dtype = p.y_dtype; P.row_bytes = p.k;
+    return launch_fmt<FMT_LOGITS>(P, st);
+}
+
+} /* namespace r3d */
+
+extern "C" int r3d_b200_stream_status(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, r3d::g_stream_status, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}

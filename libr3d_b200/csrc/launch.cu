@@ -1,0 +1,161 @@
+/* launch.cu -- the thin C ABI between the host-side row entries and the CUDA kernels
+ * (declared in r3d_b200.h). Operands arrive validated; this layer only picks an arm.
+ * There is no CPU path: when no CUDA device of the right generation is present every call
+ * returns RAD_E_UNSUPPORTED, loudly once. */
+#include "r3d_kernels.h"
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+namespace r3d {
+
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+/* The kernels are compiled for sm_100a only. Checked once per process (the reference's
+ * chip gate: src/r3d_gemm_fp8a8.hip:903-913). */
+bool device_is_sm100() {
+    static int ok = -1;
+    if (ok < 0) {
+        int dev = 0;
+        cudaDeviceProp pr{};
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaGetDeviceProperties(&pr, dev) != cudaSuccess) {
+            fprintf(stderr, "libr3d_b200: no usable CUDA device -- every row refuses\n");
+            ok = 0;
+        } else {
+            ok = (pr.major == 10) ? 1 : 0;
+            if (!ok)
+                fprintf(stderr, "libr3d_b200: device '%s' is sm_%d%d; this library holds sm_100a "
+                                "code only -- every row refuses\n", pr.name, pr.major, pr.minor);
+        }
+    }
+    return ok == 1;
+}
+
+static void debug_arm(const char* band, const char* arm, int m) {
+    /* one line per distinct (band, arm), the reference's R3D_DEBUG_GEMM law
+     * (src/r3d_gemm_fp8a8.hip:976-983): a lever that never dispatches must not look live */
+    static const bool on = getenv("R3D_DEBUG_GEMM") != nullptr;
+    if (!on) return;
+    static char seen[16][48];
+    static int nseen = 0;
+    char key[48];
+    snprintf(key, sizeof key, "%s/%s", band, arm);
+    for (int i = 0; i < nseen; ++i) if (!strcmp(seen[i], key)) return;
+    if (nseen < 16) { strcpy(seen[nseen++], key); }
+    fprintf(stderr, "libr3d_b200: %s -> %s arm launched (m=%d)\n", band, arm, m);
+}
+
+} /* namespace r3d */
+
+using namespace r3d;
+
+extern "C" long long r3d_b200_launch_count(void) { return g_launches.load(); }
+
+extern "C" int r3d_b200_pick_arm_fp8a8(const R3dGemmQ* q) {
+    if (!q) return -1;
+    if (q->arm != R3D_ARM_AUTO) return q->arm;
+    return stream_fp8a8_ok(*q) || (q->m > 64) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+}
+extern "C" int r3d_b200_pick_arm_mxfp4a8(const R3dGemmQ* q) {
+    if (!q) return -1;
+    if (q->arm != R3D_ARM_AUTO) return q->arm;
+    return stream_mxfp4a8_ok(*q) || (q->m > 64) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+}
+
+/* M above the streaming arm's 64 rides it in passes of 64 tokens, each pass re-reading the
+ * weights (the reference's own rule for M above its register group,
+ * src/r3d_gemm_logits.hip:24-26). */
+template <typename OkFn, typename RunFn>
+static int gemm_passes(const R3dGemmQ& q, OkFn ok, RunFn run, cudaStream_t st) {
+    for (int m0 = 0; m0 < q.m; m0 += 64) {
+        R3dGemmQ c = q;
+        c.m = q.m - m0 < 64 ? q.m - m0 : 64;
+        c.a = (const uint8_t*)q.a + (int64_t)m0 * q.a_pitch;
+        c.a_scale = q.a_scale + (int64_t)m0 * q.as_pitch;
+        c.y = (uint16_t*)q.y + (int64_t)m0 * q.y_pitch;
+        if (!ok(c)) return RAD_E_UNSUPPORTED;
+        const int rc = run(c, st);
+        if (rc != RAD_OK) return rc;
+    }
+    return RAD_OK;
+}
+
+extern "C" int r3d_b200_gemm_fp8a8(const R3dGemmQ* q, void* stream) {
+    if (!q || !device_is_sm100()) return RAD_E_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    int arm = q->arm;
+    if (arm == R3D_ARM_AUTO) {
+        R3dGemmQ probe = *q; if (probe.m > 64) probe.m = 64;
+        arm = stream_fp8a8_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+    }
+    if (arm == R3D_ARM_STREAM) {
+        debug_arm("fp8a8", "stream", q->m);
+        return gemm_passes(*q, stream_fp8a8_ok, stream_fp8a8, st);
+    }
+    if (arm == R3D_ARM_EXACT) { debug_arm("fp8a8", "exact", q->m); return exact_fp8a8(*q, st); }
+    return RAD_E_UNSUPPORTED;
+}
+
+extern "C" int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream) {
+    if (!q || !device_is_sm100()) return RAD_E_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    int arm = q->arm;
+    if (arm == R3D_ARM_AUTO) {
+        R3dGemmQ probe = *q; if (probe.m > 64) probe.m = 64;
+        arm = stream_mxfp4a8_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+    }
+    if (arm == R3D_ARM_STREAM) {
+        debug_arm("mxfp4a8", "stream", q->m);
+        return gemm_passes(*q, stream_mxfp4a8_ok, stream_mxfp4a8, st);
+    }
+    if (arm == R3D_ARM_EXACT) { debug_arm("mxfp4a8", "exact", q->m); return exact_mxfp4a8(*q, st); }
+    return RAD_E_UNSUPPORTED;
+}
+
+extern "C" int r3d_b200_gemm_mxfp4a8_q8x(const R3dGemmQ* q, int8_t* x8, float* sg, int walk,
+                                         void* stream) {
+    if (!q || !x8 || !sg || !device_is_sm100()) return RAD_E_UNSUPPORTED;
+    if (q->m < 1 || q->m > 8 || (q->k & 255)) return RAD_E_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc = q8x_requant(*q, x8, sg, st);
+    if (rc != RAD_OK) return rc;
+    debug_arm("mxfp4a8", walk ? "q8x lane-map" : "q8x dot4", q->m);
+    return q8x_gemv(*q, x8, sg, walk, st);
+}
+
+extern "C" int r3d_b200_logits(const R3dLogits* l, void* stream) {
+    if (!l || !device_is_sm100()) return RAD_E_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    int arm = l->arm;
+    if (arm == R3D_ARM_AUTO) {
+        R3dLogits probe = *l; if (probe.m > 64) probe.m = 64;
+        arm = stream_logits_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+    }
+    if (arm == R3D_ARM_EXACT) { debug_arm("logits", "exact", l->m); return exact_logits(*l, st); }
+    if (arm != R3D_ARM_STREAM) return RAD_E_UNSUPPORTED;
+    debug_arm("logits", "stream", l->m);
+    const int ysz = l->y_dtype == RAD_F32 ? 4 : 2;
+    for (int m0 = 0; m0 < l->m; m0 += 64) {
+        R3dLogits c = *l;
+        c.m = l->m - m0 < 64 ? l->m - m0 : 64;
+        c.x = (const uint16_t*)l->x + (int64_t)m0 * l->x_pitch;
+        c.y = (uint8_t*)l->y + (int64_t)m0 * l->y_pitch * ysz;
+        if (!stream_logits_ok(c)) return RAD_E_UNSUPPORTED;
+        const int rc = stream_logits(c, st);
+        if (rc != RAD_OK) return rc;
+    }
+    return RAD_OK;
+}
+
+extern "C" int r3d_b200_quant_act_fp8(const void* x, int32_t x_dtype, int64_t x_pitch, void* q,
+                                      int64_t q_pitch, float* scale, int64_t s_pitch,
+                                      int32_t rows, int32_t n, int32_t group, void* stream) {
+    if (!x || !q || !scale || rows <= 0 || n <= 0) return RAD_E_INVAL;
+    if (x_dtype != RAD_BF16 && x_dtype != RAD_F32) return RAD_E_DTYPE;
+    if (!device_is_sm100()) return RAD_E_UNSUPPORTED;
+    return launch_quant_act_fp8(x, x_dtype, x_pitch, q, q_pitch, scale, s_pitch, rows, n, group,
+                                (cudaStream_t)stream);
+}

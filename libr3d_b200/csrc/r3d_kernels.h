@@ -1,0 +1,34 @@
+/* r3d_kernels.h -- internal declarations shared by the translation units of libr3d_b200.so:
+ * one launcher per (band, arm). Host C++ only sees these; the CUDA lives behind them. */
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+#include "r3d_b200.h"
+
+namespace r3d {
+
+void count_launch(int n = 1);          /* bookkeeping behind r3d_b200_launch_count() */
+bool device_is_sm100();                /* chip gate: these kernels are built for sm_100a only */
+
+/* oracle-order arm (kern_exact.cu) */
+int exact_fp8a8(const R3dGemmQ& p, cudaStream_t st);
+int exact_mxfp4a8(const R3dGemmQ& p, cudaStream_t st);
+int exact_logits(const R3dLogits& p, cudaStream_t st);
+int launch_quant_act_fp8(const void* x, int x_dtype, int64_t x_pitch, void* q, int64_t q_pitch,
+                         float* scale, int64_t s_pitch, int rows, int n, int group,
+                         cudaStream_t st);
+
+/* weight-streaming tensor-core arm (kern_stream.cu); *_ok say whether the arm can take
+ * the call's shape and alignment */
+bool stream_fp8a8_ok(const R3dGemmQ& p);
+bool stream_mxfp4a8_ok(const R3dGemmQ& p);
+bool stream_logits_ok(const R3dLogits& p);
+int  stream_fp8a8(const R3dGemmQ& p, cudaStream_t st);
+int  stream_mxfp4a8(const R3dGemmQ& p, cudaStream_t st);
+int  stream_logits(const R3dLogits& p, cudaStream_t st);
+
+/* int8-per-32 activation arm (kern_q8x.cu) */
+int q8x_requant(const R3dGemmQ& p, int8_t* x8, float* sg, cudaStream_t st);
+int q8x_gemv(const R3dGemmQ& p, const int8_t* x8, const float* sg, int walk, cudaStream_t st);
+
+} /* namespace r3d */

@@ -1,0 +1,200 @@
+/* rows_table.cpp -- what the engine's loader sees: plugin identity, the op schemas of the
+ * quantised-matmul bands, the kernel rows with their constraints and priorities, and the
+ * registration gate where the environment kill switches act.
+ *
+ * Row names, ops, constraint tables, priorities and lever names are those of libr3d
+ * (src/r3d_rows.cpp:1042-1091, :1167-1177, :1588-1718, :2216-2278), so a resolver query
+ * lands on the same row name it would there. Schemas list parameters and operands in the
+ * same order with the same kinds (src/r3d_rows.cpp:190-245): a loader that compares a
+ * second declarer's schema entry for entry accepts them. Prose fields describe this
+ * library's B200 kernels. Pure host C++.
+ *
+ * Kill switches act HERE, by not enumerating a row, because the engine picks a row when a
+ * band is declared: a row that refuses at launch time is an abort, not a re-resolve
+ * (src/r3d_rows.cpp:2197-2200). The entries repeat the check only as a backstop.
+ */
+#include <cstdlib>
+#include <cstring>
+#include "rad_abi.h"
+#include "r3d_b200.h"
+
+#define COUNT_OF(x) ((int)(sizeof(x) / sizeof((x)[0])))
+
+namespace {
+
+/* ------------------------------------------------------------------ schemas */
+const RadParamSpec kGemmQParams[] = {
+    { "M", RAD_P_INT, RAD_REQUIRED, 0 },     { "N", RAD_P_INT, RAD_REQUIRED, 0 },
+    { "K", RAD_P_INT, RAD_REQUIRED, 0 },     { "group", RAD_P_INT, RAD_REQUIRED, 0 },
+    { "dtype", RAD_P_STR, RAD_REQUIRED, 0 }, { "pb1", RAD_P_INT, RAD_OPTIONAL, 0 },
+    { "pb2", RAD_P_INT, RAD_OPTIONAL, 0 },
+    { "split_n", RAD_P_INT, RAD_OPTIONAL, 0 },   /* a K-split hint: accepted, ignored */
+};
+const RadOperandSpec kGemmQOperands[] = {
+    { "a", RAD_OPD_IN, 0 },        { "a_scale", RAD_OPD_IN, 1 },
+    { "b", RAD_OPD_WEIGHT, 0 },    { "b_scale", RAD_OPD_WEIGHT, 0 },
+    { "y", RAD_OPD_OUT, 0 },       { "a_sum", RAD_OPD_IN, 1 },
+    { "b_ref", RAD_OPD_WEIGHT, 1 },
+};
+
+const RadParamSpec kGemmQGatedParams[] = {
+    { "M", RAD_P_INT, RAD_REQUIRED, 0 },     { "N", RAD_P_INT, RAD_REQUIRED, 0 },
+    { "K", RAD_P_INT, RAD_REQUIRED, 0 },     { "group", RAD_P_INT, RAD_REQUIRED, 0 },
+    { "dtype", RAD_P_STR, RAD_REQUIRED, 0 }, { "act", RAD_P_STR, RAD_REQUIRED, 0 },
+};
+const RadOperandSpec kGemmQGatedOperands[] = {
+    { "a", RAD_OPD_IN, 0 },        { "a_scale", RAD_OPD_IN, 0 },
+    { "b", RAD_OPD_WEIGHT, 0 },    { "b_scale", RAD_OPD_WEIGHT, 0 },
+    { "q", RAD_OPD_OUT, 0 },       { "scale", RAD_OPD_OUT, 0 },
+    { "out_bf16", RAD_OPD_OUT, 1 },
+};
+
+const RadParamSpec kLogitsParams[] = {
+    { "M", RAD_P_INT, RAD_REQUIRED, 0 },      { "n_vocab", RAD_P_INT, RAD_REQUIRED, 0 },
+    { "n_embd", RAD_P_INT, RAD_REQUIRED, 0 }, { "dtype", RAD_P_STR, RAD_REQUIRED, 0 },
+};
+const RadOperandSpec kLogitsOperands[] = {
+    { "x", RAD_OPD_IN, 0 }, { "lm_head", RAD_OPD_WEIGHT, 0 }, { "logits", RAD_OPD_OUT, 0 },
+};
+
+const RadOpSchema kSchemas[] = {
+    { "logits_gemm", kLogitsParams, COUNT_OF(kLogitsParams), kLogitsOperands,
+      COUNT_OF(kLogitsOperands),
+      "LM-head projection: logits[M, n_vocab] = x[M, n_embd] @ head^T, one row per sampled "
+      "position." },
+    { "gemm_nt_q", kGemmQParams, COUNT_OF(kGemmQParams), kGemmQOperands,
+      COUNT_OF(kGemmQOperands),
+      "y[M,N] = a[M,K] @ dequant(b)[N,K]^T; `dtype` names the operand-format combination." },
+    /* declared so a co-loaded declarer's schema comparison passes; this library ships no
+     * row for it yet */
+    { "gemm_nt_q_gated", kGemmQGatedParams, COUNT_OF(kGemmQGatedParams), kGemmQGatedOperands,
+      COUNT_OF(kGemmQGatedOperands),
+      "gemm_nt_q over a [2n, K] gate_up plane with the gated activation quantiser folded into "
+      "the epilogue; outputs are [M, N/2]." },
+};
+
+/* ------------------------------------------------------------------ constraints */
+const RadConstraint kCLogits[] = {
+    { "n_vocab", RAD_C_GE, 1, nullptr }, { "n_embd", RAD_C_GE, 128, nullptr },
+    { "dtype", RAD_C_IN, 0, "bf16" },
+};
+const RadConstraint kCMxfp4[] = { { "dtype", RAD_C_IN, 0, "mxfp4a8" } };
+const RadConstraint kCFp8[] = {
+    { "dtype", RAD_C_IN, 0, "fp8a8" }, { "K", RAD_C_DIV, 128, nullptr },
+    { "group", RAD_C_EQ, 128, nullptr },
+};
+const RadConstraint kCFp8Decode[] = {
+    { "dtype", RAD_C_IN, 0, "fp8a8" }, { "M", RAD_C_LE, 8, nullptr },
+    { "K", RAD_C_DIV, 128, nullptr },  { "group", RAD_C_EQ, 128, nullptr },
+};
+/* no constraint on N anywhere: the engine's gemm ops may omit N at issue and a constraint
+ * on a key the query lacks never holds (src/r3d_rows.cpp:1105-1110) */
+const RadConstraint kCMxfp4Decode[] = {
+    { "dtype", RAD_C_IN, 0, "mxfp4a8" }, { "M", RAD_C_LE, 8, nullptr },
+    { "K", RAD_C_DIV, 128, nullptr },
+};
+
+enum { kPrioPlain = 1000, kPrioDecode = 1100, kPrioQ8x = 1200 };
+
+#define ROW(name, op, family, summary, shapes, dtypes, prio, cons, launch)               \
+    { name, op, family, summary, shapes, dtypes, RAD_DOMAIN_DEVICE, prio, cons,          \
+      COUNT_OF(cons), nullptr, 0, nullptr, nullptr, nullptr, launch, nullptr, nullptr,    \
+      nullptr, nullptr, nullptr, nullptr }
+
+const RadKernelInfo kRows[] = {
+    { "logits_gemm_e4m3", "logits_gemm", "vocab",
+      "weight-streaming GEMV over the joined LM head: e4m3 codes ride bf16 tensor-core "
+      "fragments exactly, the block scale is applied to each 128-column partial in f32",
+      "codes [n_vocab, n_embd] e4m3 dense, scale per (1 or 128 rows, 128 cols); M from "
+      "numel(logits)/n_vocab, passes of 64 rows",
+      "bf16 x, joined e4m3 + bf16/f16/f32 head, f32 logits",
+      RAD_DOMAIN_DEVICE, kPrioPlain, kCLogits, COUNT_OF(kCLogits), nullptr, 0, nullptr,
+      nullptr, nullptr, r3d_rad_logits_gemm_e4m3, nullptr, r3d_layout_head,
+      r3d_relayout_head, nullptr, r3d_unrelayout_head, nullptr },
+
+    ROW("gemm_nt_q_mxfp4", "gemm_nt_q", "gemm",
+        "mxfp4a8, any M: e2m1 codes expanded in registers to exact e4m3 images and fed to "
+        "fp8 tensor-core fragments, E8M0 applied per 32-of-K partial, a_scale per 128",
+        "b:32 / a:128 scale grids; nibble rows byte-packed; M from numel(y)/N",
+        "e4m3 a + f32 a_scale, e2m1 b + E8M0 b_scale, bf16 y; b_ref ignored; a_sum refused",
+        kPrioPlain, kCMxfp4, r3d_rad_gemm_nt_q),
+
+    ROW("gemm_nt_q_fp8a8", "gemm_nt_q", "gemm",
+        "fp8a8, any M: e4m3 codes feed fp8 tensor-core fragments untouched; each 128-of-K "
+        "partial is flushed as (sub * a_scale) * b_scale",
+        "K a multiple of 128; any N; b_scale per 128x128 block or per row; M from numel(y)/N",
+        "e4m3 a + f32 a_scale, e4m3 b + bf16 b_scale, bf16 y; a_sum and b_ref refused",
+        kPrioPlain, kCFp8, r3d_rad_gemm_nt_q_fp8),
+
+    ROW("gemm_nt_q_fp8a8_decode", "gemm_nt_q", "gemm",
+        "fp8a8 decode band: the same weight-streaming walk, every weight byte read once",
+        "M <= 8; K a multiple of 128; any N; a weight plane off the 4-byte grid resolves past "
+        "this row",
+        "as gemm_nt_q_fp8a8",
+        kPrioDecode, kCFp8Decode, r3d_rad_gemm_nt_q_fp8_decode),
+
+    ROW("gemm_nt_q_mxfp4_decode", "gemm_nt_q", "gemm",
+        "mxfp4a8 decode band, fp32 walk: per-32 group partials scaled by 2^(e8m0-127)",
+        "M <= 8; K a multiple of 128; any N",
+        "as gemm_nt_q_mxfp4",
+        kPrioDecode, kCMxfp4Decode, r3d_rad_gemm_nt_q_mxfp4_decode),
+
+    ROW("gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q", "gemm",
+        "mxfp4a8 decode band, int8-per-32 activation arm: activations requantised per "
+        "dispatch, exact integer dots per group, the arm's own flush chain; reads the nibble "
+        "plane as it is (no repacked plane). K % 256 != 0 rides the fp32 walk in place",
+        "M <= 8; K a multiple of 128; any N",
+        "as gemm_nt_q_mxfp4; R3D_MXFP4_Q8X=0 withdraws this row at registration",
+        kPrioQ8x, kCMxfp4Decode, r3d_rad_gemm_nt_q_mxfp4_decode_q8x),
+};
+
+/* ------------------------------------------------------------------ registration gate */
+bool row_hidden(const RadKernelInfo& k) {
+    static const bool no_fp8 = getenv("R3D_NO_FP8A8") != nullptr;
+    static const bool no_fp8_dec = getenv("R3D_NO_FP8_DEC") != nullptr;
+    static const bool no_mx = getenv("R3D_NO_MXFP4") != nullptr;
+    static const bool no_mx_dec = getenv("R3D_NO_FP4_DEC") != nullptr;
+    static const bool q8x_off = r3d_mxfp4_q8x_off();
+    if (!strcmp(k.name, "gemm_nt_q_fp8a8")) return no_fp8;
+    if (!strcmp(k.name, "gemm_nt_q_fp8a8_decode")) return no_fp8 || no_fp8_dec;
+    if (!strcmp(k.name, "gemm_nt_q_mxfp4")) return no_mx;
+    if (!strcmp(k.name, "gemm_nt_q_mxfp4_decode")) return no_mx || no_mx_dec;
+    /* the q8x sibling rides every lever of its band, plus its own */
+    if (!strcmp(k.name, "gemm_nt_q_mxfp4_decode_q8x")) return no_mx || no_mx_dec || q8x_off;
+    return false;
+}
+
+} /* namespace */
+
+extern "C" {
+
+uint32_t rad_plugin_abi_version(void) { return RAD_ABI_VERSION; }
+
+const RadPluginInfo* rad_plugin_info(void) {
+    static const RadPluginInfo info = {
+        RAD_PLUGIN_KERNEL, "libr3d_b200", "0.1.0",
+        "radiance kernel library for NVIDIA B200: quantised-matmul bands (fp8a8, mxfp4a8, "
+        "e4m3 LM head)",
+        "sm_100a",
+    };
+    return &info;
+}
+
+int rad_kernel_schema_count(void) { return COUNT_OF(kSchemas); }
+const RadOpSchema* rad_kernel_schema_at(int i) {
+    return (i >= 0 && i < COUNT_OF(kSchemas)) ? &kSchemas[i] : nullptr;
+}
+
+int rad_kernel_count(void) {
+    int n = 0;
+    for (const RadKernelInfo& k : kRows) if (!row_hidden(k)) ++n;
+    return n;
+}
+const RadKernelInfo* rad_kernel_at(int i) {
+    if (i < 0) return nullptr;
+    for (const RadKernelInfo& k : kRows)
+        if (!row_hidden(k) && i-- == 0) return &k;
+    return nullptr;
+}
+
+} /* extern "C" */

@@ -1,0 +1,112 @@
+"""The ops of the quantised-matmul path as a caller issues them: `gemm_nt_q` and
+`logits_gemm`, with device tensors (torch is used for device memory and streams only).
+
+Each call does what the radiance engine does for the op: resolve the band to a row by the
+rows' constraints and priorities, then call that row's `launch` with a RadArgs on the
+current CUDA stream. Nothing is computed here.
+"""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+
+from . import abi
+from .plugin import ArgPack, Plugin, Row, tensor_desc
+
+_plugin: Plugin | None = None
+
+
+def plugin() -> Plugin:
+    global _plugin
+    if _plugin is None:
+        _plugin = Plugin()
+    return _plugin
+
+
+class RowRefused(RuntimeError):
+    def __init__(self, row: str, rc: int):
+        super().__init__(f"row {row} returned {abi.STATUS_NAMES[rc] if 0 <= rc < 7 else rc}")
+        self.rc = rc
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _desc(t: torch.Tensor | None, dtype: int, shape=None, stride=None) -> abi.RadTensor:
+    if t is None:
+        return tensor_desc(None, dtype, [])
+    return tensor_desc(t.data_ptr(), dtype, shape if shape is not None else t.shape,
+                       stride if stride is not None else t.stride())
+
+
+def gemm_nt_q(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: torch.Tensor,
+              y: torch.Tensor, *, dtype: str, N: int, K: int, group: int | None = None,
+              M_param: int | None = None, row: str | None = None) -> Row:
+    """y[M,N] (bf16, given as a uint16/bfloat16 tensor) = a[M,K] @ dequant(b)[N,K]^T.
+
+    a: uint8 e4m3 codes [M,K]; a_scale: float32 [M, K/128]
+    dtype "fp8a8":   b uint8 e4m3 codes [N,K]; b_scale bf16 (or f32) [N/128 | N, K/128]
+    dtype "mxfp4a8": b uint8 packed e2m1 [N,K/2] (low nibble = even k); b_scale uint8 E8M0 [N,K/32]
+    `row` forces a row by name; otherwise the band is resolved like the engine would.
+    Returns the row that served the call; raises RowRefused on a nonzero status.
+    """
+    P = plugin()
+    M = y.numel() // N
+    if group is None:
+        group = 128 if dtype == "fp8a8" else 32
+    query: dict[str, Any] = dict(M=M_param if M_param is not None else M, N=N, K=K,
+                                 group=group, dtype=dtype)
+    if row is None:
+        r = P.resolve("gemm_nt_q", query)
+        if r is None:
+            raise RuntimeError(f"no row serves gemm_nt_q {query}")
+    else:
+        r = next(x for x in P.rows() if x.name == row)
+    if dtype == "fp8a8":
+        bdesc = _desc(b, abi.RAD_F8E4M3)
+        sdt = abi.RAD_F32 if b_scale.dtype == torch.float32 else abi.RAD_BF16
+    else:
+        bdesc = _desc(b, abi.RAD_FP4E2M1, shape=[b.shape[0], K], stride=[K, 1])
+        sdt = abi.RAD_E8M0
+    tensors = [_desc(a, abi.RAD_F8E4M3), _desc(a_scale, abi.RAD_F32), bdesc,
+               _desc(b_scale, sdt), _desc(y, abi.RAD_BF16), _desc(None, abi.RAD_F32),
+               _desc(None, abi.RAD_BF16)]
+    pack = ArgPack(tensors, query)
+    rc = P.launch_row(r, pack, _stream())
+    if rc != abi.RAD_OK:
+        raise RowRefused(r.name, rc)
+    return r
+
+
+def logits_gemm(x: torch.Tensor, head_blob: torch.Tensor, logits: torch.Tensor, *, n_vocab: int,
+                n_embd: int) -> Row:
+    """logits[M, n_vocab] f32 = x[M, n_embd] bf16 @ head^T, head a joined rad.planes blob
+    (uint8 device tensor) of e4m3 codes + block scales."""
+    P = plugin()
+    M = logits.numel() // n_vocab
+    query = dict(M=M, n_vocab=n_vocab, n_embd=n_embd, dtype="bf16")
+    r = P.resolve("logits_gemm", query)
+    if r is None:
+        raise RuntimeError(f"no row serves logits_gemm {query}")
+    tensors = [_desc(x, abi.RAD_BF16), _desc(head_blob, abi.RAD_U8), _desc(logits, abi.RAD_F32)]
+    rc = P.launch_row(r, ArgPack(tensors, query), _stream())
+    if rc != abi.RAD_OK:
+        raise RowRefused(r.name, rc)
+    return r
+
+
+def quant_act_fp8(x: torch.Tensor, group: int = 128) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16/f32 activations [rows, n] -> (e4m3 codes uint8 [rows, n], f32 scale [rows, n/group])."""
+    P = plugin()
+    rows, n = x.shape
+    ngrp = (n + group - 1) // group
+    q = torch.empty((rows, n), dtype=torch.uint8, device=x.device)
+    s = torch.empty((rows, ngrp), dtype=torch.float32, device=x.device)
+    xdt = abi.RAD_F32 if x.dtype == torch.float32 else abi.RAD_BF16
+    rc = P.lib.r3d_b200_quant_act_fp8(x.data_ptr(), xdt, x.stride(0), q.data_ptr(), q.stride(0),
+                                      s.data_ptr(), s.stride(0), rows, n, group, _stream())
+    if rc != abi.RAD_OK:
+        raise RowRefused("quant_act_fp8", rc)
+    return q, s

@@ -1,0 +1,215 @@
+"""ctypes loader for the CPU checker (oracle/liboracle.so) and the reference pin.
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by bench.py's
+CPU-baseline legs. Nothing under libr3d_b200/ may import this module.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+_lib = None
+_ref = None
+
+
+def build() -> None:
+    subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        so = HERE / "liboracle.so"
+        if not so.exists():
+            build()
+        L = C.CDLL(str(so))
+        L.orc_e4m3_to_f32.restype = C.c_float
+        L.orc_e4m3_to_f32.argtypes = [C.c_uint8]
+        L.orc_f32_to_e4m3.restype = C.c_uint8
+        L.orc_f32_to_e4m3.argtypes = [C.c_float]
+        L.orc_e2m1_to_f32.restype = C.c_float
+        L.orc_e2m1_to_f32.argtypes = [C.c_uint8]
+        L.orc_e2m1_x2.restype = C.c_int
+        L.orc_e2m1_x2.argtypes = [C.c_uint8]
+        L.orc_e8m0_to_f32.restype = C.c_float
+        L.orc_e8m0_to_f32.argtypes = [C.c_uint8]
+        L.orc_f32_to_bf16.restype = C.c_uint16
+        L.orc_f32_to_bf16.argtypes = [C.c_float]
+        L.orc_bf16_to_f32.restype = C.c_float
+        L.orc_bf16_to_f32.argtypes = [C.c_uint16]
+        L.orc_f16_to_f32.restype = C.c_float
+        L.orc_f16_to_f32.argtypes = [C.c_uint16]
+        L.orc_num_threads.restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def ref_pin() -> C.CDLL | None:
+    """The reference's own header compiled as it lies (oracle/_ref/libref_pin.so), or None."""
+    global _ref
+    if _ref is None:
+        so = HERE / "_ref" / "libref_pin.so"
+        if not so.exists():
+            return None
+        R = C.CDLL(str(so))
+        R.ref_e2m1_x2.restype = C.c_int
+        R.ref_e2m1_x2.argtypes = [C.c_int]
+        R.ref_e8m0_sc.restype = C.c_float
+        R.ref_e8m0_sc.argtypes = [C.c_ubyte]
+        _ref = R
+    return _ref
+
+
+def _p(a: np.ndarray | None):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    a = np.ascontiguousarray(a, dtype=dt)
+    return a
+
+
+I64 = C.c_int64
+
+
+def encode_e4m3(x: np.ndarray) -> np.ndarray:
+    """element-wise clamp(+-448) + RTNE-saturating e4m3 encode"""
+    x = _c(x, np.float32)
+    q = np.empty(x.shape, np.uint8)
+    lib().orc_f32_to_e4m3_n(_p(x), I64(x.size), _p(q))
+    return q
+
+
+def quant_act_fp8(x: np.ndarray, group: int = 128):
+    x = _c(x, np.float32)
+    M, n = x.shape
+    ngrp = (n + group - 1) // group
+    q = np.empty((M, n), np.uint8)
+    s = np.empty((M, ngrp), np.float32)
+    lib().orc_quant_act_fp8(_p(x), I64(M), I64(n), I64(group), _p(q), _p(s))
+    return q, s
+
+
+def quant_act_mx8(x: np.ndarray):
+    x = _c(x, np.float32)
+    M, n = x.shape
+    q = np.empty((M, n), np.uint8)
+    e = np.empty((M, (n + 31) // 32), np.uint8)
+    lib().orc_quant_act_mx8(_p(x), I64(M), I64(n), _p(q), _p(e))
+    return q, e
+
+
+def q8x_requant(A: np.ndarray):
+    A = _c(A, np.uint8)
+    M, K = A.shape
+    x8 = np.empty((M, K), np.int8)
+    sg = np.empty((M, K // 32), np.float32)
+    lib().orc_q8x_requant(_p(A), I64(M), I64(K), I64(K), _p(x8), _p(sg))
+    return x8, sg
+
+
+def gemm_fp8a8(A, AS, B, BS, rblk: int, want_acc: bool = False):
+    """BS: uint16 (bf16 bits) or float32 array [N/rblk, cols]."""
+    A, B, AS = _c(A, np.uint8), _c(B, np.uint8), _c(AS, np.float32)
+    is_f32 = BS.dtype == np.float32
+    BS = _c(BS, np.float32 if is_f32 else np.uint16)
+    M, K = A.shape
+    N = B.shape[0]
+    Y = np.empty((M, N), np.uint16)
+    acc = np.empty((M, N), np.float32) if want_acc else None
+    lib().orc_gemm_fp8a8(_p(A), _p(AS), _p(B), _p(BS), C.c_int(int(is_f32)), I64(M), I64(N), I64(K),
+                         I64(AS.shape[1]), I64(BS.shape[1]), I64(rblk), _p(Y), _p(acc))
+    return (Y, acc) if want_acc else Y
+
+
+def gemm_mxfp4a8(A, AS, B, BS, want_acc: bool = False):
+    A, B, AS, BS = _c(A, np.uint8), _c(B, np.uint8), _c(AS, np.float32), _c(BS, np.uint8)
+    M, K = A.shape
+    N = B.shape[0]
+    Y = np.empty((M, N), np.uint16)
+    acc = np.empty((M, N), np.float32) if want_acc else None
+    lib().orc_gemm_mxfp4a8(_p(A), _p(AS), _p(B), _p(BS), I64(M), I64(N), I64(K), I64(AS.shape[1]),
+                           _p(Y), _p(acc))
+    return (Y, acc) if want_acc else Y
+
+
+def gemm_mxfp4_q8x(A, AS, B, BS, walk: int):
+    """Full arm: requantise A (e4m3 codes) then the int8 chain."""
+    x8, sg = q8x_requant(A)
+    AS, B, BS = _c(AS, np.float32), _c(B, np.uint8), _c(BS, np.uint8)
+    M, K = x8.shape
+    N = B.shape[0]
+    Y = np.empty((M, N), np.uint16)
+    lib().orc_gemm_mxfp4_q8x(_p(x8), _p(sg), _p(AS), _p(B), _p(BS), I64(M), I64(N), I64(K),
+                             I64(AS.shape[1]), C.c_int(walk), _p(Y), None)
+    return Y
+
+
+def logits_e4m3(X, codes, scale, sdt: int, br: int):
+    """X uint16 bf16 bits [M,K]; scale uint16 (bf16 sdt 0 / f16 sdt 1) or float32 (sdt 2)."""
+    X, codes = _c(X, np.uint16), _c(codes, np.uint8)
+    scale = np.ascontiguousarray(scale)
+    M, K = X.shape
+    N = codes.shape[0]
+    Y = np.empty((M, N), np.float32)
+    lib().orc_logits_e4m3(_p(X), _p(codes), _p(scale), C.c_int(sdt), I64(br), I64(M), I64(N),
+                          I64(K), _p(Y))
+    return Y
+
+
+def logits_mxfp4(X, B, BS):
+    X, B, BS = _c(X, np.uint16), _c(B, np.uint8), _c(BS, np.uint8)
+    M, K = X.shape
+    N = B.shape[0]
+    Y = np.empty((M, N), np.float32)
+    lib().orc_logits_mxfp4(_p(X), _p(B), _p(BS), I64(M), I64(N), I64(K), _p(Y))
+    return Y
+
+
+def truth_fp8a8(A, AS, B, BS, rblk: int):
+    A, B, AS = _c(A, np.uint8), _c(B, np.uint8), _c(AS, np.float32)
+    is_f32 = BS.dtype == np.float32
+    BS = _c(BS, np.float32 if is_f32 else np.uint16)
+    M, K = A.shape
+    N = B.shape[0]
+    Yt = np.empty((M, N), np.float64)
+    Ya = np.empty((M, N), np.float64)
+    lib().orc_truth_fp8a8(_p(A), _p(AS), _p(B), _p(BS), C.c_int(int(is_f32)), I64(M), I64(N),
+                          I64(K), I64(AS.shape[1]), I64(BS.shape[1]), I64(rblk), _p(Yt), _p(Ya))
+    return Yt, Ya
+
+
+def truth_mxfp4a8(A, AS, B, BS):
+    A, B, AS, BS = _c(A, np.uint8), _c(B, np.uint8), _c(AS, np.float32), _c(BS, np.uint8)
+    M, K = A.shape
+    N = B.shape[0]
+    Yt = np.empty((M, N), np.float64)
+    Ya = np.empty((M, N), np.float64)
+    lib().orc_truth_mxfp4a8(_p(A), _p(AS), _p(B), _p(BS), I64(M), I64(N), I64(K),
+                            I64(AS.shape[1]), _p(Yt), _p(Ya))
+    return Yt, Ya
+
+
+# ---- numpy helpers shared by the graders ----
+def bf16_bits_to_f32(h: np.ndarray) -> np.ndarray:
+    return (h.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bits(f: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(f, np.float32).view(np.uint32).astype(np.uint64)
+    nan = (u & 0x7FFFFFFF) > 0x7F800000
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    r[nan] = ((u[nan] >> 16) | 0x40).astype(np.uint16)
+    return r
+
+
+def bf16_ulp_distance(a_bits: np.ndarray, b_bits: np.ndarray) -> np.ndarray:
+    """Distance in bf16 ulps between two bf16 bit arrays (sign-magnitude mapped to a line)."""
+    def line(h):
+        h = h.astype(np.int32)
+        return np.where(h & 0x8000, -(h & 0x7FFF), h & 0x7FFF)
+    return np.abs(line(a_bits) - line(b_bits))

@@ -1,0 +1,444 @@
+/* r3d_oracle.cpp -- CPU restatement of libr3d's quantised-matmul arithmetic.
+ *
+ * TEST INFRASTRUCTURE ONLY. This file is the checker the CUDA kernels are graded against
+ * and the timed CPU baseline. Nothing the plugin ships may call, link or load it.
+ *
+ * Each function restates one rule of the reference, in the reference's own operation
+ * order, and cites the file:line of libr3d it follows. The true arbiter behind those
+ * rules (radiance `libref`: ref_gemm.h quant_dot, ref_common.h e8m0_to_f32, ref_planes.h
+ * ScaledRows; module codeberg.org/StillDeadcode/radiance@v1.11.0) is a third-party
+ * dependency that libr3d does not vendor; the citations below are libr3d's own scalar
+ * restatements of it, which is what its unit tools grade its kernels with.
+ *
+ * Pinning: oracle/ref_pin.cpp compiles the one header of the reference that is plain
+ * C++ (src/r3d_mxfp4_q8x.h) and tests/test_oracle_pin.py checks this file's tables against
+ * it; the remaining rules are pinned by the known-answer cases the reference's tools hold
+ * (analytic unit fixture, decoder spot values, fixture generators).
+ * Extensions the reference has no row or test for -- the mxfp4 LM head, the OCP-MX
+ * activation quantiser, fp32 per-channel / per-token scale grids -- are PARITY UNPINNED:
+ * the rule is fixed by this file alone.
+ *
+ * Build: g++ -O3 -std=c++17 -fopenmp -ffp-contract=off (no -ffast-math): mul and add stay
+ * separate roundings except where fmaf is written, as the reference builds with
+ * -ffp-contract=off (CMakeLists.txt:34-37).
+ */
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <cstdlib>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORC_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+inline float bits2f(uint32_t u) { float f; std::memcpy(&f, &u, 4); return f; }
+inline uint32_t f2bits(float f) { uint32_t u; std::memcpy(&u, &f, 4); return u; }
+
+/* bf16 <-> f32: src/r3d_gemm_fp8a8.hip:101-105, src/r3d_band.hip:53-60.
+ * NaN keeps its top bits and sets the quiet bit; everything else rounds to nearest even. */
+inline float bf16_to_f32(uint16_t h) { return bits2f((uint32_t)h << 16); }
+inline uint16_t f32_to_bf16(float f) {
+    const uint32_t u = f2bits(f);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
+    return (uint16_t)((u + 0x7fffu + ((u >> 16) & 1u)) >> 16);
+}
+
+/* f16 -> f32 by the field walk of tools/test_logits_e4m3.cpp:38-44. */
+inline float f16_to_f32(uint16_t b) {
+    const int s = (b >> 15) & 1, e = (b >> 10) & 0x1F, m = b & 0x3FF;
+    const float sign = s ? -1.0f : 1.0f;
+    if (e == 0) return sign * std::ldexp((float)m / 1024.0f, -14);
+    if (e == 31) return m ? NAN : sign * INFINITY;
+    return sign * (1.0f + (float)m / 1024.0f) * std::ldexp(1.0f, e - 15);
+}
+
+/* e4m3fn decode: src/r3d_gemm_fp8a8.hip:134-150 (loop-free form). 1-4-3, bias 7, no
+ * infinities, S.1111.111 the only NaN, subnormals m * 2^-9, signed zero kept. */
+inline float e4m3_to_f32(uint8_t b) {
+    const uint32_t s = (uint32_t)(b >> 7) << 31;
+    const uint32_t e = (b >> 3) & 0xfu, m = b & 7u;
+    if (e == 0u) {
+        if (m == 0u) return bits2f(s);
+        const float f = (float)m / 512.0f;
+        return bits2f(s | (f2bits(f) & 0x7fffffffu));
+    }
+    if (e == 0xfu && m == 7u) return bits2f(s | 0x7fc00000u);
+    return bits2f(s | ((e - 7u + 127u) << 23) | (m << 20));
+}
+
+/* e4m3 encode, round-to-nearest-even, saturating: src/r3d_band.hip:61-87. */
+inline uint8_t f32_to_e4m3(float f) {
+    const uint32_t u = f2bits(f);
+    const uint8_t  s = (uint8_t)((u >> 24) & 0x80u);
+    const uint32_t a = u & 0x7fffffffu;
+    if (a > 0x7f800000u) return (uint8_t)(s | 0x7fu);
+    if (a >= 0x43e00000u) return (uint8_t)(s | 0x7eu);      /* |v| >= 448 */
+    const int e = (int)(a >> 23) - 127;
+    uint32_t m = a & 0x7fffffu;
+    if (e < -10) return s;
+    if (e < -6) {
+        const int sh = -6 - e + 20;
+        m |= 0x800000u;
+        const uint32_t lo = m & ((1u << sh) - 1u);
+        uint32_t q = m >> sh;
+        const uint32_t half = 1u << (sh - 1);
+        if (lo > half || (lo == half && (q & 1u))) ++q;
+        return (uint8_t)(s | q);
+    }
+    uint32_t q = m >> 20;
+    const uint32_t lo = m & 0xfffffu;
+    if (lo > 0x80000u || (lo == 0x80000u && (q & 1u))) ++q;
+    int ee = e + 7;
+    if (q == 8u) { q = 0; ++ee; }
+    if (ee > 15 || (ee == 15 && q >= 7u)) return (uint8_t)(s | 0x7eu);
+    return (uint8_t)(s | ((uint32_t)ee << 3) | q);
+}
+
+/* e2m1 decode: magnitudes by the low three bits, bit 3 the sign; all sixteen codes are
+ * numbers. tools/probe_m4_entry.cpp:22, src/r3d_mxfp4_q8x.h:17-22. */
+const float kE2M1Mag[8] = { 0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f };
+inline float e2m1_to_f32(uint8_t n) { return (n & 8) ? -kE2M1Mag[n & 7] : kE2M1Mag[n & 7]; }
+/* the doubled integer form the int8 arm multiplies with (src/r3d_mxfp4_q8x.h:22) */
+const int8_t kE2M1x2[16] = { 0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12 };
+
+/* E8M0 decode: src/r3d_mxfp4_q8x.h:29-37. 0xFF NaN, 0x00 the subnormal 2^-127. */
+inline float e8m0_to_f32(uint8_t x) {
+    uint32_t u = 0x7fc00000u;
+    if (x != 0xffu) u = (x == 0x00u) ? 0x00400000u : ((uint32_t)x << 23);
+    return bits2f(u);
+}
+
+/* nibble k of a packed e2m1 row: low nibble = even k (src/r3d_gemm_mxfp4.hip:265-266). */
+inline uint8_t nib_at(const uint8_t* row, int64_t k) {
+    const uint8_t b = row[k >> 1];
+    return (k & 1) ? (uint8_t)(b >> 4) : (uint8_t)(b & 0xf);
+}
+
+/* scale-grid helper: which scale column covers 128-chunk `c` when the grid has `cols`
+ * columns over `nchunk` chunks. cols == nchunk is the reference grid; cols == 1 is the
+ * per-token / per-channel extension (PARITY UNPINNED). */
+inline int64_t scol(int64_t c, int64_t cols, int64_t nchunk) {
+    return cols == nchunk ? c : (cols == 1 ? 0 : c * cols / nchunk);
+}
+
+} /* namespace */
+
+/* ------------------------------------------------------------------ scalar codecs */
+ORC_API float    orc_e4m3_to_f32(uint8_t b) { return e4m3_to_f32(b); }
+ORC_API uint8_t  orc_f32_to_e4m3(float f)   { return f32_to_e4m3(f); }
+/* array form of the encoder: clamp to +-448 first, as the quantisers do */
+ORC_API void     orc_f32_to_e4m3_n(const float* x, int64_t n, uint8_t* q) {
+    for (int64_t i = 0; i < n; ++i) {
+        float c = x[i];
+        if (c > 448.0f) c = 448.0f;
+        if (c < -448.0f) c = -448.0f;
+        q[i] = f32_to_e4m3(c);
+    }
+}
+ORC_API float    orc_e2m1_to_f32(uint8_t n) { return e2m1_to_f32(n); }
+ORC_API int      orc_e2m1_x2(uint8_t n)     { return kE2M1x2[n & 15]; }
+ORC_API float    orc_e8m0_to_f32(uint8_t x) { return e8m0_to_f32(x); }
+ORC_API uint16_t orc_f32_to_bf16(float f)   { return f32_to_bf16(f); }
+ORC_API float    orc_bf16_to_f32(uint16_t h){ return bf16_to_f32(h); }
+ORC_API float    orc_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
+
+/* ------------------------------------------------------------------ quant_act_fp8
+ * src/r3d_band.hip:119-153. Per (row, group of <= `group` columns): amax by strict `>`
+ * from 0 (NaN never wins), scale = amax > 0 ? amax * (1/448) : 1, inv = 1/scale,
+ * c = clamp(x * inv, +-448), code = e4m3(c). The scale is a dequant multiplier. */
+ORC_API void orc_quant_act_fp8(const float* x, int64_t M, int64_t n, int64_t group,
+                               uint8_t* q, float* scale) {
+    if (group <= 0 || group > n) group = n;
+    const int64_t ngrp = (n + group - 1) / group;
+    for (int64_t r = 0; r < M; ++r)
+        for (int64_t g = 0; g < ngrp; ++g) {
+            const int64_t k0 = g * group, k1 = (k0 + group < n) ? k0 + group : n;
+            float amax = 0.0f;
+            for (int64_t k = k0; k < k1; ++k) {
+                const float m = std::fabs(x[r * n + k]);
+                if (m > amax) amax = m;
+            }
+            const float sc = amax > 0.0f ? amax * (1.0f / 448.0f) : 1.0f;
+            scale[r * ngrp + g] = sc;
+            const float inv = 1.0f / sc;
+            for (int64_t k = k0; k < k1; ++k) {
+                float c = x[r * n + k] * inv;
+                if (c > 448.0f) c = 448.0f;
+                if (c < -448.0f) c = -448.0f;
+                q[r * n + k] = f32_to_e4m3(c);
+            }
+        }
+}
+
+/* ------------------------------------------------------------------ OCP-MX activation
+ * quantiser (e4m3 elements, one E8M0 scale per 32 columns). PARITY UNPINNED: the
+ * reference has no such quantiser. Rule: shared exponent = floor(log2(amax)) - 8 (8 is
+ * e4m3's largest exponent), stored biased by 127 and clamped to [0, 254]; elements are
+ * the saturating RTNE e4m3 of x * 2^-exp. An all-zero block stores exponent byte 127. */
+ORC_API void orc_quant_act_mx8(const float* x, int64_t M, int64_t n, uint8_t* q,
+                               uint8_t* e8) {
+    const int64_t ngrp = (n + 31) / 32;
+    for (int64_t r = 0; r < M; ++r)
+        for (int64_t g = 0; g < ngrp; ++g) {
+            const int64_t k0 = g * 32, k1 = (k0 + 32 < n) ? k0 + 32 : n;
+            float amax = 0.0f;
+            for (int64_t k = k0; k < k1; ++k) {
+                const float m = std::fabs(x[r * n + k]);
+                if (m > amax) amax = m;
+            }
+            int eb = 127;
+            if (amax > 0.0f && std::isfinite(amax)) {
+                int ex; (void)std::frexp(amax, &ex);      /* amax = f * 2^ex, f in [.5,1) */
+                eb = (ex - 1) - 8 + 127;
+                if (eb < 0) eb = 0;
+                if (eb > 254) eb = 254;
+            }
+            e8[r * ngrp + g] = (uint8_t)eb;
+            const float inv = std::ldexp(1.0f, 127 - eb);
+            for (int64_t k = k0; k < k1; ++k) q[r * n + k] = f32_to_e4m3(x[r * n + k] * inv);
+        }
+}
+
+/* ------------------------------------------------------------------ q8x activation arm
+ * src/r3d_gemm_mxfp4.hip:1150-1166 (tools/bench_dot4_seed.hip:371-379): per (m, 32
+ * columns) e = dec(a); mx = max|e|; s = mx ? mx/127 : 1; x8 = (int8) rintf(e / s). */
+ORC_API void orc_q8x_requant(const uint8_t* A, int64_t M, int64_t K, int64_t a_pitch,
+                             int8_t* X8, float* SG) {
+    const int64_t cols = K >> 5;
+    for (int64_t m = 0; m < M; ++m)
+        for (int64_t g = 0; g < cols; ++g) {
+            float v[32], mx = 0.0f;
+            for (int j = 0; j < 32; ++j) {
+                v[j] = e4m3_to_f32(A[m * a_pitch + g * 32 + j]);
+                mx = std::fmax(mx, std::fabs(v[j]));
+            }
+            const float s = mx ? mx / 127.0f : 1.0f;
+            SG[m * cols + g] = s;
+            for (int j = 0; j < 32; ++j)
+                X8[m * K + g * 32 + j] = (int8_t)std::rint(v[j] / s);
+        }
+}
+
+/* ------------------------------------------------------------------ fp8a8 quant_dot
+ * src/r3d_gemm_fp8a8.hip:9-26; scalar form tools/bench_fp8_skinny.cpp:408-419.
+ * Per 128-of-K group ascending: part = sum a_k * b_k (f32, ascending k, separate mul and
+ * add); acc += (part * sa[m, g]) * sb[srow, g]; y = bf16(acc).
+ * bs_is_f32 / as_cols == 1 / bs_cols == 1 are the extension grids (PARITY UNPINNED).
+ * Yacc (optional) receives the f32 accumulator before narrowing. */
+ORC_API void orc_gemm_fp8a8(const uint8_t* A, const float* AS, const uint8_t* B,
+                            const void* BS, int bs_is_f32,
+                            int64_t M, int64_t N, int64_t K,
+                            int64_t as_cols, int64_t bs_cols, int64_t rblk,
+                            uint16_t* Y, float* Yacc) {
+    const int64_t ngrp = K / 128;
+    float lut[256];
+    for (int i = 0; i < 256; ++i) lut[i] = e4m3_to_f32((uint8_t)i);
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < N; ++r) {
+        const int64_t sr = rblk > 1 ? r / rblk : r;
+        for (int64_t t = 0; t < M; ++t) {
+            float acc = 0.0f;
+            for (int64_t g = 0; g < ngrp; ++g) {
+                float part = 0.0f;
+                const uint8_t* a = A + t * K + g * 128;
+                const uint8_t* b = B + r * K + g * 128;
+                for (int s = 0; s < 128; ++s) part += lut[a[s]] * lut[b[s]];
+                const int64_t bi = sr * bs_cols + scol(g, bs_cols, ngrp);
+                const float sb = bs_is_f32 ? ((const float*)BS)[bi]
+                                           : bf16_to_f32(((const uint16_t*)BS)[bi]);
+                acc += (part * AS[t * as_cols + scol(g, as_cols, ngrp)]) * sb;
+            }
+            if (Y) Y[t * N + r] = f32_to_bf16(acc);
+            if (Yacc) Yacc[t * N + r] = acc;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------ mxfp4a8 quant_dot
+ * src/r3d_gemm_mxfp4.hip:14-15; scalar form tools/probe_m4_entry.cpp:72-91.
+ * Per 32-of-K group ascending: s = sum a_k * w_k (f32); acc += (s * sa[m, g/4]) * sc
+ * with sc = E8M0(x) (0xFF NaN; the probe's ldexpf(1, x-127) equals the table for every
+ * other byte, 0x00 included: 2^-127 is representable as an f32 subnormal). */
+ORC_API void orc_gemm_mxfp4a8(const uint8_t* A, const float* AS, const uint8_t* B,
+                              const uint8_t* BS, int64_t M, int64_t N, int64_t K,
+                              int64_t as_cols, uint16_t* Y, float* Yacc) {
+    const int64_t bs_cols = (K + 31) / 32, n128 = (K + 127) / 128;
+    float lut[256];
+    for (int i = 0; i < 256; ++i) lut[i] = e4m3_to_f32((uint8_t)i);
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+        const uint8_t* brow = B + n * (K / 2);
+        for (int64_t m = 0; m < M; ++m) {
+            float acc = 0.0f;
+            for (int64_t g = 0; g < bs_cols; ++g) {
+                float s = 0.0f;
+                const int64_t kend = (g * 32 + 32 < K) ? g * 32 + 32 : K;
+                for (int64_t kk = g * 32; kk < kend; ++kk)
+                    s += lut[A[m * K + kk]] * e2m1_to_f32(nib_at(brow, kk));
+                const float sc = e8m0_to_f32(BS[n * bs_cols + g]);
+                acc += (s * AS[m * as_cols + scol(g >> 2, as_cols, n128)]) * sc;
+            }
+            if (Y) Y[m * N + n] = f32_to_bf16(acc);
+            if (Yacc) Yacc[m * N + n] = acc;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------ mxfp4a8, q8x arm
+ * The int8 arm's own chain, bit for bit (tools/bench_dot4_seed.hip:365-401 for walk 0,
+ * src/r3d_gemm_mxfp4.hip:1341-1458 for walk 1). Inputs are the requantised activation
+ * (orc_q8x_requant) and the ORIGINAL nibble + E8M0 planes.
+ *   p  = sum x8 * (2 * e2m1)   exact int32 over the 32-group
+ *   c  = ((((float)p * SG[m,g]) * AS[m,g/4]) * sc) * 0.5f      left to right
+ *   walk 0 (dot4): per 256-of-K step T = ((c0+c1)+(c2+c3)) + ((c4+c5)+(c6+c7)); acc += T
+ *   walk 1 (lane map): lane t = g mod 32 accumulates its groups serially, then the 32
+ *          lane sums fold by a butterfly over lane xor 1, 2, 4, 8, 16.
+ * K % 256 == 0 is the arm's gate. */
+ORC_API void orc_gemm_mxfp4_q8x(const int8_t* X8, const float* SG, const float* AS,
+                                const uint8_t* B, const uint8_t* BS,
+                                int64_t M, int64_t N, int64_t K, int64_t as_cols,
+                                int walk, uint16_t* Y, float* Yacc) {
+    const int64_t K32 = K >> 5;
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+        const uint8_t* brow = B + n * (K / 2);
+        float* c = (float*)std::malloc((size_t)K32 * sizeof(float));
+        for (int64_t m = 0; m < M; ++m) {
+            for (int64_t g = 0; g < K32; ++g) {
+                int32_t p = 0;
+                for (int j = 0; j < 32; ++j) {
+                    const int64_t k = g * 32 + j;
+                    p += (int32_t)X8[m * K + k] * (int32_t)kE2M1x2[nib_at(brow, k)];
+                }
+                const float sc = e8m0_to_f32(BS[n * K32 + g]);
+                c[g] = (float)p * SG[m * K32 + g] * AS[m * as_cols + (g >> 2)] * sc * 0.5f;
+            }
+            float acc = 0.0f;
+            if (walk == 0) {
+                for (int64_t it = 0; it < (K >> 8); ++it) {
+                    const float* t = c + it * 8;
+                    const float v0 = (t[0] + t[1]) + (t[2] + t[3]);
+                    const float v1 = (t[4] + t[5]) + (t[6] + t[7]);
+                    acc += v0 + v1;
+                }
+            } else {
+                float lane[32];
+                for (int t = 0; t < 32; ++t) lane[t] = 0.0f;
+                for (int64_t g = 0; g < K32; ++g) lane[g & 31] += c[g];
+                for (int off = 1; off < 32; off <<= 1) {
+                    float nx[32];
+                    for (int t = 0; t < 32; ++t) nx[t] = lane[t] + lane[t ^ off];
+                    for (int t = 0; t < 32; ++t) lane[t] = nx[t];
+                }
+                acc = lane[0];
+            }
+            if (Y) Y[m * N + n] = f32_to_bf16(acc);
+            if (Yacc) Yacc[m * N + n] = acc;
+        }
+        std::free(c);
+    }
+}
+
+/* ------------------------------------------------------------------ logits, e4m3 head
+ * src/r3d_gemm_logits.hip:5-9; oracle walk tools/test_logits_e4m3.cpp:97-110.
+ * w = f32(code) * f32(scale[n/br, k/128]) rounded once; acc = fma(x, w, acc), k
+ * ascending. sdt: 0 bf16, 1 f16, 2 f32. Output f32. */
+ORC_API void orc_logits_e4m3(const uint16_t* X, const uint8_t* codes, const void* scale,
+                             int sdt, int64_t br, int64_t M, int64_t N, int64_t K,
+                             float* Y) {
+    const int64_t scols = (K + 127) / 128;
+    float lut[256];
+    for (int i = 0; i < 256; ++i) lut[i] = e4m3_to_f32((uint8_t)i);
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n)
+        for (int64_t m = 0; m < M; ++m) {
+            float acc = 0.0f;
+            for (int64_t k = 0; k < K; ++k) {
+                const int64_t si = (n / br) * scols + (k / 128);
+                const float sv = sdt == 2 ? ((const float*)scale)[si]
+                               : sdt == 1 ? f16_to_f32(((const uint16_t*)scale)[si])
+                                          : bf16_to_f32(((const uint16_t*)scale)[si]);
+                const float wv = lut[codes[n * K + k]] * sv;
+                acc = std::fmaf(bf16_to_f32(X[m * K + k]), wv, acc);
+            }
+            Y[m * N + n] = acc;
+        }
+}
+
+/* ------------------------------------------------------------------ logits, mxfp4 head
+ * PARITY UNPINNED (the reference has no mxfp4 head row). Rule: the e4m3 head's walk with
+ * w = e2m1(code) * E8M0(scale[n, k/32]) (exact: a power-of-two multiple). */
+ORC_API void orc_logits_mxfp4(const uint16_t* X, const uint8_t* B, const uint8_t* BS,
+                              int64_t M, int64_t N, int64_t K, float* Y) {
+    const int64_t K32 = (K + 31) / 32;
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n)
+        for (int64_t m = 0; m < M; ++m) {
+            float acc = 0.0f;
+            for (int64_t k = 0; k < K; ++k) {
+                const float wv = e2m1_to_f32(nib_at(B + n * (K / 2), k)) *
+                                 e8m0_to_f32(BS[n * K32 + (k >> 5)]);
+                acc = std::fmaf(bf16_to_f32(X[m * K + k]), wv, acc);
+            }
+            Y[m * N + n] = acc;
+        }
+}
+
+/* ------------------------------------------------------------------ f64 truth twins
+ * The same dequantised operands summed in double, plus sum |a*w*scales| per output: the
+ * grader's cancellation floor. Not part of the reference; used only to interpret misses. */
+ORC_API void orc_truth_fp8a8(const uint8_t* A, const float* AS, const uint8_t* B,
+                             const void* BS, int bs_is_f32, int64_t M, int64_t N, int64_t K,
+                             int64_t as_cols, int64_t bs_cols, int64_t rblk,
+                             double* Yt, double* Yabs) {
+    const int64_t ngrp = K / 128;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < N; ++r) {
+        const int64_t sr = rblk > 1 ? r / rblk : r;
+        for (int64_t t = 0; t < M; ++t) {
+            double acc = 0.0, ab = 0.0;
+            for (int64_t g = 0; g < ngrp; ++g) {
+                const int64_t bi = sr * bs_cols + scol(g, bs_cols, ngrp);
+                const double sb = bs_is_f32 ? ((const float*)BS)[bi]
+                                            : bf16_to_f32(((const uint16_t*)BS)[bi]);
+                const double sc = (double)AS[t * as_cols + scol(g, as_cols, ngrp)] * sb;
+                for (int s = 0; s < 128; ++s) {
+                    const double p = (double)e4m3_to_f32(A[t * K + g * 128 + s]) *
+                                     (double)e4m3_to_f32(B[r * K + g * 128 + s]) * sc;
+                    acc += p; ab += std::fabs(p);
+                }
+            }
+            Yt[t * N + r] = acc; if (Yabs) Yabs[t * N + r] = ab;
+        }
+    }
+}
+
+ORC_API void orc_truth_mxfp4a8(const uint8_t* A, const float* AS, const uint8_t* B,
+                               const uint8_t* BS, int64_t M, int64_t N, int64_t K,
+                               int64_t as_cols, double* Yt, double* Yabs) {
+    const int64_t K32 = (K + 31) / 32, n128 = (K + 127) / 128;
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n)
+        for (int64_t m = 0; m < M; ++m) {
+            double acc = 0.0, ab = 0.0;
+            for (int64_t k = 0; k < K; ++k) {
+                const double sc = (double)AS[m * as_cols + scol(k >> 7, as_cols, n128)] *
+                                  (double)e8m0_to_f32(BS[n * K32 + (k >> 5)]);
+                const double p = (double)e4m3_to_f32(A[m * K + k]) *
+                                 (double)e2m1_to_f32(nib_at(B + n * (K / 2), k)) * sc;
+                acc += p; ab += std::fabs(p);
+            }
+            Yt[m * N + n] = acc; if (Yabs) Yabs[m * N + n] = ab;
+        }
+}
+
+ORC_API int orc_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}

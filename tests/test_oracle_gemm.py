@@ -1,0 +1,160 @@
+"""The oracle's matmul rules: known-answer fixtures the reference's tools hold, independent
+numpy re-derivations on small shapes, and the committed golden vectors."""
+import math
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import gen
+from oracle import oracle as orc
+
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+def test_fp8_unit_fixture_is_analytic():
+    # tools/bench_fp8_skinny.cpp:595-624: every output must equal K * (1 + r % 3) exactly
+    for (M, K, N) in [(1, 128, 7), (14, 512, 130), (3, 2048, 64)]:
+        case, expect = gen.fixture_fp8_unit(M, K, N)
+        Y, acc = orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], 1, want_acc=True)
+        assert np.array_equal(acc, expect)
+        assert np.array_equal(Y, orc.f32_to_bf16_bits(expect.astype(np.float32)))
+
+
+def _numpy_fp8(case):
+    """independent restatement: same order, written with numpy scalars"""
+    lut = gen.e4m3_decode_table()
+    A, B, AS, BS, rblk = case["A"], case["B"], case["AS"], case["BS"], case["rblk"]
+    sb = BS if BS.dtype == np.float32 else orc.bf16_bits_to_f32(BS)
+    M, K = A.shape
+    N = B.shape[0]
+    out = np.zeros((M, N), np.float32)
+    for m in range(M):
+        for n in range(N):
+            acc = np.float32(0)
+            for g in range(K // 128):
+                part = np.float32(0)
+                for k in range(g * 128, g * 128 + 128):
+                    part = np.float32(part + np.float32(lut[A[m, k]] * lut[B[n, k]]))
+                ca = g if AS.shape[1] > 1 else 0
+                cb = g if sb.shape[1] > 1 else 0
+                acc = np.float32(acc + np.float32(np.float32(part * AS[m, ca]) * sb[n // rblk, cb]))
+            out[m, n] = acc
+    return out
+
+
+@pytest.mark.parametrize("grid", ["ref128", "row", "channel"])
+def test_fp8_oracle_matches_numpy_walk(grid):
+    case = gen.case_fp8(3, 2, 9 if grid != "ref128" else 130, 256, grid)
+    if grid == "ref128":
+        case = {k: (v[:, :] if hasattr(v, "shape") else v) for k, v in case.items()}
+    want = _numpy_fp8(case)
+    Y, acc = orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], case["rblk"], want_acc=True)
+    assert np.array_equal(acc.view(np.uint32), want.view(np.uint32))
+
+
+def _numpy_mxfp4(case):
+    lut = gen.e4m3_decode_table()
+    mag = np.array([0, .5, 1, 1.5, 2, 3, 4, 6], np.float32)
+    A, B, AS, BS = case["A"], case["B"], case["AS"], case["BS"]
+    M, K = A.shape
+    N = B.shape[0]
+    out = np.zeros((M, N), np.float32)
+    for m in range(M):
+        for n in range(N):
+            acc = np.float32(0)
+            for g in range(K // 32):
+                s = np.float32(0)
+                for k in range(g * 32, g * 32 + 32):
+                    byte = B[n, k >> 1]
+                    nib = (byte >> 4) if (k & 1) else (byte & 15)
+                    w = -mag[nib & 7] if nib & 8 else mag[nib & 7]
+                    s = np.float32(s + np.float32(lut[A[m, k]] * w))
+                x = int(BS[n, g])
+                sc = np.float32("nan") if x == 255 else np.float32(math.ldexp(1.0, x - 127))
+                with np.errstate(invalid="ignore"):
+                    acc = np.float32(acc + np.float32(np.float32(s * AS[m, g >> 2]) * sc))
+            out[m, n] = acc
+    return out
+
+
+def test_mxfp4_oracle_matches_probe_walk_on_probe_fixture():
+    # the walk of tools/probe_m4_entry.cpp:72-91 over that tool's own srand(777) fixture
+    case = gen.fixture_probe_m4(2, 256, 12)
+    want = _numpy_mxfp4(case)
+    Y, acc = orc.gemm_mxfp4a8(case["A"], case["AS"], case["B"], case["BS"], want_acc=True)
+    assert np.array_equal(acc.view(np.uint32), want.view(np.uint32))
+    assert np.count_nonzero(acc) > acc.size // 2              # not a fixture of zeros
+
+
+def test_mxfp4_scale_byte_torture():
+    case = gen.case_mxfp4(4, 1, 8, 128)
+    case["BS"][:] = 127
+    case["BS"][0, 1] = 255            # NaN scale poisons the row even if the group sums to 0
+    case["B"][0, 16:32] = 0
+    case["BS"][1, :] = 0              # 2^-127 everywhere: tiny but not zero
+    Y, acc = orc.gemm_mxfp4a8(case["A"], case["AS"], case["B"], case["BS"], want_acc=True)
+    assert math.isnan(acc[0, 0]) and not np.isnan(acc[0, 1:]).any()
+    base = case["BS"].copy(); base[1, :] = 127
+    _, acc1 = orc.gemm_mxfp4a8(case["A"], case["AS"], case["B"], base, want_acc=True)
+    assert acc[0, 1] != 0 and abs(acc[0, 1] / acc1[0, 1] - 2.0 ** -127) < 1e-6 * 2.0 ** -127
+
+
+def test_q8x_chain_integer_exact_witness():
+    # With activations that requantise exactly (all |e| in a group equal) and unit scales the
+    # int8 arm's chain must reproduce the fp32 oracle bit for bit.
+    rng = np.random.default_rng(9)
+    M, N, K = 2, 16, 512
+    A = np.where(rng.integers(0, 2, (M, K)) > 0, 0x38, 0xB8).astype(np.uint8)      # +-1.0
+    AS = np.full((M, K // 128), 127.0, np.float32)
+    B = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+    BS = np.full((N, K // 32), 127, np.uint8)
+    y_ref = orc.gemm_mxfp4a8(A, AS, B, BS)
+    for walk in (0, 1):
+        assert np.array_equal(orc.gemm_mxfp4_q8x(A, AS, B, BS, walk), y_ref)
+
+
+def test_q8x_close_to_fp32_walk_on_random_data():
+    case = gen.case_mxfp4(11, 4, 64, 1024)
+    y = orc.bf16_bits_to_f32(orc.gemm_mxfp4a8(**case))
+    for walk in (0, 1):
+        yq = orc.bf16_bits_to_f32(orc.gemm_mxfp4_q8x(case["A"], case["AS"], case["B"], case["BS"], walk))
+        rel = np.linalg.norm(yq - y) / np.linalg.norm(y)
+        assert rel < 3e-2                     # the op's tolerance; the arm grades ~1e-3..7e-3
+
+
+@pytest.mark.parametrize("N,K,M,br,sdt", [
+    (256, 512, 1, 128, 0), (256, 512, 3, 128, 0), (130, 300, 5, 128, 0), (256, 512, 9, 128, 0),
+    (200, 512, 2, 1, 0), (256, 384, 4, 128, 1), (256, 512, 8, 128, 2), (8, 4, 1, 128, 0)])
+def test_logits_oracle_on_reference_case_geometries(N, K, M, br, sdt):
+    # the eight geometries of tools/test_logits_e4m3.cpp:155-164, graded against float64
+    c = gen.case_logits(N * 31 + K * 7 + M, M, N, K, br, sdt)
+    y = orc.logits_e4m3(c["X"], c["codes"], c["scale"], sdt, br)
+    lut = gen.e4m3_decode_table().astype(np.float64)
+    sv = (c["scale"] if sdt == 2 else
+          c["scale"].view(np.float16).astype(np.float32) if sdt == 1 else
+          orc.bf16_bits_to_f32(c["scale"])).astype(np.float64)
+    w = lut[c["codes"]] * np.repeat(np.repeat(sv, br, axis=0)[:N], 128, axis=1)[:, :K]
+    want = orc.bf16_bits_to_f32(c["X"]).astype(np.float64) @ w.T
+    den = np.maximum(np.abs(lut[c["codes"]] * 1.0).max() * np.abs(want).max() * 1e-3, 1e-6)
+    assert np.abs(y - want).max() / max(np.abs(want).max(), den) < 1e-5
+
+
+def test_golden_vectors():
+    files = sorted(GOLD.glob("*.npz"))
+    assert files, "golden fixtures missing: run tests/golden/make_golden.py"
+    for f in files:
+        g = np.load(f)
+        kind = str(g["kind"])
+        if kind == "fp8a8":
+            y = orc.gemm_fp8a8(g["A"], g["AS"], g["B"], g["BS"], int(g["rblk"]))
+        elif kind == "mxfp4a8":
+            y = orc.gemm_mxfp4a8(g["A"], g["AS"], g["B"], g["BS"])
+        elif kind == "mxfp4a8_q8x":
+            y = orc.gemm_mxfp4_q8x(g["A"], g["AS"], g["B"], g["BS"], int(g["walk"]))
+        elif kind == "logits_e4m3":
+            y = orc.logits_e4m3(g["X"], g["codes"], g["scale"], int(g["sdt"]), int(g["br"]))
+        else:
+            raise AssertionError(kind)
+        a, b = np.ascontiguousarray(y), g["Y"]
+        assert a.dtype == b.dtype and np.array_equal(a.view(np.uint8), b.view(np.uint8)), f.name

@@ -1,0 +1,347 @@
+"""Host side of the plugin, no GPU needed: the loader surface, the row tables and band
+resolution, the registration-gate kill switches, the entries' refusal codes (every case here
+is refused before any device work), and the LM-head layout hooks."""
+import ctypes as C
+import os
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from libr3d_b200 import abi
+from libr3d_b200.plugin import EXPORTS, ArgPack, Plugin, planes_blob, tensor_desc
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_exports_every_declared_symbol(plug):
+    for name in EXPORTS:
+        assert hasattr(plug.lib, name), name
+    # and the list above covers every function the two headers declare
+    declared = set()
+    for h in ("rad_abi.h", "r3d_b200.h"):
+        text = (ROOT / "include" / h).read_text()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        declared |= set(re.findall(r"\b((?:rad|r3d)_[a-z0-9_]+)\s*\(", text))
+    declared -= {"rad_arg_in"}
+    assert declared <= set(EXPORTS), declared - set(EXPORTS)
+
+
+def test_identity_and_abi_pin(plug):
+    assert plug.lib.rad_plugin_abi_version() == 26            # README.md:10 of the reference
+    info = plug.info()
+    assert info["kind"] == 1 and info["targets"] == "sm_100a"
+
+
+def test_schemas_entry_for_entry(plug):
+    s = plug.schemas()
+    I, S = 0, 2
+    R, O = 0, 1
+    assert s["gemm_nt_q"]["params"] == [("M", I, R), ("N", I, R), ("K", I, R), ("group", I, R),
+                                        ("dtype", S, R), ("pb1", I, O), ("pb2", I, O),
+                                        ("split_n", I, O)]
+    IN, OUT, W = 0, 1, 3
+    assert s["gemm_nt_q"]["operands"] == [("a", IN, 0), ("a_scale", IN, 1), ("b", W, 0),
+                                          ("b_scale", W, 0), ("y", OUT, 0), ("a_sum", IN, 1),
+                                          ("b_ref", W, 1)]
+    assert s["logits_gemm"]["params"] == [("M", I, R), ("n_vocab", I, R), ("n_embd", I, R),
+                                          ("dtype", S, R)]
+    assert s["logits_gemm"]["operands"] == [("x", IN, 0), ("lm_head", W, 0), ("logits", OUT, 0)]
+    assert [p[0] for p in s["gemm_nt_q_gated"]["params"]] == ["M", "N", "K", "group", "dtype", "act"]
+    assert [o[0] for o in s["gemm_nt_q_gated"]["operands"]] == ["a", "a_scale", "b", "b_scale", "q",
+                                                                 "scale", "out_bf16"]
+    assert plug.lib.rad_kernel_schema_at(-1) is None or not plug.lib.rad_kernel_schema_at(-1)
+    assert not plug.lib.rad_kernel_schema_at(99)
+
+
+def test_rows_names_priorities_constraints(plug):
+    rows = {r.name: r for r in plug.rows()}
+    want = {"logits_gemm_e4m3": 1000, "gemm_nt_q_mxfp4": 1000, "gemm_nt_q_fp8a8": 1000,
+            "gemm_nt_q_fp8a8_decode": 1100, "gemm_nt_q_mxfp4_decode": 1100,
+            "gemm_nt_q_mxfp4_decode_q8x": 1200}
+    assert {k: v.priority for k, v in rows.items()} == want
+    assert all(r.domain == abi.RAD_DOMAIN_DEVICE and r.launch for r in rows.values())
+    assert rows["logits_gemm_e4m3"].has_layout
+    assert ("M", abi.RAD_C_LE, 8, None) in rows["gemm_nt_q_fp8a8_decode"].constraints
+    assert ("group", abi.RAD_C_EQ, 128, None) in rows["gemm_nt_q_fp8a8"].constraints
+    assert ("K", abi.RAD_C_DIV, 128, None) in rows["gemm_nt_q_mxfp4_decode"].constraints
+    # never constrain N: the engine may omit it and an absent key fails its constraint
+    assert not any(c[0] == "N" for r in rows.values() for c in r.constraints)
+    assert not plug.lib.rad_kernel_at(len(rows)) and not plug.lib.rad_kernel_at(-1)
+
+
+def test_band_resolution(plug):
+    q = dict(N=27648, K=5120)
+    name = lambda **kw: plug.resolve("gemm_nt_q", {**q, **kw}).name
+    assert name(M=1, group=32, dtype="mxfp4a8") == "gemm_nt_q_mxfp4_decode_q8x"
+    assert name(M=8, group=32, dtype="mxfp4a8") == "gemm_nt_q_mxfp4_decode_q8x"
+    assert name(M=16, group=32, dtype="mxfp4a8") == "gemm_nt_q_mxfp4"
+    assert name(M=4, group=128, dtype="fp8a8") == "gemm_nt_q_fp8a8_decode"
+    assert name(M=9, group=128, dtype="fp8a8") == "gemm_nt_q_fp8a8"
+    assert plug.resolve("gemm_nt_q", dict(M=1, N=8, K=200, group=128, dtype="fp8a8")) is None
+    assert plug.resolve("gemm_nt_q", dict(M=1, N=8, K=256, group=64, dtype="fp8a8")) is None
+    assert plug.resolve("gemm_nt_q", dict(M=1, N=8, K=256, group=128, dtype="w4a16")) is None
+    # a query without M cannot satisfy the decode rows' M <= 8
+    assert plug.resolve("gemm_nt_q", dict(N=8, K=256, group=128, dtype="fp8a8")).name == "gemm_nt_q_fp8a8"
+    assert plug.resolve("logits_gemm", dict(M=1, n_vocab=151936, n_embd=5120, dtype="bf16")).name == \
+        "logits_gemm_e4m3"
+    assert plug.resolve("logits_gemm", dict(M=1, n_vocab=10, n_embd=64, dtype="bf16")) is None
+
+
+_DUMP = r"""
+import sys
+sys.path.insert(0, %r)
+from libr3d_b200.plugin import Plugin
+p = Plugin()
+print(",".join(sorted(r.name for r in p.rows())))
+r = p.resolve("gemm_nt_q", dict(M=1, N=64, K=256, group=32, dtype="mxfp4a8"))
+print(r.name if r else "-")
+r = p.resolve("gemm_nt_q", dict(M=1, N=64, K=256, group=128, dtype="fp8a8"))
+print(r.name if r else "-")
+""" % str(ROOT)
+
+
+def _rows_under(env):
+    e = {k: v for k, v in os.environ.items() if not k.startswith("R3D_")}
+    e.update(env)
+    out = subprocess.run([sys.executable, "-c", _DUMP], env=e, capture_output=True, text=True,
+                         check=True).stdout.split()
+    return set(out[0].split(",")), out[1], out[2]
+
+
+ALL = {"logits_gemm_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode",
+       "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x"}
+
+
+@pytest.mark.parametrize("env,hidden,mx_row,f8_row", [
+    ({}, set(), "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_fp8a8_decode"),
+    ({"R3D_MXFP4_Q8X": "0"}, {"gemm_nt_q_mxfp4_decode_q8x"}, "gemm_nt_q_mxfp4_decode", "gemm_nt_q_fp8a8_decode"),
+    ({"R3D_MXFP4_Q8X": "1"}, set(), "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_fp8a8_decode"),
+    ({"R3D_NO_FP4_DEC": "1"}, {"gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x"}, "gemm_nt_q_mxfp4", "gemm_nt_q_fp8a8_decode"),
+    ({"R3D_NO_MXFP4": ""}, {"gemm_nt_q_mxfp4", "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x"}, "-", "gemm_nt_q_fp8a8_decode"),
+    ({"R3D_NO_FP8_DEC": "1"}, {"gemm_nt_q_fp8a8_decode"}, "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_fp8a8"),
+    ({"R3D_NO_FP8A8": "1"}, {"gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode"}, "gemm_nt_q_mxfp4_decode_q8x", "-"),
+])
+def test_kill_switch_matrix(env, hidden, mx_row, f8_row):
+    # levers act at registration: a hidden row is not enumerated and the band re-resolves
+    # (src/r3d_rows.cpp:2216-2236 of the reference); presence levers fire on any value, the
+    # q8x lever only on the literal "0"
+    rows, mx, f8 = _rows_under(env)
+    assert rows == ALL - hidden and mx == mx_row and f8 == f8_row
+
+
+# ------------------------------------------------------------------ refusal matrix
+def _fp8_args(M=2, N=256, K=256, drop=(), **over):
+    z = np.zeros(16, np.uint8).ctypes.data          # a live host pointer: refusals precede any use
+    t = dict(a=tensor_desc(z, abi.RAD_F8E4M3, [M, K]), a_scale=tensor_desc(z, abi.RAD_F32, [M, K // 128]),
+             b=tensor_desc(z, abi.RAD_F8E4M3, [N, K]),
+             b_scale=tensor_desc(z, abi.RAD_BF16, [(N + 127) // 128, K // 128]),
+             y=tensor_desc(z, abi.RAD_BF16, [M, N]), a_sum=tensor_desc(None, abi.RAD_F32, []),
+             b_ref=tensor_desc(None, abi.RAD_BF16, []))
+    p = dict(dtype="fp8a8", M=64, N=N, K=K, group=128)
+    for k, v in over.items():
+        if k in t:
+            t[k] = v
+        else:
+            p[k] = v
+    for k in drop:
+        p.pop(k)
+    return ArgPack(list(t.values()), p), z
+
+
+def _mx_args(M=2, N=64, K=256, drop=(), **over):
+    z = np.zeros(16, np.uint8).ctypes.data
+    t = dict(a=tensor_desc(z, abi.RAD_F8E4M3, [M, K]), a_scale=tensor_desc(z, abi.RAD_F32, [M, K // 128]),
+             b=tensor_desc(z, abi.RAD_FP4E2M1, [N, K]), b_scale=tensor_desc(z, abi.RAD_E8M0, [N, K // 32]),
+             y=tensor_desc(z, abi.RAD_BF16, [M, N]), a_sum=tensor_desc(None, abi.RAD_F32, []),
+             b_ref=tensor_desc(None, abi.RAD_BF16, []))
+    p = dict(dtype="mxfp4a8", M=64, N=N, K=K, group=32)
+    for k, v in over.items():
+        if k in t:
+            t[k] = v
+        else:
+            p[k] = v
+    for k in drop:
+        p.pop(k)
+    return ArgPack(list(t.values()), p), z
+
+
+Z = np.zeros(16, np.uint8)
+U, SH, ST = abi.RAD_E_UNSUPPORTED, abi.RAD_E_SHAPE, abi.RAD_E_STRIDE
+
+
+@pytest.mark.parametrize("over,code", [
+    (dict(dtype="mxfp4a8"), U), (dict(pb1=1), U), (dict(K=200), U), (dict(drop=("N",)), SH),
+    (dict(N=7, y=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [2, 256])), SH),                                               # numel(y) % N
+    (dict(a_sum=tensor_desc(Z.ctypes.data, abi.RAD_F32, [2])), U),
+    (dict(b_ref=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [2])), U),
+    (dict(y=tensor_desc(Z.ctypes.data, abi.RAD_F32, [2, 256])), U),
+    (dict(a=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [2, 256])), U),
+    (dict(b_scale=tensor_desc(Z.ctypes.data, abi.RAD_F16, [2, 2])), U),
+    (dict(b_scale=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [2, 4])), U),      # grid is 64 of K
+    (dict(b_scale=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [3, 2])), U),      # rows: neither N nor N/128
+    (dict(b_scale=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [300, 2])), SH),   # more rows than N
+    (dict(a_scale=tensor_desc(Z.ctypes.data, abi.RAD_F32, [1, 2])), U),       # fewer rows than M
+    (dict(group=64), SH),
+    (dict(a=tensor_desc(Z.ctypes.data, abi.RAD_F8E4M3, [2, 256], [512, 2])), ST),
+    (dict(y=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [2, 256], [512, 2])), ST),
+    (dict(a=tensor_desc(Z.ctypes.data, abi.RAD_F8E4M3, [1, 256])), SH),       # numel(a) < M*K
+    (dict(b=tensor_desc(None, abi.RAD_F8E4M3, [256, 256])), U),               # absent operand
+])
+def test_fp8_entry_refusals(plug, over, code):
+    pack, _ = _fp8_args(**over)
+    for sym in ("r3d_rad_gemm_nt_q_fp8", "r3d_rad_gemm_nt_q_fp8_decode"):
+        assert plug.entry(sym)(C.byref(pack.args), None) == code, sym
+
+
+def test_fp8_decode_row_band_bound_and_alignment(plug):
+    pack, _ = _fp8_args(M=9)
+    assert plug.entry("r3d_rad_gemm_nt_q_fp8_decode")(C.byref(pack.args), None) == U
+    # M comes from numel(y)/N, never from the M parameter (here 64)
+    pack, _ = _fp8_args(M=2, b=tensor_desc(Z.ctypes.data + 1, abi.RAD_F8E4M3, [256, 256]))
+    assert plug.entry("r3d_rad_gemm_nt_q_fp8_decode")(C.byref(pack.args), None) == U
+
+
+@pytest.mark.parametrize("over,code", [
+    (dict(dtype="fp8a8"), U), (dict(pb2=3), U), (dict(drop=("K",)), SH), (dict(drop=("N",)), SH),
+    (dict(a_sum=tensor_desc(Z.ctypes.data, abi.RAD_F32, [2])), U),
+    (dict(b=tensor_desc(Z.ctypes.data, abi.RAD_F8E4M3, [64, 256])), U),
+    (dict(b_scale=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [64, 8])), U),
+    (dict(b_scale=tensor_desc(Z.ctypes.data, abi.RAD_E8M0, [64, 4])), U),     # grid 64, not 32
+    (dict(b_scale=tensor_desc(Z.ctypes.data, abi.RAD_E8M0, [32, 8])), U),     # fewer rows than N
+    (dict(a_scale=tensor_desc(Z.ctypes.data, abi.RAD_F32, [2, 1])), U),       # grid 256, not 128
+    (dict(b=tensor_desc(Z.ctypes.data, abi.RAD_FP4E2M1, [64, 256], [512, 1])), ST),  # rows not packed
+    (dict(y=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [2, 64], [128, 2])), ST),
+])
+def test_mxfp4_entry_refusals(plug, over, code):
+    pack, _ = _mx_args(**over)
+    for sym in ("r3d_rad_gemm_nt_q", "r3d_rad_gemm_nt_q_mxfp4_decode", "r3d_rad_gemm_nt_q_mxfp4_decode_q8x"):
+        assert plug.entry(sym)(C.byref(pack.args), None) == code, sym
+
+
+def test_mxfp4_b_ref_is_accepted_and_ignored(plug):
+    # refused only later, by the chip gate (no device here) or served on a GPU box -- never for b_ref
+    pack, _ = _mx_args(b_ref=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [64]), K=96,
+                       a=tensor_desc(Z.ctypes.data, abi.RAD_F8E4M3, [2, 96]),
+                       a_scale=tensor_desc(Z.ctypes.data, abi.RAD_F32, [2, 1]),
+                       b=tensor_desc(Z.ctypes.data, abi.RAD_FP4E2M1, [64, 96]),
+                       b_scale=tensor_desc(Z.ctypes.data, abi.RAD_E8M0, [64, 3]))
+    # K = 96 passes the plan of the plain row but fails the decode rows' K % 128 gate
+    assert plug.entry("r3d_rad_gemm_nt_q_mxfp4_decode")(C.byref(pack.args), None) == U
+
+
+def test_mxfp4_decode_rows_band_bound(plug):
+    pack, _ = _mx_args(M=9)
+    for sym in ("r3d_rad_gemm_nt_q_mxfp4_decode", "r3d_rad_gemm_nt_q_mxfp4_decode_q8x"):
+        assert plug.entry(sym)(C.byref(pack.args), None) == U
+
+
+# ------------------------------------------------------------------ LM head: blob + hooks
+def _head(N=256, K=512, br=128, sdt=abi.RAD_BF16):
+    codes = np.arange(N * K, dtype=np.uint32).astype(np.uint8).reshape(N, K)
+    srows, scols = (N + br - 1) // br, (K + 127) // 128
+    scale = (np.arange(srows * scols, dtype=np.uint16) + 0x3C00).reshape(srows, scols)
+    if sdt == abi.RAD_F32:
+        scale = scale.astype(np.float32)
+    return codes, scale
+
+
+def _logits_args(blob, M=2, N=256, K=512, **over):
+    x = np.zeros(M * K, np.uint16)
+    y = np.zeros(M * N, np.float32)
+    t = dict(x=tensor_desc(x.ctypes.data, abi.RAD_BF16, [M, K]),
+             lm_head=tensor_desc(blob.ctypes.data, abi.RAD_U8, [blob.size]),
+             logits=tensor_desc(y.ctypes.data, abi.RAD_F32, [M, N]))
+    p = dict(M=M, n_vocab=N, n_embd=K, dtype="bf16")
+    for k, v in over.items():
+        if k in t:
+            t[k] = v
+        elif v is None:
+            p.pop(k)
+        else:
+            p[k] = v
+    return ArgPack(list(t.values()), p), (x, y)
+
+
+def test_logits_entry_refusals(plug):
+    codes, scale = _head()
+    good = np.frombuffer(planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), codes),
+                                      ("scale", abi.RAD_BF16, (128, 128), scale)]), np.uint8).copy()
+    f = plug.entry("r3d_rad_logits_gemm_e4m3")
+    D = abi.RAD_E_DTYPE
+
+    def rc(blob=good, **over):
+        pack, keep = _logits_args(blob, **over)
+        return f(C.byref(pack.args), None)
+
+    assert rc(dtype="f16") == U and rc(n_vocab=None) == SH and rc(n_vocab=7) == SH
+    assert rc(n_embd=510, x=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [2, 510])) == U    # K % 4
+    assert rc(logits=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [2, 256])) == U            # f32 logits only
+    assert rc(x=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [2, 512], [1024, 2])) == ST
+    assert rc(x=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [2, 512], [256, 1])) == ST      # pitch < K
+    bad = good.copy(); bad[0] ^= 0xFF
+    assert rc(blob=bad) == D                                                              # no magic
+    one = np.frombuffer(planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), codes)]), np.uint8).copy()
+    assert rc(blob=one) == D                                                              # one plane
+    i8 = np.frombuffer(planes_blob([("codes", abi.RAD_I8, (1, 1), codes),
+                                    ("scale", abi.RAD_BF16, (128, 128), scale)]), np.uint8).copy()
+    assert rc(blob=i8) == SH                                                              # int8 head
+    g64 = np.frombuffer(planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), codes),
+                                     ("scale", abi.RAD_BF16, (128, 64), scale)]), np.uint8).copy()
+    assert rc(blob=g64) == U                                                              # 64-col scale grid
+    wrongn = np.frombuffer(planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), codes[:200]),
+                                        ("scale", abi.RAD_BF16, (128, 128), scale)]), np.uint8).copy()
+    assert rc(blob=wrongn) == SH
+
+
+def _enc(roles=("codes", "scale"), dtypes=(abi.RAD_F8E4M3, abi.RAD_BF16), scheme=b"affine",
+         blocks=((1, 1), (128, 128)), transform=b""):
+    e = abi.RadEncoding()
+    e.scheme, e.n_planes, e.transform = scheme, len(roles), transform
+    for i, (r, d, b) in enumerate(zip(roles, dtypes, blocks)):
+        e.plane[i].role, e.plane[i].kind, e.plane[i].dtype = r.encode(), abi.RAD_PLANE_TILED, d
+        e.plane[i].block[0], e.plane[i].block[1] = b
+    return e
+
+
+def test_layout_hooks_roundtrip_and_gates(plug):
+    L = plug.lib
+    codes, scale = _head(N=130, K=300)
+    planes = (abi.RadTensor * 2)(tensor_desc(codes.ctypes.data, abi.RAD_F8E4M3, codes.shape),
+                                 tensor_desc(scale.ctypes.data, abi.RAD_BF16, scale.shape))
+    sel = (C.c_int * 2)(0, 1)
+    lay = abi.RadLayout()
+    enc = _enc()
+    args = (None, 0, 1, C.byref(enc), sel, planes, 2)
+    assert L.r3d_layout_head(*args, C.byref(lay)) == abi.RAD_OK and lay.bytes > codes.nbytes
+    dst = np.zeros(lay.bytes, np.uint8)
+    assert L.r3d_relayout_head(*args, C.c_void_p(dst.ctypes.data), C.c_int64(dst.size)) == abi.RAD_OK
+    want = np.frombuffer(planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), codes),
+                                      ("scale", abi.RAD_BF16, (128, 128), scale)]), np.uint8)
+    assert np.array_equal(dst, want)                     # the hook writes the documented blob
+    c2, s2 = np.zeros_like(codes), np.zeros_like(scale)
+    back = (abi.RadTensor * 2)(tensor_desc(c2.ctypes.data, abi.RAD_F8E4M3, c2.shape),
+                               tensor_desc(s2.ctypes.data, abi.RAD_BF16, s2.shape))
+    assert L.r3d_unrelayout_head(None, 0, 1, C.byref(enc), sel, C.c_void_p(dst.ctypes.data),
+                                 C.c_int64(dst.size), back, 2) == abi.RAD_OK
+    assert np.array_equal(c2, codes) and np.array_equal(s2, scale)
+    # gates (src/r3d_gemm_logits.hip:233-254 of the reference)
+    D = abi.RAD_E_DTYPE
+    assert L.r3d_layout_head(None, 0, 0, C.byref(enc), sel, planes, 2, C.byref(lay)) == U   # operand
+    assert L.r3d_layout_head(None, 0, 1, C.byref(enc), sel, planes, 1, C.byref(lay)) == U
+    for bad in (_enc(dtypes=(abi.RAD_I8, abi.RAD_BF16)), _enc(scheme=b"lattice"),
+                _enc(roles=("scale", "codes")), _enc(transform=b"givens"),
+                _enc(dtypes=(abi.RAD_F8E4M3, abi.RAD_U8)), _enc(blocks=((1, 2), (128, 128)))):
+        assert L.r3d_layout_head(None, 0, 1, C.byref(bad), sel, planes, 2, C.byref(lay)) == D
+
+
+def test_no_product_code_touches_the_oracle():
+    """The CPU checker is test infrastructure: nothing the package ships may import, load,
+    link or run it."""
+    pat = re.compile(r"liboracle|import\s+oracle|from\s+oracle|oracle[/.]")
+    for f in list((ROOT / "libr3d_b200").rglob("*")):
+        if f.is_file() and f.suffix in (".py", ".cu", ".cpp", ".h", ".cuh"):
+            assert not pat.search(f.read_text()), f
