@@ -1,0 +1,310 @@
+#!/usr/bin/env python
+"""bench.py -- decode GEMV throughput of the mxfp4a8 band on B200.
+
+Workload (N = 1 GPU): the 27B-class gate+up projection of the benchmark configuration
+"mxfp4 decode GEMV band": K = 5120, N = 27648, M in {1, 2, 4}; e2m1 codes uniform over the 16
+codes, one E8M0 scale per 32 of K uniform in [119, 123], activations bf16 N(0,1) quantised by
+quant_act_fp8 (e4m3 + f32 scale per 128 of K). One step = the three calls (M = 1, 2, 4), each
+over the next of `rot` distinct weight planes so that the stream never comes from L2.
+
+  value      algorithmic GB/s of the whole job, inputs resident in HBM, device-timed
+             (a recorded pass = CUDA graph of `rot` steps, replayed; CUDA events)
+  e2e        the same metric through the declared-op API with HOST activations: per step the
+             pinned-host -> device copy of the activations, three issues, device -> host read
+             of the outputs
+  roofline   the streaming kernel's algorithmic bytes per launch / its mean launch time
+  cpu_baseline  the CPU restatement (oracle/) of the same step on the host cores, bounded sample
+
+N > 1: every rank holds its own 27648-row slab (weak scaling: the sharded layer is G x wider),
+runs the same step and all-gathers each bf16 output over NCCL; time = max over ranks.
+
+--impl reference: the reference's arithmetic for this path on the host cores (the CPU
+restatement: the reference's kernels are HIP and cannot build here), same metric and config.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+K_DIM, N_DIM, MS = 5120, 27648, (1, 2, 4)
+METRIC = "decode GEMV GB/s (mxfp4a8 band, M in {1,2,4}, K=5120, N=27648)"
+
+
+def algo_bytes(M: int, n_rows: int = N_DIM) -> int:
+    """codes + E8M0 scales + activation codes and scales + bf16 output"""
+    return n_rows * K_DIM // 2 + n_rows * K_DIM // 32 + M * (K_DIM + K_DIM // 128 * 4) + M * n_rows * 2
+
+
+STEP_BYTES = sum(algo_bytes(m) for m in MS)
+
+
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        self.rows = []
+        if self.proc:
+            self.proc.terminate()
+            try:
+                out, _ = self.proc.communicate(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+                out = ""
+            self.rows = [l.split(", ") for l in out.strip().splitlines() if l.count(",") >= 8]
+
+    def summary(self) -> dict:
+        if not getattr(self, "rows", None):
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = [float(r[1]) for r in self.rows if r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows for n, v in zip(names, r[5:9]) if v.strip().lower() == "active"})
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": float(self.rows[0][2]) if self.rows else None,
+                "power_w_max": max(float(r[3]) for r in self.rows), "samples": len(self.rows),
+                "reasons": reasons}
+
+
+def cpu_step_sample(rows: int, reps: int):
+    """The CPU restatement over `rows` weight rows of one plane for M = 1, 2, 4."""
+    import gen
+    from oracle import oracle as orc
+    cases = [gen.case_mxfp4(100 + m, m, rows, K_DIM) for m in MS]
+    orc.gemm_mxfp4a8(**cases[0])
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        for c in cases:
+            orc.gemm_mxfp4a8(**c)
+    dt = (time.perf_counter() - t0) / reps
+    nbytes = sum(algo_bytes(m, rows) for m in MS)
+    return nbytes / dt / 1e9, dt, orc.lib().orc_num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = 1728            # 1/16 of the plane per step: the whole run stays within minutes
+    import gen
+    from oracle import oracle as orc
+    cases = [gen.case_mxfp4(100 + m, m, rows, K_DIM) for m in MS]
+    for _ in range(max(args.warmup, 1)):
+        for c in cases:
+            orc.gemm_mxfp4a8(**c)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for c in cases:
+            orc.gemm_mxfp4a8(**c)
+    dt = time.perf_counter() - t0
+    nbytes = sum(algo_bytes(m, rows) for m in MS)
+    val = nbytes * args.steps / dt / 1e9
+    threads = orc.lib().orc_num_threads()
+    sample = f"{rows} of {N_DIM} weight rows per step, M=1,2,4, full K"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "C2 mxfp4a8 decode GEMV, M in {1,2,4}, K=5120, N=27648", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--rot", type=int, default=4, help="distinct weight planes cycled (footprint > L2)")
+    ap.add_argument("--row", default="gemm_nt_q_mxfp4_decode")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from libr3d_b200 import ops, shard
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    P = ops.plugin()
+    rot = max(args.rot, 1)
+
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    planes = [(torch.randint(0, 256, (N_DIM, K_DIM // 2), dtype=torch.uint8, device=dev, generator=g),
+               torch.randint(119, 124, (N_DIM, K_DIM // 32), dtype=torch.uint8, device=dev, generator=g))
+              for _ in range(rot)]
+    acts, outs, ops_ = {}, {}, {}
+    for m in MS:
+        x = torch.randn((m, K_DIM), device=dev, generator=g).to(torch.bfloat16)
+        acts[m] = ops.quant_act_fp8(x, 128)
+        outs[m] = torch.zeros((m, N_DIM), dtype=torch.bfloat16, device=dev)
+        for p in range(rot):
+            ops_[m, p] = ops.BoundGemm(acts[m][0], acts[m][1], planes[p][0], planes[p][1], outs[m],
+                                       dtype="mxfp4a8", N=N_DIM, K=K_DIM, row=args.row)
+    gathered = {m: torch.empty((world, m, N_DIM), dtype=torch.bfloat16, device=dev) for m in MS} if world > 1 else None
+
+    def step(i: int):
+        for m in MS:
+            ops_[m, i % rot].issue()
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[m], outs[m])
+
+    def fence():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    fence()
+    assert int(torch.count_nonzero(outs[4].view(torch.int16))) > 0.9 * outs[4].numel()
+
+    # ---- device-timed region: exactly `steps` steps
+    graph = None
+    if world == 1:
+        # a recorded pass: `rot` steps captured once, replayed (what the engine's pass replay does)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=s):
+                for i in range(rot):
+                    step(i)
+        torch.cuda.current_stream().wait_stream(s)
+        replays, rem = divmod(args.steps, rot)
+        for _ in range(3):
+            graph.replay()
+    fence()
+    l0 = P.lib.r3d_b200_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        time.sleep(0.25)
+        fence()
+        e0.record()
+        if graph is not None:
+            for _ in range(replays):
+                graph.replay()
+            for i in range(rem):
+                step(i)
+        else:
+            for i in range(args.steps):
+                step(i)
+        e1.record()
+        fence()
+        time.sleep(0.25)
+    ms = e0.elapsed_time(e1)
+    launches = (P.lib.r3d_b200_launch_count() - l0) if graph is None else 3 * args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = STEP_BYTES * args.steps * world / (ms * 1e-3) / 1e9
+
+    # ---- end to end: host activations in, host outputs back, through the declared ops
+    h_in = {m: (acts[m][0].cpu().pin_memory(), acts[m][1].cpu().pin_memory()) for m in MS}
+    h_out = {m: torch.empty((m, N_DIM), dtype=torch.bfloat16).pin_memory() for m in MS}
+    h2d = sum(a.numel() + s_.numel() * 4 for a, s_ in h_in.values())
+    d2h = sum(o.numel() * 2 for o in h_out.values())
+
+    def step_e2e(i: int):
+        for m in MS:
+            acts[m][0].copy_(h_in[m][0], non_blocking=True)
+            acts[m][1].copy_(h_in[m][1], non_blocking=True)
+            ops_[m, i % rot].issue()
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[m], outs[m])
+            h_out[m].copy_(outs[m], non_blocking=True)
+        torch.cuda.current_stream().synchronize()          # the caller reads the step's result
+
+    e2e_steps = min(args.steps, 200)
+    for i in range(3):
+        step_e2e(i)
+    fence()
+    e0.record()
+    for i in range(e2e_steps):
+        step_e2e(i)
+    e1.record()
+    fence()
+    ms_e = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e = float(t.item())
+    e2e = STEP_BYTES * e2e_steps * world / (ms_e * 1e-3) / 1e9
+
+    if rank == 0:
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+        peak, which = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+        per_launch_s = ms * 1e-3 / (3 * args.steps)
+        achieved = (STEP_BYTES / 3) / per_launch_s / 1e9
+        traffic = None
+        tf = ROOT / "profiles" / "traffic.json"
+        if tf.exists():
+            traffic = json.loads(tf.read_text()).get("k_stream_mxfp4_c2_bytes_per_launch")
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "e2m1 x e4m3 -> f32", "data": "synthetic",
+            "config": {"workload": "C2 mxfp4a8 decode GEMV, M in {1,2,4}, K=5120, N=27648 per GPU",
+                       "row": args.row, "rot_planes": rot,
+                       "l2": f"inputs larger than L2: {rot} rotating weight planes, "
+                             f"{rot * (N_DIM * K_DIM // 2 + N_DIM * K_DIM // 32) / 1e6:.0f} MB",
+                       "timed_as": "CUDA graph replay of recorded steps" if graph is not None else "direct issue",
+                       "parallelism": "1 GPU" if world == 1 else f"column slabs x{world} + NCCL all_gather per call"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_source": which, "traffic": traffic,
+                         "kernel": "k_stream<mxfp4>", "bytes_per_launch": STEP_BYTES / 3,
+                         "us_per_launch": per_launch_s * 1e6},
+            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "clocks": clk.summary(),
+        }
+        if world == 1 and not args.no_cpu:
+            v, dt, threads = cpu_step_sample(N_DIM, 3)
+            line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
+                                    "sample": f"3 full steps (M=1,2,4 over one 27648x5120 plane), {dt:.2f} s each"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -126,6 +126,11 @@ int r3d_b200_quant_act_fp8(const void* x, int32_t x_dtype, int64_t x_pitch, void
 int r3d_b200_pick_arm_fp8a8(const R3dGemmQ* q);
 int r3d_b200_pick_arm_mxfp4a8(const R3dGemmQ* q);
 
+/* 0 when no bounded device-side wait of the streaming arm has ever expired in this process;
+ * otherwise the code of the wait that gave up (1 producer, 2 consumer). The affected launch
+ * stored nothing. No counterpart in the reference (its kernels have no device-side waits). */
+int r3d_b200_stream_status(void);
+
 /* Kernels this library launched since load (all arms): bench bookkeeping. */
 long long r3d_b200_launch_count(void);
 

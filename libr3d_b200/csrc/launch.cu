@@ -57,12 +57,14 @@ extern "C" long long r3d_b200_launch_count(void) { return g_launches.load(); }
 extern "C" int r3d_b200_pick_arm_fp8a8(const R3dGemmQ* q) {
     if (!q) return -1;
     if (q->arm != R3D_ARM_AUTO) return q->arm;
-    return stream_fp8a8_ok(*q) || (q->m > 64) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+    R3dGemmQ probe = *q; if (probe.m > 64) probe.m = 64;
+    return stream_fp8a8_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
 }
 extern "C" int r3d_b200_pick_arm_mxfp4a8(const R3dGemmQ* q) {
     if (!q) return -1;
     if (q->arm != R3D_ARM_AUTO) return q->arm;
-    return stream_mxfp4a8_ok(*q) || (q->m > 64) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+    R3dGemmQ probe = *q; if (probe.m > 64) probe.m = 64;
+    return stream_mxfp4a8_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
 }
 
 /* M above the streaming arm's 64 rides it in passes of 64 tokens, each pass re-reading the

@@ -110,3 +110,41 @@ def quant_act_fp8(x: torch.Tensor, group: int = 128) -> tuple[torch.Tensor, torc
     if rc != abi.RAD_OK:
         raise RowRefused("quant_act_fp8", rc)
     return q, s
+
+
+class BoundGemm:
+    """A gemm_nt_q band declared once and issued many times, the way the engine uses a row:
+    the row is resolved and the RadArgs built at declare time over fixed device buffers; each
+    `issue()` is one call of the row's launch pointer on the current stream. Buffers must
+    outlive the object."""
+
+    def __init__(self, a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor,
+                 b_scale: torch.Tensor, y: torch.Tensor, *, dtype: str, N: int, K: int,
+                 row: str | None = None):
+        P = plugin()
+        M = y.numel() // N
+        group = 128 if dtype == "fp8a8" else 32
+        query: dict[str, Any] = dict(M=M, N=N, K=K, group=group, dtype=dtype)
+        self.row = (P.resolve("gemm_nt_q", query) if row is None
+                    else next(x for x in P.rows() if x.name == row))
+        if self.row is None:
+            raise RuntimeError(f"no row serves gemm_nt_q {query}")
+        if dtype == "fp8a8":
+            bdesc = _desc(b, abi.RAD_F8E4M3)
+            sdt = abi.RAD_F32 if b_scale.dtype == torch.float32 else abi.RAD_BF16
+        else:
+            bdesc = _desc(b, abi.RAD_FP4E2M1, shape=[b.shape[0], K], stride=[K, 1])
+            sdt = abi.RAD_E8M0
+        self._keep = (a, a_scale, b, b_scale, y)
+        self.pack = ArgPack([_desc(a, abi.RAD_F8E4M3), _desc(a_scale, abi.RAD_F32), bdesc,
+                             _desc(b_scale, sdt), _desc(y, abi.RAD_BF16),
+                             _desc(None, abi.RAD_F32), _desc(None, abi.RAD_BF16)], query)
+        self._fn = P._launch_t(self.row.launch)
+        import ctypes as _C
+        self._argp = _C.byref(self.pack.args)
+        self._C = _C
+
+    def issue(self) -> None:
+        rc = self._fn(self._argp, self._C.c_void_p(_stream()))
+        if rc != abi.RAD_OK:
+            raise RowRefused(self.row.name, rc)

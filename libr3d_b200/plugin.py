@@ -27,7 +27,7 @@ EXPORTS = [
     "r3d_unrelayout_head",
     "r3d_b200_gemm_fp8a8", "r3d_b200_gemm_mxfp4a8", "r3d_b200_gemm_mxfp4a8_q8x",
     "r3d_b200_logits", "r3d_b200_quant_act_fp8", "r3d_b200_pick_arm_fp8a8",
-    "r3d_b200_pick_arm_mxfp4a8", "r3d_b200_launch_count",
+    "r3d_b200_pick_arm_mxfp4a8", "r3d_b200_launch_count", "r3d_b200_stream_status",
 ]
 
 

@@ -1,0 +1,259 @@
+"""GPU parity of gemm_nt_q at fp8a8 and mxfp4a8: every arm against the CPU oracle on the same
+seeded operands, through the C ABI (launch layer with a forced arm, and the row entries with
+RadArgs). Integer/bit class where the arithmetic order is the oracle's; <= 2 bf16 ulp against
+the fp32-accumulated oracle value for the tensor-core arm."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import gen
+import gpu_util as gu
+from libr3d_b200 import abi, ops
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+EX, STREAM = abi.R3D_ARM_EXACT, abi.R3D_ARM_STREAM
+ODD_M = [1, 2, 3, 5, 7, 8, 9, 16, 17]
+
+
+# ------------------------------------------------------------------ bit-exact dequantisation
+def test_fp8_dequant_all_codes_bit_exact():
+    """y = w * 1: one-hot activation of code 1.0 picks each of the 256 weight codes."""
+    K, N = 256, 256
+    A = np.zeros((1, K), np.uint8); A[0, 3] = 0x38
+    B = np.zeros((N, K), np.uint8); B[:, 3] = np.arange(256)
+    case = dict(A=A, AS=np.ones((1, 2), np.float32), B=B, BS=np.full((N, 2), 0x3F80, np.uint16), rblk=1)
+    want = orc.gemm_fp8a8(**case)
+    lut = gen.e4m3_decode_table()
+    ok = ~np.isnan(lut)
+    assert np.array_equal(want[0, ok], orc.f32_to_bf16_bits(lut[ok]))
+    for arm in (EX, STREAM):
+        got = gu.gemm_launch("fp8a8", case, arm)
+        assert gu.same_bits_or_both_nan(got, want).all(), arm
+
+
+@pytest.mark.parametrize("arm", [EX, STREAM])
+def test_mxfp4_dequant_all_codes_all_scales_bit_exact(arm):
+    """every e2m1 code under every E8M0 byte: y[n] = e2m1(c) * 2^(x-127), selected one-hot."""
+    K = 512
+    codes = np.arange(16, dtype=np.uint8)
+    N = 16 * 256
+    B = np.zeros((N, K // 2), np.uint8)
+    BS = np.full((N, K // 32), 127, np.uint8)
+    n = np.arange(N)
+    B[n, 5] = (n % 16).astype(np.uint8) << 4          # k = 11 (odd nibble) holds the code
+    BS[n, 0] = (n // 16).astype(np.uint8)             # its group's scale byte
+    A = np.zeros((1, K), np.uint8); A[0, 11] = 0x38
+    case = dict(A=A, AS=np.ones((1, K // 128), np.float32), B=B, BS=BS)
+    want = orc.gemm_mxfp4a8(**case)
+    got = gu.gemm_launch("mxfp4a8", case, arm)
+    assert gu.same_bits_or_both_nan(got, want).all()
+    assert np.count_nonzero(got & 0x7FFF) > N // 2
+
+
+# ------------------------------------------------------------------ fp8a8
+def test_fp8_unit_fixture_analytic():
+    for arm in (EX, STREAM):
+        for (M, K, N) in [(14, 512, 130), (4, 2048, 64)]:
+            case, expect = gen.fixture_fp8_unit(M, K, N)
+            got = gu.gemm_launch("fp8a8", case, arm)
+            assert np.array_equal(got, orc.f32_to_bf16_bits(expect.astype(np.float32)))
+
+
+@pytest.mark.parametrize("grid", ["ref128", "row", "channel"])
+@pytest.mark.parametrize("M", ODD_M)
+def test_fp8_exact_arm_is_bit_identical_to_oracle(grid, M):
+    N, K = (200, 384) if M % 2 else (131, 640)
+    case = gen.case_fp8(1000 + M, M, N, K, grid)
+    want = orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], case["rblk"])
+    got = gu.gemm_launch("fp8a8", case, EX)
+    assert np.array_equal(got, want)
+    assert np.count_nonzero(got & 0x7FFF) > got.size * 0.9
+
+
+@pytest.mark.parametrize("grid", ["ref128", "row", "channel"])
+@pytest.mark.parametrize("M", ODD_M + [33, 64])
+def test_fp8_stream_arm_within_2ulp(grid, M):
+    N, K = (200, 384) if M % 2 else (136, 1280)
+    case = gen.case_fp8(2000 + M, M, N, K, grid)
+    _, acc = orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], case["rblk"], want_acc=True)
+    _, ab = orc.truth_fp8a8(case["A"], case["AS"], case["B"], case["BS"], case["rblk"])
+    g = gu.grade_bf16(gu.gemm_launch("fp8a8", case, STREAM), acc, ab)
+    assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 5e-3, g
+    assert g["nonzero"] > acc.size * 0.9
+
+
+def test_fp8_config_c1_full_size():
+    """M=1 K=4096 N=4096, per-channel / per-token fp32 scales, seed 0."""
+    case = gen.case_fp8(0, 1, 4096, 4096, "channel")
+    want, acc = orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], 1, want_acc=True)
+    assert np.array_equal(gu.gemm_launch("fp8a8", case, EX), want)
+    g = gu.grade_bf16(gu.gemm_launch("fp8a8", case, STREAM), acc)
+    assert g["max_ulp"] <= 2, g
+
+
+# ------------------------------------------------------------------ mxfp4a8
+@pytest.mark.parametrize("M", ODD_M)
+def test_mxfp4_exact_arm_is_bit_identical_to_oracle(M):
+    N, K = (96, 1024) if M % 2 else (77, 384)
+    case = gen.case_mxfp4(3000 + M, M, N, K)
+    assert np.array_equal(gu.gemm_launch("mxfp4a8", case, EX), orc.gemm_mxfp4a8(**case))
+
+
+def test_mxfp4_exact_arm_on_probe_fixture():
+    case = gen.fixture_probe_m4(3, 512, 40)      # tools/probe_m4_entry.cpp's own srand(777) operands
+    assert np.array_equal(gu.gemm_launch("mxfp4a8", case, EX), orc.gemm_mxfp4a8(**case))
+
+
+@pytest.mark.parametrize("M", ODD_M + [33, 64])
+def test_mxfp4_stream_arm_within_2ulp(M):
+    N, K = (200, 512) if M % 2 else (136, 1536)
+    case = gen.case_mxfp4(4000 + M, M, N, K)
+    _, acc = orc.gemm_mxfp4a8(**case, want_acc=True)
+    _, ab = orc.truth_mxfp4a8(**case)
+    g = gu.grade_bf16(gu.gemm_launch("mxfp4a8", case, STREAM), acc, ab)
+    assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 3e-2, g
+
+
+@pytest.mark.parametrize("arm", [EX, STREAM])
+def test_mxfp4_torture_scale_bytes_and_codes(arm):
+    g = np.load(GOLD / "mxfp4a8_torture.npz")
+    case = dict(A=g["A"], AS=g["AS"], B=g["B"], BS=g["BS"])
+    got = gu.gemm_launch("mxfp4a8", case, arm)
+    want = g["Y"]
+    nan_w = (want & 0x7FFF) > 0x7F80
+    assert nan_w.any() and not nan_w.all()
+    assert (((got & 0x7FFF) > 0x7F80) == nan_w).all()          # 0xFF scale bytes poison, nothing else
+    if arm == EX:
+        assert gu.same_bits_or_both_nan(got, want).all()
+    else:
+        d = orc.bf16_ulp_distance(got[~nan_w], want[~nan_w])
+        assert (d <= 2).mean() > 0.99
+
+
+def test_golden_vectors_on_device():
+    for f in sorted(GOLD.glob("*.npz")):
+        g = np.load(f)
+        kind = str(g["kind"])
+        if kind == "fp8a8":
+            case = dict(A=g["A"], AS=g["AS"], B=g["B"], BS=g["BS"], rblk=int(g["rblk"]))
+            assert np.array_equal(gu.gemm_launch("fp8a8", case, EX), g["Y"]), f.name
+        elif kind == "mxfp4a8":
+            case = dict(A=g["A"], AS=g["AS"], B=g["B"], BS=g["BS"])
+            assert gu.same_bits_or_both_nan(gu.gemm_launch("mxfp4a8", case, EX), g["Y"]).all(), f.name
+        elif kind == "mxfp4a8_q8x":
+            case = dict(A=g["A"], AS=g["AS"], B=g["B"], BS=g["BS"])
+            y, _, _ = gu.q8x_launch(case, int(g["walk"]))
+            assert np.array_equal(y, g["Y"]), f.name
+
+
+# ------------------------------------------------------------------ q8x arm
+@pytest.mark.parametrize("walk", [0, 1])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 7, 8])
+def test_q8x_arm_bit_identical_to_its_chain(walk, M):
+    K = 1280 if M % 2 else 768          # K % 1024 != 0 exercises the lane-map peel / short sweep
+    case = gen.case_mxfp4(5000 + M, M, 203, K)
+    y, x8, sg = gu.q8x_launch(case, walk)
+    x8_ref, sg_ref = orc.q8x_requant(case["A"])
+    assert np.array_equal(x8, x8_ref) and np.array_equal(sg.view(np.uint32), sg_ref.view(np.uint32))
+    assert np.array_equal(y, orc.gemm_mxfp4_q8x(case["A"], case["AS"], case["B"], case["BS"], walk))
+
+
+def test_q8x_arm_torture_bytes():
+    g = np.load(GOLD / "mxfp4a8_torture.npz")
+    case = dict(A=g["A"], AS=g["AS"], B=g["B"], BS=g["BS"])
+    case["A"][:, :32] = np.array([0x7E, 0xFE] * 16, np.uint8)      # +-448: int8 +-127 everywhere
+    for walk in (0, 1):
+        y, _, _ = gu.q8x_launch(case, walk)
+        want = orc.gemm_mxfp4_q8x(case["A"], case["AS"], case["B"], case["BS"], walk)
+        assert gu.same_bits_or_both_nan(y, want).all()
+
+
+# ------------------------------------------------------------------ through the row entries
+def _run_row(dtype, case, row=None, M_param=None):
+    A, AS, B, BS = map(gu.dev, (case["A"], case["AS"], case["B"], case["BS"]))
+    if dtype == "fp8a8" and case["BS"].dtype == np.uint16:
+        BS = BS.view(torch.bfloat16)
+    M, K = case["A"].shape
+    N = case["B"].shape[0]
+    out = gu.GuardedOut((M, N), np.uint16)
+    r = ops.gemm_nt_q(A, AS, B, BS, out.view(), dtype=dtype, N=N, K=K, row=row, M_param=M_param)
+    return r.name, out.get()
+
+
+def test_rows_resolve_and_serve_fp8():
+    case = gen.case_fp8(6000, 3, 256, 512, "ref128")
+    want, acc = orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], 128, want_acc=True)
+    name, got = _run_row("fp8a8", case)
+    assert name == "gemm_nt_q_fp8a8_decode"
+    assert gu.grade_bf16(got, acc)["max_ulp"] <= 2
+    # M is numel(y)/N: an arena-capacity M parameter must not change a byte
+    name2, got2 = _run_row("fp8a8", case, row="gemm_nt_q_fp8a8", M_param=64)
+    assert name2 == "gemm_nt_q_fp8a8" and np.array_equal(got, got2)
+    case16 = gen.case_fp8(6001, 16, 256, 512, "ref128")
+    name3, got3 = _run_row("fp8a8", case16)
+    _, acc3 = orc.gemm_fp8a8(case16["A"], case16["AS"], case16["B"], case16["BS"], 128, want_acc=True)
+    assert name3 == "gemm_nt_q_fp8a8" and gu.grade_bf16(got3, acc3)["max_ulp"] <= 2
+
+
+def test_rows_resolve_and_serve_mxfp4():
+    case = gen.case_mxfp4(6100, 4, 128, 1024)
+    name, got = _run_row("mxfp4a8", case)
+    assert name == "gemm_nt_q_mxfp4_decode_q8x"
+    assert np.array_equal(got, orc.gemm_mxfp4_q8x(case["A"], case["AS"], case["B"], case["BS"], 1))
+    case1 = gen.case_mxfp4(6101, 1, 128, 1024)
+    _, got1 = _run_row("mxfp4a8", case1)                      # M <= 2 rides the tree walk
+    assert np.array_equal(got1, orc.gemm_mxfp4_q8x(case1["A"], case1["AS"], case1["B"], case1["BS"], 0))
+    _, acc = orc.gemm_mxfp4a8(**case, want_acc=True)
+    name2, got2 = _run_row("mxfp4a8", case, row="gemm_nt_q_mxfp4_decode")
+    assert name2 == "gemm_nt_q_mxfp4_decode" and gu.grade_bf16(got2, acc)["max_ulp"] <= 2
+    # K % 256 == 128: the q8x row serves the fp32 walk in place, never a refusal
+    case3 = gen.case_mxfp4(6102, 2, 64, 384)
+    _, acc3 = orc.gemm_mxfp4a8(**case3, want_acc=True)
+    name3, got3 = _run_row("mxfp4a8", case3, row="gemm_nt_q_mxfp4_decode_q8x")
+    assert gu.grade_bf16(got3, acc3)["max_ulp"] <= 2
+    case4 = gen.case_mxfp4(6103, 17, 128, 512)
+    name4, got4 = _run_row("mxfp4a8", case4)
+    _, acc4 = orc.gemm_mxfp4a8(**case4, want_acc=True)
+    assert name4 == "gemm_nt_q_mxfp4" and gu.grade_bf16(got4, acc4)["max_ulp"] <= 2
+
+
+# ------------------------------------------------------------------ benchmark sizes
+def _stream_vs_exact_full(kind, case, tol_frac=0.9995):
+    """Full-size property: the tensor-core arm agrees with the oracle-order arm (itself
+    bit-identical to the CPU oracle at small sizes) to 2 bf16 ulp, plus a CPU-oracle check of
+    a row sample."""
+    ex = gu.gemm_launch(kind, case, EX)
+    st = gu.gemm_launch(kind, case, STREAM)
+    d = orc.bf16_ulp_distance(st, ex)
+    assert (d <= 2).mean() >= tol_frac, ((d <= 2).mean(), int(d.max()))
+    assert np.count_nonzero(st & 0x7FFF) > st.size * 0.9
+    rows = np.random.default_rng(1).choice(case["B"].shape[0], 256, replace=False)
+    sub = dict(case); sub["B"] = case["B"][rows]
+    if kind == "fp8a8":
+        sub["BS"] = case["BS"][rows] if case["rblk"] == 1 else case["BS"][rows // 128]
+        sub["rblk"] = 1
+        want = orc.gemm_fp8a8(sub["A"], sub["AS"], sub["B"], sub["BS"], 1)
+    else:
+        sub["BS"] = case["BS"][rows]
+        want = orc.gemm_mxfp4a8(**sub)
+    assert np.array_equal(ex[:, rows], want)
+
+
+@pytest.mark.parametrize("M", [1, 2, 4])
+def test_config_c2_mxfp4_decode_full_size(M):
+    _stream_vs_exact_full("mxfp4a8", gen.case_mxfp4(20 + M, M, 27648, 5120))
+
+
+@pytest.mark.parametrize("kind,N,K", [("fp8a8", 6144, 5120), ("mxfp4a8", 5120, 13824),
+                                      ("fp8a8", 5120, 13824), ("mxfp4a8", 6144, 5120)])
+def test_config_c3_m16_projections_full_size(kind, N, K):
+    case = gen.case_fp8(30, 16, N, K, "ref128") if kind == "fp8a8" else gen.case_mxfp4(31, 16, N, K)
+    _stream_vs_exact_full(kind, case)
+
+
+def test_stream_arm_status_word_clean():
+    assert ops.plugin().lib.r3d_b200_stream_status() == 0

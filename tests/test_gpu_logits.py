@@ -1,0 +1,84 @@
+"""GPU parity of logits_gemm over the joined e4m3 + block-scale head."""
+import numpy as np
+import pytest
+import torch
+
+import gen
+import gpu_util as gu
+from libr3d_b200 import abi, ops
+from libr3d_b200.plugin import planes_blob
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+EX, STREAM = abi.R3D_ARM_EXACT, abi.R3D_ARM_STREAM
+
+CASES = [(256, 512, 1, 128, 0), (256, 512, 3, 128, 0), (130, 300, 5, 128, 0), (256, 512, 9, 128, 0),
+         (200, 512, 2, 1, 0), (256, 384, 4, 128, 1), (256, 512, 8, 128, 2), (8, 4, 1, 128, 0)]
+
+
+def _rel(y, want):
+    return np.abs(y.astype(np.float64) - want).max() / max(np.abs(want).max(), 1e-6)
+
+
+@pytest.mark.parametrize("N,K,M,br,sdt", CASES)
+def test_reference_unit_geometries_exact_arm_bitwise(N, K, M, br, sdt):
+    # the eight cases of tools/test_logits_e4m3.cpp:155-164
+    c = gen.case_logits(N + K + M, M, N, K, br, sdt)
+    want = orc.logits_e4m3(c["X"], c["codes"], c["scale"], sdt, br)
+    got = gu.logits_launch(c, EX)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("N,K,M,br,sdt", [c for c in CASES if c[1] % 64 == 0] +
+                         [(1000, 1024, 16, 128, 0), (333, 640, 33, 1, 2), (512, 5120, 4, 128, 0)])
+def test_stream_arm_within_reference_tolerance(N, K, M, br, sdt):
+    # graded like the reference's own unit test: 1e-4 relative (its kernel also re-associates)
+    c = gen.case_logits(7 * N + K + M, M, N, K, br, sdt)
+    want = orc.logits_e4m3(c["X"], c["codes"], c["scale"], sdt, br)
+    got = gu.logits_launch(c, STREAM)
+    assert _rel(got, want.astype(np.float64)) < 1e-4
+    assert np.count_nonzero(got) > got.size * 0.9
+
+
+def test_stream_arm_dequant_exact_incl_subnormal_and_nan_codes():
+    """one-hot x = 1.0 picks each code times a power-of-two scale: results must be exact."""
+    K, N = 128, 256
+    codes = np.zeros((N, K), np.uint8); codes[:, 7] = np.arange(256)
+    X = np.zeros((1, K), np.uint16); X[0, 7] = 0x3F80
+    c = dict(X=X, codes=codes, scale=np.full((2, 1), 0x3E80, np.uint16), sdt=0, br=128)   # 0.25
+    want = orc.logits_e4m3(X, codes, c["scale"], 0, 128)
+    for arm in (EX, STREAM):
+        got = gu.logits_launch(c, arm)
+        nan = np.isnan(want)
+        assert nan.sum() == 2 and np.array_equal(np.isnan(got), nan)
+        assert np.array_equal(got[~nan], want[~nan]), arm
+
+
+def test_row_entry_with_joined_blob():
+    N, K, M = 1024, 1024, 5
+    c = gen.case_logits(99, M, N, K, 128, 0)
+    blob = np.frombuffer(planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), c["codes"]),
+                                      ("scale", abi.RAD_BF16, (128, 128), c["scale"])]), np.uint8)
+    out = gu.GuardedOut((M, N), np.float32)
+    x = gu.dev(c["X"]).view(torch.bfloat16)
+    r = ops.logits_gemm(x, gu.dev(blob), out.view(), n_vocab=N, n_embd=K)
+    assert r.name == "logits_gemm_e4m3"
+    want = orc.logits_e4m3(c["X"], c["codes"], c["scale"], 0, 128)
+    assert _rel(out.get(), want.astype(np.float64)) < 1e-4
+
+
+def test_vocab_size_head_sampled_rows():
+    """N = 151936, K = 5120 (the LM head of the benchmark): stream arm vs the oracle on a
+    sample of rows, and vs the exact arm on a slab."""
+    N, K, M = 151936, 5120, 4
+    rng = np.random.default_rng(5)
+    codes = rng.integers(0, 256, (N, K), dtype=np.uint8)
+    codes[(codes & 0x7F) == 0x7F] &= 0x7E
+    scale = gen.f32_to_bf16_bits(np.exp(rng.uniform(-6, -4, ((N + 127) // 128, K // 128))).astype(np.float32))
+    X = gen.f32_to_bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    c = dict(X=X, codes=codes, scale=scale, sdt=0, br=128)
+    got = gu.logits_launch(c, STREAM)
+    rows = np.concatenate([np.arange(0, 256), rng.choice(N, 256, replace=False), np.arange(N - 64, N)])
+    want = orc.logits_e4m3(X, codes[rows], np.repeat(scale, 128, axis=0)[rows], 0, 1)
+    assert _rel(got[:, rows], want.astype(np.float64)) < 1e-4
+    assert np.count_nonzero(got) > got.size * 0.99
