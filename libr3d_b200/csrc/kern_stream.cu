@@ -37,6 +37,7 @@
 #include "r3d_kernels.h"
 #include "r3d_numerics.cuh"
 #include <cstdio>
+#include <cstdlib>
 
 namespace r3d {
 
@@ -441,11 +442,14 @@ int launch_one(const StreamParams& P, cudaStream_t st) {
     return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
 }
 
-/* Rows per CTA: whole 64-row tiles when there are enough of them to fill the machine,
- * otherwise split K across the warps of a CTA so more CTAs exist. */
+/* Rows per CTA: 32-row tiles (K split in two across warps) when there are enough of them to
+ * fill the machine twice over, otherwise 16-row tiles (K split in four). */
 int pick_ks(int n) {
-    const int t64 = (n + 63) / 64;
-    if (t64 >= 296) return 1;
+    /* bench lever: R3D_STREAM_KS=1|2|4 forces the split (every value serves every call) */
+    static const int forced = [] { const char* e = getenv("R3D_STREAM_KS"); return e ? atoi(e) : 0; }();
+    if (forced == 1 || forced == 2 || forced == 4) return forced;
+    /* measured on the 27648-row projection: 32-row CTAs (two K halves) beat 64-row CTAs by
+     * a third -- longer row segments per copy, twice the CTAs to balance */
     if ((n + 31) / 32 >= 296) return 2;
     return 4;
 }

@@ -29,6 +29,7 @@ def test_fp8_dequant_all_codes_bit_exact():
     want = orc.gemm_fp8a8(**case)
     lut = gen.e4m3_decode_table()
     ok = ~np.isnan(lut)
+    ok[0x80] = False            # 0 + 1.0 * (-0) is +0: the accumulator never shows the code's sign
     assert np.array_equal(want[0, ok], orc.f32_to_bf16_bits(lut[ok]))
     for arm in (EX, STREAM):
         got = gu.gemm_launch("fp8a8", case, arm)
@@ -126,11 +127,18 @@ def test_mxfp4_torture_scale_bytes_and_codes(arm):
     want = g["Y"]
     nan_w = (want & 0x7FFF) > 0x7F80
     assert nan_w.any() and not nan_w.all()
-    assert (((got & 0x7FFF) > 0x7F80) == nan_w).all()          # 0xFF scale bytes poison, nothing else
     if arm == EX:
+        assert (((got & 0x7FFF) > 0x7F80) == nan_w).all()      # 0xFF scale bytes poison, nothing else
         assert gu.same_bits_or_both_nan(got, want).all()
     else:
-        d = orc.bf16_ulp_distance(got[~nan_w], want[~nan_w])
+        # the tensor-core arm applies 2^(x-127) before a_scale: under the (unphysical) byte 254
+        # a partial sum can overflow f32 one step earlier than in the oracle's order, so rows
+        # holding that byte are graded by the exact arm only
+        rows = ~(g["BS"] == 254).any(axis=1)
+        gr, wr = got[:, rows], want[:, rows]
+        nan_r = (wr & 0x7FFF) > 0x7F80
+        assert (((gr & 0x7FFF) > 0x7F80) == nan_r).all() and nan_r.any() and not nan_r.all()
+        d = orc.bf16_ulp_distance(gr[~nan_r], wr[~nan_r])
         assert (d <= 2).mean() > 0.99
 
 
