@@ -97,6 +97,16 @@ int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream);
 int r3d_b200_gemm_mxfp4a8_q8x(const R3dGemmQ* q, int8_t* x8, float* sg, int walk,
                               void* stream);
 
+/* The same arm with no allocation anywhere: the requantised-activation scratch is a fixed
+ * array inside the library (288 KiB per GPU, held until the process exits) instead of
+ * caller memory. For callers that cannot call cudaMalloc -- a launch issued while a pass is
+ * being recorded, or once the engine has given all device memory to weights and KV cache.
+ * Serves M <= 8 and K <= 32768 (K % 256 == 0); anything larger returns RAD_E_SHAPE. All
+ * calls on a device share the array: calls that overlap in time race, so keep them on one
+ * stream. The first call on a device resolves the array's address; make it before any
+ * stream capture. This entry point has no counterpart in the reference. */
+int r3d_b200_gemm_mxfp4a8_q8x_static(const R3dGemmQ* q, int walk, void* stream);
+
 typedef struct R3dLogits {
     const void* x;          /* bf16 [M, K] */
     const void* codes;      /* e4m3 [N, K] dense   |  e2m1 nibbles (head_fmt 1) */

@@ -28,6 +28,7 @@ SOURCES = [
     "launch.cu",
     "kern_exact.cu",
     "kern_q8x.cu",
+    "q8x_static.cu",
     "kern_stream.cu",
     "kern_tile.cu",
 ]
