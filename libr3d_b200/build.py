@@ -30,7 +30,7 @@ SOURCES = [
     "kern_q8x.cu",
     "q8x_static.cu",
     "kern_stream.cu",
-    "kern_tile.cu",
+    "kern_tc.cu",
 ]
 
 NVCC_FLAGS = [

@@ -530,5 +530,6 @@ int stream_logits(const R3dLogits& p, cudaStream_t st) {
 extern "C" int r3d_b200_stream_status(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, r3d::g_stream_status, sizeof(int)) != cudaSuccess) return -1;
-    return v;
+    const int t = r3d::tc_status();
+    return v ? v : t;
 }

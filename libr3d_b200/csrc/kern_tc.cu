@@ -1,0 +1,424 @@
+/* kern_tc.cu -- the tcgen05 arm of the decode / verify bands: weight streaming with the
+ * 5th-generation tensor cores doing the dequantisation.
+ *
+ * Shape of the problem: y[M,N] = a[M,K] . w[N,K]^T with M <= 64 tokens. The weight plane is
+ * the only large operand, so the kernel is "swap-AB": 128 weight rows sit on the M axis of
+ * tcgen05.mma (one TMEM lane per weight row) and the tokens, padded to 16/32/64, on its N
+ * axis. Everything the CUDA cores did in the mma.sync arm disappears:
+ *   - TMA tensor maps bring a [128 rows x 128 K] weight tile per stage straight into the
+ *     128-byte-swizzled shared layout the MMA descriptor wants. For mxfp4a8 the tensor map
+ *     type CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B unpacks the e2m1 nibbles on the way in (HBM
+ *     traffic stays 4 bits per weight) and kind::f8f6f4 decodes them in the tensor core:
+ *     no conversion instruction is executed anywhere.
+ *   - The activation tile [tokens x 128 K] comes the same way (rows past M are zero-filled
+ *     by the TMA unit).
+ *   - One elected thread issues four K=32 MMAs per stage; accumulators live in TMEM, double
+ *     buffered so the next stage's MMAs run while the epilogue drains this one.
+ *   - Four epilogue warps (128 threads = 128 weight rows) read the f32 partials with
+ *     tcgen05.ld and apply the scale groups in registers, in the reference's flush order:
+ *       fp8a8    acc += (sub128 * sa[m,g]) * sb[row,g]                 (one partial per stage)
+ *       mxfp4a8  t = sum_j sub32_j * 2^(x_j-127);  acc += t * sa[m,g]  (four partials per
+ *                stage: each K=32 MMA is exactly one E8M0 scale group and writes its own
+ *                TMEM columns)
+ * Warp roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-5 epilogue.
+ *
+ * Every mbarrier wait is bounded (~1 s of clock64); on expiry a status word is set
+ * (r3d_b200_stream_status() reports it) and the CTA drains, frees its TMEM and leaves
+ * without storing.
+ */
+#include <cuda.h>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+#include "r3d_kernels.h"
+#include "r3d_numerics.cuh"
+
+namespace r3d {
+
+__device__ int g_tc_status = 0;    /* nonzero = code of the bounded wait that expired */
+
+namespace {
+
+constexpr int kTcThreads = 192;
+constexpr int kTcStages = 6;
+constexpr int kTileRows = 128;
+constexpr int kStageK = 128;                       /* K elements (= smem bytes per row) per stage */
+constexpr int kABytes = kTileRows * kStageK;       /* 16 KiB */
+constexpr long long kTcSpin = 2000000000LL;
+
+enum { TC_FP8 = 0, TC_MXFP4 = 1 };
+
+struct TcParams {
+    const uint8_t* ws; int64_t ws_pitch;           /* weight scales: bf16/f32 grid or E8M0 bytes */
+    const float* as; int64_t as_pitch;
+    uint16_t* y; int64_t y_pitch;
+    int m, n, k;
+    int as_cols, ws_cols, rblk, ws_dtype;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
+                 ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try(bar, parity)) {
+        if (clock64() - t0 > kTcSpin) { atomicExch(&g_tc_status, code); return false; }
+    }
+    return true;
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+/* shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, 8-row
+ * swizzle atoms stacked 1024 bytes apart; descriptor version 1 */
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+__device__ __forceinline__ void umma_f8f6f4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float ld_scale(const uint8_t* base, int64_t idx, int dt) {
+    if (dt == RAD_F32) return __ldg((const float*)base + idx);
+    return bf16_to_f32(__ldg((const uint16_t*)base + idx));
+}
+__device__ __forceinline__ int scale_col(int c, int cols, int nchunk) {
+    return cols == nchunk ? c : (cols == 1 ? 0 : (int)((int64_t)c * cols / nchunk));
+}
+
+template <int FMT, int NTOK>
+__global__ void __launch_bounds__(kTcThreads)
+k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
+            const TcParams P) {
+    constexpr int kBBytes = NTOK * kStageK;
+    constexpr int kStage = kABytes + kBBytes;
+    constexpr int kAccCols = (FMT == TC_MXFP4 ? 4 : 1) * NTOK;     /* per buffer */
+    constexpr int kTmemCols = (2 * kAccCols) < 32 ? 32 : 2 * kAccCols;
+    static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 256, "TMEM columns");
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + kTcStages * kStage);
+    uint64_t* empty = full + kTcStages;
+    uint64_t* acc_full = empty + kTcStages;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    float* as_s = (float*)(tmem_slot + 4);                          /* [n128][NTOK] */
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r0 = blockIdx.x * kTileRows;
+    const int nk = P.k / kStageK;
+    const int n128 = nk;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTcStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < n128 * NTOK; i += kTcThreads) {
+        const int g = i / NTOK, t = i - g * NTOK;
+        as_s[i] = t < P.m ? P.as[(int64_t)t * P.as_pitch + scale_col(g, P.as_cols, n128)] : 0.0f;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        /* ---------------- TMA producer ---------------- */
+        if (elect_one()) {
+            for (int it = 0; it < nk; ++it) {
+                const int s = it % kTcStages;
+                if (!mbar_wait(&empty[s], ((it / kTcStages) & 1) ^ 1, 11)) break;
+                uint8_t* st = smem + s * kStage;
+                /* the unpacking tensor map counts the packed bytes it read, not the padded
+                 * bytes it wrote */
+                mbar_expect_tx(&full[s], (uint32_t)((FMT == TC_MXFP4 ? kABytes / 2 : kABytes) + kBBytes));
+                tma_load_2d(st, &tmW, it * kStageK, r0, &full[s]);
+                tma_load_2d(st + kABytes, &tmA, it * kStageK, 0, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        /* ---------------- MMA issuer ---------------- */
+        if (elect_one()) {
+            const uint32_t idesc = (1u << 4) | ((FMT == TC_MXFP4 ? 5u : 0u) << 7) | (0u << 10) |
+                                   ((uint32_t)(NTOK >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
+            for (int it = 0; it < nk; ++it) {
+                const int s = it % kTcStages, buf = it & 1;
+                if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, 12)) break;
+                if (!mbar_wait(&full[s], (it / kTcStages) & 1, 13)) break;
+                tc_fence_after();
+                const uint32_t a0 = smem_u32(smem + s * kStage), b0 = a0 + kABytes;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint64_t ad = smem_desc_sw128(a0 + k * 32), bd = smem_desc_sw128(b0 + k * 32);
+                    if (FMT == TC_MXFP4)
+                        umma_f8f6f4(tmem_base + buf * kAccCols + k * NTOK, ad, bd, idesc, 0u);
+                    else
+                        umma_f8f6f4(tmem_base + buf * kAccCols, ad, bd, idesc, k > 0 ? 1u : 0u);
+                }
+                umma_commit(&empty[s]);          /* smem stage reusable once these MMAs retire */
+                umma_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        /* ---------------- epilogue: thread = weight row ---------------- */
+        const int q = warp & 3;
+        const int row = r0 + q * 32 + lane;
+        const int rowc = min(row, P.n - 1);
+        const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
+        const int64_t srow = (FMT == TC_FP8) ? (int64_t)(P.rblk > 1 ? rowc / P.rblk : rowc) * P.ws_pitch
+                                             : (int64_t)rowc * P.ws_pitch;
+        float acc[NTOK];
+#pragma unroll
+        for (int t = 0; t < NTOK; ++t) acc[t] = 0.0f;
+        bool alive = true;
+        for (int it = 0; it < nk; ++it) {
+            const int buf = it & 1;
+            float sb = 0.0f;
+            uint32_t sw = 0;
+            if (FMT == TC_FP8) sb = ld_scale(P.ws, srow + scale_col(it, P.ws_cols, n128), P.ws_dtype);
+            else sw = __ldg((const uint32_t*)(P.ws + srow + it * 4));
+            if (!mbar_wait(&acc_full[buf], (it >> 1) & 1, 14)) { alive = false; break; }
+            tc_fence_after();
+            const float* sa = as_s + it * NTOK;
+            if (FMT == TC_FP8) {
+                float c[NTOK];
+#pragma unroll
+                for (int h = 0; h < NTOK / 16; ++h) tmem_ld16(tlane + buf * kAccCols + h * 16, c + h * 16);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+#pragma unroll
+                for (int t = 0; t < NTOK; ++t) acc[t] += (c[t] * sa[t]) * sb;
+            } else {
+                float tsum[NTOK];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float c[NTOK];
+#pragma unroll
+                    for (int h = 0; h < NTOK / 16; ++h)
+                        tmem_ld16(tlane + buf * kAccCols + j * NTOK + h * 16, c + h * 16);
+                    tmem_ld_wait();
+                    const float sj = e8m0_to_f32((uint8_t)(sw >> (8 * j)));
+#pragma unroll
+                    for (int t = 0; t < NTOK; ++t) tsum[t] = j == 0 ? c[t] * sj : fmaf(c[t], sj, tsum[t]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+#pragma unroll
+                for (int t = 0; t < NTOK; ++t) acc[t] += tsum[t] * sa[t];
+            }
+        }
+        if (alive && row < P.n) {
+#pragma unroll
+            for (int t = 0; t < NTOK; ++t)
+                if (t < P.m) P.y[(int64_t)t * P.y_pitch + row] = f32_to_bf16(acc[t]);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
+    }
+}
+
+/* ------------------------------------------------------------------ host: tensor maps */
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        (void)cudaGetLastError();
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
+}
+
+struct MapKey { const void* ptr; uint64_t d0, d1, pitch; int dtype; uint32_t box1; };
+struct MapEnt { MapKey k; CUtensorMap m; };
+
+/* Tensor maps are remembered per (pointer, geometry): the engine's buffers are long-lived and
+ * a launch must not do driver work in steady state. Single dispatch thread, like the
+ * reference's plane cache (src/r3d_gemm_mxfp4.hip:1879-1880). */
+const CUtensorMap* tensor_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_t pitch_bytes,
+                              CUtensorMapDataType dt, uint32_t box1) {
+    static std::vector<MapEnt*> cache;
+    for (const MapEnt* e : cache)
+        if (e->k.ptr == ptr && e->k.d0 == d0 && e->k.d1 == d1 && e->k.pitch == pitch_bytes &&
+            e->k.dtype == (int)dt && e->k.box1 == box1)
+            return &e->m;
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return nullptr;
+    MapEnt* e = new MapEnt;
+    e->k = MapKey{ptr, d0, d1, pitch_bytes, (int)dt, box1};
+    const cuuint64_t dims[2] = {d0, d1};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {128u, box1};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult rc = fn(&e->m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) { delete e; return nullptr; }
+    if (cache.size() >= 4096) { delete cache.front(); cache.erase(cache.begin()); }
+    cache.push_back(e);
+    return &e->m;
+}
+
+template <int FMT, int NTOK>
+int launch_tc(const CUtensorMap* tw, const CUtensorMap* ta, const TcParams& P, cudaStream_t st) {
+    const size_t smem = 1024 + (size_t)kTcStages * (kABytes + NTOK * kStageK) +
+                        (2 * kTcStages + 4) * sizeof(uint64_t) + 16 +
+                        (size_t)(P.k / kStageK) * NTOK * sizeof(float);
+    if (smem > 220 * 1024) return RAD_E_UNSUPPORTED;
+    static size_t attr_set = 0;
+    if (smem > attr_set) {
+        if (cudaFuncSetAttribute(k_tc_decode<FMT, NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess) return RAD_E_DEVICE;
+        attr_set = smem;
+    }
+    const unsigned grid = (unsigned)((P.n + kTileRows - 1) / kTileRows);
+    count_launch();
+    k_tc_decode<FMT, NTOK><<<grid, kTcThreads, smem, st>>>(*tw, *ta, P);
+    return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+}
+
+bool al(const void* p, int a) { return (((uintptr_t)p) & (uintptr_t)(a - 1)) == 0; }
+
+} /* anonymous namespace */
+
+bool tc_fp8a8_ok(const R3dGemmQ& p) {
+    return p.m >= 1 && p.m <= 64 && (p.k % 128) == 0 && al(p.b, 16) && (p.b_pitch % 16) == 0 &&
+           al(p.a, 16) && (p.a_pitch % 16) == 0 && encode_fn() != nullptr;
+}
+bool tc_mxfp4a8_ok(const R3dGemmQ& p) {
+    return p.m >= 1 && p.m <= 32 && (p.k % 128) == 0 && al(p.b, 32) && (p.b_pitch % 32) == 0 &&
+           al(p.b_scale, 4) && (p.bs_pitch % 4) == 0 && al(p.a, 16) && (p.a_pitch % 16) == 0 &&
+           encode_fn() != nullptr;
+}
+
+int tc_fp8a8(const R3dGemmQ& p, cudaStream_t st) {
+    const int ntok = p.m <= 16 ? 16 : p.m <= 32 ? 32 : 64;
+    const CUtensorMap* tw = tensor_map(p.b, (uint64_t)p.k, (uint64_t)p.n, (uint64_t)p.b_pitch,
+                                       CU_TENSOR_MAP_DATA_TYPE_UINT8, kTileRows);
+    const CUtensorMap* ta = tensor_map(p.a, (uint64_t)p.k, (uint64_t)p.m, (uint64_t)p.a_pitch,
+                                       CU_TENSOR_MAP_DATA_TYPE_UINT8, (uint32_t)ntok);
+    if (!tw || !ta) return RAD_E_UNSUPPORTED;
+    TcParams P{};
+    P.ws = (const uint8_t*)p.b_scale; P.ws_pitch = p.bs_pitch;
+    P.as = p.a_scale; P.as_pitch = p.as_pitch;
+    P.y = (uint16_t*)p.y; P.y_pitch = p.y_pitch;
+    P.m = p.m; P.n = p.n; P.k = p.k;
+    P.as_cols = p.as_cols; P.ws_cols = p.bs_cols; P.rblk = p.rblk; P.ws_dtype = p.bs_dtype;
+    if (ntok == 16) return launch_tc<TC_FP8, 16>(tw, ta, P, st);
+    if (ntok == 32) return launch_tc<TC_FP8, 32>(tw, ta, P, st);
+    return launch_tc<TC_FP8, 64>(tw, ta, P, st);
+}
+
+int tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st) {
+    const int ntok = p.m <= 16 ? 16 : 32;
+    const CUtensorMap* tw = tensor_map(p.b, (uint64_t)p.k, (uint64_t)p.n, (uint64_t)p.b_pitch,
+                                       CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, kTileRows);
+    const CUtensorMap* ta = tensor_map(p.a, (uint64_t)p.k, (uint64_t)p.m, (uint64_t)p.a_pitch,
+                                       CU_TENSOR_MAP_DATA_TYPE_UINT8, (uint32_t)ntok);
+    if (!tw || !ta) return RAD_E_UNSUPPORTED;
+    TcParams P{};
+    P.ws = (const uint8_t*)p.b_scale; P.ws_pitch = p.bs_pitch;
+    P.as = p.a_scale; P.as_pitch = p.as_pitch;
+    P.y = (uint16_t*)p.y; P.y_pitch = p.y_pitch;
+    P.m = p.m; P.n = p.n; P.k = p.k;
+    P.as_cols = p.as_cols; P.ws_cols = p.bs_cols; P.rblk = 1; P.ws_dtype = RAD_E8M0;
+    if (ntok == 16) return launch_tc<TC_MXFP4, 16>(tw, ta, P, st);
+    return launch_tc<TC_MXFP4, 32>(tw, ta, P, st);
+}
+
+int tc_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+
+} /* namespace r3d */

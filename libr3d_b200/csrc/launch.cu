@@ -52,29 +52,42 @@ static void debug_arm(const char* band, const char* arm, int m) {
 
 using namespace r3d;
 
+/* AUTO: the tcgen05 arm when the operands meet TMA's alignment rules, else the mma.sync
+ * streaming arm, else the oracle-order arm (any shape, any alignment). M above one pass is
+ * probed at the pass size. */
+static int auto_arm_fp8a8(const R3dGemmQ& q) {
+    R3dGemmQ probe = q; if (probe.m > 64) probe.m = 64;
+    if (tc_fp8a8_ok(probe)) return R3D_ARM_TILE;
+    return stream_fp8a8_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+}
+static int auto_arm_mxfp4a8(const R3dGemmQ& q) {
+    R3dGemmQ probe = q; if (probe.m > 32) probe.m = 32;
+    if (tc_mxfp4a8_ok(probe)) return R3D_ARM_TILE;
+    probe = q; if (probe.m > 64) probe.m = 64;
+    return stream_mxfp4a8_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+}
+
 extern "C" long long r3d_b200_launch_count(void) { return g_launches.load(); }
 
 extern "C" int r3d_b200_pick_arm_fp8a8(const R3dGemmQ* q) {
     if (!q) return -1;
     if (q->arm != R3D_ARM_AUTO) return q->arm;
-    R3dGemmQ probe = *q; if (probe.m > 64) probe.m = 64;
-    return stream_fp8a8_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+    return auto_arm_fp8a8(*q);
 }
 extern "C" int r3d_b200_pick_arm_mxfp4a8(const R3dGemmQ* q) {
     if (!q) return -1;
     if (q->arm != R3D_ARM_AUTO) return q->arm;
-    R3dGemmQ probe = *q; if (probe.m > 64) probe.m = 64;
-    return stream_mxfp4a8_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+    return auto_arm_mxfp4a8(*q);
 }
 
 /* M above the streaming arm's 64 rides it in passes of 64 tokens, each pass re-reading the
  * weights (the reference's own rule for M above its register group,
  * src/r3d_gemm_logits.hip:24-26). */
 template <typename OkFn, typename RunFn>
-static int gemm_passes(const R3dGemmQ& q, OkFn ok, RunFn run, cudaStream_t st) {
-    for (int m0 = 0; m0 < q.m; m0 += 64) {
+static int gemm_passes(const R3dGemmQ& q, OkFn ok, RunFn run, cudaStream_t st, int step = 64) {
+    for (int m0 = 0; m0 < q.m; m0 += step) {
         R3dGemmQ c = q;
-        c.m = q.m - m0 < 64 ? q.m - m0 : 64;
+        c.m = q.m - m0 < step ? q.m - m0 : step;
         c.a = (const uint8_t*)q.a + (int64_t)m0 * q.a_pitch;
         c.a_scale = q.a_scale + (int64_t)m0 * q.as_pitch;
         c.y = (uint16_t*)q.y + (int64_t)m0 * q.y_pitch;
@@ -89,15 +102,16 @@ extern "C" int r3d_b200_gemm_fp8a8(const R3dGemmQ* q, void* stream) {
     if (!q || !device_is_sm100()) return RAD_E_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
     int arm = q->arm;
-    if (arm == R3D_ARM_AUTO) {
-        R3dGemmQ probe = *q; if (probe.m > 64) probe.m = 64;
-        arm = stream_fp8a8_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
-    }
+    if (arm == R3D_ARM_AUTO) arm = auto_arm_fp8a8(*q);
     if (arm == R3D_ARM_STREAM) {
         debug_arm("fp8a8", "stream", q->m);
         return gemm_passes(*q, stream_fp8a8_ok, stream_fp8a8, st);
     }
     if (arm == R3D_ARM_EXACT) { debug_arm("fp8a8", "exact", q->m); return exact_fp8a8(*q, st); }
+    if (arm == R3D_ARM_TILE) {
+        debug_arm("fp8a8", "tcgen05", q->m);
+        return gemm_passes(*q, tc_fp8a8_ok, tc_fp8a8, st, 64);
+    }
     return RAD_E_UNSUPPORTED;
 }
 
@@ -105,15 +119,16 @@ extern "C" int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream) {
     if (!q || !device_is_sm100()) return RAD_E_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
     int arm = q->arm;
-    if (arm == R3D_ARM_AUTO) {
-        R3dGemmQ probe = *q; if (probe.m > 64) probe.m = 64;
-        arm = stream_mxfp4a8_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
-    }
+    if (arm == R3D_ARM_AUTO) arm = auto_arm_mxfp4a8(*q);
     if (arm == R3D_ARM_STREAM) {
         debug_arm("mxfp4a8", "stream", q->m);
         return gemm_passes(*q, stream_mxfp4a8_ok, stream_mxfp4a8, st);
     }
     if (arm == R3D_ARM_EXACT) { debug_arm("mxfp4a8", "exact", q->m); return exact_mxfp4a8(*q, st); }
+    if (arm == R3D_ARM_TILE) {
+        debug_arm("mxfp4a8", "tcgen05", q->m);
+        return gemm_passes(*q, tc_mxfp4a8_ok, tc_mxfp4a8, st, 32);
+    }
     return RAD_E_UNSUPPORTED;
 }
 

@@ -27,6 +27,14 @@ int  stream_fp8a8(const R3dGemmQ& p, cudaStream_t st);
 int  stream_mxfp4a8(const R3dGemmQ& p, cudaStream_t st);
 int  stream_logits(const R3dLogits& p, cudaStream_t st);
 
+/* tcgen05 arm (kern_tc.cu): TMA tensor maps + TMEM accumulators, swap-AB, M <= 64 (fp8a8) /
+ * M <= 32 (mxfp4a8) per pass */
+bool tc_fp8a8_ok(const R3dGemmQ& p);
+bool tc_mxfp4a8_ok(const R3dGemmQ& p);
+int  tc_fp8a8(const R3dGemmQ& p, cudaStream_t st);
+int  tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st);
+int  tc_status();                      /* 0, or the code of a bounded wait that expired */
+
 /* int8-per-32 activation arm (kern_q8x.cu) */
 int q8x_requant(const R3dGemmQ& p, int8_t* x8, float* sg, cudaStream_t st);
 int q8x_gemv(const R3dGemmQ& p, const int8_t* x8, const float* sg, int walk, cudaStream_t st);

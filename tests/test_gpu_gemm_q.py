@@ -15,7 +15,8 @@ from oracle import oracle as orc
 
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
-EX, STREAM = abi.R3D_ARM_EXACT, abi.R3D_ARM_STREAM
+EX, STREAM, TILE = abi.R3D_ARM_EXACT, abi.R3D_ARM_STREAM, abi.R3D_ARM_TILE
+FAST = [STREAM, TILE]          # the two tensor-core arms: mma.sync streaming, tcgen05
 ODD_M = [1, 2, 3, 5, 7, 8, 9, 16, 17]
 
 
@@ -31,12 +32,12 @@ def test_fp8_dequant_all_codes_bit_exact():
     ok = ~np.isnan(lut)
     ok[0x80] = False            # 0 + 1.0 * (-0) is +0: the accumulator never shows the code's sign
     assert np.array_equal(want[0, ok], orc.f32_to_bf16_bits(lut[ok]))
-    for arm in (EX, STREAM):
+    for arm in (EX, STREAM, TILE):
         got = gu.gemm_launch("fp8a8", case, arm)
         assert gu.same_bits_or_both_nan(got, want).all(), arm
 
 
-@pytest.mark.parametrize("arm", [EX, STREAM])
+@pytest.mark.parametrize("arm", [EX, STREAM, TILE])
 def test_mxfp4_dequant_all_codes_all_scales_bit_exact(arm):
     """every e2m1 code under every E8M0 byte: y[n] = e2m1(c) * 2^(x-127), selected one-hot."""
     K = 512
@@ -57,7 +58,7 @@ def test_mxfp4_dequant_all_codes_all_scales_bit_exact(arm):
 
 # ------------------------------------------------------------------ fp8a8
 def test_fp8_unit_fixture_analytic():
-    for arm in (EX, STREAM):
+    for arm in (EX, STREAM, TILE):
         for (M, K, N) in [(14, 512, 130), (4, 2048, 64)]:
             case, expect = gen.fixture_fp8_unit(M, K, N)
             got = gu.gemm_launch("fp8a8", case, arm)
@@ -75,14 +76,15 @@ def test_fp8_exact_arm_is_bit_identical_to_oracle(grid, M):
     assert np.count_nonzero(got & 0x7FFF) > got.size * 0.9
 
 
+@pytest.mark.parametrize("arm", FAST)
 @pytest.mark.parametrize("grid", ["ref128", "row", "channel"])
 @pytest.mark.parametrize("M", ODD_M + [33, 64])
-def test_fp8_stream_arm_within_2ulp(grid, M):
+def test_fp8_fast_arms_within_2ulp(grid, M, arm):
     N, K = (200, 384) if M % 2 else (136, 1280)
     case = gen.case_fp8(2000 + M, M, N, K, grid)
     _, acc = orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], case["rblk"], want_acc=True)
     _, ab = orc.truth_fp8a8(case["A"], case["AS"], case["B"], case["BS"], case["rblk"])
-    g = gu.grade_bf16(gu.gemm_launch("fp8a8", case, STREAM), acc, ab)
+    g = gu.grade_bf16(gu.gemm_launch("fp8a8", case, arm), acc, ab)
     assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 5e-3, g
     assert g["nonzero"] > acc.size * 0.9
 
@@ -92,8 +94,9 @@ def test_fp8_config_c1_full_size():
     case = gen.case_fp8(0, 1, 4096, 4096, "channel")
     want, acc = orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], 1, want_acc=True)
     assert np.array_equal(gu.gemm_launch("fp8a8", case, EX), want)
-    g = gu.grade_bf16(gu.gemm_launch("fp8a8", case, STREAM), acc)
-    assert g["max_ulp"] <= 2, g
+    for arm in FAST:
+        g = gu.grade_bf16(gu.gemm_launch("fp8a8", case, arm), acc)
+        assert g["max_ulp"] <= 2, (arm, g)
 
 
 # ------------------------------------------------------------------ mxfp4a8
@@ -109,17 +112,18 @@ def test_mxfp4_exact_arm_on_probe_fixture():
     assert np.array_equal(gu.gemm_launch("mxfp4a8", case, EX), orc.gemm_mxfp4a8(**case))
 
 
+@pytest.mark.parametrize("arm", FAST)
 @pytest.mark.parametrize("M", ODD_M + [33, 64])
-def test_mxfp4_stream_arm_within_2ulp(M):
+def test_mxfp4_fast_arms_within_2ulp(M, arm):
     N, K = (200, 512) if M % 2 else (136, 1536)
     case = gen.case_mxfp4(4000 + M, M, N, K)
     _, acc = orc.gemm_mxfp4a8(**case, want_acc=True)
     _, ab = orc.truth_mxfp4a8(**case)
-    g = gu.grade_bf16(gu.gemm_launch("mxfp4a8", case, STREAM), acc, ab)
+    g = gu.grade_bf16(gu.gemm_launch("mxfp4a8", case, arm), acc, ab)
     assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 3e-2, g
 
 
-@pytest.mark.parametrize("arm", [EX, STREAM])
+@pytest.mark.parametrize("arm", [EX, STREAM, TILE])
 def test_mxfp4_torture_scale_bytes_and_codes(arm):
     g = np.load(GOLD / "mxfp4a8_torture.npz")
     case = dict(A=g["A"], AS=g["AS"], B=g["B"], BS=g["BS"])
@@ -235,10 +239,11 @@ def _stream_vs_exact_full(kind, case, tol_frac=0.9995):
     bit-identical to the CPU oracle at small sizes) to 2 bf16 ulp, plus a CPU-oracle check of
     a row sample."""
     ex = gu.gemm_launch(kind, case, EX)
-    st = gu.gemm_launch(kind, case, STREAM)
-    d = orc.bf16_ulp_distance(st, ex)
-    assert (d <= 2).mean() >= tol_frac, ((d <= 2).mean(), int(d.max()))
-    assert np.count_nonzero(st & 0x7FFF) > st.size * 0.9
+    for arm in FAST:
+        st = gu.gemm_launch(kind, case, arm)
+        d = orc.bf16_ulp_distance(st, ex)
+        assert (d <= 2).mean() >= tol_frac, (arm, (d <= 2).mean(), int(d.max()))
+        assert np.count_nonzero(st & 0x7FFF) > st.size * 0.9
     rows = np.random.default_rng(1).choice(case["B"].shape[0], 256, replace=False)
     sub = dict(case); sub["B"] = case["B"][rows]
     if kind == "fp8a8":
