@@ -41,7 +41,6 @@ __device__ int g_tc_status = 0;    /* nonzero = code of the bounded wait that ex
 namespace {
 
 constexpr int kTcThreads = 192;
-constexpr int kTcStages = 6;
 constexpr int kTileRows = 128;
 constexpr int kStageK = 128;                       /* K elements (= smem bytes per row) per stage */
 constexpr int kABytes = kTileRows * kStageK;       /* 16 KiB */
@@ -55,6 +54,7 @@ struct TcParams {
     uint16_t* y; int64_t y_pitch;
     int m, n, k;
     int as_cols, ws_cols, rblk, ws_dtype;
+    int ksplit;                                    /* CTAs per cluster = K shares per row tile */
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -128,6 +128,33 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
+/* tcgen05.ld 32x32b: thread i of the warp reads N consecutive 32-bit columns of TMEM lane
+ * (lane base + i) */
+__device__ __forceinline__ void tmem_ld1(uint32_t taddr, float* v) {
+    uint32_t r0;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r0) : "r"(taddr) : "memory");
+    v[0] = __uint_as_float(r0);
+}
+__device__ __forceinline__ void tmem_ld2(uint32_t taddr, float* v) {
+    uint32_t r0, r1;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(taddr) : "memory");
+    v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1);
+}
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, float* v) {
+    uint32_t r[4];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                   "=r"(r[7]) : "r"(taddr) : "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
     uint32_t r[16];
     asm volatile(
@@ -139,6 +166,18 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
         : "r"(taddr) : "memory");
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+/* the first ML columns (ML = 1, 2, 4, 8 or a multiple of 16) */
+template <int ML>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, float* v) {
+    if (ML == 1) tmem_ld1(taddr, v);
+    else if (ML == 2) tmem_ld2(taddr, v);
+    else if (ML == 4) tmem_ld4(taddr, v);
+    else if (ML == 8) tmem_ld8(taddr, v);
+    else {
+#pragma unroll
+        for (int h = 0; h < ML / 16; ++h) tmem_ld16(taddr + h * 16, v + h * 16);
+    }
 }
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -152,14 +191,36 @@ __device__ __forceinline__ int scale_col(int c, int cols, int nchunk) {
     return cols == nchunk ? c : (cols == 1 ? 0 : (int)((int64_t)c * cols / nchunk));
 }
 
-template <int FMT, int NTOK>
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
+    uint32_t ra;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+    return v;
+}
+
+/* NTOK: tokens on the MMA's N axis (16, 32 or 64; rows past M are zero). ML: tokens the
+ * epilogue actually reads and stores (M rounded up to 1, 2, 4, 8, 16, ...): the TMEM columns
+ * of padding tokens are never touched. The CTAs of a cluster split K between them and the
+ * leader adds the partial sums through distributed shared memory, in rank order. */
+template <int FMT, int NTOK, int ML, int kTcStages>
 __global__ void __launch_bounds__(kTcThreads)
 k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
             const TcParams P) {
     constexpr int kBBytes = NTOK * kStageK;
     constexpr int kStage = kABytes + kBBytes;
     constexpr int kAccCols = (FMT == TC_MXFP4 ? 4 : 1) * NTOK;     /* per buffer */
-    constexpr int kTmemCols = (2 * kAccCols) < 32 ? 32 : 2 * kAccCols;
+    constexpr int kBufs = (4 * kAccCols <= 256) ? 4 : 2;           /* accumulator ring in TMEM */
+    constexpr int kTmemCols = (kBufs * kAccCols) < 32 ? 32 : kBufs * kAccCols;
     static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 256, "TMEM columns");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -167,18 +228,21 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     uint64_t* full = (uint64_t*)(smem + kTcStages * kStage);
     uint64_t* empty = full + kTcStages;
     uint64_t* acc_full = empty + kTcStages;
-    uint64_t* acc_empty = acc_full + 2;
-    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    uint64_t* acc_empty = acc_full + 4;
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 4);
     float* as_s = (float*)(tmem_slot + 4);                          /* [n128][NTOK] */
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r0 = blockIdx.x * kTileRows;
-    const int nk = P.k / kStageK;
-    const int n128 = nk;
+    const int ks = P.ksplit;
+    const int crank = ks > 1 ? (int)cluster_rank() : 0;
+    const int r0 = (blockIdx.x / ks) * kTileRows;
+    const int n128 = P.k / kStageK;
+    const int it0 = (int)((int64_t)n128 * crank / ks);             /* this CTA's K stages */
+    const int nk = (int)((int64_t)n128 * (crank + 1) / ks) - it0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTcStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        for (int b = 0; b < kBufs; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int i = threadIdx.x; i < n128 * NTOK; i += kTcThreads) {
@@ -195,6 +259,13 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    const int q = warp & 3;                                    /* TMEM lane quarter of an epilogue warp */
+    const int row = r0 + q * 32 + lane;
+    float acc[ML];
+#pragma unroll
+    for (int t = 0; t < ML; ++t) acc[t] = 0.0f;
+    bool alive = true;
+
     if (warp == 0) {
         /* ---------------- TMA producer ---------------- */
         if (elect_one()) {
@@ -205,8 +276,8 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                 /* the unpacking tensor map counts the packed bytes it read, not the padded
                  * bytes it wrote */
                 mbar_expect_tx(&full[s], (uint32_t)((FMT == TC_MXFP4 ? kABytes / 2 : kABytes) + kBBytes));
-                tma_load_2d(st, &tmW, it * kStageK, r0, &full[s]);
-                tma_load_2d(st + kABytes, &tmA, it * kStageK, 0, &full[s]);
+                tma_load_2d(st, &tmW, (it0 + it) * kStageK, r0, &full[s]);
+                tma_load_2d(st + kABytes, &tmA, (it0 + it) * kStageK, 0, &full[s]);
             }
         }
     } else if (warp == 1) {
@@ -215,8 +286,8 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             const uint32_t idesc = (1u << 4) | ((FMT == TC_MXFP4 ? 5u : 0u) << 7) | (0u << 10) |
                                    ((uint32_t)(NTOK >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
             for (int it = 0; it < nk; ++it) {
-                const int s = it % kTcStages, buf = it & 1;
-                if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, 12)) break;
+                const int s = it % kTcStages, buf = it % kBufs;
+                if (!mbar_wait(&acc_empty[buf], ((it / kBufs) & 1) ^ 1, 12)) break;
                 if (!mbar_wait(&full[s], (it / kTcStages) & 1, 13)) break;
                 tc_fence_after();
                 const uint32_t a0 = smem_u32(smem + s * kStage), b0 = a0 + kABytes;
@@ -234,61 +305,97 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         }
     } else {
         /* ---------------- epilogue: thread = weight row ---------------- */
-        const int q = warp & 3;
-        const int row = r0 + q * 32 + lane;
         const int rowc = min(row, P.n - 1);
         const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
         const int64_t srow = (FMT == TC_FP8) ? (int64_t)(P.rblk > 1 ? rowc / P.rblk : rowc) * P.ws_pitch
                                              : (int64_t)rowc * P.ws_pitch;
-        float acc[NTOK];
+        /* Weight scales of this row, fetched eight stages ahead of their use: the loads are
+         * DRAM-latency long and sit on the epilogue's serial path otherwise. */
+        constexpr int PF = 8;
+        float sbn[PF];
+        uint32_t swn[PF];
+        auto fetch = [&](int blk) {
 #pragma unroll
-        for (int t = 0; t < NTOK; ++t) acc[t] = 0.0f;
-        bool alive = true;
-        for (int it = 0; it < nk; ++it) {
-            const int buf = it & 1;
-            float sb = 0.0f;
-            uint32_t sw = 0;
-            if (FMT == TC_FP8) sb = ld_scale(P.ws, srow + scale_col(it, P.ws_cols, n128), P.ws_dtype);
-            else sw = __ldg((const uint32_t*)(P.ws + srow + it * 4));
-            if (!mbar_wait(&acc_full[buf], (it >> 1) & 1, 14)) { alive = false; break; }
-            tc_fence_after();
-            const float* sa = as_s + it * NTOK;
-            if (FMT == TC_FP8) {
-                float c[NTOK];
+            for (int j = 0; j < PF; ++j) {
+                const int it = blk * PF + j;
+                if (FMT == TC_FP8)
+                    sbn[j] = it < nk ? ld_scale(P.ws, srow + scale_col(it0 + it, P.ws_cols, n128), P.ws_dtype) : 0.0f;
+                else
+                    swn[j] = it < nk ? __ldg((const uint32_t*)(P.ws + srow + (it0 + it) * 4)) : 0u;
+            }
+        };
+        fetch(0);
+        for (int blk = 0; blk * PF < nk && alive; ++blk) {
+            float sbc[PF];
+            uint32_t swc[PF];
 #pragma unroll
-                for (int h = 0; h < NTOK / 16; ++h) tmem_ld16(tlane + buf * kAccCols + h * 16, c + h * 16);
-                tmem_ld_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            for (int j = 0; j < PF; ++j) { sbc[j] = sbn[j]; swc[j] = swn[j]; }
+            fetch(blk + 1);
 #pragma unroll
-                for (int t = 0; t < NTOK; ++t) acc[t] += (c[t] * sa[t]) * sb;
-            } else {
-                float tsum[NTOK];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float c[NTOK];
-#pragma unroll
-                    for (int h = 0; h < NTOK / 16; ++h)
-                        tmem_ld16(tlane + buf * kAccCols + j * NTOK + h * 16, c + h * 16);
+            for (int j8 = 0; j8 < PF; ++j8) {
+                const int it = blk * PF + j8;
+                if (it >= nk) break;
+                const int buf = it % kBufs;
+                if (!mbar_wait(&acc_full[buf], (it / kBufs) & 1, 14)) { alive = false; break; }
+                tc_fence_after();
+                const float* sa = as_s + (it0 + it) * NTOK;
+                if (FMT == TC_FP8) {
+                    const float sb = sbc[j8];
+                    float c[ML];
+                    tmem_ld<ML>(tlane + buf * kAccCols, c);
                     tmem_ld_wait();
-                    const float sj = e8m0_to_f32((uint8_t)(sw >> (8 * j)));
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
 #pragma unroll
-                    for (int t = 0; t < NTOK; ++t) tsum[t] = j == 0 ? c[t] * sj : fmaf(c[t], sj, tsum[t]);
+                    for (int t = 0; t < ML; ++t) acc[t] += (c[t] * sa[t]) * sb;
+                } else {
+                    const uint32_t sw = swc[j8];
+                    float c[4][ML];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) tmem_ld<ML>(tlane + buf * kAccCols + j * NTOK, c[j]);
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    float sj[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) sj[j] = e8m0_to_f32((uint8_t)(sw >> (8 * j)));
+#pragma unroll
+                    for (int t = 0; t < ML; ++t) {
+                        float ts = c[0][t] * sj[0];
+                        ts = fmaf(c[1][t], sj[1], ts);
+                        ts = fmaf(c[2][t], sj[2], ts);
+                        ts = fmaf(c[3][t], sj[3], ts);
+                        acc[t] += ts * sa[t];
+                    }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[buf]);
-#pragma unroll
-                for (int t = 0; t < NTOK; ++t) acc[t] += tsum[t] * sa[t];
             }
         }
-        if (alive && row < P.n) {
+        if (ks > 1 && crank != 0) {
+            /* every stage of this CTA has been consumed: the stage ring is free to carry the
+             * partial sums to the leader */
+            float* red = (float*)smem;
 #pragma unroll
-            for (int t = 0; t < NTOK; ++t)
-                if (t < P.m) P.y[(int64_t)t * P.y_pitch + row] = f32_to_bf16(acc[t]);
+            for (int t = 0; t < ML; ++t) red[t * kTileRows + q * 32 + lane] = alive ? acc[t] : __int_as_float(0x7fc00000);
         }
     }
+
+    if (ks > 1) {
+        cluster_sync_all();                                   /* partial sums are in place */
+        if (warp >= 2 && crank == 0) {
+            const float* red = (const float*)smem;
+            for (int r = 1; r < ks; ++r)
+#pragma unroll
+                for (int t = 0; t < ML; ++t) acc[t] += ld_peer_f32(red + t * kTileRows + q * 32 + lane, (uint32_t)r);
+        }
+    }
+    if (warp >= 2 && crank == 0 && alive && row < P.n) {
+#pragma unroll
+        for (int t = 0; t < ML; ++t)
+            if (t < P.m) P.y[(int64_t)t * P.y_pitch + row] = f32_to_bf16(acc[t]);
+    }
+    if (ks > 1) cluster_sync_all();                           /* peers' smem was read: they may leave */
 
     tc_fence_before();
     __syncthreads();
@@ -348,22 +455,70 @@ const CUtensorMap* tensor_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_
     return &e->m;
 }
 
-template <int FMT, int NTOK>
-int launch_tc(const CUtensorMap* tw, const CUtensorMap* ta, const TcParams& P, cudaStream_t st) {
+int sm_count();
+
+template <int FMT, int NTOK, int ML, int kTcStages>
+int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaStream_t st) {
     const size_t smem = 1024 + (size_t)kTcStages * (kABytes + NTOK * kStageK) +
-                        (2 * kTcStages + 4) * sizeof(uint64_t) + 16 +
+                        (2 * kTcStages + 8) * sizeof(uint64_t) + 16 +
                         (size_t)(P.k / kStageK) * NTOK * sizeof(float);
     if (smem > 220 * 1024) return RAD_E_UNSUPPORTED;
     static size_t attr_set = 0;
     if (smem > attr_set) {
-        if (cudaFuncSetAttribute(k_tc_decode<FMT, NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(k_tc_decode<FMT, NTOK, ML, kTcStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) return RAD_E_DEVICE;
         attr_set = smem;
     }
-    const unsigned grid = (unsigned)((P.n + kTileRows - 1) / kTileRows);
+    /* K shares per row tile: enough CTAs to put two on every SM (their stage rings are the
+     * bytes in flight), never more shares than whole stages, at most 8 (portable cluster) */
+    const int tiles = (P.n + kTileRows - 1) / kTileRows;
+    static const int forced = [] { const char* e = getenv("R3D_TC_KSPLIT"); return e ? atoi(e) : 0; }();
+    /* measured: a CTA costs ~3 us of fill and drain, so K is split only when the row tiles
+     * alone cannot occupy the machine */
+    int ks = forced > 0 ? forced : (tiles >= sm_count() / 2 ? 1 : tiles >= sm_count() / 4 ? 2 : 4);
+    if (ks > 8) ks = 8;
+    if (ks > P.k / kStageK) ks = P.k / kStageK;
+    if (ks < 1) ks = 1;
+    P.ksplit = ks;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(tiles * ks));
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)ks; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
     count_launch();
-    k_tc_decode<FMT, NTOK><<<grid, kTcThreads, smem, st>>>(*tw, *ta, P);
-    return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_decode<FMT, NTOK, ML, kTcStages>, *tw, *ta, P);
+    return e == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+}
+
+template <int FMT, int NTOK, int ML>
+int launch_tc(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaStream_t st) {
+    static const int deep = [] { const char* e = getenv("R3D_TC_STAGES"); return e ? atoi(e) : 6; }();
+    if (deep >= 12) return launch_tc_s<FMT, NTOK, ML, 11>(tw, ta, P, st);
+    return launch_tc_s<FMT, NTOK, ML, 6>(tw, ta, P, st);
+}
+
+int sm_count() {
+    static int n = [] {
+        int dev = 0, v = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        return v > 0 ? v : 148;
+    }();
+    return n;
+}
+
+template <int FMT, int NTOK>
+int launch_tc_ml(const CUtensorMap* tw, const CUtensorMap* ta, const TcParams& P, cudaStream_t st) {
+    if (NTOK == 16) {
+        if (P.m <= 1) return launch_tc<FMT, 16, 1>(tw, ta, P, st);
+        if (P.m <= 2) return launch_tc<FMT, 16, 2>(tw, ta, P, st);
+        if (P.m <= 4) return launch_tc<FMT, 16, 4>(tw, ta, P, st);
+        if (P.m <= 8) return launch_tc<FMT, 16, 8>(tw, ta, P, st);
+    }
+    return launch_tc<FMT, NTOK, NTOK>(tw, ta, P, st);
 }
 
 bool al(const void* p, int a) { return (((uintptr_t)p) & (uintptr_t)(a - 1)) == 0; }
@@ -393,9 +548,9 @@ int tc_fp8a8(const R3dGemmQ& p, cudaStream_t st) {
     P.y = (uint16_t*)p.y; P.y_pitch = p.y_pitch;
     P.m = p.m; P.n = p.n; P.k = p.k;
     P.as_cols = p.as_cols; P.ws_cols = p.bs_cols; P.rblk = p.rblk; P.ws_dtype = p.bs_dtype;
-    if (ntok == 16) return launch_tc<TC_FP8, 16>(tw, ta, P, st);
-    if (ntok == 32) return launch_tc<TC_FP8, 32>(tw, ta, P, st);
-    return launch_tc<TC_FP8, 64>(tw, ta, P, st);
+    if (ntok == 16) return launch_tc_ml<TC_FP8, 16>(tw, ta, P, st);
+    if (ntok == 32) return launch_tc_ml<TC_FP8, 32>(tw, ta, P, st);
+    return launch_tc_ml<TC_FP8, 64>(tw, ta, P, st);
 }
 
 int tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st) {
@@ -411,8 +566,8 @@ int tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st) {
     P.y = (uint16_t*)p.y; P.y_pitch = p.y_pitch;
     P.m = p.m; P.n = p.n; P.k = p.k;
     P.as_cols = p.as_cols; P.ws_cols = p.bs_cols; P.rblk = 1; P.ws_dtype = RAD_E8M0;
-    if (ntok == 16) return launch_tc<TC_MXFP4, 16>(tw, ta, P, st);
-    return launch_tc<TC_MXFP4, 32>(tw, ta, P, st);
+    if (ntok == 16) return launch_tc_ml<TC_MXFP4, 16>(tw, ta, P, st);
+    return launch_tc_ml<TC_MXFP4, 32>(tw, ta, P, st);
 }
 
 int tc_status() {
