@@ -65,7 +65,7 @@ enum {
     R3D_ARM_AUTO   = 0,
     R3D_ARM_EXACT  = 1,   /* oracle-order walk: bit-identical to the CPU restatement */
     R3D_ARM_STREAM = 2,   /* weight-streaming tensor-core walk, M <= 64 */
-    R3D_ARM_TILE   = 3    /* tcgen05 + TMA + TMEM walk (swap-AB), passes of <= 64 tokens */
+    R3D_ARM_TILE   = 3    /* tcgen05 + TMA + TMEM walk (swap-AB), one CTA (or cluster) per row tile */
 };
 
 /* Operands of one gemm_nt_q call. Pitches are in elements of the tensor they belong to,

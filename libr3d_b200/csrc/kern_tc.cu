@@ -74,7 +74,7 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
@@ -245,19 +245,26 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         for (int b = 0; b < kBufs; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = threadIdx.x; i < n128 * NTOK; i += kTcThreads) {
-        const int g = i / NTOK, t = i - g * NTOK;
-        as_s[i] = t < P.m ? P.as[(int64_t)t * P.as_pitch + scale_col(g, P.as_cols, n128)] : 0.0f;
-    }
+    __syncthreads();                       /* barriers are initialised: the producer may start */
+    /* The rest of the set-up overlaps the first weight loads: the MMA warp owns the TMEM
+     * allocation, the epilogue warps stage the activation scales (rows past M read as 0);
+     * the five warps then meet on a named barrier, which the producer does not wait for. */
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    } else if (warp >= 2) {
+        for (int i = threadIdx.x - 64; i < n128 * NTOK; i += 128) {
+            const int g = i / NTOK, t = i - g * NTOK;
+            as_s[i] = t < P.m ? __ldg(P.as + (int64_t)t * P.as_pitch + scale_col(g, P.as_cols, n128)) : 0.0f;
+        }
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    if (warp >= 1) {
+        tc_fence_before();
+        asm volatile("bar.sync 2, 160;" ::: "memory");
+        tc_fence_after();
+    }
+    const uint32_t tmem_base = warp >= 1 ? *tmem_slot : 0u;
 
     const int q = warp & 3;                                    /* TMEM lane quarter of an epilogue warp */
     const int row = r0 + q * 32 + lane;
@@ -269,6 +276,8 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     if (warp == 0) {
         /* ---------------- TMA producer ---------------- */
         if (elect_one()) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
             for (int it = 0; it < nk; ++it) {
                 const int s = it % kTcStages;
                 if (!mbar_wait(&empty[s], ((it / kTcStages) & 1) ^ 1, 11)) break;
@@ -319,7 +328,7 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             for (int j = 0; j < PF; ++j) {
                 const int it = blk * PF + j;
                 if (FMT == TC_FP8)
-                    sbn[j] = it < nk ? ld_scale(P.ws, srow + scale_col(it0 + it, P.ws_cols, n128), P.ws_dtype) : 0.0f;
+                    sbn[j] = it < nk ? ld_scale(P.ws, srow + scale_col((it0 + it), P.ws_cols, n128), P.ws_dtype) : 0.0f;
                 else
                     swn[j] = it < nk ? __ldg((const uint32_t*)(P.ws + srow + (it0 + it) * 4)) : 0u;
             }
@@ -467,6 +476,9 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
     if (smem > attr_set) {
         if (cudaFuncSetAttribute(k_tc_decode<FMT, NTOK, ML, kTcStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) return RAD_E_DEVICE;
+        /* ask for the largest shared-memory carve-out so that two CTAs fit on an SM */
+        (void)cudaFuncSetAttribute(k_tc_decode<FMT, NTOK, ML, kTcStages>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                   (int)cudaSharedmemCarveoutMaxShared);
         attr_set = smem;
     }
     /* K shares per row tile: enough CTAs to put two on every SM (their stage rings are the
@@ -496,9 +508,15 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
 
 template <int FMT, int NTOK, int ML>
 int launch_tc(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaStream_t st) {
-    static const int deep = [] { const char* e = getenv("R3D_TC_STAGES"); return e ? atoi(e) : 6; }();
-    if (deep >= 12) return launch_tc_s<FMT, NTOK, ML, 11>(tw, ta, P, st);
-    return launch_tc_s<FMT, NTOK, ML, 6>(tw, ta, P, st);
+    /* the deepest ring that still lets two CTAs share an SM (233472 bytes of shared memory,
+     * 1 KiB of it reserved per CTA): two CTAs' streams together are what saturates HBM */
+    const size_t fixed = 1024 + (2 * 6 + 8) * sizeof(uint64_t) + 16 + (size_t)(P.k / kStageK) * NTOK * sizeof(float);
+    const size_t stage = kABytes + NTOK * kStageK;
+    const size_t half = 233472 / 2 - 1024;
+    if (fixed + 6 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 6>(tw, ta, P, st);
+    if (fixed + 4 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 4>(tw, ta, P, st);
+    if (fixed + 3 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 3>(tw, ta, P, st);
+    return launch_tc_s<FMT, NTOK, ML, 6>(tw, ta, P, st);          /* one CTA per SM */
 }
 
 int sm_count() {

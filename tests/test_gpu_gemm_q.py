@@ -16,7 +16,7 @@ from oracle import oracle as orc
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
 EX, STREAM, TILE = abi.R3D_ARM_EXACT, abi.R3D_ARM_STREAM, abi.R3D_ARM_TILE
-FAST = [STREAM, TILE]          # the two tensor-core arms: mma.sync streaming, tcgen05
+FAST = [STREAM, TILE]          # the tensor-core arms: mma.sync streaming, tcgen05
 ODD_M = [1, 2, 3, 5, 7, 8, 9, 16, 17]
 
 
