@@ -134,6 +134,87 @@ def run_reference(args):
     }))
 
 
+def run_c5(args):
+    """LM-head logits (configuration C5): N = 151936, K = 5120, M in {1, 4, 16}, e4m3 head with a
+    bf16 scale per 128x128 block, column-sharded over the ranks (strong scaling: the head is
+    split, every rank keeps 1/G of it), f32 logits all-gathered over NCCL. One JSON line with
+    per-M times, the per-GPU HBM fraction of the GEMV alone and of GEMV + gather."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from libr3d_b200 import abi, ops, shard
+    from libr3d_b200.plugin import planes_blob
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    NV, K = 151936, 5120
+    slab = shard.slab_of(NV, world, rank)
+    rows = max(slab.rows, 128)
+    g = torch.Generator(device=dev).manual_seed(99 + rank)
+    rot = 2 if rows * K > 200e6 else 4
+    blobs = []
+    for _ in range(rot):
+        codes = torch.randint(0, 127, (rows, K), dtype=torch.uint8, device=dev, generator=g)
+        scale = (torch.rand(((rows + 127) // 128, K // 128), device=dev, generator=g) * 0.01 + 0.001).to(torch.bfloat16)
+        hb = np.frombuffer(planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), np.zeros((rows, K), np.uint8)),
+                                        ("scale", abi.RAD_BF16, (128, 128), np.zeros(tuple(scale.shape), np.uint16))]),
+                           np.uint8)
+        blob = torch.from_numpy(hb.copy()).to(dev)
+        hdr = abi.planes_round(blob.numel() - abi.planes_round(rows * K) - abi.planes_round(scale.numel() * 2))
+        blob[hdr:hdr + rows * K] = codes.flatten()
+        so = hdr + abi.planes_round(rows * K)
+        blob[so:so + scale.numel() * 2] = scale.flatten().view(torch.uint8)
+        blobs.append(blob)
+        del codes
+    res = {}
+    peak = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["hbm_gbs"] if (ROOT / "MEASURED_PEAKS.json").exists() else 6650.0
+    for M in (1, 4, 16):
+        x = torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
+        y = torch.zeros((M, slab.padded), dtype=torch.float32, device=dev)
+        yv = y[:, :rows]
+        out_all = torch.empty((world * M, slab.padded), dtype=torch.float32, device=dev)
+
+        def step(i, gather=True):
+            ops.logits_gemm(x, blobs[i % rot], yv, n_vocab=rows, n_embd=K)
+            if world > 1 and gather:
+                dist.all_gather_into_tensor(out_all, y)
+
+        times = {}
+        for gather in (False, True):
+            for i in range(args.warmup):
+                step(i, gather)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier(); torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(args.steps):
+                step(i, gather)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            if world > 1:
+                t = torch.tensor([ms], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+            times[gather] = ms / args.steps * 1e3
+        wbytes = rows * K + ((rows + 127) // 128) * (K // 128) * 2 + M * K * 2 + M * rows * 4
+        res[f"M{M}"] = {"us_gemv": times[False], "us_gemv_gather": times[True],
+                        "per_gpu_GBs_gemv": wbytes / times[False] / 1e3,
+                        "per_gpu_hbm_frac_gemv": wbytes / times[False] / 1e3 / peak,
+                        "job_GBs_with_gather": wbytes * world / times[True] / 1e3}
+    if rank == 0:
+        print(json.dumps({"metric": "LM-head logits GEMV (e4m3 head, N=151936, K=5120), column-sharded",
+                          "n_gpus": world, "scaling": "strong", "steps": args.steps, "warmup": args.warmup,
+                          "rows_per_gpu": rows, "peak_GBs": peak, "issue": "ops.logits_gemm per call (host-issued, not a graph)",
+                          "results": res}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -143,10 +224,13 @@ def main():
     ap.add_argument("--rot", type=int, default=4, help="distinct weight planes cycled (footprint > L2)")
     ap.add_argument("--row", default="gemm_nt_q_mxfp4_decode")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--workload", default="c2", help="c2 (default, the headline) or c5 (sharded LM head)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "c5":
+        return run_c5(args)
 
     import torch
     import torch.distributed as dist
@@ -174,7 +258,7 @@ def main():
         for p in range(rot):
             ops_[m, p] = ops.BoundGemm(acts[m][0], acts[m][1], planes[p][0], planes[p][1], outs[m],
                                        dtype="mxfp4a8", N=N_DIM, K=K_DIM, row=args.row)
-    gathered = {m: torch.empty((world, m, N_DIM), dtype=torch.bfloat16, device=dev) for m in MS} if world > 1 else None
+    gathered = {m: torch.empty((world * m, N_DIM), dtype=torch.bfloat16, device=dev) for m in MS} if world > 1 else None
 
     def step(i: int):
         for m in MS:

@@ -45,6 +45,7 @@ def gather_columns(y_local: torch.Tensor, n_rows: int, granule: int = 128,
     if world == 1:
         return y_local[:, :n_rows]
     buf = torch.empty((world, M, padded), dtype=y_local.dtype, device=y_local.device)
-    dist.all_gather_into_tensor(buf, y_local.contiguous(), group=group)
+    # concatenation form: [world * M, P] <- [M, P] from every rank, rank-major
+    dist.all_gather_into_tensor(buf.view(world * M, padded), y_local.contiguous(), group=group)
     # [G, M, P] -> [M, G*P]: rank-major columns are already in weight-row order
     return buf.permute(1, 0, 2).reshape(M, world * padded)[:, :n_rows]
