@@ -27,6 +27,7 @@
  * without storing.
  */
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -51,8 +52,8 @@ enum { TC_FP8 = 0, TC_MXFP4 = 1 };
 struct TcParams {
     const uint8_t* ws; int64_t ws_pitch;           /* weight scales: bf16/f32 grid or E8M0 bytes */
     const float* as; int64_t as_pitch;
-    uint16_t* y; int64_t y_pitch;
-    int m, n, k;
+    void* y; int64_t y_pitch; int y_dtype;
+    int m, mlive, n, k;                            /* m: activation rows staged; mlive: rows stored */
     int as_cols, ws_cols, rblk, ws_dtype;
     int ksplit;                                    /* CTAs per cluster = K shares per row tile */
 };
@@ -185,6 +186,7 @@ __device__ __forceinline__ void tmem_ld_wait() {
 
 __device__ __forceinline__ float ld_scale(const uint8_t* base, int64_t idx, int dt) {
     if (dt == RAD_F32) return __ldg((const float*)base + idx);
+    if (dt == RAD_F16) return __half2float(__ushort_as_half(__ldg((const unsigned short*)base + idx)));
     return bf16_to_f32(__ldg((const uint16_t*)base + idx));
 }
 __device__ __forceinline__ int scale_col(int c, int cols, int nchunk) {
@@ -212,7 +214,7 @@ __device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) 
  * epilogue actually reads and stores (M rounded up to 1, 2, 4, 8, 16, ...): the TMEM columns
  * of padding tokens are never touched. The CTAs of a cluster split K between them and the
  * leader adds the partial sums through distributed shared memory, in rank order. */
-template <int FMT, int NTOK, int ML, int kTcStages>
+template <int FMT, int NTOK, int ML, int kTcStages, int LG>
 __global__ void __launch_bounds__(kTcThreads)
 k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
             const TcParams P) {
@@ -357,7 +359,12 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
 #pragma unroll
-                    for (int t = 0; t < ML; ++t) acc[t] += (c[t] * sa[t]) * sb;
+                    for (int t = 0; t < ML; ++t) {
+                        /* logits: the piece scale is a power of two, so scaling by it last costs
+                         * no rounding and cannot overflow before the weight scale shrinks c */
+                        if (LG) acc[t] += (c[t] * sb) * sa[t];
+                        else acc[t] += (c[t] * sa[t]) * sb;
+                    }
                 } else {
                     const uint32_t sw = swc[j8];
                     float c[4][ML];
@@ -400,9 +407,21 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         }
     }
     if (warp >= 2 && crank == 0 && alive && row < P.n) {
+        if (LG) {
+            /* activation rows [0, ML/2) carry the leading piece of each token and rows
+             * [ML/2, ML) the residual piece: their sums are the token's logit */
 #pragma unroll
-        for (int t = 0; t < ML; ++t)
-            if (t < P.m) P.y[(int64_t)t * P.y_pitch + row] = f32_to_bf16(acc[t]);
+            for (int t = 0; t < ML / 2; ++t) {
+                if (t >= P.mlive) break;
+                const float v = acc[t] + acc[t + ML / 2];
+                if (P.y_dtype == RAD_F32) ((float*)P.y)[(int64_t)t * P.y_pitch + row] = v;
+                else ((uint16_t*)P.y)[(int64_t)t * P.y_pitch + row] = f32_to_bf16(v);
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < ML; ++t)
+                if (t < P.mlive) ((uint16_t*)P.y)[(int64_t)t * P.y_pitch + row] = f32_to_bf16(acc[t]);
+        }
     }
     if (ks > 1) cluster_sync_all();                           /* peers' smem was read: they may leave */
 
@@ -466,7 +485,7 @@ const CUtensorMap* tensor_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_
 
 int sm_count();
 
-template <int FMT, int NTOK, int ML, int kTcStages>
+template <int FMT, int NTOK, int ML, int kTcStages, int LG>
 int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaStream_t st) {
     const size_t smem = 1024 + (size_t)kTcStages * (kABytes + NTOK * kStageK) +
                         (2 * kTcStages + 8) * sizeof(uint64_t) + 16 +
@@ -474,10 +493,10 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
     if (smem > 220 * 1024) return RAD_E_UNSUPPORTED;
     static size_t attr_set = 0;
     if (smem > attr_set) {
-        if (cudaFuncSetAttribute(k_tc_decode<FMT, NTOK, ML, kTcStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(k_tc_decode<FMT, NTOK, ML, kTcStages, LG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) return RAD_E_DEVICE;
         /* ask for the largest shared-memory carve-out so that two CTAs fit on an SM */
-        (void)cudaFuncSetAttribute(k_tc_decode<FMT, NTOK, ML, kTcStages>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        (void)cudaFuncSetAttribute(k_tc_decode<FMT, NTOK, ML, kTcStages, LG>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                    (int)cudaSharedmemCarveoutMaxShared);
         attr_set = smem;
     }
@@ -502,21 +521,21 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
     at[0].val.clusterDim.x = (unsigned)ks; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
     count_launch();
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_decode<FMT, NTOK, ML, kTcStages>, *tw, *ta, P);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_decode<FMT, NTOK, ML, kTcStages, LG>, *tw, *ta, P);
     return e == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
 }
 
-template <int FMT, int NTOK, int ML>
+template <int FMT, int NTOK, int ML, int LG = 0>
 int launch_tc(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaStream_t st) {
     /* the deepest ring that still lets two CTAs share an SM (233472 bytes of shared memory,
      * 1 KiB of it reserved per CTA): two CTAs' streams together are what saturates HBM */
     const size_t fixed = 1024 + (2 * 6 + 8) * sizeof(uint64_t) + 16 + (size_t)(P.k / kStageK) * NTOK * sizeof(float);
     const size_t stage = kABytes + NTOK * kStageK;
     const size_t half = 233472 / 2 - 1024;
-    if (fixed + 6 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 6>(tw, ta, P, st);
-    if (fixed + 4 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 4>(tw, ta, P, st);
-    if (fixed + 3 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 3>(tw, ta, P, st);
-    return launch_tc_s<FMT, NTOK, ML, 6>(tw, ta, P, st);          /* one CTA per SM */
+    if (fixed + 6 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 6, LG>(tw, ta, P, st);
+    if (fixed + 4 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 4, LG>(tw, ta, P, st);
+    if (fixed + 3 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 3, LG>(tw, ta, P, st);
+    return launch_tc_s<FMT, NTOK, ML, 6, LG>(tw, ta, P, st);          /* one CTA per SM */
 }
 
 int sm_count() {
@@ -526,6 +545,88 @@ int sm_count() {
         return v > 0 ? v : 148;
     }();
     return n;
+}
+
+
+/* ------------------------------------------------------------------ logits: activation split
+ * The LM head multiplies bf16 activations (not quantised ones) with e4m3 codes. tcgen05 has no
+ * mixed bf16 x e4m3 kind, so each bf16 activation is written as the exact sum of two e4m3
+ * numbers on a per-(token, 128-column block) power-of-two grid:
+ *     x = s * (hi + lo / 16),   s = 2^(floor(log2(amax)) - 7)   (amax of the block -> [128, 256))
+ * hi = RNE_e4m3(x / s) keeps the leading four significant bits; the residual x/s - hi is a
+ * multiple of 2^(e-7) no larger than 2^(e-4) (e = exponent of x/s), so 16 * residual has at
+ * most four significant bits and is an e4m3 number as long as e >= -6. Elements more than
+ * 2^13 below their block's amax lose bits below amax * 2^-22; every other element is exact.
+ * hi rows and lo rows ride the MMA's N axis as separate "tokens" with scales s and s/16. */
+constexpr int kLgMaxTok = 32;                      /* tokens per pass (two piece rows each) */
+constexpr int kLgMaxK = 16384;
+__device__ __align__(256) uint8_t g_lg_pieces[2 * kLgMaxTok * kLgMaxK];
+__device__ __align__(256) float g_lg_scale[2 * kLgMaxTok * (kLgMaxK / 128)];
+
+/* one warp per (token slot t < mp, 128-column block g); slots t >= m are written as zeros */
+__global__ void __launch_bounds__(128)
+k_lg_split(const uint16_t* __restrict__ x, int64_t x_pitch, int m, int mp, int k,
+           uint8_t* __restrict__ pieces, float* __restrict__ scale) {
+    const int n128 = k / 128;
+    const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= mp * n128) return;
+    const int t = w / n128, g = w - t * n128;
+    uint8_t* hi = pieces + (int64_t)t * k + g * 128 + lane * 4;
+    uint8_t* lo = pieces + (int64_t)(mp + t) * k + g * 128 + lane * 4;
+    if (t >= m) {
+        *(uint32_t*)hi = 0u; *(uint32_t*)lo = 0u;
+        if (lane == 0) { scale[t * n128 + g] = 0.0f; scale[(mp + t) * n128 + g] = 0.0f; }
+        return;
+    }
+    const uint2 raw = __ldg((const uint2*)(x + (int64_t)t * x_pitch + g * 128 + lane * 4));
+    float v[4] = {bf16_to_f32((uint16_t)(raw.x & 0xffff)), bf16_to_f32((uint16_t)(raw.x >> 16)),
+                  bf16_to_f32((uint16_t)(raw.y & 0xffff)), bf16_to_f32((uint16_t)(raw.y >> 16))};
+    float amax = 0.0f;
+    bool finite = true;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float a = fabsf(v[i]);
+        if (a <= 3.4028234e38f) amax = fmaxf(amax, a); else finite = false;   /* false for inf, NaN */
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    int e = 0;
+    if (amax > 0.0f) { (void)frexpf(amax, &e); e -= 1; }        /* amax = f * 2^e, f in [1, 2) */
+    const int sh = amax > 0.0f ? e - 7 : 0;
+    uint32_t ph = 0, pl = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint8_t ch, cl;
+        if (!(fabsf(v[i]) <= 3.4028234e38f)) { ch = 0x7f; cl = 0; }   /* inf, NaN -> e4m3 NaN */
+        else {
+            const float xs = scalbnf(v[i], -sh);
+            ch = f32_to_e4m3(xs);
+            cl = f32_to_e4m3((xs - e4m3_to_f32(ch)) * 16.0f);
+        }
+        ph |= (uint32_t)ch << (8 * i); pl |= (uint32_t)cl << (8 * i);
+    }
+    (void)finite;
+    *(uint32_t*)hi = ph; *(uint32_t*)lo = pl;
+    if (lane == 0) {
+        scale[t * n128 + g] = scalbnf(1.0f, sh);
+        scale[(mp + t) * n128 + g] = scalbnf(1.0f, sh - 4);
+    }
+}
+
+struct LgScratch { uint8_t* pieces; float* scale; };
+/* address of the static scratch on the current device, looked up once per device */
+bool lg_scratch(LgScratch* out) {
+    static LgScratch per_dev[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (!per_dev[dev].pieces) {
+        void *p = nullptr, *q = nullptr;
+        if (cudaGetSymbolAddress(&p, g_lg_pieces) != cudaSuccess ||
+            cudaGetSymbolAddress(&q, g_lg_scale) != cudaSuccess) { (void)cudaGetLastError(); return false; }
+        per_dev[dev].pieces = (uint8_t*)p; per_dev[dev].scale = (float*)q;
+    }
+    *out = per_dev[dev];
+    return true;
 }
 
 template <int FMT, int NTOK>
@@ -563,8 +664,8 @@ int tc_fp8a8(const R3dGemmQ& p, cudaStream_t st) {
     TcParams P{};
     P.ws = (const uint8_t*)p.b_scale; P.ws_pitch = p.bs_pitch;
     P.as = p.a_scale; P.as_pitch = p.as_pitch;
-    P.y = (uint16_t*)p.y; P.y_pitch = p.y_pitch;
-    P.m = p.m; P.n = p.n; P.k = p.k;
+    P.y = p.y; P.y_pitch = p.y_pitch; P.y_dtype = RAD_BF16;
+    P.m = p.m; P.mlive = p.m; P.n = p.n; P.k = p.k;
     P.as_cols = p.as_cols; P.ws_cols = p.bs_cols; P.rblk = p.rblk; P.ws_dtype = p.bs_dtype;
     if (ntok == 16) return launch_tc_ml<TC_FP8, 16>(tw, ta, P, st);
     if (ntok == 32) return launch_tc_ml<TC_FP8, 32>(tw, ta, P, st);
@@ -581,11 +682,53 @@ int tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st) {
     TcParams P{};
     P.ws = (const uint8_t*)p.b_scale; P.ws_pitch = p.bs_pitch;
     P.as = p.a_scale; P.as_pitch = p.as_pitch;
-    P.y = (uint16_t*)p.y; P.y_pitch = p.y_pitch;
-    P.m = p.m; P.n = p.n; P.k = p.k;
+    P.y = p.y; P.y_pitch = p.y_pitch; P.y_dtype = RAD_BF16;
+    P.m = p.m; P.mlive = p.m; P.n = p.n; P.k = p.k;
     P.as_cols = p.as_cols; P.ws_cols = p.bs_cols; P.rblk = 1; P.ws_dtype = RAD_E8M0;
     if (ntok == 16) return launch_tc_ml<TC_MXFP4, 16>(tw, ta, P, st);
     return launch_tc_ml<TC_MXFP4, 32>(tw, ta, P, st);
+}
+
+bool tc_logits_ok(const R3dLogits& l) {
+    return l.head_fmt == 0 && l.m >= 1 && l.m <= kLgMaxTok && l.k >= 128 && (l.k % 128) == 0 &&
+           l.k <= kLgMaxK && (l.br == 1 || l.br == 128) && al(l.codes, 16) && (l.code_pitch % 16) == 0 &&
+           al(l.x, 8) && (l.x_pitch % 4) == 0 &&
+           (l.scale_dtype == RAD_BF16 || l.scale_dtype == RAD_F16 || l.scale_dtype == RAD_F32) &&
+           (l.y_dtype == RAD_F32 || l.y_dtype == RAD_BF16) && encode_fn() != nullptr;
+}
+
+/* Two launches: the activation split (a few microseconds of work on M x K elements), then the
+ * weight-streaming kernel with the piece rows as its "tokens". The scratch between them is a
+ * file-scope device array: calls must be ordered on one stream (or otherwise serialised). */
+int tc_logits(const R3dLogits& l, cudaStream_t st) {
+    LgScratch sc;
+    if (!lg_scratch(&sc)) return RAD_E_DEVICE;
+    const int mp = l.m <= 1 ? 1 : l.m <= 2 ? 2 : l.m <= 4 ? 4 : l.m <= 8 ? 8 : l.m <= 16 ? 16 : 32;
+    const int n128 = l.k / 128;
+    count_launch();
+    k_lg_split<<<(mp * n128 + 3) / 4, 128, 0, st>>>((const uint16_t*)l.x, l.x_pitch, l.m, mp, l.k,
+                                                    sc.pieces, sc.scale);
+    if (cudaGetLastError() != cudaSuccess) return RAD_E_DEVICE;
+    const int ntok = 2 * mp <= 16 ? 16 : 2 * mp;
+    const CUtensorMap* tw = tensor_map(l.codes, (uint64_t)l.k, (uint64_t)l.n, (uint64_t)l.code_pitch,
+                                       CU_TENSOR_MAP_DATA_TYPE_UINT8, kTileRows);
+    const CUtensorMap* ta = tensor_map(sc.pieces, (uint64_t)l.k, (uint64_t)(2 * mp), (uint64_t)l.k,
+                                       CU_TENSOR_MAP_DATA_TYPE_UINT8, (uint32_t)ntok);
+    if (!tw || !ta) return RAD_E_UNSUPPORTED;
+    TcParams P{};
+    P.ws = (const uint8_t*)l.scale; P.ws_pitch = l.scale_pitch;
+    P.as = sc.scale; P.as_pitch = n128;
+    P.y = l.y; P.y_pitch = l.y_pitch; P.y_dtype = l.y_dtype;
+    P.m = 2 * mp; P.mlive = l.m; P.n = l.n; P.k = l.k;
+    P.as_cols = n128; P.ws_cols = n128; P.rblk = l.br; P.ws_dtype = l.scale_dtype;
+    switch (mp) {
+    case 1:  return launch_tc<TC_FP8, 16, 2, 1>(tw, ta, P, st);
+    case 2:  return launch_tc<TC_FP8, 16, 4, 1>(tw, ta, P, st);
+    case 4:  return launch_tc<TC_FP8, 16, 8, 1>(tw, ta, P, st);
+    case 8:  return launch_tc<TC_FP8, 16, 16, 1>(tw, ta, P, st);
+    case 16: return launch_tc<TC_FP8, 32, 32, 1>(tw, ta, P, st);
+    default: return launch_tc<TC_FP8, 64, 64, 1>(tw, ta, P, st);
+    }
 }
 
 int tc_status() {

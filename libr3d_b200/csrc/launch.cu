@@ -148,20 +148,26 @@ extern "C" int r3d_b200_logits(const R3dLogits* l, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     int arm = l->arm;
     if (arm == R3D_ARM_AUTO) {
-        R3dLogits probe = *l; if (probe.m > 64) probe.m = 64;
-        arm = stream_logits_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+        R3dLogits probe = *l; if (probe.m > 32) probe.m = 32;
+        if (tc_logits_ok(probe)) arm = R3D_ARM_TILE;
+        else {
+            probe = *l; if (probe.m > 64) probe.m = 64;
+            arm = stream_logits_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
+        }
     }
     if (arm == R3D_ARM_EXACT) { debug_arm("logits", "exact", l->m); return exact_logits(*l, st); }
-    if (arm != R3D_ARM_STREAM) return RAD_E_UNSUPPORTED;
-    debug_arm("logits", "stream", l->m);
+    if (arm != R3D_ARM_STREAM && arm != R3D_ARM_TILE) return RAD_E_UNSUPPORTED;
+    const bool tile = arm == R3D_ARM_TILE;
+    debug_arm("logits", tile ? "tcgen05" : "stream", l->m);
     const int ysz = l->y_dtype == RAD_F32 ? 4 : 2;
-    for (int m0 = 0; m0 < l->m; m0 += 64) {
+    const int step = tile ? 32 : 64;
+    for (int m0 = 0; m0 < l->m; m0 += step) {
         R3dLogits c = *l;
-        c.m = l->m - m0 < 64 ? l->m - m0 : 64;
+        c.m = l->m - m0 < step ? l->m - m0 : step;
         c.x = (const uint16_t*)l->x + (int64_t)m0 * l->x_pitch;
         c.y = (uint8_t*)l->y + (int64_t)m0 * l->y_pitch * ysz;
-        if (!stream_logits_ok(c)) return RAD_E_UNSUPPORTED;
-        const int rc = stream_logits(c, st);
+        if (!(tile ? tc_logits_ok(c) : stream_logits_ok(c))) return RAD_E_UNSUPPORTED;
+        const int rc = tile ? tc_logits(c, st) : stream_logits(c, st);
         if (rc != RAD_OK) return rc;
     }
     return RAD_OK;

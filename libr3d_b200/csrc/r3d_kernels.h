@@ -33,6 +33,8 @@ bool tc_fp8a8_ok(const R3dGemmQ& p);
 bool tc_mxfp4a8_ok(const R3dGemmQ& p);
 int  tc_fp8a8(const R3dGemmQ& p, cudaStream_t st);
 int  tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st);
+bool tc_logits_ok(const R3dLogits& l);    /* e4m3 head, M <= 32 per pass, K <= 16384 */
+int  tc_logits(const R3dLogits& l, cudaStream_t st);
 int  tc_status();                      /* 0, or the code of a bounded wait that expired */
 
 /* int8-per-32 activation arm (kern_q8x.cu) */

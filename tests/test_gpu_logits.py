@@ -10,7 +10,7 @@ from libr3d_b200.plugin import planes_blob
 from oracle import oracle as orc
 
 pytestmark = pytest.mark.gpu
-EX, STREAM = abi.R3D_ARM_EXACT, abi.R3D_ARM_STREAM
+EX, STREAM, TILE = abi.R3D_ARM_EXACT, abi.R3D_ARM_STREAM, abi.R3D_ARM_TILE
 
 CASES = [(256, 512, 1, 128, 0), (256, 512, 3, 128, 0), (130, 300, 5, 128, 0), (256, 512, 9, 128, 0),
          (200, 512, 2, 1, 0), (256, 384, 4, 128, 1), (256, 512, 8, 128, 2), (8, 4, 1, 128, 0)]
@@ -40,6 +40,36 @@ def test_stream_arm_within_reference_tolerance(N, K, M, br, sdt):
     assert np.count_nonzero(got) > got.size * 0.9
 
 
+@pytest.mark.parametrize("N,K,M,br,sdt", [c for c in CASES if c[1] % 128 == 0] +
+                         [(1000, 1024, 16, 128, 0), (333, 640, 33, 1, 2), (512, 5120, 4, 128, 0),
+                          (700, 2048, 32, 128, 1), (129, 128, 17, 1, 0), (4096, 16384, 2, 128, 0)])
+def test_tcgen05_arm_within_reference_tolerance(N, K, M, br, sdt):
+    # bf16 activations enter as two e4m3 pieces on a power-of-two grid (exact for all but
+    # elements 2^13 below their block's amax); the grade is the reference unit test's 1e-4
+    c = gen.case_logits(11 * N + K + M, M, N, K, br, sdt)
+    want = orc.logits_e4m3(c["X"], c["codes"], c["scale"], sdt, br)
+    got = gu.logits_launch(c, TILE)
+    assert _rel(got, want.astype(np.float64)) < 2e-5
+    assert np.count_nonzero(got) > got.size * 0.9
+
+
+def test_tcgen05_arm_wide_dynamic_range_activations():
+    """activations spanning 2^-20 .. 2^20 inside one 128-column block, zeros and denormal-small
+    blocks: the split must stay within the grade and produce no NaN."""
+    N, K, M = 384, 1024, 3
+    c = gen.case_logits(4242, M, N, K, 128, 0)
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((M, K)).astype(np.float32) * np.exp2(rng.integers(-20, 21, (M, K))).astype(np.float32)
+    x[0, 128:256] = 0.0
+    x[1, 256:384] *= np.float32(2.0 ** -120)
+    x[2, 512:640] *= np.float32(2.0 ** 60)
+    c["X"] = gen.f32_to_bf16_bits(x)
+    want = orc.logits_e4m3(c["X"], c["codes"], c["scale"], 0, 128)
+    got = gu.logits_launch(c, TILE)
+    assert np.isfinite(got).all()
+    assert _rel(got, want.astype(np.float64)) < 2e-5
+
+
 def test_stream_arm_dequant_exact_incl_subnormal_and_nan_codes():
     """one-hot x = 1.0 picks each code times a power-of-two scale: results must be exact."""
     K, N = 128, 256
@@ -47,7 +77,7 @@ def test_stream_arm_dequant_exact_incl_subnormal_and_nan_codes():
     X = np.zeros((1, K), np.uint16); X[0, 7] = 0x3F80
     c = dict(X=X, codes=codes, scale=np.full((2, 1), 0x3E80, np.uint16), sdt=0, br=128)   # 0.25
     want = orc.logits_e4m3(X, codes, c["scale"], 0, 128)
-    for arm in (EX, STREAM):
+    for arm in (EX, STREAM, TILE):
         got = gu.logits_launch(c, arm)
         nan = np.isnan(want)
         assert nan.sum() == 2 and np.array_equal(np.isnan(got), nan)
@@ -77,8 +107,9 @@ def test_vocab_size_head_sampled_rows():
     scale = gen.f32_to_bf16_bits(np.exp(rng.uniform(-6, -4, ((N + 127) // 128, K // 128))).astype(np.float32))
     X = gen.f32_to_bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
     c = dict(X=X, codes=codes, scale=scale, sdt=0, br=128)
-    got = gu.logits_launch(c, STREAM)
     rows = np.concatenate([np.arange(0, 256), rng.choice(N, 256, replace=False), np.arange(N - 64, N)])
     want = orc.logits_e4m3(X, codes[rows], np.repeat(scale, 128, axis=0)[rows], 0, 1)
-    assert _rel(got[:, rows], want.astype(np.float64)) < 1e-4
-    assert np.count_nonzero(got) > got.size * 0.99
+    for arm, tol in ((STREAM, 1e-4), (TILE, 2e-5)):
+        got = gu.logits_launch(c, arm)
+        assert _rel(got[:, rows], want.astype(np.float64)) < tol, arm
+        assert np.count_nonzero(got) > got.size * 0.99
