@@ -28,7 +28,7 @@ RAD_PLANE_TILED = 1
 RAD_PLANES_MAGIC = 0x534E4C50
 RAD_PLANES_ALIGN = 256
 
-R3D_ARM_AUTO, R3D_ARM_EXACT, R3D_ARM_STREAM, R3D_ARM_TILE = 0, 1, 2, 3
+R3D_ARM_AUTO, R3D_ARM_EXACT, R3D_ARM_STREAM, R3D_ARM_TILE, R3D_ARM_PACK = 0, 1, 2, 3, 4
 
 
 class RadTensor(C.Structure):

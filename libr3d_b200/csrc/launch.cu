@@ -61,6 +61,8 @@ static int auto_arm_fp8a8(const R3dGemmQ& q) {
     return stream_fp8a8_ok(probe) ? R3D_ARM_STREAM : R3D_ARM_EXACT;
 }
 static int auto_arm_mxfp4a8(const R3dGemmQ& q) {
+    static const bool pack_off = [] { const char* e = getenv("R3D_NO_PACK"); return e && *e && *e != '0'; }();
+    if (!pack_off && tc_mxf4_ok(q)) return R3D_ARM_PACK;
     R3dGemmQ probe = q; if (probe.m > 32) probe.m = 32;
     if (tc_mxfp4a8_ok(probe)) return R3D_ARM_TILE;
     probe = q; if (probe.m > 64) probe.m = 64;
@@ -128,6 +130,11 @@ extern "C" int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream) {
     if (arm == R3D_ARM_TILE) {
         debug_arm("mxfp4a8", "tcgen05", q->m);
         return gemm_passes(*q, tc_mxfp4a8_ok, tc_mxfp4a8, st, 32);
+    }
+    if (arm == R3D_ARM_PACK) {
+        if (!tc_mxf4_ok(*q)) return RAD_E_UNSUPPORTED;
+        debug_arm("mxfp4a8", "tcgen05 packed", q->m);
+        return tc_mxf4(*q, st);
     }
     return RAD_E_UNSUPPORTED;
 }

@@ -2,6 +2,7 @@
 seeded operands, through the C ABI (launch layer with a forced arm, and the row entries with
 RadArgs). Integer/bit class where the arithmetic order is the oracle's; <= 2 bf16 ulp against
 the fp32-accumulated oracle value for the tensor-core arm."""
+import ctypes as C
 from pathlib import Path
 
 import numpy as np
@@ -16,6 +17,7 @@ from oracle import oracle as orc
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
 EX, STREAM, TILE = abi.R3D_ARM_EXACT, abi.R3D_ARM_STREAM, abi.R3D_ARM_TILE
+PACK = abi.R3D_ARM_PACK          # mxfp4a8, M <= 4: packed nibbles straight into tcgen05 kind::mxf4
 FAST = [STREAM, TILE]          # the tensor-core arms: mma.sync streaming, tcgen05
 ODD_M = [1, 2, 3, 5, 7, 8, 9, 16, 17]
 
@@ -37,7 +39,7 @@ def test_fp8_dequant_all_codes_bit_exact():
         assert gu.same_bits_or_both_nan(got, want).all(), arm
 
 
-@pytest.mark.parametrize("arm", [EX, STREAM, TILE])
+@pytest.mark.parametrize("arm", [EX, STREAM, TILE, PACK])
 def test_mxfp4_dequant_all_codes_all_scales_bit_exact(arm):
     """every e2m1 code under every E8M0 byte: y[n] = e2m1(c) * 2^(x-127), selected one-hot."""
     K = 512
@@ -123,9 +125,11 @@ def test_mxfp4_fast_arms_within_2ulp(M, arm):
     assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 3e-2, g
 
 
-@pytest.mark.parametrize("arm", [EX, STREAM, TILE])
+@pytest.mark.parametrize("arm", [EX, STREAM, TILE, PACK])
 def test_mxfp4_torture_scale_bytes_and_codes(arm):
     g = np.load(GOLD / "mxfp4a8_torture.npz")
+    if arm == PACK and (g["A"].shape[0] > 4 or g["A"].shape[1] % 512):
+        pytest.skip("packed arm: M <= 4, scale rows 16-byte aligned")
     case = dict(A=g["A"], AS=g["AS"], B=g["B"], BS=g["BS"])
     got = gu.gemm_launch("mxfp4a8", case, arm)
     want = g["Y"]
@@ -233,13 +237,88 @@ def test_rows_resolve_and_serve_mxfp4():
     assert name4 == "gemm_nt_q_mxfp4" and gu.grade_bf16(got4, acc4)["max_ulp"] <= 2
 
 
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+def test_mxfp4_packed_arm_within_2ulp(M):
+    N, K = (200, 512) if M % 2 else (136, 1536)
+    case = gen.case_mxfp4(4100 + M, M, N, K)
+    _, acc = orc.gemm_mxfp4a8(**case, want_acc=True)
+    _, ab = orc.truth_mxfp4a8(**case)
+    g = gu.grade_bf16(gu.gemm_launch("mxfp4a8", case, PACK), acc, ab)
+    assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 3e-2, g
+
+
+def test_mxfp4_packed_arm_every_activation_code_exact():
+    """The packed arm rewrites each e4m3 activation as two e2m1 pieces on one of six windows:
+    every finite e4m3 code, against a one-hot unit weight, must come back exactly."""
+    K, N = 512, 256
+    A = np.zeros((2, K), np.uint8)
+    A[0, :256] = np.arange(256); A[1, 256:] = np.arange(256)[::-1]
+    A[(A & 0x7F) == 0x7F] = 0                        # the two NaN codes are covered below
+    B = np.zeros((N, K // 2), np.uint8)
+    n = np.arange(N)
+    B[n, n // 2] = np.where(n % 2 == 0, 0x02, 0x20)  # weight row n: e2m1 1.0 at k = n
+    B[n, 128 + n // 2] |= np.where(n % 2 == 0, 0x0A, 0xA0).astype(np.uint8)   # and -1.0 at k = 256 + n
+    case = dict(A=A, AS=np.array([[1.0] * 4, [0.5] * 4], np.float32), B=B, BS=np.full((N, K // 32), 127, np.uint8))
+    want = orc.gemm_mxfp4a8(**case)
+    got = gu.gemm_launch("mxfp4a8", case, PACK)
+    assert np.array_equal(got, want)
+    assert np.count_nonzero(want & 0x7FFF) >= 2 * 250
+
+
+def test_mxfp4_packed_arm_nan_activation_poisons_its_token_only_and_leaves_no_trace():
+    case = gen.case_mxfp4(4200, 3, 200, 1024)
+    clean = gu.gemm_launch("mxfp4a8", case, PACK)
+    bad = dict(case); bad["A"] = case["A"].copy(); bad["A"][1, 777] = 0xFF
+    want = orc.gemm_mxfp4a8(**bad)
+    got = gu.gemm_launch("mxfp4a8", bad, PACK)
+    nan = lambda v: (v & 0x7FFF) > 0x7F80
+    assert nan(want[1]).all() and nan(got[1]).all()
+    assert np.array_equal(got[[0, 2]], clean[[0, 2]]) and not nan(got[[0, 2]]).any()
+    again = gu.gemm_launch("mxfp4a8", case, PACK)     # the flag of the poisoned call must be gone
+    assert np.array_equal(again, clean)
+
+
+def test_mxfp4_packed_arm_back_to_back_calls_with_rewritten_activation():
+    """The packed arm's kernels start early (programmatic stream serialisation) and order
+    themselves with griddepcontrol.wait: a chain quantise -> gemm -> quantise -> gemm ... over
+    ONE activation buffer, rewritten before every call, must see each call's own activation."""
+    M, N, K = 4, 1024, 2048
+    case = gen.case_mxfp4(4300, M, N, K)
+    B, BS = gu.dev(case["B"]), gu.dev(case["BS"])
+    rng = np.random.default_rng(3)
+    xs = [torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32) * (1 + i)).cuda().to(torch.bfloat16)
+          for i in range(12)]
+    a = torch.empty((M, K), dtype=torch.uint8, device="cuda")
+    sa = torch.empty((M, K // 128), dtype=torch.float32, device="cuda")
+    ys = [torch.zeros((M, N), dtype=torch.bfloat16, device="cuda") for _ in xs]
+    P = ops.plugin()
+    torch.cuda.synchronize()
+    for x, y in zip(xs, ys):
+        rc = P.lib.r3d_b200_quant_act_fp8(x.data_ptr(), abi.RAD_BF16, K, a.data_ptr(), K, sa.data_ptr(), K // 128,
+                                          M, K, 128, None)
+        assert rc == 0
+        q = abi.R3dGemmQ()
+        q.a, q.a_scale, q.b, q.b_scale, q.y = a.data_ptr(), sa.data_ptr(), B.data_ptr(), BS.data_ptr(), y.data_ptr()
+        q.m, q.n, q.k, q.as_cols, q.bs_cols = M, N, K, K // 128, K // 32
+        q.a_pitch, q.b_pitch, q.y_pitch, q.as_pitch, q.bs_pitch = K, K // 2, N, K // 128, K // 32
+        q.rblk, q.bs_dtype, q.arm = 1, abi.RAD_E8M0, PACK
+        assert P.lib.r3d_b200_gemm_mxfp4a8(C.byref(q), None) == 0
+    torch.cuda.synchronize()
+    for x, y in zip(xs, ys):
+        xa = x.view(torch.int16).cpu().numpy().view(np.uint16)
+        A, AS = orc.quant_act_fp8(orc.bf16_bits_to_f32(xa), 128)
+        want = orc.gemm_mxfp4a8(A=A, AS=AS, B=case["B"], BS=case["BS"])
+        d = orc.bf16_ulp_distance(y.view(torch.int16).cpu().numpy().view(np.uint16), want)
+        assert (d <= 2).mean() > 0.999, float((d <= 2).mean())
+
+
 # ------------------------------------------------------------------ benchmark sizes
 def _stream_vs_exact_full(kind, case, tol_frac=0.9995):
     """Full-size property: the tensor-core arm agrees with the oracle-order arm (itself
     bit-identical to the CPU oracle at small sizes) to 2 bf16 ulp, plus a CPU-oracle check of
     a row sample."""
     ex = gu.gemm_launch(kind, case, EX)
-    for arm in FAST:
+    for arm in FAST + ([PACK] if kind == "mxfp4a8" and case["A"].shape[0] <= 4 else []):
         st = gu.gemm_launch(kind, case, arm)
         d = orc.bf16_ulp_distance(st, ex)
         assert (d <= 2).mean() >= tol_frac, (arm, (d <= 2).mean(), int(d.max()))
