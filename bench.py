@@ -285,9 +285,11 @@ def main():
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
             graph = torch.cuda.CUDAGraph()
+            lc = P.lib.r3d_b200_launch_count()
             with torch.cuda.graph(graph, stream=s):
                 for i in range(rot):
                     step(i)
+            per_replay = P.lib.r3d_b200_launch_count() - lc     # kernels recorded in one replay
         torch.cuda.current_stream().wait_stream(s)
         replays, rem = divmod(args.steps, rot)
         for _ in range(3):
@@ -311,7 +313,9 @@ def main():
         fence()
         time.sleep(0.25)
     ms = e0.elapsed_time(e1)
-    launches = (P.lib.r3d_b200_launch_count() - l0) if graph is None else 3 * args.steps
+    launches = P.lib.r3d_b200_launch_count() - l0
+    if graph is not None:
+        launches += per_replay * replays
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -378,7 +382,7 @@ def main():
         traffic = None
         tf = ROOT / "profiles" / "traffic.json"
         if tf.exists():
-            traffic = json.loads(tf.read_text()).get("k_stream_mxfp4_c2_bytes_per_launch")
+            traffic = json.loads(tf.read_text()).get("k_tc_mxf4_c2_bytes_per_call")
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -391,7 +395,7 @@ def main():
                        "parallelism": "1 GPU" if world == 1 else f"column slabs x{world} + NCCL all_gather per call"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": which, "traffic": traffic,
-                         "kernel": "k_tc_decode<mxfp4,16,ML>", "bytes_per_launch": STEP_BYTES / 3,
+                         "kernel": "k_tc_mxf4<NP,MT> (one per call, after its k_mxf4_split)", "bytes_per_launch": STEP_BYTES / 3,
                          "us_per_launch": per_launch_s * 1e6},
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps},
