@@ -37,6 +37,7 @@ namespace r3d { __device__ int g_tc_status = 0; }   /* nonzero = code of the bou
 namespace r3d {
 
 int tc_mxf4_status();                               /* kern_tc_mxf4.cu's status word */
+int tc_gemm_status();                               /* kern_tc_gemm.cu's status word */
 
 namespace {
 
@@ -590,7 +591,9 @@ int tc_sm_count() { return sm_count(); }
 int tc_status() {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
-    return v ? v : tc_mxf4_status();
+    if (v) return v;
+    v = tc_mxf4_status();
+    return v ? v : tc_gemm_status();
 }
 
 } /* namespace r3d */

@@ -55,6 +55,11 @@ using namespace r3d;
 /* AUTO: the tcgen05 arm when the operands meet TMA's alignment rules, else the mma.sync
  * streaming arm, else the oracle-order arm (any shape, any alignment). M above one pass is
  * probed at the pass size. */
+/* R3D_NO_GEMM=1 keeps M > 64 on passes of the decode kernels (each pass re-reads the weights) */
+static bool no_gemm() {
+    static const bool off = [] { const char* e = getenv("R3D_NO_GEMM"); return e && *e && *e != '0'; }();
+    return off;
+}
 static int auto_arm_fp8a8(const R3dGemmQ& q) {
     R3dGemmQ probe = q; if (probe.m > 64) probe.m = 64;
     if (tc_fp8a8_ok(probe)) return R3D_ARM_TILE;
@@ -111,6 +116,10 @@ extern "C" int r3d_b200_gemm_fp8a8(const R3dGemmQ* q, void* stream) {
     }
     if (arm == R3D_ARM_EXACT) { debug_arm("fp8a8", "exact", q->m); return exact_fp8a8(*q, st); }
     if (arm == R3D_ARM_TILE) {
+        if (q->m > 64 && !no_gemm() && tc_gemm_fp8a8_ok(*q)) {
+            debug_arm("fp8a8", "tcgen05 tile", q->m);
+            return tc_gemm_fp8a8(*q, st);
+        }
         debug_arm("fp8a8", "tcgen05", q->m);
         return gemm_passes(*q, tc_fp8a8_ok, tc_fp8a8, st, 64);
     }
@@ -128,6 +137,10 @@ extern "C" int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream) {
     }
     if (arm == R3D_ARM_EXACT) { debug_arm("mxfp4a8", "exact", q->m); return exact_mxfp4a8(*q, st); }
     if (arm == R3D_ARM_TILE) {
+        if (q->m > 64 && !no_gemm() && tc_gemm_mxfp4a8_ok(*q)) {
+            debug_arm("mxfp4a8", "tcgen05 tile", q->m);
+            return tc_gemm_mxfp4a8(*q, st);
+        }
         debug_arm("mxfp4a8", "tcgen05", q->m);
         return gemm_passes(*q, tc_mxfp4a8_ok, tc_mxfp4a8, st, 32);
     }

@@ -39,6 +39,11 @@ int  tc_logits(const R3dLogits& l, cudaStream_t st);
  * K a multiple of 256 */
 bool tc_mxf4_ok(const R3dGemmQ& p);
 int  tc_mxf4(const R3dGemmQ& p, cudaStream_t st);
+/* prefill tile kernel (kern_tc_gemm.cu): [128 weight rows x 192 tokens] per CTA, M > 64 */
+bool tc_gemm_fp8a8_ok(const R3dGemmQ& p);
+bool tc_gemm_mxfp4a8_ok(const R3dGemmQ& p);
+int  tc_gemm_fp8a8(const R3dGemmQ& p, cudaStream_t st);
+int  tc_gemm_mxfp4a8(const R3dGemmQ& p, cudaStream_t st);
 int  tc_status();                      /* 0, or the code of a bounded wait that expired */
 
 /* int8-per-32 activation arm (kern_q8x.cu) */

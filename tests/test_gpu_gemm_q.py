@@ -312,6 +312,54 @@ def test_mxfp4_packed_arm_back_to_back_calls_with_rewritten_activation():
         assert (d <= 2).mean() > 0.999, float((d <= 2).mean())
 
 
+# ------------------------------------------------------------------ prefill band (M > 64): tile kernel
+@pytest.mark.parametrize("kind,M,N,K,grid", [
+    ("fp8a8", 100, 128, 512, "ref128"), ("fp8a8", 240, 256, 1024, "ref128"), ("fp8a8", 300, 200, 512, "row"),
+    ("fp8a8", 481, 384, 1536, "ref128"), ("fp8a8", 65, 130, 256, "channel"), ("fp8a8", 722, 1000, 2560, "ref128"),
+    ("mxfp4a8", 100, 128, 512, ""), ("mxfp4a8", 240, 256, 1024, ""), ("mxfp4a8", 300, 200, 512, ""),
+    ("mxfp4a8", 481, 384, 1536, ""), ("mxfp4a8", 722, 1000, 2560, "")])
+def test_prefill_tile_kernel_within_2ulp(kind, M, N, K, grid):
+    """[128 weight rows x 240 tokens] tcgen05 tiles with one flush per 128 of K: ragged token and row
+    tiles, one to three token tiles, both fp8 scale grids and the per-channel superset."""
+    if kind == "fp8a8":
+        case = gen.case_fp8(5000 + M, M, N, K, grid)
+        _, acc = orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], case["rblk"], want_acc=True)
+        _, ab = orc.truth_fp8a8(case["A"], case["AS"], case["B"], case["BS"], case["rblk"])
+    else:
+        case = gen.case_mxfp4(5000 + M, M, N, K)
+        _, acc = orc.gemm_mxfp4a8(**case, want_acc=True)
+        _, ab = orc.truth_mxfp4a8(**case)
+    g = gu.grade_bf16(gu.gemm_launch(kind, case, TILE), acc, ab)
+    assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 5e-3, g
+
+
+@pytest.mark.parametrize("kind,N,K", [("mxfp4a8", 27648, 5120), ("fp8a8", 5120, 13824)])
+def test_config_c4_prefill_full_size_sampled(kind, N, K):
+    """M = 8192 at the benchmark's layer geometry: the tile kernel against the CPU oracle on a
+    sample of 48 token rows x 384 weight rows (first, last and random), and nothing left unwritten."""
+    M = 8192
+    rng = np.random.default_rng(77)
+    if kind == "fp8a8":
+        case = gen.case_fp8(41, 256, N, K, "ref128")
+    else:
+        case = gen.case_mxfp4(42, 256, N, K)
+    reps = M // 256
+    case["A"] = np.ascontiguousarray(np.tile(case["A"], (reps, 1))); case["AS"] = np.ascontiguousarray(np.tile(case["AS"], (reps, 1)))
+    perm = rng.permutation(M)                         # every token row distinct in position, 256 distinct contents
+    case["A"], case["AS"] = case["A"][perm], case["AS"][perm]
+    got = gu.gemm_launch(kind, case, TILE)
+    assert np.count_nonzero(got & 0x7FFF) > got.size * 0.99
+    ts = np.concatenate([np.arange(8), np.arange(M - 8, M), rng.choice(M, 32, replace=False)])
+    ns = np.concatenate([np.arange(128), np.arange(N - 128, N), rng.choice(N, 128, replace=False)])
+    if kind == "fp8a8":
+        bs = np.repeat(case["BS"], 128, axis=0)[ns]
+        _, acc = orc.gemm_fp8a8(case["A"][ts], case["AS"][ts], case["B"][ns], bs, 1, want_acc=True)
+    else:
+        _, acc = orc.gemm_mxfp4a8(A=case["A"][ts], AS=case["AS"][ts], B=case["B"][ns], BS=case["BS"][ns], want_acc=True)
+    g = gu.grade_bf16(got[np.ix_(ts, ns)], acc)
+    assert g["frac_le2"] > 0.999 and g["rel_l2"] < 5e-3, g
+
+
 # ------------------------------------------------------------------ benchmark sizes
 def _stream_vs_exact_full(kind, case, tol_frac=0.9995):
     """Full-size property: the tensor-core arm agrees with the oracle-order arm (itself
