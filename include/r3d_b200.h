@@ -145,6 +145,36 @@ int r3d_b200_stream_status(void);
 /* Kernels this library launched since load (all arms): bench bookkeeping. */
 long long r3d_b200_launch_count(void);
 
+/* ------------------------------------------------------------------ (3) column-sharded calls
+ * No reference counterpart: the reference is single-rank (src/r3d_rows.cpp:281-284 of libr3d keeps
+ * vocab_off at 0). One process per GPU; every rank holds a contiguous slab of weight rows
+ * (= output columns) and the all-gather of the outputs is fused into the GEMV's epilogue: each
+ * rank's kernel stores its columns into the gathered [M, world * n_pad] buffer of every rank
+ * through CUDA IPC peer mappings (plain stores over NVLink), and the last CTA raises a flag.
+ *
+ *   r3d_b200_gather_create   allocate this rank's exchange buffer (slots x slot_bytes, use two
+ *                            slots alternately so a peer's next push never overwrites a result
+ *                            still being read) and export its 64-byte IPC handle
+ *   r3d_b200_gather_connect  map the peers' buffers from their handles (world x 64 bytes, rank-major;
+ *                            the caller moves handles between processes)
+ *   r3d_b200_*_push          the sharded call; output only in the gathered buffers. y of the operand
+ *                            struct is used as scratch when the serving kernel cannot push itself
+ *                            (may be NULL when the tcgen05 arms are eligible)
+ *   r3d_b200_gather_wait     enqueue the wait for every rank's push of the same call; bounded (~1 s),
+ *                            after which r3d_b200_gather_status() != 0
+ *   r3d_b200_gather_buffer   this rank's gathered buffer of a slot
+ * Ranks must issue the same sequence of push calls. */
+int   r3d_b200_gather_create(int world, int rank, int64_t slot_bytes, int slots, void** out,
+                             unsigned char handle[64]);
+int   r3d_b200_gather_connect(void* gather, const unsigned char* handles);
+void* r3d_b200_gather_buffer(void* gather, int slot);
+int   r3d_b200_gather_wait(void* gather, void* stream);
+int   r3d_b200_gather_status(void* gather);
+void  r3d_b200_gather_destroy(void* gather);
+int   r3d_b200_gemm_mxfp4a8_push(const R3dGemmQ* q, void* gather, int slot, int64_t n_pad, void* stream);
+int   r3d_b200_gemm_fp8a8_push(const R3dGemmQ* q, void* gather, int slot, int64_t n_pad, void* stream);
+int   r3d_b200_logits_push(const R3dLogits* l, void* gather, int slot, int64_t n_pad, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -33,6 +33,7 @@
 #define R3D_TC_STATUS_WORD ::r3d::g_tc_status
 namespace r3d { __device__ int g_tc_status = 0; }   /* nonzero = code of the bounded wait that expired */
 #include "tc_common.cuh"
+#include "push.cuh"
 
 namespace r3d {
 
@@ -55,6 +56,7 @@ struct TcParams {
     int m, mlive, n, k;                            /* m: activation rows staged; mlive: rows stored */
     int as_cols, ws_cols, rblk, ws_dtype;
     int ksplit;                                    /* CTAs per cluster = K shares per row tile */
+    PushCfg push;                                  /* world > 0: store into every rank's gathered buffer */
 };
 
 using namespace tcdev;
@@ -263,14 +265,27 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             for (int t = 0; t < ML / 2; ++t) {
                 if (t >= P.mlive) break;
                 const float v = acc[t] + acc[t + ML / 2];
-                if (P.y_dtype == RAD_F32) ((float*)P.y)[(int64_t)t * P.y_pitch + row] = v;
-                else ((uint16_t*)P.y)[(int64_t)t * P.y_pitch + row] = f32_to_bf16(v);
+                if (P.y_dtype == RAD_F32) {
+                    if (P.push.world) push_store<float>(P.push, t, row, v);
+                    else ((float*)P.y)[(int64_t)t * P.y_pitch + row] = v;
+                } else {
+                    if (P.push.world) push_store<uint16_t>(P.push, t, row, f32_to_bf16(v));
+                    else ((uint16_t*)P.y)[(int64_t)t * P.y_pitch + row] = f32_to_bf16(v);
+                }
             }
         } else {
 #pragma unroll
-            for (int t = 0; t < ML; ++t)
-                if (t < P.mlive) ((uint16_t*)P.y)[(int64_t)t * P.y_pitch + row] = f32_to_bf16(acc[t]);
+            for (int t = 0; t < ML; ++t) {
+                if (t >= P.mlive) break;
+                if (P.push.world) push_store<uint16_t>(P.push, t, row, f32_to_bf16(acc[t]));
+                else ((uint16_t*)P.y)[(int64_t)t * P.y_pitch + row] = f32_to_bf16(acc[t]);
+            }
         }
+    }
+    if (P.push.world) {
+        /* every CTA of the grid reports once; the last one raises this rank's flag everywhere */
+        if (warp >= 2) { __threadfence_system(); asm volatile("bar.sync 4, 128;" ::: "memory"); }
+        if (threadIdx.x == 64) push_signal(P.push);
     }
     if (ks > 1) cluster_sync_all();                           /* peers' smem was read: they may leave */
 
@@ -504,7 +519,7 @@ bool tc_mxfp4a8_ok(const R3dGemmQ& p) {
            encode_fn() != nullptr;
 }
 
-int tc_fp8a8(const R3dGemmQ& p, cudaStream_t st) {
+int tc_fp8a8(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push) {
     const int ntok = p.m <= 16 ? 16 : p.m <= 32 ? 32 : 64;
     const CUtensorMap* tw = tensor_map(p.b, (uint64_t)p.k, (uint64_t)p.n, (uint64_t)p.b_pitch,
                                        CU_TENSOR_MAP_DATA_TYPE_UINT8, kTileRows);
@@ -517,12 +532,13 @@ int tc_fp8a8(const R3dGemmQ& p, cudaStream_t st) {
     P.y = p.y; P.y_pitch = p.y_pitch; P.y_dtype = RAD_BF16;
     P.m = p.m; P.mlive = p.m; P.n = p.n; P.k = p.k;
     P.as_cols = p.as_cols; P.ws_cols = p.bs_cols; P.rblk = p.rblk; P.ws_dtype = p.bs_dtype;
+    if (push) P.push = *push;
     if (ntok == 16) return launch_tc_ml<TC_FP8, 16>(tw, ta, P, st);
     if (ntok == 32) return launch_tc_ml<TC_FP8, 32>(tw, ta, P, st);
     return launch_tc_ml<TC_FP8, 64>(tw, ta, P, st);
 }
 
-int tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st) {
+int tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push) {
     const int ntok = p.m <= 16 ? 16 : 32;
     const CUtensorMap* tw = tensor_map(p.b, (uint64_t)p.k, (uint64_t)p.n, (uint64_t)p.b_pitch,
                                        CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, kTileRows);
@@ -535,6 +551,7 @@ int tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st) {
     P.y = p.y; P.y_pitch = p.y_pitch; P.y_dtype = RAD_BF16;
     P.m = p.m; P.mlive = p.m; P.n = p.n; P.k = p.k;
     P.as_cols = p.as_cols; P.ws_cols = p.bs_cols; P.rblk = 1; P.ws_dtype = RAD_E8M0;
+    if (push) P.push = *push;
     if (ntok == 16) return launch_tc_ml<TC_MXFP4, 16>(tw, ta, P, st);
     return launch_tc_ml<TC_MXFP4, 32>(tw, ta, P, st);
 }
@@ -550,7 +567,7 @@ bool tc_logits_ok(const R3dLogits& l) {
 /* Two launches: the activation split (a few microseconds of work on M x K elements), then the
  * weight-streaming kernel with the piece rows as its "tokens". The scratch between them is a
  * file-scope device array: calls must be ordered on one stream (or otherwise serialised). */
-int tc_logits(const R3dLogits& l, cudaStream_t st) {
+int tc_logits(const R3dLogits& l, cudaStream_t st, const PushCfg* push) {
     LgScratch sc;
     if (!lg_scratch(&sc)) return RAD_E_DEVICE;
     const int mp = l.m <= 1 ? 1 : l.m <= 2 ? 2 : l.m <= 4 ? 4 : l.m <= 8 ? 8 : l.m <= 16 ? 16 : 32;
@@ -571,6 +588,7 @@ int tc_logits(const R3dLogits& l, cudaStream_t st) {
     P.y = l.y; P.y_pitch = l.y_pitch; P.y_dtype = l.y_dtype;
     P.m = 2 * mp; P.mlive = l.m; P.n = l.n; P.k = l.k;
     P.as_cols = n128; P.ws_cols = n128; P.rblk = l.br; P.ws_dtype = l.scale_dtype;
+    if (push) P.push = *push;
     switch (mp) {
     case 1:  return launch_tc<TC_FP8, 16, 2, 1>(tw, ta, P, st);
     case 2:  return launch_tc<TC_FP8, 16, 4, 1>(tw, ta, P, st);

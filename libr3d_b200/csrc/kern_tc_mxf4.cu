@@ -42,6 +42,7 @@
 #define R3D_TC_STATUS_WORD ::r3d::g_tc4_status
 namespace r3d { __device__ int g_tc4_status = 0; }
 #include "tc_common.cuh"
+#include "push.cuh"
 
 namespace r3d {
 
@@ -60,6 +61,7 @@ struct P4 {
     const uint32_t* nanflag; int nan_blocks;       /* nanflag[t * nan_blocks + b] != 0: token t held an e4m3 NaN */
     uint16_t* y; int64_t y_pitch;
     int m, n, k;
+    PushCfg push;                                  /* world > 0: store into every rank's gathered buffer */
 };
 
 /* window scales of the twelve piece rows */
@@ -315,8 +317,15 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                 uint32_t nan = 0u;
                 for (int b = 0; b < P.nan_blocks; ++b) nan |= __ldg(P.nanflag + t * P.nan_blocks + b);
                 const float v = nan ? __int_as_float(0x7fc00000) : acc[t];
-                P.y[(int64_t)t * P.y_pitch + row] = f32_to_bf16(v);
+                if (P.push.world) push_store<uint16_t>(P.push, t, row, f32_to_bf16(v));
+                else P.y[(int64_t)t * P.y_pitch + row] = f32_to_bf16(v);
             }
+        }
+        if (P.push.world) {
+            /* every CTA of the grid reports once; the last one raises this rank's flag everywhere */
+            __threadfence_system();
+            asm volatile("bar.sync 4, 128;" ::: "memory");
+            if (threadIdx.x == 64) push_signal(P.push);
         }
     }
     tc_fence_before();
@@ -437,7 +446,7 @@ bool tc_mxf4_ok(const R3dGemmQ& p) {
 
 /* Two launches: the activation split into e2m1 piece rows (file-scope device scratch: calls must
  * be ordered on one stream), then the weight-streaming kernel. */
-int tc_mxf4(const R3dGemmQ& p, cudaStream_t st) {
+int tc_mxf4(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push) {
     Scratch sc;
     if (!scratch(&sc)) return RAD_E_DEVICE;
     const int nb = (p.k / 8 + 127) / 128;
@@ -457,6 +466,7 @@ int tc_mxf4(const R3dGemmQ& p, cudaStream_t st) {
     P.nanflag = sc.nan; P.nan_blocks = nb;
     P.y = (uint16_t*)p.y; P.y_pitch = p.y_pitch;
     P.m = p.m; P.n = p.n; P.k = p.k;
+    if (push) P.push = *push;
     if (p.m == 1) return launch<16, 1>(tw, ts, tp, P, st);
     if (p.m == 2) return launch<32, 2>(tw, ts, tp, P, st);
     return launch<48, 4>(tw, ts, tp, P, st);

@@ -3,6 +3,7 @@
  * There is no CPU path: when no CUDA device of the right generation is present every call
  * returns RAD_E_UNSUPPORTED, loudly once. */
 #include "r3d_kernels.h"
+#include "push.cuh"
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -121,7 +122,7 @@ extern "C" int r3d_b200_gemm_fp8a8(const R3dGemmQ* q, void* stream) {
             return tc_gemm_fp8a8(*q, st);
         }
         debug_arm("fp8a8", "tcgen05", q->m);
-        return gemm_passes(*q, tc_fp8a8_ok, tc_fp8a8, st, 64);
+        return gemm_passes(*q, tc_fp8a8_ok, [](const R3dGemmQ& c, cudaStream_t s) { return tc_fp8a8(c, s); }, st, 64);
     }
     return RAD_E_UNSUPPORTED;
 }
@@ -142,7 +143,7 @@ extern "C" int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream) {
             return tc_gemm_mxfp4a8(*q, st);
         }
         debug_arm("mxfp4a8", "tcgen05", q->m);
-        return gemm_passes(*q, tc_mxfp4a8_ok, tc_mxfp4a8, st, 32);
+        return gemm_passes(*q, tc_mxfp4a8_ok, [](const R3dGemmQ& c, cudaStream_t s) { return tc_mxfp4a8(c, s); }, st, 32);
     }
     if (arm == R3D_ARM_PACK) {
         if (!tc_mxf4_ok(*q)) return RAD_E_UNSUPPORTED;
@@ -191,6 +192,56 @@ extern "C" int r3d_b200_logits(const R3dLogits* l, void* stream) {
         if (rc != RAD_OK) return rc;
     }
     return RAD_OK;
+}
+
+/* ---- column-sharded calls with the all-gather fused into the epilogue. The output goes to
+ * the gathered [M, world * n_pad] buffer of slot `slot` on every rank (column offset rank * n_pad);
+ * kernels that cannot push themselves (exact and streaming arms, multi-pass M) compute into
+ * the caller's y and a copy kernel pushes it. */
+extern "C" int r3d_b200_gemm_mxfp4a8_push(const R3dGemmQ* q, void* gather, int slot, int64_t n_pad, void* stream) {
+    if (!q || !gather || !device_is_sm100()) return RAD_E_UNSUPPORTED;
+    if (n_pad < q->n) return RAD_E_SHAPE;
+    PushCfg cfg;
+    if (!gather_push_cfg((const Gather*)gather, slot, n_pad, q->m, 2, &cfg)) return RAD_E_INVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (q->arm == R3D_ARM_AUTO || q->arm == R3D_ARM_PACK || q->arm == R3D_ARM_TILE) {
+        if (q->arm != R3D_ARM_TILE && tc_mxf4_ok(*q)) { debug_arm("mxfp4a8", "tcgen05 packed + push", q->m); return tc_mxf4(*q, st, &cfg); }
+        if (q->m <= 32 && tc_mxfp4a8_ok(*q)) { debug_arm("mxfp4a8", "tcgen05 + push", q->m); return tc_mxfp4a8(*q, st, &cfg); }
+    }
+    if (!q->y) return RAD_E_INVAL;
+    const int rc = r3d_b200_gemm_mxfp4a8(q, stream);
+    return rc != RAD_OK ? rc : push_copy(q->y, q->y_pitch, q->m, q->n, 2, cfg, st);
+}
+
+extern "C" int r3d_b200_gemm_fp8a8_push(const R3dGemmQ* q, void* gather, int slot, int64_t n_pad, void* stream) {
+    if (!q || !gather || !device_is_sm100()) return RAD_E_UNSUPPORTED;
+    if (n_pad < q->n) return RAD_E_SHAPE;
+    PushCfg cfg;
+    if (!gather_push_cfg((const Gather*)gather, slot, n_pad, q->m, 2, &cfg)) return RAD_E_INVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if ((q->arm == R3D_ARM_AUTO || q->arm == R3D_ARM_TILE) && q->m <= 64 && tc_fp8a8_ok(*q)) {
+        debug_arm("fp8a8", "tcgen05 + push", q->m);
+        return tc_fp8a8(*q, st, &cfg);
+    }
+    if (!q->y) return RAD_E_INVAL;
+    const int rc = r3d_b200_gemm_fp8a8(q, stream);
+    return rc != RAD_OK ? rc : push_copy(q->y, q->y_pitch, q->m, q->n, 2, cfg, st);
+}
+
+extern "C" int r3d_b200_logits_push(const R3dLogits* l, void* gather, int slot, int64_t n_pad, void* stream) {
+    if (!l || !gather || !device_is_sm100()) return RAD_E_UNSUPPORTED;
+    if (n_pad < l->n) return RAD_E_SHAPE;
+    const int ysz = l->y_dtype == RAD_F32 ? 4 : 2;
+    PushCfg cfg;
+    if (!gather_push_cfg((const Gather*)gather, slot, n_pad, l->m, ysz, &cfg)) return RAD_E_INVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if ((l->arm == R3D_ARM_AUTO || l->arm == R3D_ARM_TILE) && tc_logits_ok(*l)) {
+        debug_arm("logits", "tcgen05 + push", l->m);
+        return tc_logits(*l, st, &cfg);
+    }
+    if (!l->y) return RAD_E_INVAL;
+    const int rc = r3d_b200_logits(l, stream);
+    return rc != RAD_OK ? rc : push_copy(l->y, l->y_pitch, l->m, l->n, ysz, cfg, st);
 }
 
 extern "C" int r3d_b200_quant_act_fp8(const void* x, int32_t x_dtype, int64_t x_pitch, void* q,

@@ -7,6 +7,11 @@
 
 namespace r3d {
 
+struct PushCfg;                        /* push.cuh: fused all-gather destination, or nullptr */
+struct Gather;
+bool gather_push_cfg(const Gather* g, int slot, int64_t n_pad, int m, int elem_bytes, PushCfg* out);
+int  push_copy(const void* y, int64_t y_pitch, int m, int n, int elem_bytes, const PushCfg& g, cudaStream_t st);
+
 void count_launch(int n = 1);          /* bookkeeping behind r3d_b200_launch_count() */
 bool device_is_sm100();                /* chip gate: these kernels are built for sm_100a only */
 
@@ -31,14 +36,14 @@ int  stream_logits(const R3dLogits& p, cudaStream_t st);
  * M <= 32 (mxfp4a8) per pass */
 bool tc_fp8a8_ok(const R3dGemmQ& p);
 bool tc_mxfp4a8_ok(const R3dGemmQ& p);
-int  tc_fp8a8(const R3dGemmQ& p, cudaStream_t st);
-int  tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st);
+int  tc_fp8a8(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push = nullptr);
+int  tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push = nullptr);
 bool tc_logits_ok(const R3dLogits& l);    /* e4m3 head, M <= 32 per pass, K <= 16384 */
-int  tc_logits(const R3dLogits& l, cudaStream_t st);
+int  tc_logits(const R3dLogits& l, cudaStream_t st, const PushCfg* push = nullptr);
 /* packed-fp4 tcgen05 walk (kern_tc_mxf4.cu): kind::mxf4 with hardware group scales, M <= 4,
  * K a multiple of 256 */
 bool tc_mxf4_ok(const R3dGemmQ& p);
-int  tc_mxf4(const R3dGemmQ& p, cudaStream_t st);
+int  tc_mxf4(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push = nullptr);
 /* prefill tile kernel (kern_tc_gemm.cu): [128 weight rows x 192 tokens] per CTA, M > 64 */
 bool tc_gemm_fp8a8_ok(const R3dGemmQ& p);
 bool tc_gemm_mxfp4a8_ok(const R3dGemmQ& p);

@@ -12,6 +12,7 @@ backend for CPU tests.
 """
 from __future__ import annotations
 
+import ctypes as C
 from dataclasses import dataclass
 
 import torch
@@ -49,3 +50,55 @@ def gather_columns(y_local: torch.Tensor, n_rows: int, granule: int = 128,
     dist.all_gather_into_tensor(buf.view(world * M, padded), y_local.contiguous(), group=group)
     # [G, M, P] -> [M, G*P]: rank-major columns are already in weight-row order
     return buf.permute(1, 0, 2).reshape(M, world * padded)[:, :n_rows]
+
+
+class PushGather:
+    """The fused form of the gather: the serving kernel's epilogue stores this rank's columns
+    into every rank's [M, world * n_pad] buffer over NVLink (CUDA IPC peer mappings) and raises
+    a flag; wait() enqueues the bounded device-side wait for all ranks. Two slots are used
+    alternately by the caller so that a peer's next push never lands on a result still in use.
+
+    Construction is collective: every rank of `group` creates its buffer and the 64-byte IPC
+    handles are exchanged with all_gather_object. Needs the CUDA plugin (no CPU path)."""
+
+    def __init__(self, plugin, slot_bytes: int, slots: int = 2, group: dist.ProcessGroup | None = None):
+        self.lib = plugin.lib
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.slots, self.slot_bytes = slots, slot_bytes
+        handle = C.create_string_buffer(64)
+        ptr = C.c_void_p()
+        rc = self.lib.r3d_b200_gather_create(self.world, self.rank, slot_bytes, slots, C.byref(ptr), handle)
+        if rc != 0:
+            raise RuntimeError(f"r3d_b200_gather_create failed with status {rc}")
+        self.ptr = ptr
+        handles: list = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        rc = self.lib.r3d_b200_gather_connect(self.ptr, b"".join(handles))
+        if rc != 0:
+            raise RuntimeError(f"r3d_b200_gather_connect failed with status {rc}")
+        dist.barrier(group=group)
+
+    def buffer(self, slot: int, M: int, n_pad: int, dtype: torch.dtype) -> torch.Tensor:
+        """This rank's gathered [M, world * n_pad] view of a slot (valid after wait())."""
+        esz = torch.empty((), dtype=dtype).element_size()
+        n = M * self.world * n_pad
+        if n * esz > self.slot_bytes:
+            raise ValueError("slot too small for this shape")
+        base = self.lib.r3d_b200_gather_buffer(self.ptr, slot)
+        iface = {"shape": (n * esz,), "typestr": "|u1", "data": (int(base), False), "version": 3}
+        holder = type("_Dev", (), {"__cuda_array_interface__": iface})()
+        return torch.as_tensor(holder, device="cuda").view(dtype).view(M, self.world * n_pad)
+
+    def wait(self, stream: int | None = None) -> None:
+        st = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        rc = self.lib.r3d_b200_gather_wait(self.ptr, C.c_void_p(st))
+        if rc != 0:
+            raise RuntimeError(f"r3d_b200_gather_wait failed with status {rc}")
+
+    def status(self) -> int:
+        return int(self.lib.r3d_b200_gather_status(self.ptr))
+
+    def close(self) -> None:
+        if self.ptr:
+            self.lib.r3d_b200_gather_destroy(self.ptr)
+            self.ptr = None
