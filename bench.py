@@ -224,6 +224,8 @@ def main():
     ap.add_argument("--rot", type=int, default=4, help="distinct weight planes cycled (footprint > L2)")
     ap.add_argument("--row", default="gemm_nt_q_mxfp4_decode")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--gather", default="push", choices=["push", "nccl"],
+                    help="N > 1: all-gather fused into the GEMV epilogue (push) or NCCL after it")
     ap.add_argument("--workload", default="c2", help="c2 (default, the headline) or c5 (sharded LM head)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -259,9 +261,19 @@ def main():
             ops_[m, p] = ops.BoundGemm(acts[m][0], acts[m][1], planes[p][0], planes[p][1], outs[m],
                                        dtype="mxfp4a8", N=N_DIM, K=K_DIM, row=args.row)
     gathered = {m: torch.empty((world * m, N_DIM), dtype=torch.bfloat16, device=dev) for m in MS} if world > 1 else None
+    push = world > 1 and args.gather == "push"
+    if push:
+        # the all-gather fused into the GEMV epilogue: peer stores over NVLink + flags, two slots
+        pg = shard.PushGather(P, slot_bytes=max(MS) * world * N_DIM * 2, slots=2)
+        pushed = {(m, p): shard.PushedGemm(pg, acts[m][0], acts[m][1], planes[p][0], planes[p][1], dtype="mxfp4a8",
+                                           M=m, n_local=N_DIM, n_pad=N_DIM, K=K_DIM, scratch=outs[m])
+                  for m in MS for p in range(rot)}
 
     def step(i: int):
         for m in MS:
+            if push:
+                pushed[m, i % rot].issue(i % 2)
+                continue
             ops_[m, i % rot].issue()
             if world > 1:
                 dist.all_gather_into_tensor(gathered[m], outs[m])
@@ -275,11 +287,12 @@ def main():
     for i in range(args.warmup):
         step(i)
     fence()
-    assert int(torch.count_nonzero(outs[4].view(torch.int16))) > 0.9 * outs[4].numel()
+    probe = pushed[4, (args.warmup - 1) % rot].result((args.warmup - 1) % 2) if push else outs[4]
+    assert int(torch.count_nonzero(probe.view(torch.int16))) > 0.9 * probe.numel()
 
     # ---- device-timed region: exactly `steps` steps
     graph = None
-    if world == 1:
+    if world == 1 or push:
         # a recorded pass: `rot` steps captured once, replayed (what the engine's pass replay does)
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
@@ -339,19 +352,28 @@ def main():
         s_v = d_in[off + na:off + na + ns].view(torch.float32).view(m, K_DIM // 128)
         e2e_out[m] = d_out[row:row + m]
         for p in range(rot):
-            e2e_ops[m, p] = ops.BoundGemm(a_v, s_v, planes[p][0], planes[p][1], e2e_out[m],
-                                          dtype="mxfp4a8", N=N_DIM, K=K_DIM, row=args.row)
+            e2e_ops[m, p] = (shard.PushedGemm(pg, a_v, s_v, planes[p][0], planes[p][1], dtype="mxfp4a8", M=m,
+                                              n_local=N_DIM, n_pad=N_DIM, K=K_DIM, scratch=e2e_out[m]) if push else
+                             ops.BoundGemm(a_v, s_v, planes[p][0], planes[p][1], e2e_out[m],
+                                           dtype="mxfp4a8", N=N_DIM, K=K_DIM, row=args.row))
         off += na + ns
         row += m
     h2d, d2h = in_bytes, h_out.numel() * 2
 
     def step_e2e(i: int):
         d_in.copy_(h_in, non_blocking=True)
-        for m in MS:
-            e2e_ops[m, i % rot].issue()
-        if world > 1:
+        if push:
+            # every rank ends up with the full [m, world * N] result in its slot; the host reads
+            # back this rank's own columns of it (the same bytes per rank as at N = 1)
             for m in MS:
-                dist.all_gather_into_tensor(gathered[m], e2e_out[m])
+                e2e_ops[m, i % rot].issue(i % 2)
+                e2e_out[m].copy_(e2e_ops[m, i % rot].result(i % 2)[:, rank * N_DIM:(rank + 1) * N_DIM])
+        else:
+            for m in MS:
+                e2e_ops[m, i % rot].issue()
+            if world > 1:
+                for m in MS:
+                    dist.all_gather_into_tensor(gathered[m], e2e_out[m])
         h_out.copy_(d_out, non_blocking=True)
         torch.cuda.current_stream().synchronize()          # the caller reads the step's result
 
@@ -392,7 +414,9 @@ def main():
                        "l2": f"inputs larger than L2: {rot} rotating weight planes, "
                              f"{rot * (N_DIM * K_DIM // 2 + N_DIM * K_DIM // 32) / 1e6:.0f} MB",
                        "timed_as": "CUDA graph replay of recorded steps" if graph is not None else "direct issue",
-                       "parallelism": "1 GPU" if world == 1 else f"column slabs x{world} + NCCL all_gather per call"},
+                       "parallelism": "1 GPU" if world == 1 else
+                                      (f"column slabs x{world}, all-gather fused into the GEMV epilogue (peer stores + flags)"
+                                       if push else f"column slabs x{world} + NCCL all_gather per call")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": which, "traffic": traffic,
                          "kernel": "k_tc_mxf4<NP,MT> (one per call, after its k_mxf4_split)", "bytes_per_launch": STEP_BYTES / 3,

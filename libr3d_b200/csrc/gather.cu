@@ -15,24 +15,39 @@ namespace r3d {
 struct Gather {
     int world, rank, slots;
     int64_t slot_bytes;
-    uint8_t* local;                    /* [flags: 256 B][counter, epoch, waited, status: 256 B][slots x slot_bytes] */
+    uint8_t* local;                    /* [flag word per rank: 256 B][epoch, status: 256 B][slots x slot_bytes] */
     uint8_t* peer[kMaxRanks];          /* peer[rank] == local */
     bool opened[kMaxRanks];
 };
 
 namespace {
-constexpr int64_t kHdr = 512;
-__global__ void k_gather_wait(volatile uint32_t* flags, uint32_t* waited, int* status, int world) {
+constexpr int64_t kHdr = 512;      /* [0,256): flag word per rank; [256,512): epoch, status */
+
+struct FlagPtrs { uint32_t* p[kMaxRanks]; };
+
+/* Runs after the pushing kernel of the same call. It may be made resident early (programmatic
+ * stream serialisation) and lets its own successor be scheduled at once, but does nothing before
+ * the pushing grid has completed and flushed. Then: one system-scope fence, this rank's call
+ * count into its flag word on every rank, and a bounded wait for every rank's count. */
+__global__ void k_gather_wait(volatile uint32_t* flags, FlagPtrs mine, uint32_t* epoch, int* status, int world) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ uint32_t want;
-    if (threadIdx.x == 0) { want = *waited + 1u; *waited = want; }
+    if (threadIdx.x == 0) {
+        want = *epoch + 1u;
+        *epoch = want;
+        __threadfence_system();
+    }
     __syncthreads();
     if ((int)threadIdx.x < world) {
+        *(volatile uint32_t*)mine.p[threadIdx.x] = want;
         const long long t0 = clock64();
         while ((int)(flags[threadIdx.x] - want) < 0) {
             if (clock64() - t0 > 2000000000LL) { atomicExch(status, 1 + (int)threadIdx.x); break; }
         }
     }
-    __threadfence_system();
+    /* kernels that follow in the stream read the gathered buffer from this GPU's own memory,
+     * where the peers' stores have landed before their flag did */
 }
 } /* namespace */
 
@@ -43,10 +58,7 @@ bool gather_push_cfg(const Gather* g, int slot, int64_t n_pad, int m, int elem_b
     for (int p = 0; p < g->world; ++p) {
         if (!g->peer[p]) return false;
         c.dst[p] = g->peer[p] + kHdr + (int64_t)slot * g->slot_bytes;
-        c.flag[p] = (uint32_t*)g->peer[p] + g->rank;
     }
-    c.counter = (uint32_t*)(g->local + 256);
-    c.epoch = (uint32_t*)(g->local + 256) + 1;
     c.pitch = n_pad * g->world;
     c.col0 = n_pad * g->rank;
     c.world = g->world;
@@ -63,9 +75,7 @@ __global__ void k_push_copy(const T* __restrict__ y, int64_t y_pitch, int m, int
         const int t = (int)(i / n), c = (int)(i - (int64_t)t * n);
         push_store<T>(g, t, c, y[(int64_t)t * y_pitch + c]);
     }
-    __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0) push_signal(g);
 }
 } /* namespace */
 
@@ -137,9 +147,21 @@ int r3d_b200_gather_wait(void* gp, void* stream) {
     Gather* g = (Gather*)gp;
     if (!g) return RAD_E_INVAL;
     count_launch();
-    k_gather_wait<<<1, 32, 0, (cudaStream_t)stream>>>((volatile uint32_t*)g->local, (uint32_t*)(g->local + 256) + 2,
-                                                     (int*)(g->local + 256) + 3, g->world);
-    return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+    FlagPtrs mine{};
+    for (int p = 0; p < g->world; ++p) {
+        if (!g->peer[p]) return RAD_E_INVAL;
+        mine.p[p] = (uint32_t*)g->peer[p] + g->rank;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1); cfg.blockDim = dim3(32); cfg.dynamicSmemBytes = 0; cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    static const bool off = [] { const char* e = getenv("R3D_NO_PDL"); return e && *e && *e != '0'; }();
+    cfg.attrs = at; cfg.numAttrs = off ? 0 : 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, k_gather_wait, (volatile uint32_t*)g->local, mine,
+                                             (uint32_t*)(g->local + 256), (int*)(g->local + 256) + 1, g->world);
+    return e == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
 }
 
 /* 0, or 1 + the rank whose push did not arrive within the wait's limit (synchronises the device) */
@@ -147,7 +169,7 @@ int r3d_b200_gather_status(void* gp) {
     Gather* g = (Gather*)gp;
     if (!g) return -1;
     int v = 0;
-    if (cudaMemcpy(&v, (int*)(g->local + 256) + 3, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (cudaMemcpy(&v, (int*)(g->local + 256) + 1, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     return v;
 }
 

@@ -282,11 +282,6 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             }
         }
     }
-    if (P.push.world) {
-        /* every CTA of the grid reports once; the last one raises this rank's flag everywhere */
-        if (warp >= 2) { __threadfence_system(); asm volatile("bar.sync 4, 128;" ::: "memory"); }
-        if (threadIdx.x == 64) push_signal(P.push);
-    }
     if (ks > 1) cluster_sync_all();                           /* peers' smem was read: they may leave */
 
     tc_fence_before();

@@ -321,12 +321,6 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                 else P.y[(int64_t)t * P.y_pitch + row] = f32_to_bf16(v);
             }
         }
-        if (P.push.world) {
-            /* every CTA of the grid reports once; the last one raises this rank's flag everywhere */
-            __threadfence_system();
-            asm volatile("bar.sync 4, 128;" ::: "memory");
-            if (threadIdx.x == 64) push_signal(P.push);
-        }
     }
     tc_fence_before();
     __syncthreads();

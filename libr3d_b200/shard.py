@@ -102,3 +102,41 @@ class PushGather:
         if self.ptr:
             self.lib.r3d_b200_gather_destroy(self.ptr)
             self.ptr = None
+
+
+class PushedGemm:
+    """One column slab of an mxfp4a8 / fp8a8 gemm_nt_q band, declared once over fixed device buffers
+    and issued many times: issue(slot) launches the slab's GEMV with the all-gather fused into
+    its epilogue, then the wait; result(slot) is this rank's [M, world * n_pad] view."""
+
+    def __init__(self, pg: PushGather, a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor,
+                 b_scale: torch.Tensor, *, dtype: str, M: int, n_local: int, n_pad: int, K: int,
+                 scratch: torch.Tensor | None = None):
+        from . import abi
+        self.pg, self.M, self.n_pad = pg, M, n_pad
+        q = abi.R3dGemmQ()
+        q.a, q.a_scale, q.b, q.b_scale = a.data_ptr(), a_scale.data_ptr(), b.data_ptr(), b_scale.data_ptr()
+        q.y = scratch.data_ptr() if scratch is not None else None
+        q.m, q.n, q.k = M, n_local, K
+        q.as_cols, q.a_pitch, q.as_pitch, q.y_pitch = a_scale.shape[1], a.stride(0), a_scale.stride(0), n_local
+        if dtype == "mxfp4a8":
+            q.bs_cols, q.rblk, q.bs_dtype = K // 32, 1, abi.RAD_E8M0
+            q.b_pitch, q.bs_pitch = b.stride(0), b_scale.stride(0)
+            self._fn = pg.lib.r3d_b200_gemm_mxfp4a8_push
+        else:
+            q.bs_cols, q.bs_dtype = b_scale.shape[1], (abi.RAD_F32 if b_scale.dtype == torch.float32 else abi.RAD_BF16)
+            q.rblk = 128 if b_scale.shape[0] < n_local else 1
+            q.b_pitch, q.bs_pitch = b.stride(0), b_scale.stride(0)
+            self._fn = pg.lib.r3d_b200_gemm_fp8a8_push
+        q.arm = abi.R3D_ARM_AUTO
+        self._q, self._keep = q, (a, a_scale, b, b_scale, scratch)
+
+    def issue(self, slot: int) -> None:
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        rc = self._fn(C.byref(self._q), self.pg.ptr, slot, self.n_pad, st)
+        if rc != 0:
+            raise RuntimeError(f"sharded gemm refused with status {rc}")
+        self.pg.wait(st.value)
+
+    def result(self, slot: int) -> torch.Tensor:
+        return self.pg.buffer(slot, self.M, self.n_pad, torch.bfloat16)
