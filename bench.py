@@ -236,6 +236,139 @@ def run_c5(args):
         dist.destroy_process_group()
 
 
+def run_all(args):
+    """Every configuration of the hot path on one GPU, through the C-ABI launch layer with the
+    arm left to AUTO: C1 (fp8a8 M=1, 4096x4096), C2 (mxfp4a8 M=1,2,4), C3 (M=16 projections, both
+    formats), C4 (prefill M=8192, both formats), C5 (LM head M=1,4,16). Decode shapes rotate
+    enough distinct weight planes to exceed L2 and are timed as a replayed CUDA graph; prefill
+    calls are timed directly. One JSON line: per configuration us per call, GB/s and fraction of the
+    measured HBM peak (decode) or TFLOP/s (prefill)."""
+    import ctypes as C
+    import numpy as np
+    import torch
+    from libr3d_b200 import abi, ops
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    P = ops.plugin()
+    g = torch.Generator(device=dev).manual_seed(7)
+    peak = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["hbm_gbs"] if (ROOT / "MEASURED_PEAKS.json").exists() else 6650.0
+
+    def timed(calls, reps):
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        for fn in calls:
+            fn(st)
+        torch.cuda.synchronize()
+        graph = None
+        if len(calls) > 1:
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=s):
+                    for fn in calls:
+                        fn(C.c_void_p(torch.cuda.current_stream().cuda_stream))
+            torch.cuda.current_stream().wait_stream(s)
+            for _ in range(3):
+                graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            if graph is not None:
+                graph.replay()
+            else:
+                calls[0](st)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (reps * len(calls))
+
+    def gemm(kind, M, N, K, rot):
+        x = torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
+        A, AS = ops.quant_act_fp8(x, 128)
+        keep, calls = [], []
+        for _ in range(rot):
+            if kind == "mxfp4a8":
+                B = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=g)
+                BS = torch.randint(119, 124, (N, K // 32), dtype=torch.uint8, device=dev, generator=g)
+            else:
+                B = torch.randint(0, 127, (N, K), dtype=torch.uint8, device=dev, generator=g)
+                BS = (torch.rand(((N + 127) // 128, K // 128), device=dev, generator=g) * 0.01 + 0.001).to(torch.bfloat16)
+            Y = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
+            q = abi.R3dGemmQ()
+            q.a, q.a_scale, q.b, q.b_scale, q.y = A.data_ptr(), AS.data_ptr(), B.data_ptr(), BS.data_ptr(), Y.data_ptr()
+            q.m, q.n, q.k, q.as_cols = M, N, K, K // 128
+            q.a_pitch, q.y_pitch, q.as_pitch, q.arm = K, N, K // 128, abi.R3D_ARM_AUTO
+            if kind == "mxfp4a8":
+                q.bs_cols, q.rblk, q.bs_dtype, q.b_pitch, q.bs_pitch = K // 32, 1, abi.RAD_E8M0, K // 2, K // 32
+                fn = P.lib.r3d_b200_gemm_mxfp4a8
+            else:
+                q.bs_cols, q.rblk, q.bs_dtype, q.b_pitch, q.bs_pitch = K // 128, 128, abi.RAD_BF16, K, K // 128
+                fn = P.lib.r3d_b200_gemm_fp8a8
+            keep.append((B, BS, Y, q))
+            calls.append(lambda st, q=q, fn=fn: fn(C.byref(q), st))
+        wbytes = N * K // 2 + N * K // 32 if kind == "mxfp4a8" else N * K + ((N + 127) // 128) * (K // 128) * 2
+        return calls, keep, wbytes + M * (K + K // 128 * 4) + M * N * 2
+
+    out = []
+
+    def decode_case(cfg, kind, M, N, K):
+        wb = N * K // 2 if kind == "mxfp4a8" else N * K
+        rot = max(2, int(400e6 // wb) + 1)
+        calls, keep, nbytes = gemm(kind, M, N, K, rot)
+        us = timed(calls, max(2, 400 // rot))
+        ok = int(torch.count_nonzero(keep[0][2].view(torch.int16))) > 0.9 * M * N
+        out.append({"cfg": cfg, "band": kind, "M": M, "N": N, "K": K, "us_per_call": round(us, 2),
+                    "GBs": round(nbytes / us / 1e3, 1), "hbm_frac_of_measured": round(nbytes / us / 1e3 / peak, 3),
+                    "planes": rot, "nonzero_ok": ok})
+        del calls, keep
+        torch.cuda.empty_cache()
+
+    decode_case("C1", "fp8a8", 1, 4096, 4096)
+    for M in (1, 2, 4):
+        decode_case("C2", "mxfp4a8", M, 27648, 5120)
+    for kind in ("fp8a8", "mxfp4a8"):
+        for (K, N) in ((5120, 6144), (5120, 5120), (5120, 27648), (13824, 5120)):
+            decode_case("C3", kind, 16, N, K)
+    for kind in ("fp8a8", "mxfp4a8"):
+        for (K, N) in ((5120, 27648), (13824, 5120)):
+            calls, keep, _ = gemm(kind, 8192, N, K, 1)
+            us = timed(calls, 5)
+            out.append({"cfg": "C4", "band": kind, "M": 8192, "N": N, "K": K, "us_per_call": round(us, 1),
+                        "TFLOPs": round(2 * 8192 * N * K / us / 1e6, 1),
+                        "nonzero_ok": int(torch.count_nonzero(keep[0][2].view(torch.int16))) > 0.9 * 8192 * N})
+            del calls, keep
+            torch.cuda.empty_cache()
+    # C5: e4m3 head with a bf16 scale per 128x128 block, f32 logits
+    NV, K = 151936, 5120
+    heads = []
+    for _ in range(2):
+        codes = torch.randint(0, 127, (NV, K), dtype=torch.uint8, device=dev, generator=g)
+        scale = (torch.rand(((NV + 127) // 128, K // 128), device=dev, generator=g) * 0.01 + 0.001).to(torch.bfloat16)
+        heads.append((codes, scale))
+    for M in (1, 4, 16):
+        x = torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
+        y = torch.zeros((M, NV), dtype=torch.float32, device=dev)
+        ls = []
+        for codes, scale in heads:
+            l = abi.R3dLogits()
+            l.x, l.codes, l.scale, l.y = x.data_ptr(), codes.data_ptr(), scale.data_ptr(), y.data_ptr()
+            l.m, l.n, l.k, l.br = M, NV, K, 128
+            l.scale_dtype, l.y_dtype, l.head_fmt, l.arm = abi.RAD_BF16, abi.RAD_F32, 0, abi.R3D_ARM_AUTO
+            l.x_pitch, l.code_pitch, l.y_pitch, l.scale_pitch = K, K, NV, K // 128
+            ls.append(l)
+        calls = [lambda st, l=l: P.lib.r3d_b200_logits(C.byref(l), st) for l in ls]
+        us = timed(calls, 20)
+        nbytes = NV * K + ((NV + 127) // 128) * (K // 128) * 2 + M * K * 2 + M * NV * 4
+        out.append({"cfg": "C5", "band": "logits e4m3", "M": M, "N": NV, "K": K, "us_per_call": round(us, 1),
+                    "GBs": round(nbytes / us / 1e3, 1), "hbm_frac_of_measured": round(nbytes / us / 1e3 / peak, 3),
+                    "planes": 2, "nonzero_ok": int(torch.count_nonzero(y)) > 0.9 * M * NV})
+    for r in out:
+        sys.stderr.write(json.dumps(r) + "\n")
+    print(json.dumps({"workload": "all", "n_gpus": 1, "peak_GBs": peak, "peak_source": "measured", "timed_as":
+                      "CUDA graph replay over rotating weight planes (decode), direct calls (prefill)",
+                      "status": int(P.lib.r3d_b200_stream_status()), "results": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -247,13 +380,15 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--gather", default="push", choices=["push", "nccl"],
                     help="N > 1: all-gather fused into the GEMV epilogue (push) or NCCL after it")
-    ap.add_argument("--workload", default="c2", help="c2 (default, the headline) or c5 (sharded LM head)")
+    ap.add_argument("--workload", default="c2", help="c2 (default, the headline), c5 (sharded LM head) or all (every configuration, one GPU)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference(args)
     if args.workload == "c5":
         return run_c5(args)
+    if args.workload == "all":
+        return run_all(args)
 
     import torch
     import torch.distributed as dist

@@ -167,6 +167,9 @@ long long r3d_b200_launch_count(void);
 int   r3d_b200_gather_create(int world, int rank, int64_t slot_bytes, int slots, void** out,
                              unsigned char handle[64]);
 int   r3d_b200_gather_connect(void* gather, const unsigned char* handles);
+/* same-process peers: the peer's r3d_b200_gather_base() instead of an IPC handle */
+int   r3d_b200_gather_connect_ptr(void* gather, int peer, void* base);
+void* r3d_b200_gather_base(void* gather);
 void* r3d_b200_gather_buffer(void* gather, int slot);
 int   r3d_b200_gather_wait(void* gather, void* stream);
 int   r3d_b200_gather_status(void* gather);

@@ -135,6 +135,17 @@ int r3d_b200_gather_connect(void* gp, const unsigned char* handles) {
     return RAD_OK;
 }
 
+/* A peer that lives in the same process (one process driving several GPUs with peer access
+ * enabled, or a test): hand over the base pointer of its exchange buffer instead of a handle. */
+int r3d_b200_gather_connect_ptr(void* gp, int peer, void* base) {
+    Gather* g = (Gather*)gp;
+    if (!g || !base || peer < 0 || peer >= g->world || peer == g->rank) return RAD_E_INVAL;
+    g->peer[peer] = (uint8_t*)base; g->opened[peer] = false;
+    return RAD_OK;
+}
+
+void* r3d_b200_gather_base(void* gp) { return gp ? ((Gather*)gp)->local : nullptr; }
+
 /* this rank's gathered buffer of a slot: [M, world * n_pad] elements once all ranks have pushed */
 void* r3d_b200_gather_buffer(void* gp, int slot) {
     Gather* g = (Gather*)gp;

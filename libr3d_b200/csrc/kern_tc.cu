@@ -99,6 +99,7 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();                       /* barriers are initialised: the producer may start */
+    dep_launch();                          /* the next kernel of the stream may begin its own prologue */
     /* The rest of the set-up overlaps the first weight loads: the MMA warp owns the TMEM
      * allocation, the epilogue warps stage the activation scales (rows past M read as 0);
      * the five warps then meet on a named barrier, which the producer does not wait for. */
@@ -107,6 +108,7 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                      ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     } else if (warp >= 2) {
+        dep_wait();                        /* activation scales are the previous kernel's output */
         for (int i = threadIdx.x - 64; i < n128 * NTOK; i += 128) {
             const int g = i / NTOK, t = i - g * NTOK;
             as_s[i] = t < P.m ? __ldg(P.as + (int64_t)t * P.as_pitch + scale_col(g, P.as_cols, n128)) : 0.0f;
@@ -131,6 +133,10 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         if (elect_one()) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+            /* Weights depend on nothing that runs before this kernel: the first ring of weight
+             * tiles is requested at once. Activation tiles are the previous kernel's output and
+             * are requested after dep_wait(); they complete the same stage barriers. */
+            const int first = nk < kTcStages ? nk : kTcStages;
             for (int it = 0; it < nk; ++it) {
                 const int s = it % kTcStages;
                 if (!mbar_wait(&empty[s], ((it / kTcStages) & 1) ^ 1, 11)) break;
@@ -139,7 +145,13 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                  * bytes it wrote */
                 mbar_expect_tx(&full[s], (uint32_t)((FMT == TC_MXFP4 ? kABytes / 2 : kABytes) + kBBytes));
                 tma_load_2d(st, &tmW, (it0 + it) * kStageK, r0, &full[s]);
-                tma_load_2d(st + kABytes, &tmA, (it0 + it) * kStageK, 0, &full[s]);
+                if (it == first - 1) {
+                    dep_wait();
+                    for (int j = 0; j < first; ++j)
+                        tma_load_2d(smem + j * kStage + kABytes, &tmA, (it0 + j) * kStageK, 0, &full[j]);
+                } else if (it >= first) {
+                    tma_load_2d(st + kABytes, &tmA, (it0 + it) * kStageK, 0, &full[s]);
+                }
             }
         }
     } else if (warp == 1) {
@@ -376,10 +388,12 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
     cfg.blockDim = dim3(kTcThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = (unsigned)ks; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = tc_pdl_on() ? 2 : 1;
     count_launch();
     const cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_decode<FMT, NTOK, ML, kTcStages, LG>, *tw, *ta, P);
     return e == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
@@ -427,6 +441,9 @@ __device__ __align__(256) float g_lg_scale[2 * kLgMaxTok * (kLgMaxK / 128)];
 __global__ void __launch_bounds__(128)
 k_lg_split(const uint16_t* __restrict__ x, int64_t x_pitch, int m, int mp, int k,
            uint8_t* __restrict__ pieces, float* __restrict__ scale) {
+    dep_launch();
+    dep_wait();                    /* x is the previous kernel's output; the previous reader of the
+                                      piece rows must have finished */
     const int n128 = k / 128;
     const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (w >= mp * n128) return;
@@ -568,9 +585,16 @@ int tc_logits(const R3dLogits& l, cudaStream_t st, const PushCfg* push) {
     const int mp = l.m <= 1 ? 1 : l.m <= 2 ? 2 : l.m <= 4 ? 4 : l.m <= 8 ? 8 : l.m <= 16 ? 16 : 32;
     const int n128 = l.k / 128;
     count_launch();
-    k_lg_split<<<(mp * n128 + 3) / 4, 128, 0, st>>>((const uint16_t*)l.x, l.x_pitch, l.m, mp, l.k,
-                                                    sc.pieces, sc.scale);
-    if (cudaGetLastError() != cudaSuccess) return RAD_E_DEVICE;
+    {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)((mp * n128 + 3) / 4)); cfg.blockDim = dim3(128); cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = tc_pdl_on() ? 1 : 0;
+        if (cudaLaunchKernelEx(&cfg, k_lg_split, (const uint16_t*)l.x, (int64_t)l.x_pitch, (int)l.m, mp, (int)l.k,
+                               sc.pieces, sc.scale) != cudaSuccess) return RAD_E_DEVICE;
+    }
     const int ntok = 2 * mp <= 16 ? 16 : 2 * mp;
     const CUtensorMap* tw = tensor_map(l.codes, (uint64_t)l.k, (uint64_t)l.n, (uint64_t)l.code_pitch,
                                        CU_TENSOR_MAP_DATA_TYPE_UINT8, kTileRows);
@@ -600,6 +624,10 @@ const CUtensorMap* tc_tensor_map(const void* ptr, uint64_t d0, uint64_t d1, uint
 }
 bool tc_have_encoder() { return encode_fn() != nullptr; }
 int tc_sm_count() { return sm_count(); }
+bool tc_pdl_on() {
+    static const bool off = [] { const char* e = getenv("R3D_NO_PDL"); return e && *e && *e != '0'; }();
+    return !off;
+}
 
 int tc_status() {
     int v = 0;

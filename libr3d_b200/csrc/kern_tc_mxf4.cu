@@ -101,12 +101,6 @@ __device__ __forceinline__ void umma_mxf4(uint32_t d_tmem, uint64_t adesc, uint6
         "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate) : "memory");
 }
-/* Programmatic dependent launch: the next kernel in the stream may start its own prologue as
- * soon as every CTA of this grid has said so; a kernel reads what its predecessor wrote only
- * after dep_wait(), which returns once the predecessor has completed and flushed. */
-__device__ __forceinline__ void dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
 constexpr int kScTiles = 3;                        /* ring of weight-scale tiles (4 stages each) */
 constexpr int kScBytes = kRows * 32;
 

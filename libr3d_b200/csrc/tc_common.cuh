@@ -167,8 +167,17 @@ __device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) 
     return v;
 }
 
+/* Programmatic dependent launch: the next kernel in the stream may start its own prologue as
+ * soon as every CTA of this grid has said so; a kernel reads what its predecessor wrote only
+ * after dep_wait(), which returns once the predecessor has completed and flushed. */
+__device__ __forceinline__ void dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+
+/* true unless R3D_NO_PDL is set: kernels are launched with programmatic stream serialisation */
 } /* namespace tcdev */
+
+bool tc_pdl_on();
 
 /* host side (kern_tc.cu): cached 2-D tensor maps, box = box0 x box1 elements; an inner box of 128
  * elements gets the 128-byte swizzle, any other none */

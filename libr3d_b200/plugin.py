@@ -30,7 +30,7 @@ EXPORTS = [
     "r3d_b200_logits", "r3d_b200_quant_act_fp8", "r3d_b200_pick_arm_fp8a8",
     "r3d_b200_pick_arm_mxfp4a8", "r3d_b200_launch_count", "r3d_b200_stream_status",
     "r3d_b200_gather_create", "r3d_b200_gather_connect", "r3d_b200_gather_buffer", "r3d_b200_gather_wait",
-    "r3d_b200_gather_status", "r3d_b200_gather_destroy", "r3d_b200_gemm_mxfp4a8_push",
+    "r3d_b200_gather_status", "r3d_b200_gather_destroy", "r3d_b200_gather_connect_ptr", "r3d_b200_gather_base", "r3d_b200_gemm_mxfp4a8_push",
     "r3d_b200_gemm_fp8a8_push", "r3d_b200_logits_push",
 ]
 
@@ -99,6 +99,9 @@ class Plugin:
         L.r3d_b200_gather_status.argtypes = [C.c_void_p]
         L.r3d_b200_gather_destroy.argtypes = [C.c_void_p]
         L.r3d_b200_gather_destroy.restype = None
+        L.r3d_b200_gather_connect_ptr.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.r3d_b200_gather_base.argtypes = [C.c_void_p]
+        L.r3d_b200_gather_base.restype = C.c_void_p
         for f in ("r3d_b200_gemm_mxfp4a8_push", "r3d_b200_gemm_fp8a8_push"):
             getattr(L, f).argtypes = [C.POINTER(abi.R3dGemmQ), C.c_void_p, C.c_int, C.c_int64, C.c_void_p]
         L.r3d_b200_logits_push.argtypes = [C.POINTER(abi.R3dLogits), C.c_void_p, C.c_int, C.c_int64, C.c_void_p]
