@@ -32,6 +32,11 @@ int r3d_rad_gemm_nt_q_fp8(const RadArgs* a, RadStream s);
 /* gemm_nt_q @ fp8a8, decode band M <= 8. Replaces r3d_rad_gemm_nt_q_fp8_decode
  * (src/r3d_gemm_fp8a8.hip:1098-1130). */
 int r3d_rad_gemm_nt_q_fp8_decode(const RadArgs* a, RadStream s);
+/* gemm_nt_q_gated @ fp8a8, M <= 64: the fp8a8 band into the launch scratch plus the gated
+ * activation quantiser. Replaces r3d_rad_gemm_nt_q_gated_fp8 and its scratch hook
+ * (src/r3d_gemm_fp8a8.hip:1167-1253). */
+int r3d_rad_gemm_nt_q_gated_fp8(const RadArgs* a, RadStream s);
+int64_t r3d_rad_gemm_nt_q_gated_fp8_scratch(const RadArgs* a);
 /* gemm_nt_q @ mxfp4a8, any M. Replaces r3d_rad_gemm_nt_q
  * (src/r3d_gemm_mxfp4.hip:1587-1691). */
 int r3d_rad_gemm_nt_q(const RadArgs* a, RadStream s);
@@ -140,6 +145,11 @@ int r3d_b200_pick_arm_mxfp4a8(const R3dGemmQ* q);
 /* 0 when no bounded device-side wait of the streaming arm has ever expired in this process;
  * otherwise the code of the wait that gave up (1 producer, 2 consumer). The affected launch
  * stored nothing. No counterpart in the reference (its kernels have no device-side waits). */
+/* The gated activation quantiser on its own (the reference's gated_quant_fp8 arithmetic,
+ * src/r3d_band.hip:167-235, over a bf16 gate_up plane [rows, 2n], pitches in elements). */
+int r3d_b200_gated_quant_fp8(const void* gu, int64_t gu_pitch, void* q, int64_t q_pitch, float* scale,
+                             int64_t s_pitch, void* ob, int32_t ob_dtype, int64_t ob_pitch, int32_t rows,
+                             int32_t n, int32_t group, int32_t silu, void* stream);
 int r3d_b200_stream_status(void);
 
 /* Kernels this library launched since load (all arms): bench bookkeeping. */

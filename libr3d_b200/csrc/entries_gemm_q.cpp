@@ -265,6 +265,70 @@ int r3d_rad_gemm_nt_q_mxfp4_decode_q8x(const RadArgs* a, RadStream s) {
     return run_mxfp4_decode(a, s, true);
 }
 
+/* gemm_nt_q_gated @ fp8a8 (src/r3d_gemm_fp8a8.hip:1167-1253 of libr3d): operands a, a_scale, b, b_scale,
+ * q (e4m3 [M, n]), scale (f32 [M, n/group]), out_bf16 (optional, bf16 or f32), a_sum (refused). The
+ * [2n, K] gate_up weight's product lands as bf16 [M, 2n] in the launch scratch, then the gated
+ * quantiser reads it: byte-identical to gemm_nt_q followed by gated_quant_fp8, because it is that
+ * pair. M = numel(q) / n; `act` is required; the arena (64 * N * 2 bytes, the scratch hook) is
+ * checked, never overrun. */
+int r3d_rad_gemm_nt_q_gated_fp8(const RadArgs* a, RadStream s) {
+    static const bool off = env_present("R3D_NO_FP8A8");
+    if (off) return RAD_E_UNSUPPORTED;
+    const RadTensor* A = rad_arg_in(a, 0);
+    const RadTensor* AS = rad_arg_in(a, 1);
+    const RadTensor* B = rad_arg_in(a, 2);
+    const RadTensor* BS = rad_arg_in(a, 3);
+    const RadTensor* Q = rad_arg_in(a, 4);
+    const RadTensor* SC = rad_arg_in(a, 5);
+    const RadTensor* OB = rad_arg_in(a, 6);
+    if (!A || !AS || !B || !BS || !Q || !SC) return RAD_E_UNSUPPORTED;
+    if (rad_arg_in(a, 7)) return RAD_E_UNSUPPORTED;                       /* a_sum */
+    if (Q->dtype != RAD_F8E4M3 || SC->dtype != RAD_F32) return RAD_E_UNSUPPORTED;
+    if (OB && OB->dtype != RAD_BF16 && OB->dtype != RAD_F32) return RAD_E_UNSUPPORTED;
+    const char* act = rad_args_gets(a, "act");
+    if (!act) return RAD_E_UNSUPPORTED;
+    const int silu = strcmp(act, "sigmoid") != 0;
+    if (silu && strcmp(act, "silu") != 0) return RAD_E_UNSUPPORTED;
+
+    long long N = 0;
+    if (!rad_args_geti(a, "N", &N) || N <= 0 || (N & 1)) return RAD_E_SHAPE;
+    const long long n = N / 2;
+    long long g = 0;
+    if (!rad_args_geti(a, "group", &g) || g <= 0) g = n;
+    if (g > n) g = n;
+    const long long ngrp = (n + g - 1) / g;
+    const long long Qn = rad_tensor_numel(Q);
+    if (Qn <= 0 || Qn % n) return RAD_E_SHAPE;
+    const long long M = Qn / n;
+    if (rad_tensor_numel(SC) < M * ngrp) return RAD_E_SHAPE;
+    if (OB && rad_tensor_numel(OB) < M * n) return RAD_E_SHAPE;
+
+    const int64_t need = M * N * (int64_t)sizeof(uint16_t);
+    RadTensor plane{};                                  /* the gate_up product, bf16 [M, N] in the arena */
+    plane.data = a->scratch; plane.dtype = RAD_BF16; plane.rank = 2;
+    plane.shape[0] = M; plane.shape[1] = N; plane.stride[0] = N; plane.stride[1] = 1;
+    R3dGemmQ q{};
+    /* the plain row's plan on the same operands; its "group" rule (128 of K) is the gated row's
+     * constraint too, while `g` above is the quantiser's own group over n */
+    const int rc = plan_fp8a8(a, A, AS, B, BS, &plane, M, N, &q);
+    if (rc != RAD_OK) return rc;
+    if (!a->scratch || a->scratch_bytes < need) return RAD_E_UNSUPPORTED;
+    if (!inner_contiguous(Q) || !inner_contiguous(SC) || (OB && !inner_contiguous(OB))) return RAD_E_STRIDE;
+
+    const int rg = r3d_b200_gemm_fp8a8(&q, (void*)s);
+    if (rg != RAD_OK) return rg;
+    return r3d_b200_gated_quant_fp8(a->scratch, N, Q->data, row_pitch(Q, n), (float*)SC->data, row_pitch(SC, ngrp),
+                                    OB ? OB->data : nullptr, OB ? (int32_t)OB->dtype : RAD_BF16,
+                                    OB ? row_pitch(OB, n) : 0, (int32_t)M, (int32_t)n, (int32_t)g, silu, (void*)s);
+}
+
+/* the arena of the fused row: the [M, N] bf16 plane at the band's M bound (M <= 64) */
+int64_t r3d_rad_gemm_nt_q_gated_fp8_scratch(const RadArgs* a) {
+    long long N = 0;
+    if (!rad_args_geti(a, "N", &N) || N <= 0 || N > (1LL << 34)) return 0;
+    return 64 * N * (int64_t)sizeof(uint16_t);
+}
+
 bool r3d_mxfp4_q8x_off(void) {
     static const bool off = env_is_zero("R3D_MXFP4_Q8X");
     return off;

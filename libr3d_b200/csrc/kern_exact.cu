@@ -257,6 +257,63 @@ __global__ __launch_bounds__(128) void k_quant_act_fp8(
     }
 }
 
+/* ------------------------------------------------------------------ gated activation quantiser
+ * The epilogue of gemm_nt_q_gated (src/r3d_gemm_fp8a8.hip:700-825 of libr3d, itself
+ * src/r3d_band.hip:167-235): one block per row of the bf16 gate_up plane [M, 2n], gate half
+ * first; per group of <= g columns the gated value h = bf16((silu ? gt*sg : sg) * up),
+ * sg = 1/(1 + (float)exp((double)-gt)), its amax (strict >, NaN never wins), the dequant scale
+ * amax/448 and the saturating RTNE e4m3 codes of h/scale. */
+__global__ __launch_bounds__(256) void k_gated_quant_fp8(
+    const uint16_t* __restrict__ gu, const int64_t gu_pitch, uint8_t* __restrict__ q, const int64_t q_pitch,
+    float* __restrict__ scale, const int64_t s_pitch, void* __restrict__ ob, const int ob_dtype,
+    const int64_t ob_pitch, const int n, const int g, const int ngrp, const int silu) {
+    __shared__ float red[8];
+    __shared__ float s_sc;
+    const int64_t row = blockIdx.x;
+    const uint16_t* gr = gu + row * gu_pitch;
+    auto gated = [&](int i) -> float {
+        const float gt = bf16_to_f32(gr[i]), up = bf16_to_f32(gr[n + i]);
+        const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, (float)exp((double)(-gt))));
+        const float a = silu ? __fmul_rn(gt, sg) : sg;
+        return bf16_to_f32(f32_to_bf16(__fmul_rn(a, up)));
+    };
+    for (int gi = 0; gi < ngrp; ++gi) {
+        const int k0 = gi * g, k1 = min(k0 + g, n);
+        float amax = 0.0f;
+        for (int i = k0 + threadIdx.x; i < k1; i += 256) {
+            const float m = fabsf(gated(i));
+            if (m > amax) amax = m;
+        }
+        for (int off = 16; off; off >>= 1) {
+            const float o = __shfl_xor_sync(0xffffffffu, amax, off);
+            if (o > amax) amax = o;
+        }
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float r = red[0];
+            for (int w = 1; w < 8; ++w) if (red[w] > r) r = red[w];
+            const float sc = r > 0.0f ? __fmul_rn(r, 1.0f / 448.0f) : 1.0f;
+            s_sc = sc;
+            scale[row * s_pitch + gi] = sc;
+        }
+        __syncthreads();
+        const float inv = __fdiv_rn(1.0f, s_sc);
+        for (int i = k0 + threadIdx.x; i < k1; i += 256) {
+            const float h = gated(i);
+            if (ob) {
+                if (ob_dtype == RAD_F32) ((float*)ob)[row * ob_pitch + i] = h;
+                else ((uint16_t*)ob)[row * ob_pitch + i] = f32_to_bf16(h);
+            }
+            float c = __fmul_rn(h, inv);
+            if (c > 448.0f) c = 448.0f;
+            if (c < -448.0f) c = -448.0f;
+            q[row * q_pitch + i] = f32_to_e4m3(c);
+        }
+        __syncthreads();                              /* s_sc is reused by the next group */
+    }
+}
+
 /* ------------------------------------------------------------------ launchers */
 
 template <typename P, typename F>
@@ -320,6 +377,17 @@ int launch_quant_act_fp8(const void* x, int x_dtype, int64_t x_pitch, void* q, i
     count_launch();
     k_quant_act_fp8<<<(unsigned)(rows * ngrp), 128, 0, st>>>(
         x, x_dtype, x_pitch, (uint8_t*)q, q_pitch, scale, s_pitch, n, group, ngrp);
+    return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+}
+
+int launch_gated_quant_fp8(const void* gu, int64_t gu_pitch, void* q, int64_t q_pitch, float* scale,
+                           int64_t s_pitch, void* ob, int ob_dtype, int64_t ob_pitch, int rows, int n, int g,
+                           int silu, cudaStream_t st) {
+    if (g <= 0 || g > n) g = n;
+    const int ngrp = (n + g - 1) / g;
+    count_launch();
+    k_gated_quant_fp8<<<(unsigned)rows, 256, 0, st>>>((const uint16_t*)gu, gu_pitch, (uint8_t*)q, q_pitch, scale,
+                                                      s_pitch, ob, ob_dtype, ob_pitch, n, g, ngrp, silu);
     return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
 }
 

@@ -253,3 +253,16 @@ extern "C" int r3d_b200_quant_act_fp8(const void* x, int32_t x_dtype, int64_t x_
     return launch_quant_act_fp8(x, x_dtype, x_pitch, q, q_pitch, scale, s_pitch, rows, n, group,
                                 (cudaStream_t)stream);
 }
+
+/* gate_up bf16 [rows, 2n] (pitch in elements) -> e4m3 codes [rows, n], f32 scale per (row, group of g),
+ * optional gated product `ob` (bf16 or f32): the quantiser that closes gemm_nt_q_gated. */
+extern "C" int r3d_b200_gated_quant_fp8(const void* gu, int64_t gu_pitch, void* q, int64_t q_pitch,
+                                        float* scale, int64_t s_pitch, void* ob, int32_t ob_dtype,
+                                        int64_t ob_pitch, int32_t rows, int32_t n, int32_t group, int32_t silu,
+                                        void* stream) {
+    if (!gu || !q || !scale || rows <= 0 || n <= 0) return RAD_E_INVAL;
+    if (ob && ob_dtype != RAD_BF16 && ob_dtype != RAD_F32) return RAD_E_DTYPE;
+    if (!device_is_sm100()) return RAD_E_UNSUPPORTED;
+    return launch_gated_quant_fp8(gu, gu_pitch, q, q_pitch, scale, s_pitch, ob, ob_dtype, ob_pitch, rows, n,
+                                  group, silu, (cudaStream_t)stream);
+}

@@ -23,6 +23,10 @@ int launch_quant_act_fp8(const void* x, int x_dtype, int64_t x_pitch, void* q, i
                          float* scale, int64_t s_pitch, int rows, int n, int group,
                          cudaStream_t st);
 
+int launch_gated_quant_fp8(const void* gu, int64_t gu_pitch, void* q, int64_t q_pitch, float* scale,
+                           int64_t s_pitch, void* ob, int ob_dtype, int64_t ob_pitch, int rows, int n, int g,
+                           int silu, cudaStream_t st);
+
 /* weight-streaming tensor-core arm (kern_stream.cu); *_ok say whether the arm can take
  * the call's shape and alignment */
 bool stream_fp8a8_ok(const R3dGemmQ& p);

@@ -94,6 +94,13 @@ const RadConstraint kCMxfp4Decode[] = {
     { "K", RAD_C_DIV, 128, nullptr },
 };
 
+/* src/r3d_rows.cpp:1114-1124: the composed row's arena is sized at M = 64, so the band stops there */
+const RadConstraint kCFp8Gated[] = {
+    { "dtype", RAD_C_IN, 0, "fp8a8" }, { "M", RAD_C_LE, 64, nullptr },
+    { "K", RAD_C_DIV, 128, nullptr },  { "group", RAD_C_EQ, 128, nullptr },
+    { "act", RAD_C_IN, 0, "silu sigmoid" },
+};
+
 enum { kPrioPlain = 1000, kPrioDecode = 1100, kPrioQ8x = 1200 };
 
 #define ROW(name, op, family, summary, shapes, dtypes, prio, cons, launch)               \
@@ -103,25 +110,26 @@ enum { kPrioPlain = 1000, kPrioDecode = 1100, kPrioQ8x = 1200 };
 
 const RadKernelInfo kRows[] = {
     { "logits_gemm_e4m3", "logits_gemm", "vocab",
-      "weight-streaming GEMV over the joined LM head: e4m3 codes ride bf16 tensor-core "
-      "fragments exactly, the block scale is applied to each 128-column partial in f32",
+      "weight-streaming GEMV over the joined LM head on tcgen05: e4m3 codes feed the tensor core "
+      "untouched, each bf16 activation travels as two exact e4m3 pieces, the block scale is "
+      "applied to each 128-column partial in f32",
       "codes [n_vocab, n_embd] e4m3 dense, scale per (1 or 128 rows, 128 cols); M from "
-      "numel(logits)/n_vocab, passes of 64 rows",
+      "numel(logits)/n_vocab, passes of 32 rows",
       "bf16 x, joined e4m3 + bf16/f16/f32 head, f32 logits",
       RAD_DOMAIN_DEVICE, kPrioPlain, kCLogits, COUNT_OF(kCLogits), nullptr, 0, nullptr,
       nullptr, nullptr, r3d_rad_logits_gemm_e4m3, nullptr, r3d_layout_head,
       r3d_relayout_head, nullptr, r3d_unrelayout_head, nullptr },
 
     ROW("gemm_nt_q_mxfp4", "gemm_nt_q", "gemm",
-        "mxfp4a8, any M: e2m1 codes expanded in registers to exact e4m3 images and fed to "
-        "fp8 tensor-core fragments, E8M0 applied per 32-of-K partial, a_scale per 128",
+        "mxfp4a8, any M: e2m1 nibbles go to tcgen05 packed (M <= 4, hardware E8M0 group scales) or "
+        "unpacked by the tensor map; a_scale applied per 128 of K; M > 64 on 128x192 tiles",
         "b:32 / a:128 scale grids; nibble rows byte-packed; M from numel(y)/N",
         "e4m3 a + f32 a_scale, e2m1 b + E8M0 b_scale, bf16 y; b_ref ignored; a_sum refused",
         kPrioPlain, kCMxfp4, r3d_rad_gemm_nt_q),
 
     ROW("gemm_nt_q_fp8a8", "gemm_nt_q", "gemm",
-        "fp8a8, any M: e4m3 codes feed fp8 tensor-core fragments untouched; each 128-of-K "
-        "partial is flushed as (sub * a_scale) * b_scale",
+        "fp8a8, any M: e4m3 codes feed tcgen05 untouched (swap-AB weight streaming up to M = 64, "
+        "128x192 tiles above); each 128-of-K partial is flushed with a_scale and b_scale",
         "K a multiple of 128; any N; b_scale per 128x128 block or per row; M from numel(y)/N",
         "e4m3 a + f32 a_scale, e4m3 b + bf16 b_scale, bf16 y; a_sum and b_ref refused",
         kPrioPlain, kCFp8, r3d_rad_gemm_nt_q_fp8),
@@ -146,6 +154,18 @@ const RadKernelInfo kRows[] = {
         "M <= 8; K a multiple of 128; any N",
         "as gemm_nt_q_mxfp4; R3D_MXFP4_Q8X=0 withdraws this row at registration",
         kPrioQ8x, kCMxfp4Decode, r3d_rad_gemm_nt_q_mxfp4_decode_q8x),
+
+    { "gemm_nt_q_gated_fp8a8", "gemm_nt_q_gated", "gemm",
+      "the fp8a8 band writing its bf16 gate_up plane into the launch scratch, closed by the gated "
+      "activation quantiser in the same call: byte-identical to gemm_nt_q followed by "
+      "gated_quant_fp8; no [M, 2n] tensor reaches the caller",
+      "M <= 64 (the scratch is sized at the band's bound); K a multiple of 128; N = 2n; M derives "
+      "from numel(q)/n",
+      "e4m3 a + f32 a_scale per (row, 128 K), e4m3 b + bf16 scale per 128x128 tile, e4m3 q + f32 scale "
+      "out, optional bf16/f32 product; act silu or sigmoid; a_sum refused",
+      RAD_DOMAIN_DEVICE, kPrioPlain, kCFp8Gated, COUNT_OF(kCFp8Gated), nullptr, 0, nullptr,
+      nullptr, nullptr, r3d_rad_gemm_nt_q_gated_fp8, r3d_rad_gemm_nt_q_gated_fp8_scratch, nullptr,
+      nullptr, nullptr, nullptr, nullptr },
 };
 
 /* ------------------------------------------------------------------ registration gate */
@@ -157,6 +177,7 @@ bool row_hidden(const RadKernelInfo& k) {
     static const bool q8x_off = r3d_mxfp4_q8x_off();
     if (!strcmp(k.name, "gemm_nt_q_fp8a8")) return no_fp8;
     if (!strcmp(k.name, "gemm_nt_q_fp8a8_decode")) return no_fp8 || no_fp8_dec;
+    if (!strcmp(k.name, "gemm_nt_q_gated_fp8a8")) return no_fp8;       /* src/r3d_rows.cpp:2235 */
     if (!strcmp(k.name, "gemm_nt_q_mxfp4")) return no_mx;
     if (!strcmp(k.name, "gemm_nt_q_mxfp4_decode")) return no_mx || no_mx_dec;
     /* the q8x sibling rides every lever of its band, plus its own */

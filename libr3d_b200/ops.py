@@ -80,6 +80,36 @@ def gemm_nt_q(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: 
     return r
 
 
+def gemm_nt_q_gated(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: torch.Tensor,
+                    q: torch.Tensor, scale: torch.Tensor, *, N: int, K: int, act: str = "silu",
+                    group: int = 128, out: torch.Tensor | None = None,
+                    scratch: torch.Tensor | None = None) -> Row:
+    """q[M, N/2] (e4m3 codes), scale[M, N/2/group] (f32) = gated_quant_fp8(a @ dequant(b)^T) for a
+    [N = 2n, K] fp8a8 gate_up weight, gate half first; `out` optionally receives the gated product
+    (bf16 or f32). `scratch` is the launch arena (default: what the row's scratch hook asks for)."""
+    P = plugin()
+    n = N // 2
+    M = q.numel() // n
+    query: dict[str, Any] = dict(M=M, N=N, K=K, group=group, dtype="fp8a8", act=act)
+    r = P.resolve("gemm_nt_q_gated", query)
+    if r is None:
+        raise RuntimeError(f"no row serves gemm_nt_q_gated {query}")
+    sdt = abi.RAD_F32 if b_scale.dtype == torch.float32 else abi.RAD_BF16
+    odt = abi.RAD_F32 if (out is not None and out.dtype == torch.float32) else abi.RAD_BF16
+    tensors = [_desc(a, abi.RAD_F8E4M3), _desc(a_scale, abi.RAD_F32), _desc(b, abi.RAD_F8E4M3),
+               _desc(b_scale, sdt), _desc(q, abi.RAD_F8E4M3), _desc(scale, abi.RAD_F32),
+               _desc(out, odt), _desc(None, abi.RAD_F32)]
+    if scratch is None:
+        probe = ArgPack(tensors, query)
+        need = int(P.lib.r3d_rad_gemm_nt_q_gated_fp8_scratch(probe.args))
+        scratch = torch.empty(need, dtype=torch.uint8, device=a.device)
+    pack = ArgPack(tensors, query, scratch=scratch.data_ptr(), scratch_bytes=scratch.numel() * scratch.element_size())
+    rc = P.launch_row(r, pack, _stream())
+    if rc != abi.RAD_OK:
+        raise RowRefused(r.name, rc)
+    return r
+
+
 def logits_gemm(x: torch.Tensor, head_blob: torch.Tensor, logits: torch.Tensor, *, n_vocab: int,
                 n_embd: int) -> Row:
     """logits[M, n_vocab] f32 = x[M, n_embd] bf16 @ head^T, head a joined rad.planes blob

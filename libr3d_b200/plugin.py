@@ -23,6 +23,7 @@ EXPORTS = [
     "rad_kernel_schema_at", "rad_kernel_count", "rad_kernel_at",
     "r3d_rad_gemm_nt_q_fp8", "r3d_rad_gemm_nt_q_fp8_decode", "r3d_rad_gemm_nt_q",
     "r3d_rad_gemm_nt_q_mxfp4_decode", "r3d_rad_gemm_nt_q_mxfp4_decode_q8x",
+    "r3d_rad_gemm_nt_q_gated_fp8", "r3d_rad_gemm_nt_q_gated_fp8_scratch", "r3d_b200_gated_quant_fp8",
     "r3d_mxfp4_q8x_off", "r3d_rad_logits_gemm_e4m3", "r3d_layout_head", "r3d_relayout_head",
     "r3d_unrelayout_head",
     "r3d_b200_gemm_fp8a8", "r3d_b200_gemm_mxfp4a8", "r3d_b200_gemm_mxfp4a8_q8x",
@@ -91,6 +92,11 @@ class Plugin:
                                                 C.c_int, C.c_void_p]
         L.r3d_b200_gemm_mxfp4a8_q8x_static.argtypes = [C.POINTER(abi.R3dGemmQ), C.c_int, C.c_void_p]
         L.r3d_b200_logits.argtypes = [C.POINTER(abi.R3dLogits), C.c_void_p]
+        L.r3d_rad_gemm_nt_q_gated_fp8_scratch.restype = C.c_int64
+        L.r3d_rad_gemm_nt_q_gated_fp8_scratch.argtypes = [C.POINTER(abi.RadArgs)]
+        L.r3d_b200_gated_quant_fp8.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                               C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
+                                               C.c_int32, C.c_void_p]
         L.r3d_b200_gather_create.argtypes = [C.c_int, C.c_int, C.c_int64, C.c_int, C.POINTER(C.c_void_p), C.c_char_p]
         L.r3d_b200_gather_connect.argtypes = [C.c_void_p, C.c_char_p]
         L.r3d_b200_gather_buffer.argtypes = [C.c_void_p, C.c_int]

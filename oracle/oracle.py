@@ -94,6 +94,21 @@ def quant_act_fp8(x: np.ndarray, group: int = 128):
     return q, s
 
 
+def gated_quant_fp8(gu_bits: np.ndarray, group: int = 128, silu: bool = True, want_ob: bool = False):
+    """bf16 gate_up bits [M, 2n] -> (e4m3 codes [M, n], f32 scales [M, n/group][, bf16 product bits])."""
+    gu = _c(gu_bits, np.uint16)
+    M, N2 = gu.shape
+    n = N2 // 2
+    g = min(group, n) if group > 0 else n
+    ngrp = (n + g - 1) // g
+    q = np.empty((M, n), np.uint8)
+    s = np.empty((M, ngrp), np.float32)
+    ob = np.empty((M, n), np.uint16) if want_ob else None
+    lib().orc_gated_quant_fp8(_p(gu), I64(M), I64(n), I64(g), C.c_int(1 if silu else 0), _p(q), _p(s),
+                              _p(ob) if ob is not None else None)
+    return (q, s, ob) if want_ob else (q, s)
+
+
 def quant_act_mx8(x: np.ndarray):
     x = _c(x, np.float32)
     M, n = x.shape

@@ -173,6 +173,45 @@ ORC_API void orc_quant_act_fp8(const float* x, int64_t M, int64_t n, int64_t gro
         }
 }
 
+/* ------------------------------------------------------------------ gated activation quantiser
+ * src/r3d_gemm_fp8a8.hip:700-825 (the epilogue of gemm_nt_q_gated, itself
+ * src/r3d_band.hip:167-235 verbatim). Input: the bf16 gate_up plane [M, 2n], gate half first.
+ * h = bf16((silu ? gt * sg : sg) * up) with sg = 1 / (1 + (float)exp((double)-gt)); per (row,
+ * group of <= g columns): amax by strict `>` from 0, scale = amax > 0 ? amax * (1/448) : 1,
+ * code = e4m3(clamp(h * (1/scale), +-448)). `ob`, when given, receives h as bf16. */
+ORC_API void orc_gated_quant_fp8(const uint16_t* gu, int64_t M, int64_t n, int64_t g, int silu,
+                                 uint8_t* q, float* scale, uint16_t* ob) {
+    if (g <= 0 || g > n) g = n;
+    const int64_t ngrp = (n + g - 1) / g;
+    auto gated = [&](int64_t r, int64_t i) -> float {
+        const float gt = bf16_to_f32(gu[r * 2 * n + i]);
+        const float up = bf16_to_f32(gu[r * 2 * n + n + i]);
+        const float sg = 1.0f / (1.0f + (float)std::exp((double)(-gt)));
+        const float a = silu ? gt * sg : sg;
+        return bf16_to_f32(f32_to_bf16(a * up));
+    };
+    for (int64_t r = 0; r < M; ++r)
+        for (int64_t gi = 0; gi < ngrp; ++gi) {
+            const int64_t k0 = gi * g, k1 = (k0 + g < n) ? k0 + g : n;
+            float amax = 0.0f;
+            for (int64_t i = k0; i < k1; ++i) {
+                const float m = std::fabs(gated(r, i));
+                if (m > amax) amax = m;
+            }
+            const float sc = amax > 0.0f ? amax * (1.0f / 448.0f) : 1.0f;
+            scale[r * ngrp + gi] = sc;
+            const float inv = 1.0f / sc;
+            for (int64_t i = k0; i < k1; ++i) {
+                const float h = gated(r, i);
+                if (ob) ob[r * n + i] = f32_to_bf16(h);
+                float c = h * inv;
+                if (c > 448.0f) c = 448.0f;
+                if (c < -448.0f) c = -448.0f;
+                q[r * n + i] = f32_to_e4m3(c);
+            }
+        }
+}
+
 /* ------------------------------------------------------------------ OCP-MX activation
  * quantiser (e4m3 elements, one E8M0 scale per 32 columns). PARITY UNPINNED: the
  * reference has no such quantiser. Rule: shared exponent = floor(log2(amax)) - 8 (8 is

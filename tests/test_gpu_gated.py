@@ -1,0 +1,87 @@
+"""gemm_nt_q_gated @ fp8a8 on the GPU: the gated activation quantiser bit for bit against the oracle,
+and the fused row byte-identical to gemm_nt_q followed by the quantiser."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import gen
+import gpu_util as gu
+from libr3d_b200 import abi, ops
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _gated_on_device(gu_bits, group, silu, ob_dtype=None):
+    P = ops.plugin()
+    M, N2 = gu_bits.shape
+    n = N2 // 2
+    g = min(group, n)
+    ngrp = (n + g - 1) // g
+    d = gu.dev(gu_bits)
+    q = gu.GuardedOut((M, n), np.uint8)
+    s = gu.GuardedOut((M, ngrp), np.float32)
+    ob = None if ob_dtype is None else gu.GuardedOut((M, n), np.float32 if ob_dtype == abi.RAD_F32 else np.uint16)
+    rc = P.lib.r3d_b200_gated_quant_fp8(d.data_ptr(), N2, q.ptr, n, s.ptr, ngrp, ob.ptr if ob else None,
+                                        ob_dtype or abi.RAD_BF16, n, M, n, group, 1 if silu else 0, None)
+    assert rc == 0
+    return q.get(), s.get(), (ob.get() if ob else None)
+
+
+@pytest.mark.parametrize("silu", [True, False])
+@pytest.mark.parametrize("M,n,group", [(1, 128, 128), (5, 300, 128), (64, 1024, 128), (3, 200, 0)])
+def test_gated_quantiser_bit_identical_to_oracle(M, n, group, silu):
+    rng = np.random.default_rng(M * 1000 + n)
+    bits = gen.f32_to_bf16_bits((rng.standard_normal((M, 2 * n)) * 4).astype(np.float32))
+    bits[0, :4] = [0x0000, 0x8000, 0x7F80, 0xFF80]
+    want_q, want_s, want_ob = orc.gated_quant_fp8(bits, group, silu, want_ob=True)
+    q, s, ob = _gated_on_device(bits, group, silu, abi.RAD_BF16)
+    assert np.array_equal(s.view(np.uint32), want_s.view(np.uint32))
+    assert np.array_equal(ob, want_ob)
+    assert np.array_equal(q, want_q)
+    _, _, obf = _gated_on_device(bits, group, silu, abi.RAD_F32)
+    assert np.array_equal(obf.view(np.uint32), orc.bf16_bits_to_f32(want_ob).view(np.uint32))
+
+
+@pytest.mark.parametrize("M,N,K,act", [(1, 512, 256, "silu"), (7, 768, 512, "silu"), (16, 1024, 1024, "sigmoid"),
+                                       (64, 512, 384, "silu")])
+def test_fused_row_is_the_unfused_pair_byte_for_byte(M, N, K, act):
+    case = gen.case_fp8(600 + M, M, N, K, "ref128")
+    t = {k: gu.dev(case[k]) for k in ("A", "AS", "B", "BS")}
+    n = N // 2
+    # the unfused pair: the plain row, then the quantiser over its bf16 plane
+    y = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_nt_q(t["A"], t["AS"], t["B"], t["BS"].view(torch.bfloat16), y, dtype="fp8a8", N=N, K=K)
+    torch.cuda.synchronize()
+    ybits = y.view(torch.int16).cpu().numpy().view(np.uint16)
+    want_q, want_s, want_ob = orc.gated_quant_fp8(ybits, 128, act == "silu", want_ob=True)
+    # the fused row
+    q = torch.zeros((M, n), dtype=torch.uint8, device="cuda")
+    s = torch.zeros((M, n // 128), dtype=torch.float32, device="cuda")
+    ob = torch.zeros((M, n), dtype=torch.bfloat16, device="cuda")
+    r = ops.gemm_nt_q_gated(t["A"], t["AS"], t["B"], t["BS"].view(torch.bfloat16), q, s, N=N, K=K, act=act, out=ob)
+    assert r.name == "gemm_nt_q_gated_fp8a8"
+    torch.cuda.synchronize()
+    assert np.array_equal(q.cpu().numpy(), want_q)
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), want_s.view(np.uint32))
+    assert np.array_equal(ob.view(torch.int16).cpu().numpy().view(np.uint16), want_ob)
+    assert np.count_nonzero(want_q & 0x7F) > want_q.size // 2
+
+
+def test_fused_row_refusals():
+    from libr3d_b200.ops import RowRefused
+    M, N, K = 4, 512, 256
+    case = gen.case_fp8(1, M, N, K, "ref128")
+    t = {k: gu.dev(case[k]) for k in ("A", "AS", "B", "BS")}
+    q = torch.zeros((M, N // 2), dtype=torch.uint8, device="cuda")
+    s = torch.zeros((M, N // 256), dtype=torch.float32, device="cuda")
+    small = torch.empty(M * N * 2 - 2, dtype=torch.uint8, device="cuda")     # an arena one element short
+    with pytest.raises(RowRefused) as e:
+        ops.gemm_nt_q_gated(t["A"], t["AS"], t["B"], t["BS"].view(torch.bfloat16), q, s, N=N, K=K, scratch=small)
+    assert e.value.rc == abi.RAD_E_UNSUPPORTED
+    exact = torch.empty(M * N * 2, dtype=torch.uint8, device="cuda")
+    ops.gemm_nt_q_gated(t["A"], t["AS"], t["B"], t["BS"].view(torch.bfloat16), q, s, N=N, K=K, scratch=exact)
+    torch.cuda.synchronize()
+    assert int(torch.count_nonzero(q)) > 0

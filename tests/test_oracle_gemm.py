@@ -158,3 +158,33 @@ def test_golden_vectors():
             raise AssertionError(kind)
         a, b = np.ascontiguousarray(y), g["Y"]
         assert a.dtype == b.dtype and np.array_equal(a.view(np.uint8), b.view(np.uint8)), f.name
+
+
+def test_gated_quant_matches_independent_numpy_walk():
+    """orc_gated_quant_fp8 (src/r3d_gemm_fp8a8.hip:700-825 of libr3d) against a numpy restatement
+    written from the rule: h = bf16((silu ? g*sig(g) : sig(g)) * up), sig through double exp,
+    amax/448 scale per group, saturating RTNE codes."""
+    rng = np.random.default_rng(11)
+    M, n = 5, 300                                        # a ragged last group
+    gu = gen.f32_to_bf16_bits((rng.standard_normal((M, 2 * n)) * 3).astype(np.float32))
+    gu[0, :4] = [0x0000, 0x8000, 0x7F80, 0xFF80]         # zeros and infinities in the gate
+    gu[1, n:n + 128] = 0                                 # an all-zero group: scale 1
+    gf = orc.bf16_bits_to_f32(gu)
+    for silu in (True, False):
+        q, s, ob = orc.gated_quant_fp8(gu, 128, silu, want_ob=True)
+        gt, up = gf[:, :n], gf[:, n:]
+        with np.errstate(over="ignore", invalid="ignore"):
+            sg = (np.float32(1) / (np.float32(1) + np.exp(-gt.astype(np.float64)).astype(np.float32))).astype(np.float32)
+            a = (gt * sg).astype(np.float32) if silu else sg
+            h = orc.bf16_bits_to_f32(gen.f32_to_bf16_bits((a * up).astype(np.float32)))
+        assert np.array_equal(ob, gen.f32_to_bf16_bits(h))
+        for gi in range(3):
+            blk = h[:, gi * 128:min(gi * 128 + 128, n)]
+            am = np.zeros(M, np.float32)
+            for k in range(blk.shape[1]):                # strict >: NaN never wins
+                m = np.abs(blk[:, k]); am = np.where(m > am, m, am)
+            sc = np.where(am > 0, (am * np.float32(1 / 448)).astype(np.float32), np.float32(1))
+            assert np.array_equal(s[:, gi].view(np.uint32), sc.astype(np.float32).view(np.uint32))
+            c = np.clip((blk * (np.float32(1) / sc)[:, None]).astype(np.float32), -448, 448)
+            assert np.array_equal(q[:, gi * 128:gi * 128 + blk.shape[1]], orc.encode_e4m3(c))
+        assert s[1, 0] == 1.0 and (q[1, :128] & 0x7F).max() == 0

@@ -61,7 +61,7 @@ def test_rows_names_priorities_constraints(plug):
     rows = {r.name: r for r in plug.rows()}
     want = {"logits_gemm_e4m3": 1000, "gemm_nt_q_mxfp4": 1000, "gemm_nt_q_fp8a8": 1000,
             "gemm_nt_q_fp8a8_decode": 1100, "gemm_nt_q_mxfp4_decode": 1100,
-            "gemm_nt_q_mxfp4_decode_q8x": 1200}
+            "gemm_nt_q_mxfp4_decode_q8x": 1200, "gemm_nt_q_gated_fp8a8": 1000}
     assert {k: v.priority for k, v in rows.items()} == want
     assert all(r.domain == abi.RAD_DOMAIN_DEVICE and r.launch for r in rows.values())
     assert rows["logits_gemm_e4m3"].has_layout
@@ -89,6 +89,13 @@ def test_band_resolution(plug):
     assert plug.resolve("logits_gemm", dict(M=1, n_vocab=151936, n_embd=5120, dtype="bf16")).name == \
         "logits_gemm_e4m3"
     assert plug.resolve("logits_gemm", dict(M=1, n_vocab=10, n_embd=64, dtype="bf16")) is None
+    # the fused gate_up row: act is required, the band stops at the arena's M = 64
+    gq = dict(N=512, K=256, group=128, dtype="fp8a8")
+    assert plug.resolve("gemm_nt_q_gated", dict(M=64, act="silu", **gq)).name == "gemm_nt_q_gated_fp8a8"
+    assert plug.resolve("gemm_nt_q_gated", dict(M=3, act="sigmoid", **gq)).name == "gemm_nt_q_gated_fp8a8"
+    assert plug.resolve("gemm_nt_q_gated", dict(M=65, act="silu", **gq)) is None
+    assert plug.resolve("gemm_nt_q_gated", dict(M=4, **gq)) is None
+    assert plug.resolve("gemm_nt_q_gated", dict(M=4, act="gelu", **gq)) is None
 
 
 _DUMP = r"""
@@ -113,7 +120,7 @@ def _rows_under(env):
 
 
 ALL = {"logits_gemm_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode",
-       "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x"}
+       "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_gated_fp8a8"}
 
 
 @pytest.mark.parametrize("env,hidden,mx_row,f8_row", [
@@ -123,7 +130,7 @@ ALL = {"logits_gemm_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a
     ({"R3D_NO_FP4_DEC": "1"}, {"gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x"}, "gemm_nt_q_mxfp4", "gemm_nt_q_fp8a8_decode"),
     ({"R3D_NO_MXFP4": ""}, {"gemm_nt_q_mxfp4", "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x"}, "-", "gemm_nt_q_fp8a8_decode"),
     ({"R3D_NO_FP8_DEC": "1"}, {"gemm_nt_q_fp8a8_decode"}, "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_fp8a8"),
-    ({"R3D_NO_FP8A8": "1"}, {"gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode"}, "gemm_nt_q_mxfp4_decode_q8x", "-"),
+    ({"R3D_NO_FP8A8": "1"}, {"gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode", "gemm_nt_q_gated_fp8a8"}, "gemm_nt_q_mxfp4_decode_q8x", "-"),
 ])
 def test_kill_switch_matrix(env, hidden, mx_row, f8_row):
     # levers act at registration: a hidden row is not enumerated and the band re-resolves
