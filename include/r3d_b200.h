@@ -71,7 +71,7 @@ enum {
     R3D_ARM_EXACT  = 1,   /* oracle-order walk: bit-identical to the CPU restatement */
     R3D_ARM_STREAM = 2,   /* weight-streaming tensor-core walk, M <= 64 */
     R3D_ARM_TILE   = 3,   /* tcgen05 + TMA + TMEM walk (swap-AB), one CTA (or cluster) per row tile */
-    R3D_ARM_PACK   = 4    /* mxfp4a8 only, M <= 4: tcgen05 kind::mxf4 on packed nibbles, hardware group scales */
+    R3D_ARM_PACK   = 4    /* mxfp4a8 only, M <= 8: tcgen05 kind::mxf4 on packed nibbles, hardware group scales */
 };
 
 /* Operands of one gemm_nt_q call. Pitches are in elements of the tensor they belong to,

@@ -1,4 +1,4 @@
-/* kern_tc_mxf4.cu -- the packed-fp4 tcgen05 walk of the mxfp4a8 decode band (M <= 4).
+/* kern_tc_mxf4.cu -- the packed-fp4 tcgen05 walk of the mxfp4a8 decode band (M <= 8).
  *
  * The unpacking tensor map of the other tcgen05 walk fetches 64-byte row segments and tops out
  * near 70 % of HBM bandwidth. This walk never unpacks: the weight plane travels as packed
@@ -54,13 +54,14 @@ constexpr int kRows = 128;
 constexpr int kStageK = 256;                       /* K elements per stage = 128 packed bytes per row */
 constexpr int kWBytes = kRows * 128;               /* 16 KiB of weights per stage */
 constexpr int kPieces = 12;
-constexpr int kMaxTok = 4;
+constexpr int kMaxTok = 8;
 
 struct P4 {
     const float* as; int64_t as_pitch; int as_cols;
     const uint32_t* nanflag; int nan_blocks;       /* nanflag[t * nan_blocks + b] != 0: token t held an e4m3 NaN */
     uint16_t* y; int64_t y_pitch;
     int m, n, k;
+    int ksplit, kper;                              /* CTAs per cluster = K shares per row tile; stages per share (a multiple of 4) */
     PushCfg push;                                  /* world > 0: store into every rank's gathered buffer */
 };
 
@@ -109,19 +110,20 @@ constexpr size_t smem_fixed() {
     return 1024 + (size_t)kScTiles * kScBytes + (4 * kStages + 8 + 2 * kScTiles) * sizeof(uint64_t) + 64;
 }
 
-/* NP: piece rows on the MMA's N axis (12 per token, padded to 16 / 32 / 48); MT: tokens. */
+/* NP: piece rows on the MMA's N axis (12 per token, padded to 16 / 32 / 48 / 96); MT: tokens
+ * (1, 2, 4, 8: M rounds up, rows past M are zero-filled by the tensor map and never stored). */
 template <int NP, int MT, int kStages>
 __global__ void __launch_bounds__(kThreads)
 k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
           const __grid_constant__ CUtensorMap tmP, const P4 P) {
     constexpr int kPBytes = NP * 128;
     constexpr int kStage = kWBytes + kPBytes;
-    constexpr int kBufs = NP <= 16 ? 4 : 2;                      /* accumulator ring */
+    constexpr int kBufs = NP <= 16 ? 4 : (NP <= 48 ? 2 : 1);     /* accumulator ring */
     constexpr int kAccCols = 2 * NP;                             /* two 128-column groups per stage */
     constexpr int kSfBase = kBufs * kAccCols;                    /* multiple of 4 */
     constexpr int kSfbCol = kSfBase + kStages * 8;
     constexpr int kTmemCols = 256;
-    static_assert(kSfbCol + 8 <= kTmemCols && (kSfBase % 4) == 0 && kStages >= 4, "TMEM columns");
+    static_assert(kSfbCol + 8 <= kTmemCols && (kSfBase % 4) == 0 && kStages >= 3, "TMEM columns");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -138,8 +140,12 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     float* as_s = (float*)(tmem_slot + 4);                        /* [n128][MT] */
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r0 = blockIdx.x * kRows;
-    const int nk = P.k / kStageK;
+    const int ks = P.ksplit;
+    const int crank = ks > 1 ? (int)cluster_rank() : 0;
+    const int r0 = (blockIdx.x / ks) * kRows;
+    const int nk_all = P.k / kStageK;
+    const int it0 = crank * P.kper;                                /* this CTA's first K stage */
+    const int nk = min(P.kper, nk_all - it0);                      /* ... and how many (>= 1: the host's rule) */
     const int n128 = P.k / 128;
     const int ntile = (nk + 3) / 4;
 
@@ -184,13 +190,13 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                 const int r = tl % kScTiles;
                 if (!mbar_wait(&sc_empty[r], ((tl / kScTiles) & 1) ^ 1, 21)) return false;
                 mbar_expect_tx(&sc_full[r], (uint32_t)kScBytes);
-                tma_load_2d(sc + r * kScBytes, &tmS, tl * 32, r0, &sc_full[r]);
+                tma_load_2d(sc + r * kScBytes, &tmS, (it0 / 4 + tl) * 32, r0, &sc_full[r]);
                 return true;
             };
             auto pieces = [&](int it) {
                 const int s = it % kStages;
                 mbar_expect_tx(&pfull[s], (uint32_t)kPBytes);
-                tma_load_2d(smem + s * kStage + kWBytes, &tmP, it * 128, 0, &pfull[s]);
+                tma_load_2d(smem + s * kStage + kWBytes, &tmP, (it0 + it) * 128, 0, &pfull[s]);
             };
             bool ok = scale_tile(0);
             if (ok && ntile > 1) ok = scale_tile(1);
@@ -199,7 +205,7 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                 const int s = it % kStages;
                 if (!mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1, 22)) break;
                 mbar_expect_tx(&full[s], (uint32_t)kWBytes);
-                tma_load_2d(smem + s * kStage, &tmW, it * 128, r0, &full[s]);
+                tma_load_2d(smem + s * kStage, &tmW, (it0 + it) * 128, r0, &full[s]);
                 if (it == first - 1) {
                     dep_wait();
                     for (int j = 0; j < first; ++j) pieces(j);
@@ -239,7 +245,7 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     } else {
         /* ---------------- scale writers + epilogue: thread = weight row ---------------- */
         const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
-        constexpr int LEAD = 3;
+        constexpr int LEAD = kStages > 3 ? 3 : 2;
         /* the token-side scale factors are 2^0 everywhere: each warp fills its own lane quarter
          * once; the first preparation's wait::st and barrier arrival publish these stores too */
 #pragma unroll
@@ -280,42 +286,58 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
             const int ab = it % kBufs;
             if (!mbar_wait(&acc_full[ab], (it / kBufs) & 1, 28)) { alive = false; break; }
             tc_fence_after();
-            float c[2][MT * kPieces <= 16 ? 16 : (MT * kPieces <= 32 ? 32 : 48)];
+            constexpr int NC = (MT * kPieces + 15) / 16 * 16;       /* piece columns read per group */
+            const float* sa = as_s + (2 * (it0 + it)) * MT;
 #pragma unroll
             for (int g = 0; g < 2; ++g) {
+                float c[NC];
                 const uint32_t ta = tlane + ab * kAccCols + g * NP;
-                tmem_ld16(ta, c[g]);
-                if (MT * kPieces > 16) tmem_ld16(ta + 16, c[g] + 16);
-                if (MT * kPieces > 32) tmem_ld16(ta + 32, c[g] + 32);
-            }
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[ab]);
-            const float* sa = as_s + (2 * it) * MT;
 #pragma unroll
-            for (int t = 0; t < MT; ++t) {
+                for (int h = 0; h < NC / 16; ++h) tmem_ld16(ta + h * 16, c + h * 16);
+                tmem_ld_wait();
+                if (g == 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[ab]);
+                }
 #pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    float v = c[g][t * kPieces] * wj[0];
+                for (int t = 0; t < MT; ++t) {
+                    float v = c[t * kPieces] * wj[0];
 #pragma unroll
-                    for (int j = 1; j < kPieces; ++j) v = fmaf(c[g][t * kPieces + j], wj[j], v);
+                    for (int j = 1; j < kPieces; ++j) v = fmaf(c[t * kPieces + j], wj[j], v);
                     acc[t] += v * sa[g * MT + t];
                 }
             }
         }
-        if (alive && row < P.n) {
+        if (ks > 1 && crank != 0) {
+            /* every stage of this CTA has been consumed: the stage ring is free to carry the partial
+             * sums to the cluster's leader */
+            float* red = (float*)smem;
 #pragma unroll
-            for (int t = 0; t < MT; ++t) {
-                if (t >= P.m) break;
-                uint32_t nan = 0u;
-                for (int b = 0; b < P.nan_blocks; ++b) nan |= __ldg(P.nanflag + t * P.nan_blocks + b);
-                const float v = nan ? __int_as_float(0x7fc00000) : acc[t];
-                if (P.push.world) push_store<uint16_t>(P.push, t, row, f32_to_bf16(v));
-                else P.y[(int64_t)t * P.y_pitch + row] = f32_to_bf16(v);
-            }
+            for (int t = 0; t < MT; ++t) red[t * kRows + q * 32 + lane] = alive ? acc[t] : __int_as_float(0x7fc00000);
         }
     }
+    if (ks > 1) {
+        cluster_sync_all();                                   /* partial sums are in place */
+        if (warp >= 2 && crank == 0) {
+            const float* red = (const float*)smem;
+            for (int r = 1; r < ks; ++r)
+#pragma unroll
+                for (int t = 0; t < MT; ++t) acc[t] += ld_peer_f32(red + t * kRows + q * 32 + lane, (uint32_t)r);
+        }
+    }
+    if (warp >= 2 && crank == 0 && alive && row < P.n) {
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+            if (t >= P.m) break;
+            uint32_t nan = 0u;
+            for (int b = 0; b < P.nan_blocks; ++b) nan |= __ldg(P.nanflag + t * P.nan_blocks + b);
+            const float v = nan ? __int_as_float(0x7fc00000) : acc[t];
+            if (P.push.world) push_store<uint16_t>(P.push, t, row, f32_to_bf16(v));
+            else P.y[(int64_t)t * P.y_pitch + row] = f32_to_bf16(v);
+        }
+    }
+    if (ks > 1) cluster_sync_all();                           /* peers' smem was read: they may leave */
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -388,8 +410,7 @@ cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
-    static const bool off = [] { const char* e = getenv("R3D_NO_PDL"); return e && *e && *e != '0'; }();
-    cfg.attrs = at; cfg.numAttrs = off ? 0 : 1;
+    cfg.attrs = at; cfg.numAttrs = tc_pdl_on() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
@@ -405,9 +426,30 @@ int launch_s(const CUtensorMap* tw, const CUtensorMap* ts, const CUtensorMap* tp
                                    (int)cudaSharedmemCarveoutMaxShared);
         attr_set = smem;
     }
+    /* K shares per row tile: split K over a cluster only when the row tiles alone cannot occupy the
+     * machine (a CTA costs ~3 us of fill and drain); shares are whole scale tiles (4 stages) */
+    P4 Q = P;
+    const int tiles = (P.n + kRows - 1) / kRows, nk_all = P.k / kStageK;
+    static const int forced = [] { const char* e = getenv("R3D_TC_KSPLIT"); return e ? atoi(e) : 0; }();
+    int ks = forced > 0 ? forced : (tiles >= tc_sm_count() / 2 ? 1 : tiles >= tc_sm_count() / 4 ? 2 : 4);
+    if (ks > 8) ks = 8;
+    int per = nk_all;
+    for (; ks > 1; --ks) {
+        per = ((nk_all + ks - 1) / ks + 3) / 4 * 4;
+        if ((ks - 1) * per < nk_all) break;                   /* every share holds at least one stage */
+    }
+    if (ks <= 1) { ks = 1; per = nk_all; }
+    Q.ksplit = ks; Q.kper = per;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(tiles * ks)); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)ks; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = tc_pdl_on() ? 2 : 1;
     count_launch();
-    const cudaError_t e = launch_pdl(k_tc_mxf4<NP, MT, kStages>, dim3((unsigned)((P.n + kRows - 1) / kRows)),
-                                     dim3(kThreads), smem, st, *tw, *ts, *tp, P);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_mxf4<NP, MT, kStages>, *tw, *ts, *tp, Q);
     return e == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
 }
 
@@ -419,7 +461,8 @@ int launch(const CUtensorMap* tw, const CUtensorMap* ts, const CUtensorMap* tp, 
     const size_t half = 233472 / 2 - 1024;
     if (smem_fixed<6>() + extra + 6 * stage <= half) return launch_s<NP, MT, 6>(tw, ts, tp, P, st);
     if (smem_fixed<5>() + extra + 5 * stage <= half) return launch_s<NP, MT, 5>(tw, ts, tp, P, st);
-    return launch_s<NP, MT, 4>(tw, ts, tp, P, st);
+    if (smem_fixed<4>() + extra + 4 * stage <= half) return launch_s<NP, MT, 4>(tw, ts, tp, P, st);
+    return launch_s<NP, MT, 3>(tw, ts, tp, P, st);
 }
 
 bool al(const void* p, int a) { return (((uintptr_t)p) & (uintptr_t)(a - 1)) == 0; }
@@ -441,7 +484,7 @@ int tc_mxf4(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push) {
     count_launch();
     if (launch_pdl(k_mxf4_split, dim3((unsigned)nb, (unsigned)p.m), dim3(128), 0, st, (const uint8_t*)p.a,
                    (int64_t)p.a_pitch, (int)p.k, sc.pieces, sc.nan) != cudaSuccess) return RAD_E_DEVICE;
-    const int np = p.m == 1 ? 16 : (p.m == 2 ? 32 : 48);
+    const int np = p.m == 1 ? 16 : (p.m == 2 ? 32 : (p.m <= 4 ? 48 : 96));
     const CUtensorMap* tw = tc_tensor_map(p.b, (uint64_t)(p.k / 2), (uint64_t)p.n, (uint64_t)p.b_pitch,
                                           CU_TENSOR_MAP_DATA_TYPE_UINT8, kRows);
     const CUtensorMap* ts = tc_tensor_map(p.b_scale, (uint64_t)(p.k / 32), (uint64_t)p.n, (uint64_t)p.bs_pitch,
@@ -457,7 +500,8 @@ int tc_mxf4(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push) {
     if (push) P.push = *push;
     if (p.m == 1) return launch<16, 1>(tw, ts, tp, P, st);
     if (p.m == 2) return launch<32, 2>(tw, ts, tp, P, st);
-    return launch<48, 4>(tw, ts, tp, P, st);
+    if (p.m <= 4) return launch<48, 4>(tw, ts, tp, P, st);
+    return launch<96, 8>(tw, ts, tp, P, st);
 }
 
 int tc_mxf4_status() {

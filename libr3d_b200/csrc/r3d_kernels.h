@@ -44,7 +44,7 @@ int  tc_fp8a8(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push = nullptr)
 int  tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push = nullptr);
 bool tc_logits_ok(const R3dLogits& l);    /* e4m3 head, M <= 32 per pass, K <= 16384 */
 int  tc_logits(const R3dLogits& l, cudaStream_t st, const PushCfg* push = nullptr);
-/* packed-fp4 tcgen05 walk (kern_tc_mxf4.cu): kind::mxf4 with hardware group scales, M <= 4,
+/* packed-fp4 tcgen05 walk (kern_tc_mxf4.cu): kind::mxf4 with hardware group scales, M <= 8,
  * K a multiple of 256 */
 bool tc_mxf4_ok(const R3dGemmQ& p);
 int  tc_mxf4(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push = nullptr);

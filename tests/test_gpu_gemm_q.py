@@ -17,7 +17,7 @@ from oracle import oracle as orc
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
 EX, STREAM, TILE = abi.R3D_ARM_EXACT, abi.R3D_ARM_STREAM, abi.R3D_ARM_TILE
-PACK = abi.R3D_ARM_PACK          # mxfp4a8, M <= 4: packed nibbles straight into tcgen05 kind::mxf4
+PACK = abi.R3D_ARM_PACK          # mxfp4a8, M <= 8: packed nibbles straight into tcgen05 kind::mxf4
 FAST = [STREAM, TILE]          # the tensor-core arms: mma.sync streaming, tcgen05
 ODD_M = [1, 2, 3, 5, 7, 8, 9, 16, 17]
 
@@ -128,8 +128,8 @@ def test_mxfp4_fast_arms_within_2ulp(M, arm):
 @pytest.mark.parametrize("arm", [EX, STREAM, TILE, PACK])
 def test_mxfp4_torture_scale_bytes_and_codes(arm):
     g = np.load(GOLD / "mxfp4a8_torture.npz")
-    if arm == PACK and (g["A"].shape[0] > 4 or g["A"].shape[1] % 512):
-        pytest.skip("packed arm: M <= 4, scale rows 16-byte aligned")
+    if arm == PACK and (g["A"].shape[0] > 8 or g["A"].shape[1] % 512):
+        pytest.skip("packed arm: M <= 8, scale rows 16-byte aligned")
     case = dict(A=g["A"], AS=g["AS"], B=g["B"], BS=g["BS"])
     got = gu.gemm_launch("mxfp4a8", case, arm)
     want = g["Y"]
@@ -237,10 +237,21 @@ def test_rows_resolve_and_serve_mxfp4():
     assert name4 == "gemm_nt_q_mxfp4" and gu.grade_bf16(got4, acc4)["max_ulp"] <= 2
 
 
-@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 7, 8])
 def test_mxfp4_packed_arm_within_2ulp(M):
     N, K = (200, 512) if M % 2 else (136, 1536)
     case = gen.case_mxfp4(4100 + M, M, N, K)
+    _, acc = orc.gemm_mxfp4a8(**case, want_acc=True)
+    _, ab = orc.truth_mxfp4a8(**case)
+    g = gu.grade_bf16(gu.gemm_launch("mxfp4a8", case, PACK), acc, ab)
+    assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 3e-2, g
+
+
+@pytest.mark.parametrize("M,N,K", [(2, 256, 8192), (1, 128, 2560), (8, 640, 13824), (4, 5120, 13824)])
+def test_mxfp4_packed_arm_cluster_k_split(M, N, K):
+    """few row tiles: K is shared by a thread-block cluster (whole scale tiles per share, the last
+    share short) and the partial sums meet in the leader through distributed shared memory"""
+    case = gen.case_mxfp4(4400 + M, M, N, K)
     _, acc = orc.gemm_mxfp4a8(**case, want_acc=True)
     _, ab = orc.truth_mxfp4a8(**case)
     g = gu.grade_bf16(gu.gemm_launch("mxfp4a8", case, PACK), acc, ab)
@@ -366,7 +377,7 @@ def _stream_vs_exact_full(kind, case, tol_frac=0.9995):
     bit-identical to the CPU oracle at small sizes) to 2 bf16 ulp, plus a CPU-oracle check of
     a row sample."""
     ex = gu.gemm_launch(kind, case, EX)
-    for arm in FAST + ([PACK] if kind == "mxfp4a8" and case["A"].shape[0] <= 4 else []):
+    for arm in FAST + ([PACK] if kind == "mxfp4a8" and case["A"].shape[0] <= 8 else []):
         st = gu.gemm_launch(kind, case, arm)
         d = orc.bf16_ulp_distance(st, ex)
         assert (d <= 2).mean() >= tol_frac, (arm, (d <= 2).mean(), int(d.max()))
@@ -383,7 +394,7 @@ def _stream_vs_exact_full(kind, case, tol_frac=0.9995):
     assert np.array_equal(ex[:, rows], want)
 
 
-@pytest.mark.parametrize("M", [1, 2, 4])
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
 def test_config_c2_mxfp4_decode_full_size(M):
     _stream_vs_exact_full("mxfp4a8", gen.case_mxfp4(20 + M, M, 27648, 5120))
 
