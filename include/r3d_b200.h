@@ -65,7 +65,16 @@ int r3d_unrelayout_head(const RadParam* p, int n_p, int operand, const RadEncodi
 
 /* ------------------------------------------------------------------ (2) launch layer */
 
-/* Which kernel serves a call. AUTO picks by shape and alignment the way the entries do. */
+/* Which kernel serves a call. AUTO picks by shape and alignment the way the entries do.
+ *
+ * The tcgen05 arms are launched with programmatic stream serialisation: a call's kernel may begin
+ * while the previous kernel of the stream is still running, prefetches WEIGHT tiles and weight
+ * scales at once and touches everything else (activations, activation scales, outputs) only after
+ * griddepcontrol.wait. Weight planes must therefore be complete before the kernel that precedes
+ * the call starts (they are written when a model is loaded and not again: the reference's plane
+ * cache relies on the same, src/r3d_gemm_mxfp4.hip:1879-1880). R3D_NO_PDL=1 disables the early start.
+ * Some arms keep activation pieces in device arrays owned by the library: calls on one device
+ * must be ordered on one stream (one dispatch thread, as in the reference). */
 enum {
     R3D_ARM_AUTO   = 0,
     R3D_ARM_EXACT  = 1,   /* oracle-order walk: bit-identical to the CPU restatement */

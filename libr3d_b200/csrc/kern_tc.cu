@@ -17,9 +17,9 @@
  *   - Four epilogue warps (128 threads = 128 weight rows) read the f32 partials with
  *     tcgen05.ld and apply the scale groups in registers, in the reference's flush order:
  *       fp8a8    acc += (sub128 * sa[m,g]) * sb[row,g]                 (one partial per stage)
- *       mxfp4a8  t = sum_j sub32_j * 2^(x_j-127);  acc += t * sa[m,g]  (four partials per
- *                stage: each K=32 MMA is exactly one E8M0 scale group and writes its own
- *                TMEM columns)
+ *       mxfp4a8  acc += (sum_j sub32_j * 2^(x_j-127)) * sa[m,g]: the E8M0 group scales are applied
+ *                by the tensor core (kind::mxf8f6f4.block_scale, one scale per K=32 MMA) from
+ *                tensor memory, where the epilogue warps put each row's four bytes per stage
  * Warp roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-5 epilogue.
  *
  * Every mbarrier wait is bounded (~1 s of clock64); on expiry a status word is set
@@ -71,10 +71,16 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             const TcParams P) {
     constexpr int kBBytes = NTOK * kStageK;
     constexpr int kStage = kABytes + kBBytes;
-    constexpr int kAccCols = (FMT == TC_MXFP4 ? 4 : 1) * NTOK;     /* per buffer */
-    constexpr int kBufs = (4 * kAccCols <= 256) ? 4 : 2;           /* accumulator ring in TMEM */
-    constexpr int kTmemCols = (kBufs * kAccCols) < 32 ? 32 : kBufs * kAccCols;
-    static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 256, "TMEM columns");
+    constexpr int kAccCols = NTOK;                                 /* per buffer */
+    constexpr int kBufs = 4;                                       /* accumulator ring in TMEM */
+    /* mxfp4a8: after the accumulators, four scale-factor columns per smem stage (one 32-bit word
+     * per weight row, in column base + lane quarter) and eight columns of token-side factors */
+    constexpr int kSfBase = kBufs * kAccCols;
+    constexpr int kSfbCol = kSfBase + kTcStages * 4;
+    constexpr int kNeedCols = FMT == TC_MXFP4 ? kSfbCol + 8 : kBufs * kAccCols;
+    constexpr int kTmemCols = kNeedCols <= 32 ? 32 : (kNeedCols <= 64 ? 64 : (kNeedCols <= 128 ? 128 : 256));
+    static_assert(kNeedCols <= 256, "TMEM columns");
+    constexpr int LEAD = kTcStages >= 4 ? 3 : 2;                   /* mxfp4a8: scale words go to TMEM this many stages ahead */
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -82,7 +88,8 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     uint64_t* empty = full + kTcStages;
     uint64_t* acc_full = empty + kTcStages;
     uint64_t* acc_empty = acc_full + 4;
-    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 4);
+    uint64_t* prep = acc_empty + 4;                                 /* [kTcStages] mxfp4a8: scale factors are in TMEM */
+    uint32_t* tmem_slot = (uint32_t*)(prep + kTcStages);
     float* as_s = (float*)(tmem_slot + 4);                          /* [n128][NTOK] */
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -94,7 +101,7 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     const int nk = (int)((int64_t)n128 * (crank + 1) / ks) - it0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kTcStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < kTcStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&prep[s], 4); }
         for (int b = 0; b < kBufs; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -157,10 +164,15 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     } else if (warp == 1) {
         /* ---------------- MMA issuer ---------------- */
         if (elect_one()) {
-            const uint32_t idesc = (1u << 4) | ((FMT == TC_MXFP4 ? 5u : 0u) << 7) | (0u << 10) |
-                                   ((uint32_t)(NTOK >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
+            /* plain kinds: f32 accumulate at bit 4, a format at bit 7, N >> 3 at bit 17, M >> 4 at bit
+             * 24. Block-scaled kinds: a format e2m1 (5) at bit 7, scale format ue8m0 at bit 23,
+             * a_sf_id (which byte of the row's scale word this K=32 step uses) at bit 29 */
+            const uint32_t idesc = FMT == TC_MXFP4
+                ? ((5u << 7) | ((uint32_t)(NTOK >> 3) << 17) | (1u << 23) | ((uint32_t)(kTileRows >> 4) << 24))
+                : ((1u << 4) | ((uint32_t)(NTOK >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24));
             for (int it = 0; it < nk; ++it) {
                 const int s = it % kTcStages, buf = it % kBufs;
+                if (FMT == TC_MXFP4 && !mbar_wait(&prep[s], (it / kTcStages) & 1, 15)) break;
                 if (!mbar_wait(&acc_empty[buf], ((it / kBufs) & 1) ^ 1, 12)) break;
                 if (!mbar_wait(&full[s], (it / kTcStages) & 1, 13)) break;
                 tc_fence_after();
@@ -169,7 +181,8 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                 for (int k = 0; k < 4; ++k) {
                     const uint64_t ad = smem_desc_sw128(a0 + k * 32), bd = smem_desc_sw128(b0 + k * 32);
                     if (FMT == TC_MXFP4)
-                        umma_f8f6f4(tmem_base + buf * kAccCols + k * NTOK, ad, bd, idesc, 0u);
+                        umma_mxf8(tmem_base + buf * kAccCols, ad, bd, idesc | ((uint32_t)k << 29),
+                                  tmem_base + kSfBase + s * 4, tmem_base + kSfbCol, k > 0 ? 1u : 0u);
                     else
                         umma_f8f6f4(tmem_base + buf * kAccCols, ad, bd, idesc, k > 0 ? 1u : 0u);
                 }
@@ -199,6 +212,27 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             }
         };
         fetch(0);
+        /* mxfp4a8: stage x's scale word goes to tensor memory LEAD stages ahead of its MMAs; the
+         * column set belongs to the smem stage slot, free once the MMAs of stage x - stages retired */
+        auto prepare = [&](int x, uint32_t sw) -> bool {
+            const int s = x % kTcStages;
+            if (!mbar_wait(&empty[s], ((x / kTcStages) & 1) ^ 1, 16)) return false;
+            tc_fence_after();
+            tmem_st1(tlane + kSfBase + s * 4 + q, sw);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&prep[s]);
+            return true;
+        };
+        if (FMT == TC_MXFP4) {
+            /* the token-side scale factors are 2^0 everywhere */
+#pragma unroll
+            for (int c = 0; c < 8; ++c) tmem_st1(tlane + kSfbCol + c, 0x7f7f7f7fu);
+#pragma unroll
+            for (int x = 0; x < LEAD; ++x)
+                if (x < nk && alive) alive = prepare(x, swn[x]);
+        }
         for (int blk = 0; blk * PF < nk && alive; ++blk) {
             float sbc[PF];
             uint32_t swc[PF];
@@ -210,6 +244,10 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                 const int it = blk * PF + j8;
                 if (it >= nk) break;
                 const int buf = it % kBufs;
+                if (FMT == TC_MXFP4 && it + LEAD < nk) {
+                    alive = prepare(it + LEAD, j8 + LEAD < PF ? swc[(j8 + LEAD) % PF] : swn[(j8 + LEAD) % PF]);
+                    if (!alive) break;
+                }
                 if (!mbar_wait(&acc_full[buf], (it / kBufs) & 1, 14)) { alive = false; break; }
                 tc_fence_after();
                 const float* sa = as_s + (it0 + it) * NTOK;
@@ -229,25 +267,14 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                         else acc[t] += (c[t] * sa[t]) * sb;
                     }
                 } else {
-                    const uint32_t sw = swc[j8];
-                    float c[4][ML];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) tmem_ld<ML>(tlane + buf * kAccCols + j * NTOK, c[j]);
+                    float c[ML];
+                    tmem_ld<ML>(tlane + buf * kAccCols, c);
                     tmem_ld_wait();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
-                    float sj[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) sj[j] = e8m0_to_f32((uint8_t)(sw >> (8 * j)));
-#pragma unroll
-                    for (int t = 0; t < ML; ++t) {
-                        float ts = c[0][t] * sj[0];
-                        ts = fmaf(c[1][t], sj[1], ts);
-                        ts = fmaf(c[2][t], sj[2], ts);
-                        ts = fmaf(c[3][t], sj[3], ts);
-                        acc[t] += ts * sa[t];
-                    }
+                    for (int t = 0; t < ML; ++t) acc[t] += c[t] * sa[t];
                 }
             }
         }
@@ -360,7 +387,7 @@ int sm_count();
 template <int FMT, int NTOK, int ML, int kTcStages, int LG>
 int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaStream_t st) {
     const size_t smem = 1024 + (size_t)kTcStages * (kABytes + NTOK * kStageK) +
-                        (2 * kTcStages + 8) * sizeof(uint64_t) + 16 +
+                        (3 * kTcStages + 8) * sizeof(uint64_t) + 16 +
                         (size_t)(P.k / kStageK) * NTOK * sizeof(float);
     if (smem > 220 * 1024) return RAD_E_UNSUPPORTED;
     static size_t attr_set = 0;
@@ -376,10 +403,12 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
      * bytes in flight), never more shares than whole stages, at most 8 (portable cluster) */
     const int tiles = (P.n + kTileRows - 1) / kTileRows;
     static const int forced = [] { const char* e = getenv("R3D_TC_KSPLIT"); return e ? atoi(e) : 0; }();
-    /* measured: a CTA costs ~3 us of fill and drain, so K is split only when the row tiles
-     * alone cannot occupy the machine */
-    int ks = forced > 0 ? forced : (tiles >= sm_count() / 2 ? 1 : tiles >= sm_count() / 4 ? 2 : 4);
+    /* one CTA streams at most ~25-50 GB/s (ring depth over latency), so a grid needs about two CTAs
+     * per SM to reach HBM speed: when the row tiles alone are fewer, K is shared by a cluster, as many
+     * ways as still fit one wave (a second wave costs more than it brings), at least two stages per share */
+    int ks = forced > 0 ? forced : (tiles >= sm_count() ? 1 : 2 * sm_count() / tiles);
     if (ks > 8) ks = 8;
+    if (forced <= 0 && ks > P.k / kStageK / 2) ks = P.k / kStageK / 2;
     if (ks > P.k / kStageK) ks = P.k / kStageK;
     if (ks < 1) ks = 1;
     P.ksplit = ks;
@@ -403,7 +432,7 @@ template <int FMT, int NTOK, int ML, int LG = 0>
 int launch_tc(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaStream_t st) {
     /* the deepest ring that still lets two CTAs share an SM (233472 bytes of shared memory,
      * 1 KiB of it reserved per CTA): two CTAs' streams together are what saturates HBM */
-    const size_t fixed = 1024 + (2 * 6 + 8) * sizeof(uint64_t) + 16 + (size_t)(P.k / kStageK) * NTOK * sizeof(float);
+    const size_t fixed = 1024 + (3 * 6 + 8) * sizeof(uint64_t) + 16 + (size_t)(P.k / kStageK) * NTOK * sizeof(float);
     const size_t stage = kABytes + NTOK * kStageK;
     const size_t half = 233472 / 2 - 1024;
     if (fixed + 6 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 6, LG>(tw, ta, P, st);

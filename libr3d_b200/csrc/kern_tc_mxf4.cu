@@ -91,9 +91,6 @@ __device__ __forceinline__ uint64_t piece_codes(uint32_t b) {
     return ((uint64_t)hi << (4 * j)) | ((uint64_t)lo << (4 * (6 + j)));
 }
 
-__device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t v) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
-}
 __device__ __forceinline__ void umma_mxf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                           uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
     asm volatile(
@@ -426,12 +423,13 @@ int launch_s(const CUtensorMap* tw, const CUtensorMap* ts, const CUtensorMap* tp
                                    (int)cudaSharedmemCarveoutMaxShared);
         attr_set = smem;
     }
-    /* K shares per row tile: split K over a cluster only when the row tiles alone cannot occupy the
-     * machine (a CTA costs ~3 us of fill and drain); shares are whole scale tiles (4 stages) */
+    /* K shares per row tile: about two CTAs per SM are needed to reach HBM speed; when the row tiles
+     * alone are fewer, K is shared by a cluster, as many ways as still fit one wave; shares are whole
+     * scale tiles (4 stages) */
     P4 Q = P;
     const int tiles = (P.n + kRows - 1) / kRows, nk_all = P.k / kStageK;
     static const int forced = [] { const char* e = getenv("R3D_TC_KSPLIT"); return e ? atoi(e) : 0; }();
-    int ks = forced > 0 ? forced : (tiles >= tc_sm_count() / 2 ? 1 : tiles >= tc_sm_count() / 4 ? 2 : 4);
+    int ks = forced > 0 ? forced : (tiles >= tc_sm_count() ? 1 : 2 * tc_sm_count() / tiles);
     if (ks > 8) ks = 8;
     int per = nk_all;
     for (; ks > 1; --ks) {

@@ -68,7 +68,8 @@ static int auto_arm_fp8a8(const R3dGemmQ& q) {
 }
 static int auto_arm_mxfp4a8(const R3dGemmQ& q) {
     static const bool pack_off = [] { const char* e = getenv("R3D_NO_PACK"); return e && *e && *e != '0'; }();
-    if (!pack_off && tc_mxf4_ok(q)) return R3D_ARM_PACK;
+    /* measured: above M = 4 the packed kernel's single accumulator buffer loses to the unpacking kernel */
+    if (!pack_off && q.m <= 4 && tc_mxf4_ok(q)) return R3D_ARM_PACK;
     R3dGemmQ probe = q; if (probe.m > 32) probe.m = 32;
     if (tc_mxfp4a8_ok(probe)) return R3D_ARM_TILE;
     probe = q; if (probe.m > 64) probe.m = 64;
@@ -205,7 +206,7 @@ extern "C" int r3d_b200_gemm_mxfp4a8_push(const R3dGemmQ* q, void* gather, int s
     if (!gather_push_cfg((const Gather*)gather, slot, n_pad, q->m, 2, &cfg)) return RAD_E_INVAL;
     cudaStream_t st = (cudaStream_t)stream;
     if (q->arm == R3D_ARM_AUTO || q->arm == R3D_ARM_PACK || q->arm == R3D_ARM_TILE) {
-        if (q->arm != R3D_ARM_TILE && tc_mxf4_ok(*q)) { debug_arm("mxfp4a8", "tcgen05 packed + push", q->m); return tc_mxf4(*q, st, &cfg); }
+        if (q->arm != R3D_ARM_TILE && (q->m <= 4 || q->arm == R3D_ARM_PACK) && tc_mxf4_ok(*q)) { debug_arm("mxfp4a8", "tcgen05 packed + push", q->m); return tc_mxf4(*q, st, &cfg); }
         if (q->m <= 32 && tc_mxfp4a8_ok(*q)) { debug_arm("mxfp4a8", "tcgen05 + push", q->m); return tc_mxfp4a8(*q, st, &cfg); }
     }
     if (!q->y) return RAD_E_INVAL;

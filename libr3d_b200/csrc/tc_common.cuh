@@ -167,6 +167,19 @@ __device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) 
     return v;
 }
 
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+/* kind::mxf8f6f4 with hardware block scaling, one E8M0 scale per operand row per K=32 instruction:
+ * the scale words live in tensor memory at sfa / sfb */
+__device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate) : "memory");
+}
 /* Programmatic dependent launch: the next kernel in the stream may start its own prologue as
  * soon as every CTA of this grid has said so; a kernel reads what its predecessor wrote only
  * after dep_wait(), which returns once the predecessor has completed and flushed. */
