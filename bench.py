@@ -418,9 +418,22 @@ def main():
                                        dtype="mxfp4a8", N=N_DIM, K=K_DIM, row=args.row)
     gathered = {m: torch.empty((world * m, N_DIM), dtype=torch.bfloat16, device=dev) for m in MS} if world > 1 else None
     push = world > 1 and args.gather == "push"
+    gather_note = ""
     if push:
-        # the all-gather fused into the GEMV epilogue: peer stores over NVLink + flags, two slots
-        pg = shard.PushGather(P, slot_bytes=max(MS) * world * N_DIM * 2, slots=2)
+        # the all-gather fused into the GEMV epilogue: peer stores over NVLink + flags, two slots.
+        # Every rank must get its peer mappings; if one cannot, all ranks take the NCCL form.
+        pg, err = None, ""
+        try:
+            pg = shard.PushGather(P, slot_bytes=max(MS) * world * N_DIM * 2, slots=2)
+        except Exception as e:                                  # noqa: BLE001 - reported in the JSON line
+            err = f"{type(e).__name__}: {e}"
+        okt = torch.tensor([1 if pg is not None else 0], device=dev)
+        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+        if int(okt.item()) == 0:
+            push, gather_note = False, f"fused gather unavailable ({err or 'a peer failed'}): NCCL all_gather used"
+            if pg is not None:
+                pg.close()
+    if push:
         pushed = {(m, p): shard.PushedGemm(pg, acts[m][0], acts[m][1], planes[p][0], planes[p][1], dtype="mxfp4a8",
                                            M=m, n_local=N_DIM, n_pad=N_DIM, K=K_DIM, scratch=outs[m])
                   for m in MS for p in range(rot)}
@@ -572,7 +585,8 @@ def main():
                        "timed_as": "CUDA graph replay of recorded steps" if graph is not None else "direct issue",
                        "parallelism": "1 GPU" if world == 1 else
                                       (f"column slabs x{world}, all-gather fused into the GEMV epilogue (peer stores + flags)"
-                                       if push else f"column slabs x{world} + NCCL all_gather per call")},
+                                       if push else f"column slabs x{world} + NCCL all_gather per call"
+                                       + (f" [{gather_note}]" if gather_note else ""))},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": which, "traffic": traffic,
                          "kernel": "k_tc_mxf4<NP,MT> (one per call, after its k_mxf4_split)", "bytes_per_launch": STEP_BYTES / 3,

@@ -403,12 +403,11 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
      * bytes in flight), never more shares than whole stages, at most 8 (portable cluster) */
     const int tiles = (P.n + kTileRows - 1) / kTileRows;
     static const int forced = [] { const char* e = getenv("R3D_TC_KSPLIT"); return e ? atoi(e) : 0; }();
-    /* one CTA streams at most ~25-50 GB/s (ring depth over latency), so a grid needs about two CTAs
-     * per SM to reach HBM speed: when the row tiles alone are fewer, K is shared by a cluster, as many
-     * ways as still fit one wave (a second wave costs more than it brings), at least two stages per share */
-    int ks = forced > 0 ? forced : (tiles >= sm_count() ? 1 : 2 * sm_count() / tiles);
+    /* measured: a CTA costs ~3 us of fill and drain and a cluster's reduction more per member, so K
+     * is split only when the row tiles alone cannot occupy the machine, and at most four ways
+     * (six to eight shares of the same shapes ran 40 % slower than four) */
+    int ks = forced > 0 ? forced : (tiles >= sm_count() / 2 ? 1 : tiles >= sm_count() / 4 ? 2 : 4);
     if (ks > 8) ks = 8;
-    if (forced <= 0 && ks > P.k / kStageK / 2) ks = P.k / kStageK / 2;
     if (ks > P.k / kStageK) ks = P.k / kStageK;
     if (ks < 1) ks = 1;
     P.ksplit = ks;

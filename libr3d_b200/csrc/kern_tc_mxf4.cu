@@ -423,13 +423,12 @@ int launch_s(const CUtensorMap* tw, const CUtensorMap* ts, const CUtensorMap* tp
                                    (int)cudaSharedmemCarveoutMaxShared);
         attr_set = smem;
     }
-    /* K shares per row tile: about two CTAs per SM are needed to reach HBM speed; when the row tiles
-     * alone are fewer, K is shared by a cluster, as many ways as still fit one wave; shares are whole
-     * scale tiles (4 stages) */
+    /* K shares per row tile: split K over a cluster only when the row tiles alone cannot occupy the
+     * machine, at most four ways (measured); shares are whole scale tiles (4 stages) */
     P4 Q = P;
     const int tiles = (P.n + kRows - 1) / kRows, nk_all = P.k / kStageK;
     static const int forced = [] { const char* e = getenv("R3D_TC_KSPLIT"); return e ? atoi(e) : 0; }();
-    int ks = forced > 0 ? forced : (tiles >= tc_sm_count() ? 1 : 2 * tc_sm_count() / tiles);
+    int ks = forced > 0 ? forced : (tiles >= tc_sm_count() / 2 ? 1 : tiles >= tc_sm_count() / 4 ? 2 : 4);
     if (ks > 8) ks = 8;
     int per = nk_all;
     for (; ks > 1; --ks) {

@@ -68,14 +68,20 @@ class PushGather:
         handle = C.create_string_buffer(64)
         ptr = C.c_void_p()
         rc = self.lib.r3d_b200_gather_create(self.world, self.rank, slot_bytes, slots, C.byref(ptr), handle)
-        if rc != 0:
-            raise RuntimeError(f"r3d_b200_gather_create failed with status {rc}")
-        self.ptr = ptr
+        self.ptr = ptr if rc == 0 else None
+        # every rank takes part in both exchanges whatever happened locally, so that a failure on
+        # one rank becomes the same exception on all of them instead of a stuck collective
         handles: list = [None] * self.world
-        dist.all_gather_object(handles, handle.raw, group=group)
-        rc = self.lib.r3d_b200_gather_connect(self.ptr, b"".join(handles))
-        if rc != 0:
-            raise RuntimeError(f"r3d_b200_gather_connect failed with status {rc}")
+        dist.all_gather_object(handles, handle.raw if rc == 0 else None, group=group)
+        if rc == 0 and all(h is not None for h in handles):
+            rc = self.lib.r3d_b200_gather_connect(self.ptr, b"".join(handles))
+        elif rc == 0:
+            rc = -1
+        codes: list = [None] * self.world
+        dist.all_gather_object(codes, int(rc), group=group)
+        if any(c != 0 for c in codes):
+            self.close()
+            raise RuntimeError(f"fused gather set-up failed, per-rank status {codes}")
         dist.barrier(group=group)
 
     def buffer(self, slot: int, M: int, n_pad: int, dtype: torch.dtype) -> torch.Tensor:
@@ -99,9 +105,9 @@ class PushGather:
         return int(self.lib.r3d_b200_gather_status(self.ptr))
 
     def close(self) -> None:
-        if self.ptr:
+        if getattr(self, "ptr", None):
             self.lib.r3d_b200_gather_destroy(self.ptr)
-            self.ptr = None
+        self.ptr = None
 
 
 class PushedGemm:
