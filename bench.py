@@ -323,29 +323,35 @@ def run_all(args):
         del calls, keep
         torch.cuda.empty_cache()
 
-    decode_case("C1", "fp8a8", 1, 4096, 4096)
-    for M in (1, 2, 4):
-        decode_case("C2", "mxfp4a8", M, 27648, 5120)
-    for kind in ("fp8a8", "mxfp4a8"):
-        for (K, N) in ((5120, 6144), (5120, 5120), (5120, 27648), (13824, 5120)):
-            decode_case("C3", kind, 16, N, K)
-    for kind in ("fp8a8", "mxfp4a8"):
-        for (K, N) in ((5120, 27648), (13824, 5120)):
-            calls, keep, _ = gemm(kind, 8192, N, K, 1)
-            us = timed(calls, 5)
-            out.append({"cfg": "C4", "band": kind, "M": 8192, "N": N, "K": K, "us_per_call": round(us, 1),
-                        "TFLOPs": round(2 * 8192 * N * K / us / 1e6, 1),
-                        "nonzero_ok": int(torch.count_nonzero(keep[0][2].view(torch.int16))) > 0.9 * 8192 * N})
-            del calls, keep
-            torch.cuda.empty_cache()
+    want = set(c.strip().upper() for c in args.cfg.split(",")) if args.cfg else {"C1", "C2", "C3", "C4", "C5"}
+    if "C1" in want:
+        decode_case("C1", "fp8a8", 1, 4096, 4096)
+    if "C2" in want:
+        for M in (1, 2, 4):
+            decode_case("C2", "mxfp4a8", M, 27648, 5120)
+    if "C3" in want:
+        for kind in ("fp8a8", "mxfp4a8"):
+            for (K, N) in ((5120, 6144), (5120, 5120), (5120, 27648), (13824, 5120)):
+                decode_case("C3", kind, 16, N, K)
+    if "C4" in want:
+        MT = args.tokens
+        for kind in ("fp8a8", "mxfp4a8"):
+            for (K, N) in ((5120, 27648), (13824, 5120)):
+                calls, keep, _ = gemm(kind, MT, N, K, 1)
+                us = timed(calls, 5)
+                out.append({"cfg": "C4", "band": kind, "M": MT, "N": N, "K": K, "us_per_call": round(us, 1),
+                            "TFLOPs": round(2 * MT * N * K / us / 1e6, 1),
+                            "nonzero_ok": int(torch.count_nonzero(keep[0][2].view(torch.int16))) > 0.9 * MT * N})
+                del calls, keep
+                torch.cuda.empty_cache()
     # C5: e4m3 head with a bf16 scale per 128x128 block, f32 logits
     NV, K = 151936, 5120
     heads = []
-    for _ in range(2):
+    for _ in range(2 if "C5" in want else 0):
         codes = torch.randint(0, 127, (NV, K), dtype=torch.uint8, device=dev, generator=g)
         scale = (torch.rand(((NV + 127) // 128, K // 128), device=dev, generator=g) * 0.01 + 0.001).to(torch.bfloat16)
         heads.append((codes, scale))
-    for M in (1, 4, 16):
+    for M in ((1, 4, 16) if "C5" in want else ()):
         x = torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
         y = torch.zeros((M, NV), dtype=torch.float32, device=dev)
         ls = []
@@ -378,6 +384,8 @@ def main():
     ap.add_argument("--rot", type=int, default=4, help="distinct weight planes cycled (footprint > L2)")
     ap.add_argument("--row", default="gemm_nt_q_mxfp4_decode")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--cfg", default="", help="--workload all: comma list of configurations to run (C1..C5), default all")
+    ap.add_argument("--tokens", type=int, default=8192, help="--workload all: M of the prefill configuration C4")
     ap.add_argument("--gather", default="push", choices=["push", "nccl"],
                     help="N > 1: all-gather fused into the GEMV epilogue (push) or NCCL after it")
     ap.add_argument("--workload", default="c2", help="c2 (default, the headline), c5 (sharded LM head) or all (every configuration, one GPU)")
