@@ -256,6 +256,7 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                     float c[ML];
                     tmem_ld<ML>(tlane + buf * kAccCols, c);
                     tmem_ld_wait();
+                    tmem_pin<ML>(c);
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
@@ -270,6 +271,7 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                     float c[ML];
                     tmem_ld<ML>(tlane + buf * kAccCols, c);
                     tmem_ld_wait();
+                    tmem_pin<ML>(c);
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);

@@ -3,9 +3,9 @@
  *
  * Orientation is the decode kernels': weight rows on the MMA's M axis (one TMEM lane per weight
  * row), tokens on its N axis (192 columns: two accumulator buffers plus the scale-factor columns fit
- * tensor memory, and 96 running sums per epilogue thread fit the register file without spills). Both operand tiles arrive by TMA in the
+ * tensor memory, and the running sums of an epilogue thread, 64 with twelve epilogue warps, fit the register file). Both operand tiles arrive by TMA in the
  * 128-byte-swizzled layout; four K=32 MMAs per stage accumulate one 128-column group of K in
- * one TMEM buffer while the eight epilogue warps drain the other:
+ * one TMEM buffer while the twelve epilogue warps drain the other:
  *   fp8a8    kind::f8f6f4;   acc[t] += sub128[t] * (sa[t,g] * sb[row/128,g])  (block grid), or
  *                            acc[t] += (sub128[t] * sa[t,g]) * sb[row,g]      (per-row grid)
  *   mxfp4a8  kind::mxf8f6f4.block_scale: the e2m1 nibbles are unpacked by the tensor map, the
@@ -16,8 +16,8 @@
  * src/r3d_gemm_fp8a8.hip:194-335, src/r3d_gemm_mxfp4.hip:176-355 of libr3d): a tolerance-class
  * walk, graded against the oracle at 2 bf16 ulp.
  *
- * Warp roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-9 epilogue (warp
- * w: TMEM lane quarter w & 3, token half (w - 2) / 4). Every wait is bounded; on expiry a status
+ * Warp roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-13 epilogue (warp
+ * w: TMEM lane quarter w & 3, token third (w - 2) / 4), warp 14 scale warp. Every wait is bounded; on expiry a status
  * word is set and the CTA drains, frees its TMEM and leaves without storing.
  */
 #include <cstdio>
@@ -32,11 +32,13 @@ namespace r3d {
 namespace {
 using namespace tcdev;
 
-constexpr int kThreads = 352;                     /* producer, MMA, 8 epilogue warps, scale warp */
+constexpr int kEpiParts = 3;                       /* epilogue warps per TMEM lane quarter: each takes kTok / 3 tokens */
+constexpr int kEpiWarps = 4 * kEpiParts;
+constexpr int kThreads = 32 * (2 + kEpiWarps + 1); /* producer, MMA, 12 epilogue warps, scale warp */
 constexpr int kFs = 4;                             /* ring of per-token factor vectors */
 constexpr int kRows = 128;                         /* weight rows per tile */
 constexpr int kTok = 192;                          /* tokens per tile */
-constexpr int kHalf = kTok / 2;                    /* tokens per epilogue warp */
+constexpr int kHalf = kTok / kEpiParts;            /* tokens per epilogue warp: 64 */
 constexpr int kStageK = 128;
 constexpr int kWBytes = kRows * kStageK;           /* 16 KiB (as laid out in shared memory) */
 constexpr int kABytes = kTok * kStageK;            /* 30 KiB */
@@ -76,7 +78,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     uint64_t* sc_full = prep + kSfSlots;
     uint64_t* sc_empty = sc_full + kScTiles;
     uint64_t* f_full = sc_empty + kScTiles;                       /* [kFs] factor vector written */
-    uint64_t* f_empty = f_full + kFs;                             /* [kFs] ... and read by all eight epilogue warps */
+    uint64_t* f_empty = f_full + kFs;                             /* [kFs] ... and read by all epilogue warps */
     uint32_t* tmem_slot = (uint32_t*)(f_empty + kFs);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -87,10 +89,10 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], kEpiWarps); }
         for (int b = 0; b < kSfSlots; ++b) mbar_init(&prep[b], 4);
         for (int b = 0; b < kScTiles; ++b) { mbar_init(&sc_full[b], 1); mbar_init(&sc_empty[b], 4); }
-        for (int b = 0; b < kFs; ++b) { mbar_init(&f_full[b], 1); mbar_init(&f_empty[b], 8); }
+        for (int b = 0; b < kFs; ++b) { mbar_init(&f_full[b], 1); mbar_init(&f_empty[b], kEpiWarps); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -99,12 +101,12 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                      ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (warp >= 1 && warp <= 9) {
+    if (warp >= 1 && warp <= 1 + kEpiWarps) {
         tc_fence_before();
-        asm volatile("bar.sync 2, 288;" ::: "memory");
+        asm volatile("bar.sync 2, %0;" ::"n"(32 * (1 + kEpiWarps)) : "memory");
         tc_fence_after();
     }
-    const uint32_t tmem_base = (warp >= 1 && warp <= 9) ? *tmem_slot : 0u;
+    const uint32_t tmem_base = (warp >= 1 && warp <= 1 + kEpiWarps) ? *tmem_slot : 0u;
     bool alive = true;
 
     if (warp == 0) {
@@ -162,14 +164,15 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                 umma_commit(&acc_full[ab]);
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == 2 + kEpiWarps) {
         /* ---------------- scale warp: the per-token factor of every stage ----------------
          * factor[t] = sa[t, g] (times the tile's weight scale on the fp8 block grid). Lane l owns
-         * tokens l, l+32, ...; values are fetched a block of eight stages ahead so that no stage
-         * waits on a global load. */
+         * tokens l, l+32, ...; values are fetched eight stages ahead (two blocks of four) so that no
+         * stage waits on a global load. */
         constexpr bool block_grid = FMT == G_FP8;
-        constexpr int TPL = (kTok + 31) / 32;                          /* tokens per lane: 8 */
-        float cur[TPL][8], nxt[TPL][8], wcur[8], wnxt[8];
+        constexpr int TPL = (kTok + 31) / 32;                          /* tokens per lane: 6 */
+        constexpr int BLK = 4;                                         /* stages per prefetch block */
+        float cur[TPL][BLK], nxt[TPL][BLK], wcur[BLK], wnxt[BLK];
         const int n128 = nk;
         const float* pt[TPL];
 #pragma unroll
@@ -179,37 +182,39 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
         }
         const bool vec = P.as_cols == n128 && (P.as_pitch & 3) == 0 && (((uintptr_t)P.as) & 15) == 0;
         const int64_t wrow = (int64_t)(r0 / kRows) * P.ws_pitch;
-        auto load_block = [&](int b, float (*f)[8], float* w) {
-            const bool whole = 8 * b + 8 <= nk;
+        auto load_block = [&](int b, float (*f)[BLK], float* w) {
+            const bool whole = BLK * b + BLK <= nk;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int x = 8 * b + j;
+            for (int j = 0; j < BLK; ++j) {
+                const int x = BLK * b + j;
                 w[j] = (block_grid && x < nk) ? ld_scale(P.ws, wrow + (P.ws_cols == n128 ? x : scale_col(x, P.ws_cols, n128)), P.ws_dtype) : 1.0f;
             }
 #pragma unroll
             for (int i = 0; i < TPL; ++i) {
-                if (pt[i] == nullptr || 8 * b >= nk) {
+                if (pt[i] == nullptr || BLK * b >= nk) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) f[i][j] = 0.0f;
+                    for (int j = 0; j < BLK; ++j) f[i][j] = 0.0f;
                 } else if (vec && whole) {
-                    const float4 lo = __ldg((const float4*)(pt[i] + 8 * b)), hi = __ldg((const float4*)(pt[i] + 8 * b + 4));
-                    f[i][0] = lo.x; f[i][1] = lo.y; f[i][2] = lo.z; f[i][3] = lo.w;
-                    f[i][4] = hi.x; f[i][5] = hi.y; f[i][6] = hi.z; f[i][7] = hi.w;
+                    const float4 v = __ldg((const float4*)(pt[i] + BLK * b));
+                    f[i][0] = v.x; f[i][1] = v.y; f[i][2] = v.z; f[i][3] = v.w;
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int x = 8 * b + j;
+                    for (int j = 0; j < BLK; ++j) {
+                        const int x = BLK * b + j;
                         f[i][j] = x < nk ? __ldg(pt[i] + scale_col(x, P.as_cols, n128)) : 0.0f;
                     }
                 }
             }
         };
+        /* two blocks (eight stages) are in flight ahead of the one being handed out */
+        float nx2[TPL][BLK], wnx2[BLK];
         load_block(0, cur, wcur);
-        for (int b8 = 0; b8 * 8 < nk; ++b8) {
-            load_block(b8 + 1, nxt, wnxt);
+        load_block(1, nxt, wnxt);
+        for (int b4 = 0; b4 * BLK < nk; ++b4) {
+            load_block(b4 + 2, nx2, wnx2);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int it = b8 * 8 + j;
+            for (int j = 0; j < BLK; ++j) {
+                const int it = b4 * BLK + j;
                 if (it >= nk) break;
                 const int sl = it % kFs;
                 if (!mbar_wait(&f_empty[sl], ((it / kFs) & 1) ^ 1, 48)) { alive = false; break; }
@@ -221,14 +226,14 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
             }
             if (!alive) break;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                wcur[j] = wnxt[j];
+            for (int j = 0; j < BLK; ++j) {
+                wcur[j] = wnxt[j]; wnxt[j] = wnx2[j];
 #pragma unroll
-                for (int i = 0; i < TPL; ++i) cur[i][j] = nxt[i][j];
+                for (int i = 0; i < TPL; ++i) { cur[i][j] = nxt[i][j]; nxt[i][j] = nx2[i][j]; }
             }
         }
     } else {
-        /* ---------------- epilogue: thread = weight row, warp half = token half ---------------- */
+        /* ---------------- epilogue: thread = weight row, warp part = token third ---------------- */
         const int q = warp & 3, half = (warp - 2) >> 2;
         const int row = r0 + q * 32 + lane;
         const int rowc = min(row, P.n - 1);
@@ -282,6 +287,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 #pragma unroll
             for (int ch = 0; ch < kHalf / 16; ++ch) {
                 tmem_ld_wait();
+                tmem_pin16(c[ch & 1]);
                 if (ch + 1 < kHalf / 16) tmem_ld16(ta + (ch + 1) * 16, c[(ch + 1) & 1]);
                 else {
                     tc_fence_before();

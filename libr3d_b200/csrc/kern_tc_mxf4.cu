@@ -134,7 +134,8 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     uint64_t* sc_full = acc_empty + 4;
     uint64_t* sc_empty = sc_full + kScTiles;
     uint32_t* tmem_slot = (uint32_t*)(sc_empty + kScTiles);
-    float* as_s = (float*)(tmem_slot + 4);                        /* [n128][MT] */
+    uint32_t* nan_s = tmem_slot + 4;                              /* [8] token held an e4m3 NaN (from the split kernel's flags) */
+    float* as_s = (float*)(nan_s + 8);                            /* [n128][MT] */
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ks = P.ksplit;
@@ -267,8 +268,15 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 #pragma unroll
         for (int x = 0; x < LEAD; ++x)
             if (x < nk && alive) alive = prepare(x);
-        /* the activation scales are the previous kernel's output */
+        /* the activation scales and the NaN flags are the previous kernels' output */
         dep_wait();
+        if (threadIdx.x - 64 < MT) {
+            const int t = threadIdx.x - 64;
+            uint32_t nan = 0u;
+            if (t < P.m)
+                for (int b = 0; b < P.nan_blocks; ++b) nan |= __ldg(P.nanflag + t * P.nan_blocks + b);
+            nan_s[t] = nan;
+        }
         for (int i = threadIdx.x - 64; i < n128 * MT; i += 128) {
             const int g = i / MT, t = i - g * MT;
             const int c = P.as_cols == n128 ? g : (P.as_cols == 1 ? 0 : (int)((int64_t)g * P.as_cols / n128));
@@ -285,24 +293,53 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
             tc_fence_after();
             constexpr int NC = (MT * kPieces + 15) / 16 * 16;       /* piece columns read per group */
             const float* sa = as_s + (2 * (it0 + it)) * MT;
+            if (MT <= 4) {
+                /* both 128-column groups in one round trip to tensor memory */
+                float c[2][NC];
 #pragma unroll
-            for (int g = 0; g < 2; ++g) {
-                float c[NC];
-                const uint32_t ta = tlane + ab * kAccCols + g * NP;
-#pragma unroll
-                for (int h = 0; h < NC / 16; ++h) tmem_ld16(ta + h * 16, c + h * 16);
-                tmem_ld_wait();
-                if (g == 1) {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[ab]);
+                for (int g = 0; g < 2; ++g) {
+                    const uint32_t ta = tlane + ab * kAccCols + g * NP;
+                    tmem_ld16(ta, c[g]);
+                    if (NC > 16) tmem_ld16(ta + 16, c[g] + 16);
+                    if (NC > 32) tmem_ld16(ta + 32, c[g] + 32);
                 }
+                tmem_ld_wait();
+                tmem_pin<NC>(c[0]);
+                tmem_pin<NC>(c[1]);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[ab]);
 #pragma unroll
                 for (int t = 0; t < MT; ++t) {
-                    float v = c[t * kPieces] * wj[0];
 #pragma unroll
-                    for (int j = 1; j < kPieces; ++j) v = fmaf(c[t * kPieces + j], wj[j], v);
-                    acc[t] += v * sa[g * MT + t];
+                    for (int g = 0; g < 2; ++g) {
+                        float v = c[g][t * kPieces] * wj[0];
+#pragma unroll
+                        for (int j = 1; j < kPieces; ++j) v = fmaf(c[g][t * kPieces + j], wj[j], v);
+                        acc[t] += v * sa[g * MT + t];
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    float c[NC];
+                    const uint32_t ta = tlane + ab * kAccCols + g * NP;
+#pragma unroll
+                    for (int h = 0; h < NC / 16; ++h) tmem_ld16(ta + h * 16, c + h * 16);
+                    tmem_ld_wait();
+                    tmem_pin<NC>(c);
+                    if (g == 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[ab]);
+                    }
+#pragma unroll
+                    for (int t = 0; t < MT; ++t) {
+                        float v = c[t * kPieces] * wj[0];
+#pragma unroll
+                        for (int j = 1; j < kPieces; ++j) v = fmaf(c[t * kPieces + j], wj[j], v);
+                        acc[t] += v * sa[g * MT + t];
+                    }
                 }
             }
         }
@@ -327,9 +364,7 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 #pragma unroll
         for (int t = 0; t < MT; ++t) {
             if (t >= P.m) break;
-            uint32_t nan = 0u;
-            for (int b = 0; b < P.nan_blocks; ++b) nan |= __ldg(P.nanflag + t * P.nan_blocks + b);
-            const float v = nan ? __int_as_float(0x7fc00000) : acc[t];
+            const float v = nan_s[t] ? __int_as_float(0x7fc00000) : acc[t];
             if (P.push.world) push_store<uint16_t>(P.push, t, row, f32_to_bf16(v));
             else P.y[(int64_t)t * P.y_pitch + row] = f32_to_bf16(v);
         }

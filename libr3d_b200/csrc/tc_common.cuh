@@ -140,6 +140,24 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, float* v) {
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+/* tcgen05.ld is asynchronous: its destination registers hold the data only after tcgen05.wait::ld.
+ * The wait instruction does not name those registers, so nothing stops the compiler from moving
+ * arithmetic on them above it. These empty statements "rewrite" the registers right after the wait
+ * (volatile statements keep their order), which pins every use behind it. */
+__device__ __forceinline__ void tmem_pin8(float* v) {
+    asm volatile("" : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]));
+}
+__device__ __forceinline__ void tmem_pin16(float* v) { tmem_pin8(v); tmem_pin8(v + 8); }
+template <int N>
+__device__ __forceinline__ void tmem_pin(float* v) {
+    if (N == 1) asm volatile("" : "+f"(v[0]));
+    else if (N == 2) asm volatile("" : "+f"(v[0]), "+f"(v[1]));
+    else if (N == 4) asm volatile("" : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]));
+    else {
+#pragma unroll
+        for (int i = 0; i < N / 8; ++i) tmem_pin8(v + 8 * i);
+    }
+}
 
 __device__ __forceinline__ float ld_scale(const uint8_t* base, int64_t idx, int dt) {
     if (dt == RAD_F32) return __ldg((const float*)base + idx);
