@@ -15,8 +15,13 @@ over the next of `rot` distinct weight planes so that the stream never comes fro
   roofline   the streaming kernel's algorithmic bytes per launch / its mean launch time
   cpu_baseline  the CPU restatement (oracle/) of the same step on the host cores, bounded sample
 
-N > 1: every rank holds its own 27648-row slab (weak scaling: the sharded layer is G x wider),
-runs the same step and all-gathers each bf16 output over NCCL; time = max over ranks.
+N > 1: every rank holds its own 27648-row slab (weak scaling: the sharded layer is G x wider) and
+runs the same step; the all-gather of each bf16 output is fused into the GEMV epilogue (peer
+stores over NVLink + a bounded device-side wait, --gather push, the default) or done by NCCL after
+the kernel (--gather nccl); time = max over ranks.
+
+--workload c5: the column-sharded LM head (strong scaling). --workload all [--cfg C1,..,C5]: every
+configuration of the hot path on one GPU, one line each.
 
 --impl reference: the reference's arithmetic for this path on the host cores (the CPU
 restatement: the reference's kernels are HIP and cannot build here), same metric and config.
