@@ -64,6 +64,35 @@ def ref_pin() -> C.CDLL | None:
     return _ref
 
 
+_ref_band = None
+
+
+def ref_band() -> C.CDLL | None:
+    """The reference's activation-producer file (src/r3d_band.hip of libr3d) compiled as it lies by
+    nvcc through oracle/hipstub (oracle/_ref/libref_band.so), or None when it was not built.
+    Loading it needs the CUDA runtime library but no GPU for the CPU helpers."""
+    global _ref_band
+    if _ref_band is None:
+        so = HERE / "_ref" / "libref_band.so"
+        if not so.exists():
+            return None
+        try:
+            R = C.CDLL(str(so))
+        except OSError:
+            return None
+        R.ref_band_f32_to_e4m3.restype = C.c_ubyte
+        R.ref_band_f32_to_e4m3.argtypes = [C.c_float]
+        R.ref_band_f32_to_bf16.restype = C.c_ushort
+        R.ref_band_f32_to_bf16.argtypes = [C.c_float]
+        R.ref_band_sigmoid.restype = C.c_float
+        R.ref_band_sigmoid.argtypes = [C.c_float]
+        R.ref_band_f32_to_e4m3_n.argtypes = [C.c_void_p, C.c_longlong, C.c_void_p]
+        R.ref_band_quant_act_fp8.argtypes = [C.c_void_p, C.c_void_p]
+        R.ref_band_gated_quant_fp8.argtypes = [C.c_void_p, C.c_void_p]
+        _ref_band = R
+    return _ref_band
+
+
 def _p(a: np.ndarray | None):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 

@@ -152,3 +152,33 @@ def test_mx8_quantiser_rule():
     q, e = orc.quant_act_mx8(x)
     assert e[0, 0] == 127 + 8 - 8 and e[0, 1] == 127      # floor(log2 300) = 8
     assert L.orc_e4m3_to_f32(int(q[0, 0])) == 288.0 and L.orc_e4m3_to_f32(int(q[0, 1])) == 0.75
+
+
+def test_encoder_against_the_reference_file_compiled_as_it_lies():
+    """src/r3d_band.hip of libr3d, compiled where it lies (oracle/_ref/libref_band.so): its e4m3
+    encoder, bf16 narrowing and sigmoid against the oracle's restatements over every bf16-exact
+    float, every rounding midpoint of e4m3, a million random bit patterns and the specials."""
+    R = orc.ref_band()
+    if R is None:
+        pytest.skip("oracle/_ref/libref_band.so not built (reference tree or nvcc absent)")
+    rng = np.random.default_rng(0)
+    bits = np.concatenate([
+        (np.arange(1 << 16, dtype=np.uint32) << 16),                       # every bf16-exact float
+        rng.integers(0, 1 << 32, 1_000_000, dtype=np.uint64).astype(np.uint32),
+        np.array([0x7F800000, 0xFF800000, 0x7FC00000, 0xFFC00001, 0x43E00000, 0x43DFFFFF, 0x43E00001,
+                  0x3A800000, 0x3A7FFFFF, 0x3A000000, 0x39FFFFFF, 0x00000001, 0x80000001], np.uint32)])
+    x = bits.view(np.float32)
+    # every midpoint between neighbouring e4m3 values, and one ulp either side
+    vals = np.array([orc.lib().orc_e4m3_to_f32(c) for c in range(0x7F)], np.float32)
+    mid = ((vals[:-1].astype(np.float64) + vals[1:]) / 2).astype(np.float32)
+    x = np.concatenate([x, mid, -mid, np.nextafter(mid, np.float32(np.inf)), np.nextafter(mid, np.float32(-np.inf))])
+    want = np.empty(x.size, np.uint8)
+    R.ref_band_f32_to_e4m3_n(x.ctypes.data_as(orc.C.c_void_p), x.size, want.ctypes.data_as(orc.C.c_void_p))
+    got = np.empty(x.size, np.uint8)
+    orc.lib().orc_f32_to_e4m3_n(x.ctypes.data_as(orc.C.c_void_p), orc.I64(x.size), got.ctypes.data_as(orc.C.c_void_p))
+    assert np.array_equal(got, want)
+    some = x[::97]
+    assert all(orc.lib().orc_f32_to_bf16(float(v)) == R.ref_band_f32_to_bf16(float(v)) for v in some[np.isfinite(some)][:20000])
+    for v in (-1e9, -88.0, -10.5, -1.0, -1e-8, 0.0, 1e-8, 0.3, 1.0, 17.25, 88.0, 1e9):
+        e = np.float32(1) / (np.float32(1) + np.float32(np.exp(-np.float64(np.float32(v)))))
+        assert np.float32(R.ref_band_sigmoid(v)).view(np.uint32) == np.float32(e).view(np.uint32)
