@@ -93,6 +93,30 @@ def ref_band() -> C.CDLL | None:
     return _ref_band
 
 
+_ref_logits = None
+
+
+def ref_logits() -> C.CDLL | None:
+    """The reference's LM-head file (src/r3d_gemm_logits.hip of libr3d) compiled as it lies for
+    sm_100a (oracle/_ref/libref_logits.so), or None when it was not built."""
+    global _ref_logits
+    if _ref_logits is None:
+        so = HERE / "_ref" / "libref_logits.so"
+        if not so.exists():
+            return None
+        try:
+            R = C.CDLL(str(so))
+        except OSError:
+            return None
+        R.ref_logits_gemm_e4m3.argtypes = [C.c_void_p, C.c_void_p]
+        R.ref_logits_alloc.restype = C.c_void_p
+        R.ref_logits_alloc.argtypes = [C.c_longlong]
+        R.ref_logits_free.argtypes = [C.c_void_p]
+        R.ref_logits_free.restype = None
+        _ref_logits = R
+    return _ref_logits
+
+
 def _p(a: np.ndarray | None):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 

@@ -11,6 +11,7 @@
 #include <cstdlib>
 #include <cstring>
 #include "hip/hip_runtime.h"
+#include "ref_host_pass.h"
 #include "rad_abi.h"
 #include "rad_plugin.h"
 /* The file holds one empty `asm volatile("" : "+v"(..))` statement: an AMD vector-register

@@ -75,3 +75,41 @@ def test_gated_quant_fp8_matches_the_reference_kernel(rows, n, group, act):
     assert gu.same_bits_or_both_nan(o.view(torch.int16).cpu().numpy().view(np.uint16), o_ref.view(torch.int16).cpu().numpy().view(np.uint16)).all()
     want_q, want_s = orc.gated_quant_fp8(bits, g, act == "silu")
     assert np.array_equal(q_ref.cpu().numpy(), want_q) and np.array_equal(s_ref.cpu().numpy().view(np.uint32), want_s.view(np.uint32))
+
+
+@pytest.mark.parametrize("N,K,M,br,sdt", [(256, 512, 1, 128, 0), (130, 300, 5, 128, 0), (200, 512, 2, 1, 0),
+                                          (256, 384, 4, 128, 1), (256, 512, 8, 128, 2), (1000, 1024, 16, 128, 0),
+                                          (4096, 5120, 4, 128, 0)])
+def test_logits_kernels_against_the_reference_kernel(N, K, M, br, sdt):
+    """The reference's own logits_e4m3 kernel and entry (src/r3d_gemm_logits.hip of libr3d, compiled
+    for sm_100a into oracle/_ref/libref_logits.so) on the same head and activations: it re-associates
+    K across 32 lanes, so it is graded against the oracle at its own unit test's 1e-4, and this
+    library's arms are graded against IT at the same bound."""
+    from libr3d_b200.plugin import planes_blob
+    R = orc.ref_logits()
+    if R is None:
+        pytest.skip("oracle/_ref/libref_logits.so not present")
+    c = gen.case_logits(5 * N + K + M, M, N, K, br, sdt)
+    sdts = {0: abi.RAD_BF16, 1: abi.RAD_F16, 2: abi.RAD_F32}[sdt]
+    blob = planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), c["codes"]), ("scale", sdts, (br, 128), c["scale"])])
+    mem = R.ref_logits_alloc(len(blob))                 # managed: the reference entry reads the header on the host
+    assert mem
+    try:
+        C.memmove(mem, blob, len(blob))
+        x = gu.dev(c["X"]).view(torch.bfloat16)
+        y_ref = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+        pack = ArgPack([_desc(x, abi.RAD_BF16), tensor_desc(mem, abi.RAD_U8, [len(blob)]), _desc(y_ref, abi.RAD_F32)],
+                       dict(M=M, n_vocab=N, n_embd=K, dtype="bf16"))
+        assert R.ref_logits_gemm_e4m3(C.byref(pack.args), None) == 0
+        torch.cuda.synchronize()
+        ref = y_ref.cpu().numpy().astype(np.float64)
+        want = orc.logits_e4m3(c["X"], c["codes"], c["scale"], sdt, br).astype(np.float64)
+        rel = lambda a, b: np.abs(a - b).max() / max(np.abs(b).max(), 1e-6)
+        assert rel(ref, want) < 1e-4                    # the reference kernel against the oracle
+        arms = [abi.R3D_ARM_EXACT] + ([abi.R3D_ARM_STREAM] if K % 64 == 0 else []) + ([abi.R3D_ARM_TILE] if K % 128 == 0 else [])
+        for arm in arms:
+            got = gu.logits_launch(c, arm).astype(np.float64)
+            assert rel(got, ref) < 1e-4, arm            # this library against the reference kernel
+    finally:
+        torch.cuda.synchronize()
+        R.ref_logits_free(mem)
