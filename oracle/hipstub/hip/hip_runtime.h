@@ -15,9 +15,43 @@ typedef cudaError_t hipError_t;
 #define hipStreamSynchronize cudaStreamSynchronize
 #define hipGetErrorString cudaGetErrorString
 #define hipGetErrorName cudaGetErrorName
+#define hipGetDevice cudaGetDevice
+#define hipStreamNonBlocking cudaStreamNonBlocking
+#define hipStreamCreateWithFlags cudaStreamCreateWithFlags
+#define hipStreamDestroy cudaStreamDestroy
+#define hipDeviceSynchronize cudaDeviceSynchronize
+#define hipMalloc cudaMalloc
+#define hipFree cudaFree
+#define hipMemGetInfo cudaMemGetInfo
+#define hipMemcpyAsync cudaMemcpyAsync
+#define hipMemsetAsync cudaMemsetAsync
+#define hipLaunchKernelGGL(kern, grid, block, smem, stream, ...) kern<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__)
+/* the reference gates its kernels on the chip's architecture name: the pin answers with the one
+ * it expects, so that its own code paths run */
+struct hipDeviceProp_t { char gcnArchName[256]; int multiProcessorCount; size_t totalGlobalMem; };
+static inline cudaError_t hipGetDeviceProperties(hipDeviceProp_t* p, int dev) {
+    cudaDeviceProp q;
+    const cudaError_t e = cudaGetDeviceProperties(&q, dev);
+    strcpy(p->gcnArchName, "gfx1100");
+    p->multiProcessorCount = q.multiProcessorCount; p->totalGlobalMem = q.totalGlobalMem;
+    return e;
+}
 /* HIP's unsynchronised wave shuffles, on a 32-wide wave */
 #ifdef __CUDA_ARCH__
 #define __shfl_xor(v, m) __shfl_xor_sync(0xffffffffu, (v), (m))
 #define __shfl_down(v, d) __shfl_down_sync(0xffffffffu, (v), (d))
 #endif
 
+
+/* AMD cross-lane and dot builtins the reference's mxfp4 file uses, with the same meaning on a
+ * 32-wide warp: DPP row_xmask:k (control 0x160 | k) is "lane ^ k", permlanex16 with identity
+ * selectors is "lane ^ 16", sudot4 with both operands signed is the signed byte dot. */
+__device__ __forceinline__ int __builtin_amdgcn_update_dpp(int old, int src, int ctrl, int, int, bool) {
+    (void)old;
+    return __shfl_xor_sync(0xffffffffu, src, ctrl & 0xf);
+}
+__device__ __forceinline__ unsigned __builtin_amdgcn_permlanex16(unsigned old, unsigned src, unsigned, unsigned, bool, bool) {
+    (void)old;
+    return __shfl_xor_sync(0xffffffffu, src, 16);
+}
+__device__ __forceinline__ int __builtin_amdgcn_sudot4(bool, int a, bool, int b, int c, bool) { return __dp4a(a, b, c); }

@@ -117,6 +117,30 @@ def ref_logits() -> C.CDLL | None:
     return _ref_logits
 
 
+_ref_gemm: dict = {}
+
+
+def ref_gemm(which: str) -> C.CDLL | None:
+    """The reference's band files compiled as they lie for sm_100a: which = "fp8a8"
+    (src/r3d_gemm_fp8a8.hip -> oracle/_ref/libref_fp8a8.so; entries ref_fp8a8_gemm_nt_q, _decode, _gated)
+    or "mxfp4" (src/r3d_gemm_mxfp4.hip -> libref_mxfp4.so; ref_mxfp4_gemm_nt_q, _decode, _decode_q8x).
+    Every entry takes (const RadArgs*, stream). None when the library was not built."""
+    if which not in _ref_gemm:
+        so = HERE / "_ref" / f"libref_{which}.so"
+        R = None
+        if so.exists():
+            try:
+                R = C.CDLL(str(so))
+                for name in (("ref_fp8a8_gemm_nt_q", "ref_fp8a8_gemm_nt_q_decode", "ref_fp8a8_gemm_nt_q_gated")
+                             if which == "fp8a8" else
+                             ("ref_mxfp4_gemm_nt_q", "ref_mxfp4_gemm_nt_q_decode", "ref_mxfp4_gemm_nt_q_decode_q8x")):
+                    getattr(R, name).argtypes = [C.c_void_p, C.c_void_p]
+            except OSError:
+                R = None
+        _ref_gemm[which] = R
+    return _ref_gemm[which]
+
+
 def _p(a: np.ndarray | None):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 

@@ -113,3 +113,70 @@ def test_logits_kernels_against_the_reference_kernel(N, K, M, br, sdt):
     finally:
         torch.cuda.synchronize()
         R.ref_logits_free(mem)
+
+
+# ------------------------------------------------------------------ the reference's own GEMM kernels
+def _gemm_pack(t, kind, M, N, K, y):
+    bdesc = (_desc(t["B"], abi.RAD_F8E4M3) if kind == "fp8a8"
+             else tensor_desc(t["B"].data_ptr(), abi.RAD_FP4E2M1, [N, K], [K, 1]))
+    sdt = abi.RAD_BF16 if kind == "fp8a8" else abi.RAD_E8M0
+    tensors = [_desc(t["A"], abi.RAD_F8E4M3), _desc(t["AS"], abi.RAD_F32), bdesc, _desc(t["BS"], sdt),
+               _desc(y, abi.RAD_BF16), tensor_desc(None, abi.RAD_F32, []), tensor_desc(None, abi.RAD_BF16, [])]
+    return ArgPack(tensors, dict(M=M, N=N, K=K, group=128 if kind == "fp8a8" else 32, dtype=kind))
+
+
+@pytest.mark.parametrize("kind,entry,M,N,K", [
+    ("fp8a8", "ref_fp8a8_gemm_nt_q_decode", 1, 512, 1024), ("fp8a8", "ref_fp8a8_gemm_nt_q_decode", 4, 384, 2560),
+    ("fp8a8", "ref_fp8a8_gemm_nt_q_decode", 8, 1000, 512), ("fp8a8", "ref_fp8a8_gemm_nt_q", 16, 512, 1024),
+    ("fp8a8", "ref_fp8a8_gemm_nt_q", 100, 384, 512), ("fp8a8", "ref_fp8a8_gemm_nt_q", 1, 4096, 4096),
+    ("mxfp4a8", "ref_mxfp4_gemm_nt_q_decode", 1, 512, 1024), ("mxfp4a8", "ref_mxfp4_gemm_nt_q_decode", 4, 384, 2560),
+    ("mxfp4a8", "ref_mxfp4_gemm_nt_q_decode", 8, 1000, 512), ("mxfp4a8", "ref_mxfp4_gemm_nt_q", 16, 512, 1024),
+    ("mxfp4a8", "ref_mxfp4_gemm_nt_q", 100, 384, 512), ("mxfp4a8", "ref_mxfp4_gemm_nt_q_decode", 2, 27648, 5120)])
+def test_gemm_arms_against_the_reference_kernels(kind, entry, M, N, K):
+    """The reference's own band kernels and entries (src/r3d_gemm_fp8a8.hip, src/r3d_gemm_mxfp4.hip of
+    libr3d, compiled for sm_100a through the HIP / rocWMMA stand-ins) on the same operands. Graded
+    like everything else at 2 bf16 ulp: the reference against the fp32-accumulated oracle, and this
+    library's tensor-core arms against the reference's output."""
+    R = orc.ref_gemm("fp8a8" if kind == "fp8a8" else "mxfp4")
+    if R is None:
+        pytest.skip("reference band library not present")
+    case = gen.case_fp8(7000 + M, M, N, K, "ref128") if kind == "fp8a8" else gen.case_mxfp4(7000 + M, M, N, K)
+    t = {k: gu.dev(case[k]) for k in ("A", "AS", "B", "BS")}
+    y_ref = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    pack = _gemm_pack(t, kind, M, N, K, y_ref)
+    assert getattr(R, entry)(C.byref(pack.args), None) == 0
+    torch.cuda.synchronize()
+    ref = y_ref.view(torch.int16).cpu().numpy().view(np.uint16)
+    if kind == "fp8a8":
+        _, acc = orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], case["rblk"], want_acc=True)
+    else:
+        _, acc = orc.gemm_mxfp4a8(**case, want_acc=True)
+    g = gu.grade_bf16(ref, acc)
+    assert g["frac_le2"] > 0.999 and g["rel_l2"] < 5e-3, ("reference vs oracle", g)
+    got = gu.gemm_launch(kind, case, abi.R3D_ARM_AUTO)
+    d = orc.bf16_ulp_distance(got, ref)
+    assert (d <= 2).mean() > 0.999, ("this library vs reference", float((d <= 2).mean()), int(d.max()))
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+def test_q8x_arm_against_the_reference_q8x_row(M):
+    """The reference's int8-per-32 decode row (its repacked plane, requantiser and dot4 / lane-map
+    kernels, all its own code) against this library's q8x arm, which reads the nibble plane as it
+    is: the arm's chain is integer-exact inside a group, so the outputs must be identical bits."""
+    R = orc.ref_gemm("mxfp4")
+    if R is None:
+        pytest.skip("reference band library not present")
+    N, K = 640, 2048
+    case = gen.case_mxfp4(7100 + M, M, N, K)
+    t = {k: gu.dev(case[k]) for k in ("A", "AS", "B", "BS")}
+    y_ref = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    pack = _gemm_pack(t, "mxfp4a8", M, N, K, y_ref)
+    assert R.ref_mxfp4_gemm_nt_q_decode_q8x(C.byref(pack.args), None) == 0
+    torch.cuda.synchronize()
+    ref = y_ref.view(torch.int16).cpu().numpy().view(np.uint16)
+    y = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    r = ops.gemm_nt_q(t["A"], t["AS"], t["B"], t["BS"], y, dtype="mxfp4a8", N=N, K=K, row="gemm_nt_q_mxfp4_decode_q8x")
+    torch.cuda.synchronize()
+    got = y.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert r.name == "gemm_nt_q_mxfp4_decode_q8x"
+    assert np.array_equal(got, ref)
