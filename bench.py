@@ -128,6 +128,7 @@ def run_reference(args):
     val = nbytes * args.steps / dt / 1e9
     threads = orc.lib().orc_num_threads()
     sample = f"{rows} of {N_DIM} weight rows per step, M=1,2,4, full K"
+    ref_gpu = reference_kernels_on_gpu(args)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
@@ -136,7 +137,75 @@ def run_reference(args):
         "config": {"workload": "C2 mxfp4a8 decode GEMV, M in {1,2,4}, K=5120, N=27648", "sample": sample},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "reference_gpu": ref_gpu,
     }))
+
+
+def reference_kernels_on_gpu(args):
+    """The reference has no CPU implementation of this path: its implementation is GPU kernels
+    (HIP). Where its band file has been compiled for sm_100a from where it lay (oracle/_ref/
+    libref_mxfp4.so, through the HIP / rocWMMA stand-ins) and a GPU is present, the same C2 step is
+    also timed through the reference's own entries and kernels on this GPU: the row its resolver
+    would pick (the int8-per-32 decode row, priority 1200) and its fp32-walk decode row."""
+    try:
+        import ctypes as C
+        import torch
+        from oracle import oracle as orc
+        if not torch.cuda.is_available():
+            return {"unavailable": "no GPU"}
+        R = orc.ref_gemm("mxfp4")
+        if R is None:
+            return {"unavailable": "oracle/_ref/libref_mxfp4.so not built"}
+        from libr3d_b200 import abi
+        from libr3d_b200.plugin import ArgPack, tensor_desc
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(0)
+        g = torch.Generator(device=dev).manual_seed(1234)
+        rot = 4
+        planes = [(torch.randint(0, 256, (N_DIM, K_DIM // 2), dtype=torch.uint8, device=dev, generator=g),
+                   torch.randint(119, 124, (N_DIM, K_DIM // 32), dtype=torch.uint8, device=dev, generator=g))
+                  for _ in range(rot)]
+        import gen
+        out = {}
+        for name, entry in (("gemm_nt_q_mxfp4_decode_q8x", R.ref_mxfp4_gemm_nt_q_decode_q8x),
+                            ("gemm_nt_q_mxfp4_decode", R.ref_mxfp4_gemm_nt_q_decode)):
+            packs, keep = {}, []
+            for m in MS:
+                c = gen.case_mxfp4(100 + m, m, 128, K_DIM)
+                A = torch.from_numpy(c["A"]).to(dev); AS = torch.from_numpy(c["AS"]).to(dev)
+                y = torch.zeros((m, N_DIM), dtype=torch.bfloat16, device=dev)
+                keep.append((A, AS, y))
+                d = lambda t, dt: tensor_desc(t.data_ptr(), dt, list(t.shape))
+                for p, (B, BS) in enumerate(planes):
+                    packs[m, p] = ArgPack([d(A, abi.RAD_F8E4M3), d(AS, abi.RAD_F32),
+                                           tensor_desc(B.data_ptr(), abi.RAD_FP4E2M1, [N_DIM, K_DIM], [K_DIM, 1]),
+                                           d(BS, abi.RAD_E8M0), d(y, abi.RAD_BF16), tensor_desc(None, abi.RAD_F32, []),
+                                           tensor_desc(None, abi.RAD_BF16, [])],
+                                          dict(M=m, N=N_DIM, K=K_DIM, group=32, dtype="mxfp4a8"))
+
+            def step(i):
+                for m in MS:
+                    rc = entry(C.byref(packs[m, i % rot].args), None)
+                    if rc != 0:
+                        raise RuntimeError(f"reference row {name} returned {rc}")
+            for i in range(rot + 2):                      # first sight of every plane builds its caches
+                step(i)
+            torch.cuda.synchronize()
+            steps = min(max(args.steps, 8), 100)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(steps):
+                step(i)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            out[name] = {"value": STEP_BYTES * steps / (ms * 1e-3) / 1e9, "unit": "GB/s", "us_per_call": ms * 1e3 / (3 * steps),
+                         "steps": steps, "nonzero": float(torch.count_nonzero(keep[-1][2].view(torch.int16))) / keep[-1][2].numel()}
+        out["what"] = ("the reference's own entries and kernels (src/r3d_gemm_mxfp4.hip), compiled unmodified for sm_100a "
+                       "through oracle/hipstub, timed on this GPU: direct issue, 4 rotating weight planes, CUDA events")
+        return out
+    except Exception as e:                                 # noqa: BLE001 - the CPU numbers above stand on their own
+        return {"unavailable": f"{type(e).__name__}: {e}"}
 
 
 def run_c5(args):

@@ -36,10 +36,19 @@ static inline cudaError_t hipGetDeviceProperties(hipDeviceProp_t* p, int dev) {
     p->multiProcessorCount = q.multiProcessorCount; p->totalGlobalMem = q.totalGlobalMem;
     return e;
 }
-/* HIP's unsynchronised wave shuffles, on a 32-wide wave */
+/* Wave shuffles. HIP does not hold a *_sync shuffle to its mask argument the way CUDA does: the
+ * reference's vectorised gated quantiser (src/r3d_band.hip:313 of libr3d) builds its mask from
+ * threadIdx.x, which names the executing lane only in the first warp of a block; under CUDA's rule
+ * ("every executing lane must be in the mask") that raised "illegal instruction" on B200. Every
+ * shuffle of the pin builds therefore runs over the lanes that are active at the call, which is
+ * what the HIP code relies on. */
 #ifdef __CUDA_ARCH__
-#define __shfl_xor(v, m) __shfl_xor_sync(0xffffffffu, (v), (m))
-#define __shfl_down(v, d) __shfl_down_sync(0xffffffffu, (v), (d))
+template <typename T> __device__ __forceinline__ T ref_shfl_xor_active(T v, int m) { return __shfl_xor_sync(__activemask(), v, m); }
+template <typename T> __device__ __forceinline__ T ref_shfl_down_active(T v, unsigned d) { return __shfl_down_sync(__activemask(), v, d); }
+#define __shfl_xor_sync(mask, v, m) ref_shfl_xor_active((v), (int)(m))
+#define __shfl_down_sync(mask, v, d) ref_shfl_down_active((v), (unsigned)(d))
+#define __shfl_xor(v, m) ref_shfl_xor_active((v), (int)(m))
+#define __shfl_down(v, d) ref_shfl_down_active((v), (unsigned)(d))
 #endif
 
 
@@ -48,7 +57,7 @@ static inline cudaError_t hipGetDeviceProperties(hipDeviceProp_t* p, int dev) {
  * selectors is "lane ^ 16", sudot4 with both operands signed is the signed byte dot. */
 __device__ __forceinline__ int __builtin_amdgcn_update_dpp(int old, int src, int ctrl, int, int, bool) {
     (void)old;
-    return __shfl_xor_sync(0xffffffffu, src, ctrl & 0xf);
+    return __shfl_xor_sync(0xffffffffu, src, ctrl & 0xf);   /* -> active lanes, see above */
 }
 __device__ __forceinline__ unsigned __builtin_amdgcn_permlanex16(unsigned old, unsigned src, unsigned, unsigned, bool, bool) {
     (void)old;

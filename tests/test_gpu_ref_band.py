@@ -126,17 +126,20 @@ def _gemm_pack(t, kind, M, N, K, y):
 
 
 @pytest.mark.parametrize("kind,entry,M,N,K", [
-    ("fp8a8", "ref_fp8a8_gemm_nt_q_decode", 1, 512, 1024), ("fp8a8", "ref_fp8a8_gemm_nt_q_decode", 4, 384, 2560),
-    ("fp8a8", "ref_fp8a8_gemm_nt_q_decode", 8, 1000, 512), ("fp8a8", "ref_fp8a8_gemm_nt_q", 16, 512, 1024),
-    ("fp8a8", "ref_fp8a8_gemm_nt_q", 100, 384, 512), ("fp8a8", "ref_fp8a8_gemm_nt_q", 1, 4096, 4096),
+    ("fp8a8", "ref_fp8a8_gemm_nt_q_decode", 1, 512, 1024), ("fp8a8", "ref_fp8a8_gemm_nt_q_decode", 2, 384, 2560),
+    ("fp8a8", "ref_fp8a8_gemm_nt_q_decode", 3, 1000, 512), ("fp8a8", "ref_fp8a8_gemm_nt_q", 2, 512, 1024),
+    ("fp8a8", "ref_fp8a8_gemm_nt_q", 1, 4096, 4096),
     ("mxfp4a8", "ref_mxfp4_gemm_nt_q_decode", 1, 512, 1024), ("mxfp4a8", "ref_mxfp4_gemm_nt_q_decode", 4, 384, 2560),
-    ("mxfp4a8", "ref_mxfp4_gemm_nt_q_decode", 8, 1000, 512), ("mxfp4a8", "ref_mxfp4_gemm_nt_q", 16, 512, 1024),
-    ("mxfp4a8", "ref_mxfp4_gemm_nt_q", 100, 384, 512), ("mxfp4a8", "ref_mxfp4_gemm_nt_q_decode", 2, 27648, 5120)])
+    ("mxfp4a8", "ref_mxfp4_gemm_nt_q_decode", 8, 1000, 512), ("mxfp4a8", "ref_mxfp4_gemm_nt_q_decode", 2, 27648, 5120)])
 def test_gemm_arms_against_the_reference_kernels(kind, entry, M, N, K):
     """The reference's own band kernels and entries (src/r3d_gemm_fp8a8.hip, src/r3d_gemm_mxfp4.hip of
     libr3d, compiled for sm_100a through the HIP / rocWMMA stand-ins) on the same operands. Graded
     like everything else at 2 bf16 ulp: the reference against the fp32-accumulated oracle, and this
-    library's tensor-core arms against the reference's output."""
+    library's tensor-core arms against the reference's output.
+    Only the reference's GEMV kernels are run (fp8a8 at M < 4: from M = 4 its dispatch hands the call
+    to the skinny WMMA kernel; mxfp4a8 decode rows at M <= 8): its skinny and tile kernels hand rocWMMA a leading dimension of 20 elements and 16-byte
+    aligned tiles, which nvcuda::wmma (multiples of 8 elements, 32-byte alignment) does not allow,
+    so they are compiled but never launched here."""
     R = orc.ref_gemm("fp8a8" if kind == "fp8a8" else "mxfp4")
     if R is None:
         pytest.skip("reference band library not present")
