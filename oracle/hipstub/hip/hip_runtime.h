@@ -5,6 +5,8 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
+#include <cuda_bf16.h>   /* before the shuffle macros below: NVIDIA's headers use the four-argument forms */
+#include <mma.h>
 #include <cstdint>
 #include <cstring>
 
@@ -25,7 +27,15 @@ typedef cudaError_t hipError_t;
 #define hipMemGetInfo cudaMemGetInfo
 #define hipMemcpyAsync cudaMemcpyAsync
 #define hipMemsetAsync cudaMemsetAsync
-#define hipLaunchKernelGGL(kern, grid, block, smem, stream, ...) kern<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__)
+/* hipLaunchKernelGGL((kernel<...>), grid, block, smem, stream, args...): the reference passes the
+ * kernel in parentheses, which the <<< >>> syntax does not take, so the launch goes through a
+ * function pointer */
+template <typename... KArgs, typename... Args>
+static inline void ref_launch_ggl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    kern<<<grid, block, smem, st>>>(args...);
+}
+#define hipLaunchKernelGGL(kern, grid, block, smem, stream, ...) \
+    ref_launch_ggl(kern, dim3(grid), dim3(block), (size_t)(smem), (stream), __VA_ARGS__)
 /* the reference gates its kernels on the chip's architecture name: the pin answers with the one
  * it expects, so that its own code paths run */
 struct hipDeviceProp_t { char gcnArchName[256]; int multiProcessorCount; size_t totalGlobalMem; };
@@ -64,3 +74,5 @@ __device__ __forceinline__ unsigned __builtin_amdgcn_permlanex16(unsigned old, u
     return __shfl_xor_sync(0xffffffffu, src, 16);
 }
 __device__ __forceinline__ int __builtin_amdgcn_sudot4(bool, int a, bool, int b, int c, bool) { return __dp4a(a, b, c); }
+/* clang's streaming-load hint: a plain load has the same value. */
+template <typename T> __host__ __device__ __forceinline__ T __builtin_nontemporal_load(const T* p) { return *p; }

@@ -4,8 +4,21 @@
  * for radiance's. The reference's own kernels and entries (plain, decode, int8-per-32 decode) then
  * run on the B200 beside this library's, on the same operands. TEST INFRASTRUCTURE ONLY. */
 #include <cuda_runtime.h>
+#include <cmath>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+#include "hip/hip_runtime.h"
+#include "hip/hip_fp16.h"
+#include "rocwmma/rocwmma.hpp"
+/* The file holds one AMD instruction in inline asm (the f16-pair dot of an arm that an environment
+ * lever switches on and that is off by default). nvcc cannot assemble it, so, with every system
+ * header above already in, the statement is defined away; that arm is never selected here. */
+#define asm(...)
 #include "r3d_gemm_mxfp4.hip"
+#undef asm
 
 void r3d_dump_begin(R3dDumpSlot* slot, const char*, const void*, const RadArgs*, RadStream) { if (slot) slot->priv = nullptr; }
 void r3d_dump_end(R3dDumpSlot*, int) {}
