@@ -33,7 +33,8 @@
  * R3D_NO_PDL=1 turns the early start off.
  *
  * Warp roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-5 scale writers and
- * epilogue. Every wait is bounded; on expiry a status word is set and the CTA drains, frees its
+ * epilogue; in the split-roles form (SR, used for 3 and 4 tokens) warps 6-9 write the scale
+ * factors and warps 2-5 only run the epilogue. Every wait is bounded; on expiry a status word is set and the CTA drains, frees its
  * TMEM and leaves without storing.
  */
 #include <cstdio>
@@ -50,6 +51,7 @@ namespace {
 using namespace tcdev;
 
 constexpr int kThreads = 192;
+constexpr int kThreadsSR = 320;                    /* split roles: four more warps write the scale factors */
 constexpr int kRows = 128;
 constexpr int kStageK = 256;                       /* K elements per stage = 128 packed bytes per row */
 constexpr int kWBytes = kRows * 128;               /* 16 KiB of weights per stage */
@@ -109,8 +111,8 @@ constexpr size_t smem_fixed() {
 
 /* NP: piece rows on the MMA's N axis (12 per token, padded to 16 / 32 / 48 / 96); MT: tokens
  * (1, 2, 4, 8: M rounds up, rows past M are zero-filled by the tensor map and never stored). */
-template <int NP, int MT, int kStages>
-__global__ void __launch_bounds__(kThreads)
+template <int NP, int MT, int kStages, bool SR>
+__global__ void __launch_bounds__(SR ? kThreadsSR : kThreads)
 k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
           const __grid_constant__ CUtensorMap tmP, const P4 P) {
     constexpr int kPBytes = NP * 128;
@@ -164,7 +166,7 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     }
     if (warp >= 1) {
         tc_fence_before();
-        asm volatile("bar.sync 2, 160;" ::: "memory");
+        asm volatile("bar.sync 2, %0;" ::"n"(SR ? kThreadsSR - 32 : kThreads - 32) : "memory");
         tc_fence_after();
     }
     const uint32_t tmem_base = warp >= 1 ? *tmem_slot : 0u;
@@ -246,8 +248,10 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
         constexpr int LEAD = kStages > 3 ? 3 : 2;
         /* the token-side scale factors are 2^0 everywhere: each warp fills its own lane quarter
          * once; the first preparation's wait::st and barrier arrival publish these stores too */
+        if (!SR || warp >= 6) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) tmem_st1(tlane + kSfbCol + c, 0x7f7f7f7fu);
+            for (int c = 0; c < 8; ++c) tmem_st1(tlane + kSfbCol + c, 0x7f7f7f7fu);
+        }
         /* Preparation of stage x, LEAD stages ahead of its MMAs: this row's eight scale bytes go
          * from the scale tile in shared memory to tensor memory. */
         auto prepare = [&](int x) -> bool {
@@ -265,9 +269,16 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
             if (lane == 0) mbar_arrive(&prep[s]);
             return true;
         };
+        if (SR && warp >= 6) {
+            /* split roles: these four warps only write scale factors, as far ahead as the stage
+             * ring allows; the epilogue warps never wait for a tensor-memory store */
+            for (int x = 0; x < nk && alive; ++x) alive = prepare(x);
+        } else {
+        if (!SR) {
 #pragma unroll
-        for (int x = 0; x < LEAD; ++x)
-            if (x < nk && alive) alive = prepare(x);
+            for (int x = 0; x < LEAD; ++x)
+                if (x < nk && alive) alive = prepare(x);
+        }
         /* the activation scales and the NaN flags are the previous kernels' output */
         dep_wait();
         if (threadIdx.x - 64 < MT) {
@@ -287,13 +298,13 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 #pragma unroll
         for (int j = 0; j < kPieces; ++j) wj[j] = piece_scale(j);
         for (int it = 0; it < nk && alive; ++it) {
-            if (it + LEAD < nk) { alive = prepare(it + LEAD); if (!alive) break; }
+            if (!SR && it + LEAD < nk) { alive = prepare(it + LEAD); if (!alive) break; }
             const int ab = it % kBufs;
             if (!mbar_wait(&acc_full[ab], (it / kBufs) & 1, 28)) { alive = false; break; }
             tc_fence_after();
             constexpr int NC = (MT * kPieces + 15) / 16 * 16;       /* piece columns read per group */
             const float* sa = as_s + (2 * (it0 + it)) * MT;
-            if (MT <= 4) {
+            if (MT <= 2 || (MT <= 4 && !SR)) {
                 /* both 128-column groups in one round trip to tensor memory */
                 float c[2][NC];
 #pragma unroll
@@ -350,17 +361,18 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 #pragma unroll
             for (int t = 0; t < MT; ++t) red[t * kRows + q * 32 + lane] = alive ? acc[t] : __int_as_float(0x7fc00000);
         }
+        } /* epilogue warps */
     }
     if (ks > 1) {
         cluster_sync_all();                                   /* partial sums are in place */
-        if (warp >= 2 && crank == 0) {
+        if (warp >= 2 && warp < 6 && crank == 0) {
             const float* red = (const float*)smem;
             for (int r = 1; r < ks; ++r)
 #pragma unroll
                 for (int t = 0; t < MT; ++t) acc[t] += ld_peer_f32(red + t * kRows + q * 32 + lane, (uint32_t)r);
         }
     }
-    if (warp >= 2 && crank == 0 && alive && row < P.n) {
+    if (warp >= 2 && warp < 6 && crank == 0 && alive && row < P.n) {
 #pragma unroll
         for (int t = 0; t < MT; ++t) {
             if (t >= P.m) break;
@@ -446,15 +458,15 @@ cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
     return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
-template <int NP, int MT, int kStages>
+template <int NP, int MT, int kStages, bool SR>
 int launch_s(const CUtensorMap* tw, const CUtensorMap* ts, const CUtensorMap* tp, const P4& P, cudaStream_t st) {
     const size_t smem = smem_fixed<kStages>() + (size_t)kStages * (kWBytes + NP * 128) +
                         (size_t)(P.k / 128) * MT * sizeof(float);
     static size_t attr_set = 0;
     if (smem > attr_set) {
-        if (cudaFuncSetAttribute(k_tc_mxf4<NP, MT, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(k_tc_mxf4<NP, MT, kStages, SR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) return RAD_E_DEVICE;
-        (void)cudaFuncSetAttribute(k_tc_mxf4<NP, MT, kStages>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        (void)cudaFuncSetAttribute(k_tc_mxf4<NP, MT, kStages, SR>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                    (int)cudaSharedmemCarveoutMaxShared);
         attr_set = smem;
     }
@@ -473,7 +485,7 @@ int launch_s(const CUtensorMap* tw, const CUtensorMap* ts, const CUtensorMap* tp
     if (ks <= 1) { ks = 1; per = nk_all; }
     Q.ksplit = ks; Q.kper = per;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned)(tiles * ks)); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cfg.gridDim = dim3((unsigned)(tiles * ks)); cfg.blockDim = dim3(SR ? kThreadsSR : kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = (unsigned)ks; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
@@ -481,20 +493,29 @@ int launch_s(const CUtensorMap* tw, const CUtensorMap* ts, const CUtensorMap* tp
     at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = tc_pdl_on() ? 2 : 1;
     count_launch();
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_mxf4<NP, MT, kStages>, *tw, *ts, *tp, Q);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_mxf4<NP, MT, kStages, SR>, *tw, *ts, *tp, Q);
     return e == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
 }
 
-template <int NP, int MT>
-int launch(const CUtensorMap* tw, const CUtensorMap* ts, const CUtensorMap* tp, const P4& P, cudaStream_t st) {
+template <int NP, int MT, bool SR>
+int launch_r(const CUtensorMap* tw, const CUtensorMap* ts, const CUtensorMap* tp, const P4& P, cudaStream_t st) {
     /* the deepest ring that still lets two CTAs share an SM */
     const size_t extra = (size_t)(P.k / 128) * MT * sizeof(float);
     const size_t stage = kWBytes + NP * 128;
     const size_t half = 233472 / 2 - 1024;
-    if (smem_fixed<6>() + extra + 6 * stage <= half) return launch_s<NP, MT, 6>(tw, ts, tp, P, st);
-    if (smem_fixed<5>() + extra + 5 * stage <= half) return launch_s<NP, MT, 5>(tw, ts, tp, P, st);
-    if (smem_fixed<4>() + extra + 4 * stage <= half) return launch_s<NP, MT, 4>(tw, ts, tp, P, st);
-    return launch_s<NP, MT, 3>(tw, ts, tp, P, st);
+    if (smem_fixed<6>() + extra + 6 * stage <= half) return launch_s<NP, MT, 6, SR>(tw, ts, tp, P, st);
+    if (smem_fixed<5>() + extra + 5 * stage <= half) return launch_s<NP, MT, 5, SR>(tw, ts, tp, P, st);
+    if (smem_fixed<4>() + extra + 4 * stage <= half) return launch_s<NP, MT, 4, SR>(tw, ts, tp, P, st);
+    return launch_s<NP, MT, 3, SR>(tw, ts, tp, P, st);
+}
+
+template <int NP, int MT>
+int launch(const CUtensorMap* tw, const CUtensorMap* ts, const CUtensorMap* tp, const P4& P, cudaStream_t st) {
+    /* split roles pay where the epilogue is long (3 or 4 tokens: measured 18.2 -> 16.5 us on
+     * 27648 x 5120); with 1 or 2 tokens they change nothing. R3D_TC_SR=0|1 forces either form. */
+    static const int sr = [] { const char* e = getenv("R3D_TC_SR"); return e ? atoi(e) : -1; }();
+    const bool on = sr >= 0 ? sr != 0 : MT == 4;
+    return on ? launch_r<NP, MT, true>(tw, ts, tp, P, st) : launch_r<NP, MT, false>(tw, ts, tp, P, st);
 }
 
 bool al(const void* p, int a) { return (((uintptr_t)p) & (uintptr_t)(a - 1)) == 0; }
