@@ -37,6 +37,15 @@ int r3d_rad_gemm_nt_q_fp8_decode(const RadArgs* a, RadStream s);
  * (src/r3d_gemm_fp8a8.hip:1167-1253). */
 int r3d_rad_gemm_nt_q_gated_fp8(const RadArgs* a, RadStream s);
 int64_t r3d_rad_gemm_nt_q_gated_fp8_scratch(const RadArgs* a);
+/* The activation producers in front of the bands, as rows of their own.
+ * quant_act_fp8 (x, q, scale): replaces r3d_rad_quant_act_fp8 (src/r3d_band.hip:459-489).
+ * gated_quant_fp8 (gate_up, q, scale, out_bf16?): replaces r3d_rad_gated_quant_fp8
+ * (src/r3d_band.hip:491-548). rmsnorm_quant_fp8 (x, residual?, w, q, scale, out_bf16?): replaces
+ * r3d_rad_rmsnorm_quant_fp8 (src/r3d_more.hip:480-541); its sum of squares keeps the reference
+ * kernel's order, so codes, scales and the norm output carry the same bits. */
+int r3d_rad_quant_act_fp8(const RadArgs* a, RadStream s);
+int r3d_rad_gated_quant_fp8(const RadArgs* a, RadStream s);
+int r3d_rad_rmsnorm_quant_fp8(const RadArgs* a, RadStream s);
 /* gemm_nt_q @ mxfp4a8, any M. Replaces r3d_rad_gemm_nt_q
  * (src/r3d_gemm_mxfp4.hip:1587-1691). */
 int r3d_rad_gemm_nt_q(const RadArgs* a, RadStream s);

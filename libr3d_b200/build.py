@@ -24,6 +24,7 @@ SO = PKG / "libr3d_b200.so"
 SOURCES = [
     "rows_table.cpp",
     "entries_gemm_q.cpp",
+    "entries_band.cpp",
     "entries_logits.cpp",
     "launch.cu",
     "kern_exact.cu",

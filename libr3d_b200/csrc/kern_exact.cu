@@ -264,15 +264,17 @@ __global__ __launch_bounds__(128) void k_quant_act_fp8(
  * sg = 1/(1 + (float)exp((double)-gt)), its amax (strict >, NaN never wins), the dequant scale
  * amax/448 and the saturating RTNE e4m3 codes of h/scale. */
 __global__ __launch_bounds__(256) void k_gated_quant_fp8(
-    const uint16_t* __restrict__ gu, const int64_t gu_pitch, uint8_t* __restrict__ q, const int64_t q_pitch,
+    const void* __restrict__ gu, const int gu_dtype, const int64_t gu_pitch, uint8_t* __restrict__ q, const int64_t q_pitch,
     float* __restrict__ scale, const int64_t s_pitch, void* __restrict__ ob, const int ob_dtype,
     const int64_t ob_pitch, const int n, const int g, const int ngrp, const int silu) {
     __shared__ float red[8];
     __shared__ float s_sc;
     const int64_t row = blockIdx.x;
-    const uint16_t* gr = gu + row * gu_pitch;
+    const uint16_t* gr = (const uint16_t*)gu + row * gu_pitch;
+    const float* gf = (const float*)gu + row * gu_pitch;
     auto gated = [&](int i) -> float {
-        const float gt = bf16_to_f32(gr[i]), up = bf16_to_f32(gr[n + i]);
+        const float gt = gu_dtype == RAD_F32 ? gf[i] : bf16_to_f32(gr[i]);
+        const float up = gu_dtype == RAD_F32 ? gf[n + i] : bf16_to_f32(gr[n + i]);
         const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, (float)exp((double)(-gt))));
         const float a = silu ? __fmul_rn(gt, sg) : sg;
         return bf16_to_f32(f32_to_bf16(__fmul_rn(a, up)));
@@ -311,6 +313,83 @@ __global__ __launch_bounds__(256) void k_gated_quant_fp8(
             q[row * q_pitch + i] = f32_to_e4m3(c);
         }
         __syncthreads();                              /* s_sc is reused by the next group */
+    }
+}
+
+/* ------------------------------------------------------------------ rmsnorm_quant_fp8
+ * src/r3d_more.hip:248-330 of libr3d. One block of 256 threads per row; the sum of squares keeps
+ * that kernel's order (thread t adds elements t, t+256, ... ascending; a shuffle-down tree inside
+ * each warp; the eight warp sums added ascending by thread 0), so rs = 1/sqrt(ss/n + eps) has the
+ * same bits. With a residual the bf16-narrowed sum x + res is stored first and is what the
+ * variance and the norm read. h = bf16(src * rs * (w + wadd)) goes to out_bf16 and to the group
+ * quantiser (strict-max amax, scale amax/448 or 1, saturating RTNE e4m3 codes of h/scale). */
+__global__ __launch_bounds__(256) void k_rmsnorm_quant_fp8(
+    const uint16_t* __restrict__ x, const int64_t x_pitch, uint16_t* __restrict__ res, const int64_t r_pitch,
+    const void* __restrict__ w, const int w_dtype, uint8_t* __restrict__ q, const int64_t q_pitch,
+    float* __restrict__ scale, const int64_t s_pitch, void* __restrict__ ob, const int ob_dtype,
+    const int64_t ob_pitch, const int n, const int g, const int ngrp, const float eps, const float wadd) {
+    __shared__ float s_part[8];
+    __shared__ float s_rs;
+    extern __shared__ uint16_t s_h[];
+    const int64_t row = blockIdx.x;
+    const uint16_t* xr = x + row * x_pitch;
+    uint16_t* rr = res ? res + row * r_pitch : nullptr;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n; i += 256) {
+        const float v = bf16_to_f32(xr[i]);
+        if (rr) {
+            const uint16_t h = f32_to_bf16(__fadd_rn(bf16_to_f32(rr[i]), v));
+            rr[i] = h;
+            s_h[i] = h;
+            const float hv = bf16_to_f32(h);
+            ss = __fadd_rn(ss, __fmul_rn(hv, hv));
+        } else {
+            ss = __fadd_rn(ss, __fmul_rn(v, v));
+        }
+    }
+    for (int off = 16; off; off >>= 1) ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, off));
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float r = s_part[0];
+        for (int k = 1; k < 8; ++k) r = __fadd_rn(r, s_part[k]);
+        s_rs = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(r, (float)n), eps)));
+    }
+    __syncthreads();
+    const float rs = s_rs;
+    for (int i = threadIdx.x; i < n; i += 256) {
+        const float src = rr ? bf16_to_f32(s_h[i]) : bf16_to_f32(xr[i]);
+        const float wv = __fadd_rn(w_dtype == RAD_F32 ? ((const float*)w)[i] : bf16_to_f32(((const uint16_t*)w)[i]), wadd);
+        const uint16_t h = f32_to_bf16(__fmul_rn(__fmul_rn(src, rs), wv));
+        if (ob) {
+            if (ob_dtype == RAD_F32) ((float*)ob)[row * ob_pitch + i] = bf16_to_f32(h);
+            else ((uint16_t*)ob)[row * ob_pitch + i] = h;
+        }
+        s_h[i] = h;
+    }
+    __syncthreads();
+    /* one warp per group: the group's amax is order-free, the codes are per element */
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int gi = warp; gi < ngrp; gi += 8) {
+        const int k0 = gi * g, k1 = min(k0 + g, n);
+        float amax = 0.0f;
+        for (int i = k0 + lane; i < k1; i += 32) {
+            const float m = fabsf(bf16_to_f32(s_h[i]));
+            if (m > amax) amax = m;
+        }
+        for (int off = 16; off; off >>= 1) {
+            const float o = __shfl_xor_sync(0xffffffffu, amax, off);
+            if (o > amax) amax = o;
+        }
+        const float sc = amax > 0.0f ? __fmul_rn(amax, 1.0f / 448.0f) : 1.0f;
+        const float inv = __fdiv_rn(1.0f, sc);
+        if (lane == 0) scale[row * s_pitch + gi] = sc;
+        for (int i = k0 + lane; i < k1; i += 32) {
+            float c = __fmul_rn(bf16_to_f32(s_h[i]), inv);
+            if (c > 448.0f) c = 448.0f;
+            if (c < -448.0f) c = -448.0f;
+            q[row * q_pitch + i] = f32_to_e4m3(c);
+        }
     }
 }
 
@@ -382,12 +461,31 @@ int launch_quant_act_fp8(const void* x, int x_dtype, int64_t x_pitch, void* q, i
 
 int launch_gated_quant_fp8(const void* gu, int64_t gu_pitch, void* q, int64_t q_pitch, float* scale,
                            int64_t s_pitch, void* ob, int ob_dtype, int64_t ob_pitch, int rows, int n, int g,
-                           int silu, cudaStream_t st) {
+                           int silu, cudaStream_t st, int gu_dtype) {
     if (g <= 0 || g > n) g = n;
     const int ngrp = (n + g - 1) / g;
     count_launch();
-    k_gated_quant_fp8<<<(unsigned)rows, 256, 0, st>>>((const uint16_t*)gu, gu_pitch, (uint8_t*)q, q_pitch, scale,
+    k_gated_quant_fp8<<<(unsigned)rows, 256, 0, st>>>(gu, gu_dtype, gu_pitch, (uint8_t*)q, q_pitch, scale,
                                                       s_pitch, ob, ob_dtype, ob_pitch, n, g, ngrp, silu);
+    return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+}
+
+int launch_rmsnorm_quant_fp8(const void* x, int64_t x_pitch, void* res, int64_t r_pitch, const void* w, int w_dtype,
+                             void* q, int64_t q_pitch, float* scale, int64_t s_pitch, void* ob, int ob_dtype,
+                             int64_t ob_pitch, int rows, int n, int g, float eps, float wadd, cudaStream_t st) {
+    if (g <= 0 || g > n) g = n;
+    const int ngrp = (n + g - 1) / g;
+    const size_t smem = (size_t)n * 2;
+    static size_t attr_set = 0;
+    if (smem > 48 * 1024 && smem > attr_set) {
+        if (cudaFuncSetAttribute(k_rmsnorm_quant_fp8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess) return RAD_E_DEVICE;
+        attr_set = smem;
+    }
+    count_launch();
+    k_rmsnorm_quant_fp8<<<(unsigned)rows, 256, smem, st>>>((const uint16_t*)x, x_pitch, (uint16_t*)res, r_pitch, w,
+                                                           w_dtype, (uint8_t*)q, q_pitch, scale, s_pitch, ob,
+                                                           ob_dtype, ob_pitch, n, g, ngrp, eps, wadd);
     return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
 }
 

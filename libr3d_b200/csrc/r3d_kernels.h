@@ -25,7 +25,11 @@ int launch_quant_act_fp8(const void* x, int x_dtype, int64_t x_pitch, void* q, i
 
 int launch_gated_quant_fp8(const void* gu, int64_t gu_pitch, void* q, int64_t q_pitch, float* scale,
                            int64_t s_pitch, void* ob, int ob_dtype, int64_t ob_pitch, int rows, int n, int g,
-                           int silu, cudaStream_t st);
+                           int silu, cudaStream_t st, int gu_dtype = RAD_BF16);
+/* RMS norm + group quantiser, one block per row; pitches in elements; res/ob may be null */
+int launch_rmsnorm_quant_fp8(const void* x, int64_t x_pitch, void* res, int64_t r_pitch, const void* w, int w_dtype,
+                             void* q, int64_t q_pitch, float* scale, int64_t s_pitch, void* ob, int ob_dtype,
+                             int64_t ob_pitch, int rows, int n, int g, float eps, float wadd, cudaStream_t st);
 
 /* weight-streaming tensor-core arm (kern_stream.cu); *_ok say whether the arm can take
  * the call's shape and alignment */

@@ -57,7 +57,46 @@ const RadOperandSpec kLogitsOperands[] = {
     { "x", RAD_OPD_IN, 0 }, { "lm_head", RAD_OPD_WEIGHT, 0 }, { "logits", RAD_OPD_OUT, 0 },
 };
 
+/* the activation producers: src/r3d_rows.cpp:615-638 (quant_act_fp8, gated_quant_fp8),
+ * :700-716 (rmsnorm_quant_fp8) */
+const RadParamSpec kQuantActParams[] = {
+    { "M", RAD_P_INT, RAD_REQUIRED, 0 },     { "n", RAD_P_INT, RAD_REQUIRED, 0 },
+    { "group", RAD_P_INT, RAD_REQUIRED, 0 }, { "dtype", RAD_P_STR, RAD_REQUIRED, 0 },
+};
+const RadOperandSpec kQuantActOperands[] = {
+    { "x", RAD_OPD_IN, 0 }, { "q", RAD_OPD_OUT, 0 }, { "scale", RAD_OPD_OUT, 0 },
+};
+const RadParamSpec kGatedQuantParams[] = {
+    { "M", RAD_P_INT, RAD_REQUIRED, 0 },     { "n", RAD_P_INT, RAD_REQUIRED, 0 },
+    { "group", RAD_P_INT, RAD_REQUIRED, 0 }, { "dtype", RAD_P_STR, RAD_REQUIRED, 0 },
+    { "act", RAD_P_STR, RAD_OPTIONAL, 0 },
+};
+const RadOperandSpec kGatedQuantOperands[] = {
+    { "gate_up", RAD_OPD_IN, 0 }, { "q", RAD_OPD_OUT, 0 }, { "scale", RAD_OPD_OUT, 0 },
+    { "out_bf16", RAD_OPD_OUT, 1 },
+};
+const RadParamSpec kRmsQuantParams[] = {
+    { "M", RAD_P_INT, RAD_REQUIRED, 0 },     { "n", RAD_P_INT, RAD_REQUIRED, 0 },
+    { "eps", RAD_P_F64, RAD_REQUIRED, 0 },   { "group", RAD_P_INT, RAD_REQUIRED, 0 },
+    { "dtype", RAD_P_STR, RAD_REQUIRED, 0 }, { "wadd", RAD_P_F64, RAD_OPTIONAL, 0 },
+};
+const RadOperandSpec kRmsQuantOperands[] = {
+    { "x", RAD_OPD_IN, 0 },      { "residual", RAD_OPD_INOUT, 1 }, { "w", RAD_OPD_WEIGHT, 0 },
+    { "q", RAD_OPD_OUT, 0 },     { "scale", RAD_OPD_OUT, 0 },      { "out_bf16", RAD_OPD_OUT, 1 },
+};
+
 const RadOpSchema kSchemas[] = {
+    { "quant_act_fp8", kQuantActParams, COUNT_OF(kQuantActParams), kQuantActOperands,
+      COUNT_OF(kQuantActOperands),
+      "symmetric e4m3 quantisation of a token-major activation per (row, `group` columns), plain "
+      "row-major; scale = amax/448, a dequantisation multiplier." },
+    { "gated_quant_fp8", kGatedQuantParams, COUNT_OF(kGatedQuantParams), kGatedQuantOperands,
+      COUNT_OF(kGatedQuantOperands),
+      "silu(gate)*up or sigmoid(gate)*up over a [M, 2n] gate_up plane, then the same quantiser." },
+    { "rmsnorm_quant_fp8", kRmsQuantParams, COUNT_OF(kRmsQuantParams), kRmsQuantOperands,
+      COUNT_OF(kRmsQuantOperands),
+      "RMS norm (optionally after a residual add that is stored back) and the e4m3 group "
+      "quantiser in one pass; the codes are taken over the bf16 norm output." },
     { "logits_gemm", kLogitsParams, COUNT_OF(kLogitsParams), kLogitsOperands,
       COUNT_OF(kLogitsOperands),
       "LM-head projection: logits[M, n_vocab] = x[M, n_embd] @ head^T, one row per sampled "
@@ -65,8 +104,6 @@ const RadOpSchema kSchemas[] = {
     { "gemm_nt_q", kGemmQParams, COUNT_OF(kGemmQParams), kGemmQOperands,
       COUNT_OF(kGemmQOperands),
       "y[M,N] = a[M,K] @ dequant(b)[N,K]^T; `dtype` names the operand-format combination." },
-    /* declared so a co-loaded declarer's schema comparison passes; this library ships no
-     * row for it yet */
     { "gemm_nt_q_gated", kGemmQGatedParams, COUNT_OF(kGemmQGatedParams), kGemmQGatedOperands,
       COUNT_OF(kGemmQGatedOperands),
       "gemm_nt_q over a [2n, K] gate_up plane with the gated activation quantiser folded into "
@@ -99,6 +136,15 @@ const RadConstraint kCFp8Gated[] = {
     { "dtype", RAD_C_IN, 0, "fp8a8" }, { "M", RAD_C_LE, 64, nullptr },
     { "K", RAD_C_DIV, 128, nullptr },  { "group", RAD_C_EQ, 128, nullptr },
     { "act", RAD_C_IN, 0, "silu sigmoid" },
+};
+
+/* src/r3d_rows.cpp:1262-1265, :1419-1423 */
+const RadConstraint kCBand[] = {
+    { "n", RAD_C_GE, 1, nullptr }, { "dtype", RAD_C_IN, 0, "f32 bf16" },
+};
+const RadConstraint kCRmsQuant[] = {
+    { "n", RAD_C_DIV, 4, nullptr }, { "group", RAD_C_EQ, 128, nullptr },
+    { "dtype", RAD_C_IN, 0, "bf16" },
 };
 
 enum { kPrioPlain = 1000, kPrioDecode = 1100, kPrioQ8x = 1200 };
@@ -166,6 +212,31 @@ const RadKernelInfo kRows[] = {
       RAD_DOMAIN_DEVICE, kPrioPlain, kCFp8Gated, COUNT_OF(kCFp8Gated), nullptr, 0, nullptr,
       nullptr, nullptr, r3d_rad_gemm_nt_q_gated_fp8, r3d_rad_gemm_nt_q_gated_fp8_scratch, nullptr,
       nullptr, nullptr, nullptr, nullptr },
+
+    /* the activation producers in front of the bands (src/r3d_rows.cpp:1892-1907, :2093-2101) */
+    ROW("quant_act_fp8_act", "quant_act_fp8", "band",
+        "per-group symmetric e4m3 quantisation of an activation, plain row-major: one block per "
+        "(row, group)",
+        "f32/bf16 input; group clamped to n; scale = amax/448 (1 for an all-zero group)",
+        "activation in, e4m3 codes and f32 group scales out",
+        kPrioPlain, kCBand, r3d_rad_quant_act_fp8),
+
+    ROW("gated_quant_fp8_act", "gated_quant_fp8", "band",
+        "silu(gate)*up (or sigmoid(gate)*up) and the same quantiser in one pass; the gated value "
+        "narrows to bf16 once and the quantiser sees that value",
+        "f32/bf16 gate_up [M, 2n], gate half first; group clamped to n",
+        "gate_up in, e4m3 codes, f32 scales, optional bf16/f32 gated output",
+        kPrioPlain, kCBand, r3d_rad_gated_quant_fp8),
+
+    ROW("rmsnorm_quant_fp8", "rmsnorm_quant_fp8", "quant",
+        "RMS norm and the e4m3 group quantiser in one pass over the row; with a residual the "
+        "bf16-narrowed sum is stored before the variance reads it; the codes are taken over the "
+        "bf16 norm output",
+        "n a multiple of 4 and at most 30720, group 128; one block per row, the row staged in "
+        "shared memory",
+        "bf16 x (+ bf16 residual), f32/bf16 w, e4m3 codes with f32 per-group scales, optional "
+        "bf16/f32 norm output",
+        kPrioPlain, kCRmsQuant, r3d_rad_rmsnorm_quant_fp8),
 };
 
 /* ------------------------------------------------------------------ registration gate */

@@ -142,6 +142,55 @@ def quant_act_fp8(x: torch.Tensor, group: int = 128) -> tuple[torch.Tensor, torc
     return q, s
 
 
+def _act_dt(t: torch.Tensor) -> tuple[int, str]:
+    return (abi.RAD_F32, "f32") if t.dtype == torch.float32 else (abi.RAD_BF16, "bf16")
+
+
+def _issue(op: str, query: dict, tensors: list) -> Row:
+    P = plugin()
+    r = P.resolve(op, query)
+    if r is None:
+        raise RuntimeError(f"no row serves {op} {query}")
+    rc = P.launch_row(r, ArgPack(tensors, query), _stream())
+    if rc != abi.RAD_OK:
+        raise RowRefused(r.name, rc)
+    return r
+
+
+def quant_act_fp8_row(x: torch.Tensor, q: torch.Tensor, scale: torch.Tensor, *, group: int = 128) -> Row:
+    """The quant_act_fp8 op through its row: x [M, n] bf16/f32 -> q e4m3 (uint8) [M, n], scale f32."""
+    dt, name = _act_dt(x)
+    query = dict(M=x.shape[0], n=x.shape[-1], group=group, dtype=name)
+    return _issue("quant_act_fp8", query, [_desc(x, dt), _desc(q, abi.RAD_F8E4M3), _desc(scale, abi.RAD_F32)])
+
+
+def gated_quant_fp8_row(gate_up: torch.Tensor, q: torch.Tensor, scale: torch.Tensor,
+                        out: torch.Tensor | None = None, *, group: int = 128, act: str | None = None) -> Row:
+    """The gated_quant_fp8 op through its row: gate_up [M, 2n] (gate half first) -> q [M, n], scale and,
+    when `out` is given, the bf16/f32 gated product."""
+    dt, name = _act_dt(gate_up)
+    query = dict(M=gate_up.shape[0], n=gate_up.shape[-1] // 2, group=group, dtype=name)
+    if act is not None:
+        query["act"] = act
+    odt = _act_dt(out)[0] if out is not None else abi.RAD_BF16
+    return _issue("gated_quant_fp8", query, [_desc(gate_up, dt), _desc(q, abi.RAD_F8E4M3),
+                                             _desc(scale, abi.RAD_F32), _desc(out, odt)])
+
+
+def rmsnorm_quant_fp8(x: torch.Tensor, w: torch.Tensor, q: torch.Tensor, scale: torch.Tensor, *, eps: float,
+                      residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                      group: int = 128, wadd: float | None = None) -> Row:
+    """The rmsnorm_quant_fp8 op through its row: x [M, n] bf16, w [n]; `residual` (bf16, updated in place
+    with the narrowed sum) selects the fused-add form; `out` receives the bf16/f32 norm output."""
+    query = dict(M=x.shape[0], n=x.shape[-1], eps=float(eps), group=group, dtype="bf16")
+    if wadd is not None:
+        query["wadd"] = float(wadd)
+    odt = _act_dt(out)[0] if out is not None else abi.RAD_BF16
+    return _issue("rmsnorm_quant_fp8", query, [_desc(x, abi.RAD_BF16), _desc(residual, abi.RAD_BF16),
+                                               _desc(w, _act_dt(w)[0]), _desc(q, abi.RAD_F8E4M3),
+                                               _desc(scale, abi.RAD_F32), _desc(out, odt)])
+
+
 class BoundGemm:
     """A gemm_nt_q band declared once and issued many times, the way the engine uses a row:
     the row is resolved and the RadArgs built at declare time over fixed device buffers; each

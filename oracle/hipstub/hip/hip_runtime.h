@@ -27,6 +27,8 @@ typedef cudaError_t hipError_t;
 #define hipMemGetInfo cudaMemGetInfo
 #define hipMemcpyAsync cudaMemcpyAsync
 #define hipMemsetAsync cudaMemsetAsync
+#define hipFuncSetAttribute cudaFuncSetAttribute
+#define hipFuncAttributeMaxDynamicSharedMemorySize cudaFuncAttributeMaxDynamicSharedMemorySize
 /* hipLaunchKernelGGL((kernel<...>), grid, block, smem, stream, args...): the reference passes the
  * kernel in parentheses, which the <<< >>> syntax does not take, so the launch goes through a
  * function pointer */

@@ -120,6 +120,24 @@ def ref_logits() -> C.CDLL | None:
 _ref_gemm: dict = {}
 
 
+_ref_more: list = []
+
+
+def ref_more() -> C.CDLL | None:
+    """src/r3d_more.hip of libr3d compiled as it lies for sm_100a (oracle/_ref/libref_more.so): entry
+    ref_more_rmsnorm_quant_fp8(const RadArgs*, stream). None when the library was not built."""
+    if not _ref_more:
+        so, R = HERE / "_ref" / "libref_more.so", None
+        if so.exists():
+            try:
+                R = C.CDLL(str(so))
+                R.ref_more_rmsnorm_quant_fp8.argtypes = [C.c_void_p, C.c_void_p]
+            except OSError:
+                R = None
+        _ref_more.append(R)
+    return _ref_more[0]
+
+
 def ref_gemm(which: str) -> C.CDLL | None:
     """The reference's band files compiled as they lie for sm_100a: which = "fp8a8"
     (src/r3d_gemm_fp8a8.hip -> oracle/_ref/libref_fp8a8.so; entries ref_fp8a8_gemm_nt_q, _decode, _gated)
@@ -184,6 +202,26 @@ def gated_quant_fp8(gu_bits: np.ndarray, group: int = 128, silu: bool = True, wa
     lib().orc_gated_quant_fp8(_p(gu), I64(M), I64(n), I64(g), C.c_int(1 if silu else 0), _p(q), _p(s),
                               _p(ob) if ob is not None else None)
     return (q, s, ob) if want_ob else (q, s)
+
+
+def rmsnorm_quant_fp8(x_bits: np.ndarray, w: np.ndarray, eps: float, group: int = 128, wadd: float = 0.0,
+                      res_bits: np.ndarray | None = None):
+    """bf16 bits x [M, n] (+ optional bf16 residual, updated in a copy), w as bf16 bits (uint16) or f32 ->
+    dict(q e4m3 [M, n], scale f32 [M, n/group], ob bf16 bits [M, n], res updated bf16 bits or None)."""
+    x = _c(x_bits, np.uint16)
+    M, n = x.shape
+    g = min(group, n) if group > 0 else n
+    ngrp = (n + g - 1) // g
+    res = _c(res_bits, np.uint16).copy() if res_bits is not None else None
+    wb = _c(w, np.uint16) if w.dtype == np.uint16 else None
+    wf = _c(w, np.float32) if wb is None else None
+    q = np.empty((M, n), np.uint8)
+    s = np.empty((M, ngrp), np.float32)
+    ob = np.empty((M, n), np.uint16)
+    lib().orc_rmsnorm_quant_fp8(_p(x), _p(res) if res is not None else None, _p(wb) if wb is not None else None,
+                                _p(wf) if wf is not None else None, I64(M), I64(n), I64(g), C.c_float(eps),
+                                C.c_float(wadd), _p(q), _p(s), _p(ob))
+    return dict(q=q, scale=s, ob=ob, res=res)
 
 
 def quant_act_mx8(x: np.ndarray):

@@ -22,6 +22,7 @@
  * separate roundings except where fmaf is written, as the reference builds with
  * -ffp-contract=off (CMakeLists.txt:34-37).
  */
+#include <vector>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -210,6 +211,74 @@ ORC_API void orc_gated_quant_fp8(const uint16_t* gu, int64_t M, int64_t n, int64
                 q[r * n + i] = f32_to_e4m3(c);
             }
         }
+}
+
+/* ------------------------------------------------------------------ rmsnorm_quant_fp8
+ * src/r3d_more.hip:248-330 (kernel) of libr3d, restated as a scalar walk that keeps the KERNEL's
+ * summation order, because that order decides the bits of rs: the block has 256 threads, thread t
+ * adds the squares of elements t, t+256, ... ascending into its own partial; inside each warp of
+ * 32 threads the partials fold by a shuffle-down tree (offsets 16, 8, 4, 2, 1: lane l adds lane
+ * l+off, lane 0 ends with the warp's sum); thread 0 adds the eight warp sums ascending;
+ * rs = 1 / sqrtf(ss / n + eps). With a residual, sum = bf16(res + x) is stored back first and its
+ * widened value is what is squared and normed. h = bf16(src * rs * (w + wadd)) (left to right, no
+ * contraction) is the norm output; the codes are the group quantiser of quant_act_fp8 over h.
+ * x, res, w_bits are bf16 bit patterns; w_f32 (when given) replaces w_bits. */
+ORC_API void orc_rmsnorm_quant_fp8(const uint16_t* x, uint16_t* res, const uint16_t* w_bits, const float* w_f32,
+                                   int64_t M, int64_t n, int64_t g, float eps, float wadd, uint8_t* q,
+                                   float* scale, uint16_t* ob) {
+    if (g <= 0 || g > n) g = n;
+    const int64_t ngrp = (n + g - 1) / g;
+    std::vector<uint16_t> h(n);
+    for (int64_t r = 0; r < M; ++r) {
+        float part[256];
+        for (int t = 0; t < 256; ++t) {
+            float ss = 0.0f;
+            for (int64_t i = t; i < n; i += 256) {
+                float v = bf16_to_f32(x[r * n + i]);
+                if (res) {
+                    const uint16_t hb = f32_to_bf16(bf16_to_f32(res[r * n + i]) + v);
+                    res[r * n + i] = hb;
+                    h[i] = hb;
+                    v = bf16_to_f32(hb);
+                }
+                ss += v * v;
+            }
+            part[t] = ss;
+        }
+        float total = 0.0f;
+        for (int wp = 0; wp < 8; ++wp) {
+            float lane[32];
+            for (int l = 0; l < 32; ++l) lane[l] = part[wp * 32 + l];
+            for (int off = 16; off; off >>= 1)
+                for (int l = 0; l < 32; ++l)          /* ascending l: lane l+off still holds its old value */
+                    lane[l] = lane[l] + (l + off < 32 ? lane[l + off] : lane[l]);
+            total = wp == 0 ? lane[0] : total + lane[0];
+        }
+        const float rs = 1.0f / std::sqrt(total / (float)n + eps);
+        for (int64_t i = 0; i < n; ++i) {
+            const float src = res ? bf16_to_f32(h[i]) : bf16_to_f32(x[r * n + i]);
+            const float wv = (w_f32 ? w_f32[i] : bf16_to_f32(w_bits[i])) + wadd;
+            h[i] = f32_to_bf16(src * rs * wv);
+            if (ob) ob[r * n + i] = h[i];
+        }
+        for (int64_t gi = 0; gi < ngrp; ++gi) {
+            const int64_t k0 = gi * g, k1 = (k0 + g < n) ? k0 + g : n;
+            float amax = 0.0f;
+            for (int64_t i = k0; i < k1; ++i) {
+                const float m = std::fabs(bf16_to_f32(h[i]));
+                if (m > amax) amax = m;
+            }
+            const float sc = amax > 0.0f ? amax * (1.0f / 448.0f) : 1.0f;
+            const float inv = 1.0f / sc;
+            scale[r * ngrp + gi] = sc;
+            for (int64_t i = k0; i < k1; ++i) {
+                float c = bf16_to_f32(h[i]) * inv;
+                if (c > 448.0f) c = 448.0f;
+                if (c < -448.0f) c = -448.0f;
+                q[r * n + i] = f32_to_e4m3(c);
+            }
+        }
+    }
 }
 
 /* ------------------------------------------------------------------ OCP-MX activation

@@ -1,0 +1,134 @@
+"""The activation-producer rows on the GPU, called through the row table the way the engine would:
+quant_act_fp8, gated_quant_fp8 and rmsnorm_quant_fp8 bit for bit against the CPU oracle, and
+rmsnorm_quant_fp8 bit for bit against the reference's own kernel (src/r3d_more.hip of libr3d, compiled
+where it lay for sm_100a into oracle/_ref/libref_more.so)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import gen
+import gpu_util as gu
+from libr3d_b200 import abi, ops
+from libr3d_b200.plugin import ArgPack, tensor_desc
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _codes_equal(q, want):
+    """e4m3 codes equal; a NaN code (0x7f / 0xff) may differ in sign only."""
+    nan = (want & 0x7F) == 0x7F
+    return np.array_equal(q & 0x7F, want & 0x7F) and np.array_equal(q[~nan], want[~nan])
+
+
+@pytest.mark.parametrize("rows,n,group,f32", [(1, 5120, 128, False), (7, 1000, 128, False), (3, 200, 0, False),
+                                              (4, 512, 512, True)])
+def test_quant_act_row(rows, n, group, f32):
+    rng = np.random.default_rng(rows * 31 + n)
+    x = (rng.standard_normal((rows, n)) * 3).astype(np.float32)
+    x[0, :3] = [0.0, 448.0 * 4, -1e-9]
+    xb = gen.f32_to_bf16_bits(x)
+    xd = gu.dev(x) if f32 else gu.dev(xb).view(torch.bfloat16)
+    g = n if group <= 0 else group
+    q = torch.zeros((rows, n), dtype=torch.uint8, device="cuda")
+    s = torch.zeros((rows, (n + g - 1) // g), dtype=torch.float32, device="cuda")
+    r = ops.quant_act_fp8_row(xd, q, s, group=group)
+    torch.cuda.synchronize()
+    assert r.name == "quant_act_fp8_act"
+    want_q, want_s = orc.quant_act_fp8(x if f32 else orc.bf16_bits_to_f32(xb), g)
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), want_s.view(np.uint32))
+    assert _codes_equal(q.cpu().numpy(), want_q)
+
+
+@pytest.mark.parametrize("act", [None, "silu", "sigmoid"])
+@pytest.mark.parametrize("M,n,group,f32", [(1, 128, 128, False), (5, 300, 128, False), (16, 13824, 128, False),
+                                           (3, 256, 128, True)])
+def test_gated_quant_row(M, n, group, f32, act):
+    rng = np.random.default_rng(M * 1000 + n)
+    bits = gen.f32_to_bf16_bits((rng.standard_normal((M, 2 * n)) * 4).astype(np.float32))
+    # an f32 plane that holds bf16-exact values must give what the bf16 plane gives
+    gd = gu.dev(orc.bf16_bits_to_f32(bits)) if f32 else gu.dev(bits).view(torch.bfloat16)
+    q = torch.zeros((M, n), dtype=torch.uint8, device="cuda")
+    s = torch.zeros((M, (n + group - 1) // group), dtype=torch.float32, device="cuda")
+    ob = torch.zeros((M, n), dtype=torch.bfloat16, device="cuda")
+    r = ops.gated_quant_fp8_row(gd, q, s, ob, group=group, act=act)
+    torch.cuda.synchronize()
+    assert r.name == "gated_quant_fp8_act"
+    want_q, want_s, want_ob = orc.gated_quant_fp8(bits, group, act != "sigmoid", want_ob=True)
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), want_s.view(np.uint32))
+    assert gu.same_bits_or_both_nan(_bits(ob), want_ob).all()
+    assert _codes_equal(q.cpu().numpy(), want_q)
+
+
+def _rms_case(M, n, seed, w_f32):
+    rng = np.random.default_rng(seed)
+    x = gen.f32_to_bf16_bits((rng.standard_normal((M, n)) * 2).astype(np.float32))
+    res = gen.f32_to_bf16_bits((rng.standard_normal((M, n)) * 5).astype(np.float32))
+    wv = (1 + 0.2 * rng.standard_normal(n)).astype(np.float32)
+    w = wv if w_f32 else gen.f32_to_bf16_bits(wv)
+    return x, res, w
+
+
+def _rms_device(x, res, w, n, group, eps, wadd, out_f32):
+    M = x.shape[0]
+    xd = gu.dev(x).view(torch.bfloat16)
+    rd = gu.dev(res).view(torch.bfloat16) if res is not None else None
+    wd = gu.dev(w) if w.dtype == np.float32 else gu.dev(w).view(torch.bfloat16)
+    q = torch.zeros((M, n), dtype=torch.uint8, device="cuda")
+    s = torch.zeros((M, (n + group - 1) // group), dtype=torch.float32, device="cuda")
+    ob = torch.zeros((M, n), dtype=torch.float32 if out_f32 else torch.bfloat16, device="cuda")
+    return xd, rd, wd, q, s, ob
+
+
+@pytest.mark.parametrize("M,n,with_res,w_f32,wadd,out_f32", [
+    (1, 5120, False, False, None, False), (4, 5120, True, False, None, False), (3, 300, True, True, 1.0, True),
+    (2, 30720, False, False, None, False), (5, 4096, True, False, 1.0, False), (1, 4, False, True, None, True)])
+def test_rmsnorm_quant_row_bit_identical_to_oracle(M, n, with_res, w_f32, wadd, out_f32):
+    x, res, w = _rms_case(M, n, 9000 + M + n, w_f32)
+    if not with_res:
+        res = None
+    eps = 1e-6
+    xd, rd, wd, q, s, ob = _rms_device(x, res, w, n, 128, eps, wadd, out_f32)
+    r = ops.rmsnorm_quant_fp8(xd, wd, q, s, eps=eps, residual=rd, out=ob, group=128, wadd=wadd)
+    torch.cuda.synchronize()
+    assert r.name == "rmsnorm_quant_fp8"
+    want = orc.rmsnorm_quant_fp8(x, w, eps, 128, wadd or 0.0, res)
+    got_ob = gen.f32_to_bf16_bits(ob.cpu().numpy()) if out_f32 else _bits(ob)
+    assert np.array_equal(got_ob, want["ob"])
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), want["scale"].view(np.uint32))
+    assert np.array_equal(q.cpu().numpy(), want["q"])
+    if with_res:
+        assert np.array_equal(_bits(rd), want["res"])
+
+
+def _desc(t, dt):
+    return tensor_desc(t.data_ptr() if t is not None else None, dt, list(t.shape) if t is not None else [])
+
+
+@pytest.mark.parametrize("M,n,with_res", [(1, 5120, False), (4, 5120, True), (3, 300, True), (2, 13824, False)])
+def test_rmsnorm_quant_row_against_the_reference_kernel(M, n, with_res):
+    R = orc.ref_more()
+    if R is None:
+        pytest.skip("oracle/_ref/libref_more.so not present")
+    x, res, w = _rms_case(M, n, 9100 + M + n, False)
+    eps = 1e-6
+    xd, rd, wd, q, s, ob = _rms_device(x, res if with_res else None, w, n, 128, eps, None, False)
+    ops.rmsnorm_quant_fp8(xd, wd, q, s, eps=eps, residual=rd, out=ob, group=128)
+    # the reference's own entry and kernel on fresh copies of the same operands
+    xr, rr, wr, qr, sr, obr = _rms_device(x, res if with_res else None, w, n, 128, eps, None, False)
+    pack = ArgPack([_desc(xr, abi.RAD_BF16), _desc(rr, abi.RAD_BF16), _desc(wr, abi.RAD_BF16),
+                    _desc(qr, abi.RAD_F8E4M3), _desc(sr, abi.RAD_F32), _desc(obr, abi.RAD_BF16)],
+                   dict(M=M, n=n, eps=eps, group=128, dtype="bf16"))
+    assert R.ref_more_rmsnorm_quant_fp8(C.byref(pack.args), None) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(ob), _bits(obr))
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), sr.cpu().numpy().view(np.uint32))
+    assert np.array_equal(q.cpu().numpy(), qr.cpu().numpy())
+    if with_res:
+        assert np.array_equal(_bits(rd), _bits(rr))

@@ -188,3 +188,46 @@ def test_gated_quant_matches_independent_numpy_walk():
             c = np.clip((blk * (np.float32(1) / sc)[:, None]).astype(np.float32), -448, 448)
             assert np.array_equal(q[:, gi * 128:gi * 128 + blk.shape[1]], orc.encode_e4m3(c))
         assert s[1, 0] == 1.0 and (q[1, :128] & 0x7F).max() == 0
+
+
+def test_rmsnorm_quant_matches_independent_numpy_walk():
+    """orc_rmsnorm_quant_fp8 (the kernel of src/r3d_more.hip:248-330 of libr3d) against a numpy
+    restatement written from the rule: 256 strided partial sums of squares, a shuffle-down tree per
+    group of 32 partials, the eight results added ascending, rs = 1/sqrt(ss/n + eps),
+    h = bf16(src * rs * (w + wadd)), then the group quantiser; with a residual the bf16 sum is stored
+    first and is what gets squared and normed."""
+    rng = np.random.default_rng(12)
+    M, n, eps, wadd = 3, 1000, np.float32(1e-6), np.float32(1.0)
+    x = gen.f32_to_bf16_bits((rng.standard_normal((M, n)) * 2).astype(np.float32))
+    res = gen.f32_to_bf16_bits((rng.standard_normal((M, n)) * 5).astype(np.float32))
+    w = gen.f32_to_bf16_bits((0.1 * rng.standard_normal(n)).astype(np.float32))
+    for with_res in (False, True):
+        out = orc.rmsnorm_quant_fp8(x, w, float(eps), 128, float(wadd), res if with_res else None)
+        src = orc.bf16_bits_to_f32(x)
+        if with_res:
+            sb = gen.f32_to_bf16_bits((orc.bf16_bits_to_f32(res) + src).astype(np.float32))
+            assert np.array_equal(out["res"], sb)
+            src = orc.bf16_bits_to_f32(sb)
+        sq = (src * src).astype(np.float32)
+        for r in range(M):
+            part = np.zeros(256, np.float32)
+            for i in range(n):                              # thread i % 256 adds its elements ascending
+                part[i % 256] = np.float32(part[i % 256] + sq[r, i])
+            tot = None
+            for wp in range(8):
+                lane = part[wp * 32:(wp + 1) * 32].copy()
+                for off in (16, 8, 4, 2, 1):
+                    lane[:32 - off] = (lane[:32 - off] + lane[off:]).astype(np.float32)
+                tot = lane[0] if tot is None else np.float32(tot + lane[0])
+            rs = np.float32(1) / np.sqrt(np.float32(np.float32(tot / np.float32(n)) + eps), dtype=np.float32)
+            wv = (orc.bf16_bits_to_f32(w) + wadd).astype(np.float32)
+            h = gen.f32_to_bf16_bits(((src[r] * rs).astype(np.float32) * wv).astype(np.float32))
+            assert np.array_equal(out["ob"][r], h)
+            hf = orc.bf16_bits_to_f32(h)
+            for gi in range((n + 127) // 128):
+                blk = hf[gi * 128:gi * 128 + 128]
+                am = np.abs(blk).max()
+                sc = np.float32(am * np.float32(1 / 448)) if am > 0 else np.float32(1)
+                assert out["scale"][r, gi] == sc
+                c = np.clip((blk * (np.float32(1) / sc)).astype(np.float32), -448, 448)
+                assert np.array_equal(out["q"][r, gi * 128:gi * 128 + len(blk)], orc.encode_e4m3(c))

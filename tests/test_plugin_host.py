@@ -53,6 +53,18 @@ def test_schemas_entry_for_entry(plug):
     assert [p[0] for p in s["gemm_nt_q_gated"]["params"]] == ["M", "N", "K", "group", "dtype", "act"]
     assert [o[0] for o in s["gemm_nt_q_gated"]["operands"]] == ["a", "a_scale", "b", "b_scale", "q",
                                                                  "scale", "out_bf16"]
+    F = 1
+    INOUT = 2
+    assert s["quant_act_fp8"]["params"] == [("M", I, R), ("n", I, R), ("group", I, R), ("dtype", S, R)]
+    assert s["quant_act_fp8"]["operands"] == [("x", IN, 0), ("q", OUT, 0), ("scale", OUT, 0)]
+    assert s["gated_quant_fp8"]["params"] == [("M", I, R), ("n", I, R), ("group", I, R), ("dtype", S, R),
+                                              ("act", S, O)]
+    assert s["gated_quant_fp8"]["operands"] == [("gate_up", IN, 0), ("q", OUT, 0), ("scale", OUT, 0),
+                                                ("out_bf16", OUT, 1)]
+    assert s["rmsnorm_quant_fp8"]["params"] == [("M", I, R), ("n", I, R), ("eps", F, R), ("group", I, R),
+                                                ("dtype", S, R), ("wadd", F, O)]
+    assert s["rmsnorm_quant_fp8"]["operands"] == [("x", IN, 0), ("residual", INOUT, 1), ("w", W, 0),
+                                                  ("q", OUT, 0), ("scale", OUT, 0), ("out_bf16", OUT, 1)]
     assert plug.lib.rad_kernel_schema_at(-1) is None or not plug.lib.rad_kernel_schema_at(-1)
     assert not plug.lib.rad_kernel_schema_at(99)
 
@@ -61,7 +73,8 @@ def test_rows_names_priorities_constraints(plug):
     rows = {r.name: r for r in plug.rows()}
     want = {"logits_gemm_e4m3": 1000, "gemm_nt_q_mxfp4": 1000, "gemm_nt_q_fp8a8": 1000,
             "gemm_nt_q_fp8a8_decode": 1100, "gemm_nt_q_mxfp4_decode": 1100,
-            "gemm_nt_q_mxfp4_decode_q8x": 1200, "gemm_nt_q_gated_fp8a8": 1000}
+            "gemm_nt_q_mxfp4_decode_q8x": 1200, "gemm_nt_q_gated_fp8a8": 1000,
+            "quant_act_fp8_act": 1000, "gated_quant_fp8_act": 1000, "rmsnorm_quant_fp8": 1000}
     assert {k: v.priority for k, v in rows.items()} == want
     assert all(r.domain == abi.RAD_DOMAIN_DEVICE and r.launch for r in rows.values())
     assert rows["logits_gemm_e4m3"].has_layout
@@ -96,6 +109,14 @@ def test_band_resolution(plug):
     assert plug.resolve("gemm_nt_q_gated", dict(M=65, act="silu", **gq)) is None
     assert plug.resolve("gemm_nt_q_gated", dict(M=4, **gq)) is None
     assert plug.resolve("gemm_nt_q_gated", dict(M=4, act="gelu", **gq)) is None
+    # the activation producers: one row per op (src/r3d_rows.cpp:1892-1907, :2093-2101 of libr3d)
+    assert plug.resolve("quant_act_fp8", dict(M=4, n=5120, group=128, dtype="bf16")).name == "quant_act_fp8_act"
+    assert plug.resolve("quant_act_fp8", dict(M=4, n=5120, group=128, dtype="f16")) is None
+    assert plug.resolve("gated_quant_fp8", dict(M=4, n=13824, group=128, dtype="f32")).name == "gated_quant_fp8_act"
+    rq = dict(M=4, eps=1e-6, dtype="bf16")
+    assert plug.resolve("rmsnorm_quant_fp8", dict(n=5120, group=128, **rq)).name == "rmsnorm_quant_fp8"
+    assert plug.resolve("rmsnorm_quant_fp8", dict(n=5122, group=128, **rq)) is None
+    assert plug.resolve("rmsnorm_quant_fp8", dict(n=5120, group=64, **rq)) is None
 
 
 _DUMP = r"""
@@ -120,7 +141,8 @@ def _rows_under(env):
 
 
 ALL = {"logits_gemm_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode",
-       "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_gated_fp8a8"}
+       "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_gated_fp8a8",
+       "quant_act_fp8_act", "gated_quant_fp8_act", "rmsnorm_quant_fp8"}
 
 
 @pytest.mark.parametrize("env,hidden,mx_row,f8_row", [
@@ -202,6 +224,47 @@ def test_fp8_entry_refusals(plug, over, code):
     pack, _ = _fp8_args(**over)
     for sym in ("r3d_rad_gemm_nt_q_fp8", "r3d_rad_gemm_nt_q_fp8_decode"):
         assert plug.entry(sym)(C.byref(pack.args), None) == code, sym
+
+
+def test_activation_producer_refusals(plug):
+    """Status codes and their precedence as in libr3d's entries (src/r3d_band.hip:459-548,
+    src/r3d_more.hip:480-541): absent operand, dtype, shape, stride -- all before any device use."""
+    z = np.zeros(16, np.uint8).ctypes.data
+    T = tensor_desc
+    IV, DT = abi.RAD_E_INVAL, abi.RAD_E_DTYPE
+
+    def quant(x=None, q=None, sc=None, **p):
+        ts = [x or T(z, abi.RAD_BF16, [2, 256]), q or T(z, abi.RAD_F8E4M3, [2, 256]), sc or T(z, abi.RAD_F32, [2, 2])]
+        return plug.entry("r3d_rad_quant_act_fp8")(C.byref(ArgPack(ts, dict(dict(M=2, n=256, group=128, dtype="bf16"), **p)).args), None)
+    assert quant(x=T(None, abi.RAD_BF16, [2, 256])) == IV
+    assert quant(x=T(z, abi.RAD_F16, [2, 256])) == DT
+    assert quant(q=T(z, abi.RAD_U8, [2, 256])) == DT
+    assert quant(sc=T(z, abi.RAD_BF16, [2, 2])) == DT
+    assert quant(n=0) == SH
+    assert quant(q=T(z, abi.RAD_F8E4M3, [1, 256])) == SH
+    assert quant(sc=T(z, abi.RAD_F32, [2, 1])) == SH
+    assert quant(x=T(z, abi.RAD_BF16, [2, 256], [512, 2])) == ST
+
+    def gated(gu=None, ob=None, **p):
+        ts = [gu or T(z, abi.RAD_BF16, [2, 512]), T(z, abi.RAD_F8E4M3, [2, 256]), T(z, abi.RAD_F32, [2, 2]),
+              ob or T(None, abi.RAD_BF16, [])]
+        return plug.entry("r3d_rad_gated_quant_fp8")(C.byref(ArgPack(ts, dict(dict(M=2, n=256, group=128, dtype="bf16"), **p)).args), None)
+    assert gated(gu=T(z, abi.RAD_F16, [2, 512])) == DT
+    assert gated(ob=T(z, abi.RAD_F16, [2, 256])) == DT
+    assert gated(ob=T(z, abi.RAD_BF16, [1, 256])) == SH
+    assert gated(gu=T(z, abi.RAD_BF16, [1, 2, 512], [2048, 1024, 1])) == ST     # a hole between the rows
+
+    def rms(x=None, res=None, w=None, n_t=6, **p):
+        ts = [x or T(z, abi.RAD_BF16, [2, 256]), res or T(None, abi.RAD_BF16, []), w or T(z, abi.RAD_BF16, [256]),
+              T(z, abi.RAD_F8E4M3, [2, 256]), T(z, abi.RAD_F32, [2, 2]), T(None, abi.RAD_BF16, [])][:n_t]
+        return plug.entry("r3d_rad_rmsnorm_quant_fp8")(C.byref(ArgPack(ts, dict(dict(M=2, n=256, eps=1e-6, group=128, dtype="bf16"), **p)).args), None)
+    assert rms(n_t=4) == IV
+    assert rms(x=T(z, abi.RAD_F32, [2, 256])) == DT                             # the published row is bf16
+    assert rms(res=T(z, abi.RAD_F32, [2, 256])) == DT
+    assert rms(w=T(z, abi.RAD_F16, [256])) == DT
+    assert rms(n=30724) == SH                                                   # the row must fit shared memory
+    assert rms(res=T(z, abi.RAD_BF16, [1, 256])) == SH
+    assert rms(w=T(z, abi.RAD_BF16, [1, 256])) == ST                            # w is a rank-1 vector
 
 
 def test_fp8_decode_row_band_bound_and_alignment(plug):
