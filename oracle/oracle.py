@@ -224,6 +224,17 @@ def rmsnorm_quant_fp8(x_bits: np.ndarray, w: np.ndarray, eps: float, group: int 
     return dict(q=q, scale=s, ob=ob, res=res)
 
 
+def row_topk(x_bits: np.ndarray, R: int, vocab_off: int = 0):
+    """bf16 bits x [M, N] -> (idx int32 [M, R], val f32 [M, R]): exact top-R per row, descending, ties to
+    the lower column; unfillable slots are (-1, -inf)."""
+    x = _c(x_bits, np.uint16)
+    M, N = x.shape
+    idx = np.empty((M, R), np.int32)
+    val = np.empty((M, R), np.float32)
+    lib().orc_row_topk(_p(x), I64(M), I64(N), I64(R), I64(vocab_off), _p(idx), _p(val))
+    return idx, val
+
+
 def quant_act_mx8(x: np.ndarray):
     x = _c(x, np.float32)
     M, n = x.shape

@@ -281,6 +281,34 @@ ORC_API void orc_rmsnorm_quant_fp8(const uint16_t* x, uint16_t* res, const uint1
     }
 }
 
+/* ------------------------------------------------------------------ row_topk
+ * src/r3d_more.hip:179-236 of libr3d: per row, R rounds of argmax under the engine's one total
+ * order (value descending, ties to the lower column), each round looking only at what comes
+ * strictly after the previous pick in that order. A slot the row cannot fill reports id -1 and
+ * value -inf. `off` is added to every reported column. The walk below is serial (ascending column),
+ * so on rows that hold a NaN it is one of the orders the reference's block reduction may take;
+ * without NaNs the order of the walk cannot matter. x holds bf16 bit patterns. */
+ORC_API void orc_row_topk(const uint16_t* x, int64_t M, int64_t N, int64_t R, int64_t off, int32_t* idx,
+                          float* val) {
+    for (int64_t m = 0; m < M; ++m) {
+        float pv = INFINITY;
+        int64_t pi = -1;
+        for (int64_t r = 0; r < R; ++r) {
+            float bv = 0.0f;
+            int64_t bi = -1;
+            for (int64_t i = 0; i < N; ++i) {
+                const float v = bf16_to_f32(x[m * N + i]);
+                if (v > pv || (v == pv && i <= pi)) continue;          /* not after the previous pick */
+                if (bi < 0 || v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+            }
+            const bool ok = bi >= 0;
+            idx[m * R + r] = ok ? (int32_t)(bi + off) : -1;
+            val[m * R + r] = ok ? bv : -INFINITY;
+            if (ok) { pv = bv; pi = bi; }
+        }
+    }
+}
+
 /* ------------------------------------------------------------------ OCP-MX activation
  * quantiser (e4m3 elements, one E8M0 scale per 32 columns). PARITY UNPINNED: the
  * reference has no such quantiser. Rule: shared exponent = floor(log2(amax)) - 8 (8 is
