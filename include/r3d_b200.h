@@ -46,6 +46,11 @@ int64_t r3d_rad_gemm_nt_q_gated_fp8_scratch(const RadArgs* a);
 int r3d_rad_quant_act_fp8(const RadArgs* a, RadStream s);
 int r3d_rad_gated_quant_fp8(const RadArgs* a, RadStream s);
 int r3d_rad_rmsnorm_quant_fp8(const RadArgs* a, RadStream s);
+/* row_topk (x, idx, val, pairs?): exact per-row top-R, R <= 32, value descending and ties to the
+ * lower column; `vocab_off` is added to every reported column and `pairs` is the [M, R, 2]
+ * (int32 id, f32 value) plane a sharded head gathers instead of its logits. Replaces
+ * r3d_rad_row_topk (src/r3d_more.hip:179-236, :438-476). */
+int r3d_rad_row_topk(const RadArgs* a, RadStream s);
 /* gemm_nt_q @ mxfp4a8, any M. Replaces r3d_rad_gemm_nt_q
  * (src/r3d_gemm_mxfp4.hip:1587-1691). */
 int r3d_rad_gemm_nt_q(const RadArgs* a, RadStream s);

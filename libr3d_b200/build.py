@@ -28,6 +28,7 @@ SOURCES = [
     "entries_logits.cpp",
     "launch.cu",
     "kern_exact.cu",
+    "kern_topk.cu",
     "kern_q8x.cu",
     "q8x_static.cu",
     "kern_stream.cu",

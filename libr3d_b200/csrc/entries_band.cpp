@@ -8,6 +8,8 @@
  *   quant_act_fp8      src/r3d_band.hip:459-489     x, q, scale
  *   gated_quant_fp8    src/r3d_band.hip:491-548     gate_up, q, scale, out_bf16?
  *   rmsnorm_quant_fp8  src/r3d_more.hip:480-541     x, residual?, w, q, scale, out_bf16?
+ * and the logits consumer of the column-sharded LM head:
+ *   row_topk           src/r3d_more.hip:438-476     x, idx, val, pairs?
  */
 #include <cuda_runtime.h>
 #include "entry_util.h"
@@ -140,4 +142,35 @@ extern "C" int r3d_rad_rmsnorm_quant_fp8(const RadArgs* a, RadStream s) {
     return launch_rmsnorm_quant_fp8(x->data, xp, res ? res->data : nullptr, rp, w->data, (int)w->dtype, q->data, qp,
                                     (float*)sc->data, sp, ob ? ob->data : nullptr, ob ? (int)ob->dtype : RAD_F32, op,
                                     (int)rows, (int)n, (int)g, eps, wadd, (cudaStream_t)(uintptr_t)s);
+}
+
+extern "C" int r3d_rad_row_topk(const RadArgs* a, RadStream s) {
+    const RadTensor* x = rad_arg_in(a, 0);
+    const RadTensor* idx = rad_arg_in(a, 1);
+    const RadTensor* val = rad_arg_in(a, 2);
+    const RadTensor* pairs = optional_out(a, 3);
+    if (!x || !idx || !val) return RAD_E_INVAL;
+    if (!act_dtype(x->dtype)) return RAD_E_DTYPE;
+    if (idx->dtype != RAD_I32 || val->dtype != RAD_F32) return RAD_E_DTYPE;
+    if (pairs && pairs->dtype != RAD_F32) return RAD_E_DTYPE;
+    const int64_t N = int_param(a, "N", x->rank >= 2 ? x->shape[1] : 0);
+    const int64_t R = int_param(a, "R", 1);
+    const int64_t off = int_param(a, "vocab_off", 0);
+    if (N <= 0 || N > kMaxExtent || R <= 0 || R > 32) return RAD_E_SHAPE;
+    const int64_t M = rad_tensor_numel(x) / N;
+    if (M <= 0 || M > 0xffff || rad_tensor_numel(idx) < M * R || rad_tensor_numel(val) < M * R) return RAD_E_SHAPE;
+    if (pairs && rad_tensor_numel(pairs) < M * R * 2) return RAD_E_SHAPE;
+    int64_t xp, ip, vp, pp = 0;
+    if (pitch_of(x, N, &xp) || pitch_of(idx, R, &ip) || pitch_of(val, R, &vp)) return RAD_E_STRIDE;
+    if (pairs) {
+        /* [M, R, 2] as the schema describes it, or the same memory as a flat [M, 2R] */
+        if (pairs->rank == 3) {
+            if (pairs->stride[2] != 1 || pairs->stride[1] != 2 || pairs->stride[0] != 2 * R) return RAD_E_STRIDE;
+            pp = 2 * R;
+        } else if (pitch_of(pairs, 2 * R, &pp)) return RAD_E_STRIDE;
+    }
+    if (!device_is_sm100()) return RAD_E_UNSUPPORTED;
+    return launch_row_topk(x->data, (int)x->dtype, xp, (int32_t*)idx->data, ip, (float*)val->data, vp,
+                           pairs ? (float*)pairs->data : nullptr, pp, (int)M, (int)N, (int)R, off,
+                           (cudaStream_t)(uintptr_t)s);
 }

@@ -85,7 +85,21 @@ const RadOperandSpec kRmsQuantOperands[] = {
     { "q", RAD_OPD_OUT, 0 },     { "scale", RAD_OPD_OUT, 0 },      { "out_bf16", RAD_OPD_OUT, 1 },
 };
 
+/* row_topk: src/r3d_rows.cpp:686-699 */
+const RadParamSpec kRowTopkParams[] = {
+    { "M", RAD_P_INT, RAD_REQUIRED, 0 },         { "N", RAD_P_INT, RAD_REQUIRED, 0 },
+    { "R", RAD_P_INT, RAD_REQUIRED, 0 },         { "vocab_off", RAD_P_INT, RAD_OPTIONAL, 0 },
+    { "dtype", RAD_P_STR, RAD_REQUIRED, 0 },
+};
+const RadOperandSpec kRowTopkOperands[] = {
+    { "x", RAD_OPD_IN, 0 }, { "idx", RAD_OPD_OUT, 0 }, { "val", RAD_OPD_OUT, 0 }, { "pairs", RAD_OPD_OUT, 1 },
+};
+
 const RadOpSchema kSchemas[] = {
+    { "row_topk", kRowTopkParams, COUNT_OF(kRowTopkParams), kRowTopkOperands, COUNT_OF(kRowTopkOperands),
+      "exact per-row top-R, descending, ties to the lower column; `vocab_off` shifts the reported "
+      "columns to global ids and `pairs` is the [M, R, 2] (int32 id, f32 value) plane a sharded "
+      "head gathers; an unfillable slot reports id -1." },
     { "quant_act_fp8", kQuantActParams, COUNT_OF(kQuantActParams), kQuantActOperands,
       COUNT_OF(kQuantActOperands),
       "symmetric e4m3 quantisation of a token-major activation per (row, `group` columns), plain "
@@ -145,6 +159,12 @@ const RadConstraint kCBand[] = {
 const RadConstraint kCRmsQuant[] = {
     { "n", RAD_C_DIV, 4, nullptr }, { "group", RAD_C_EQ, 128, nullptr },
     { "dtype", RAD_C_IN, 0, "bf16" },
+};
+
+/* src/r3d_rows.cpp:1412-1418 */
+const RadConstraint kCRowTopk[] = {
+    { "N", RAD_C_DIV, 8, nullptr }, { "M", RAD_C_GE, 1, nullptr }, { "R", RAD_C_GE, 1, nullptr },
+    { "R", RAD_C_LE, 32, nullptr }, { "dtype", RAD_C_IN, 0, "bf16" },
 };
 
 enum { kPrioPlain = 1000, kPrioDecode = 1100, kPrioQ8x = 1200 };
@@ -237,6 +257,14 @@ const RadKernelInfo kRows[] = {
         "bf16 x (+ bf16 residual), f32/bf16 w, e4m3 codes with f32 per-group scales, optional "
         "bf16/f32 norm output",
         kPrioPlain, kCRmsQuant, r3d_rad_rmsnorm_quant_fp8),
+
+    /* the consumer behind the column-sharded LM head (src/r3d_rows.cpp:2084-2091) */
+    ROW("rowtopk_bf16", "row_topk", "select",
+        "exact per-row top-R of a bf16 matrix, descending, ties to the lower column: a tournament "
+        "of 512-item warp tiles held in registers, repeated over the survivors",
+        "any M, N a multiple of 8, R <= 32",
+        "bf16 in, f32 values + i32 columns out, optional f32 pairs plane",
+        kPrioPlain, kCRowTopk, r3d_rad_row_topk),
 };
 
 /* ------------------------------------------------------------------ registration gate */

@@ -191,6 +191,17 @@ def rmsnorm_quant_fp8(x: torch.Tensor, w: torch.Tensor, q: torch.Tensor, scale: 
                                                _desc(scale, abi.RAD_F32), _desc(out, odt)])
 
 
+def row_topk(x: torch.Tensor, idx: torch.Tensor, val: torch.Tensor, pairs: torch.Tensor | None = None, *,
+             R: int, vocab_off: int | None = None) -> Row:
+    """The row_topk op through its row: x [M, N] bf16 -> idx i32 [M, R], val f32 [M, R] and, when given,
+    pairs f32 [M, R, 2] holding (bits of the int32 id, value)."""
+    query = dict(M=x.shape[0], N=x.shape[-1], R=R, dtype="bf16")
+    if vocab_off is not None:
+        query["vocab_off"] = int(vocab_off)
+    return _issue("row_topk", query, [_desc(x, abi.RAD_BF16), _desc(idx, abi.RAD_I32), _desc(val, abi.RAD_F32),
+                                      _desc(pairs, abi.RAD_F32)])
+
+
 class BoundGemm:
     """A gemm_nt_q band declared once and issued many times, the way the engine uses a row:
     the row is resolved and the RadArgs built at declare time over fixed device buffers; each

@@ -125,13 +125,14 @@ _ref_more: list = []
 
 def ref_more() -> C.CDLL | None:
     """src/r3d_more.hip of libr3d compiled as it lies for sm_100a (oracle/_ref/libref_more.so): entry
-    ref_more_rmsnorm_quant_fp8(const RadArgs*, stream). None when the library was not built."""
+    ref_more_rmsnorm_quant_fp8 and ref_more_row_topk, each (const RadArgs*, stream). None when the library was not built."""
     if not _ref_more:
         so, R = HERE / "_ref" / "libref_more.so", None
         if so.exists():
             try:
                 R = C.CDLL(str(so))
                 R.ref_more_rmsnorm_quant_fp8.argtypes = [C.c_void_p, C.c_void_p]
+                R.ref_more_row_topk.argtypes = [C.c_void_p, C.c_void_p]
             except OSError:
                 R = None
         _ref_more.append(R)

@@ -12,3 +12,4 @@ void r3d_dump_end(R3dDumpSlot*, int) {}
 
 #define REF_API extern "C" __attribute__((visibility("default")))
 REF_API int ref_more_rmsnorm_quant_fp8(const RadArgs* a, void* stream) { return r3d_rad_rmsnorm_quant_fp8(a, (RadStream)stream); }
+REF_API int ref_more_row_topk(const RadArgs* a, void* stream) { return r3d_rad_row_topk(a, (RadStream)stream); }

@@ -132,3 +132,78 @@ def test_rmsnorm_quant_row_against_the_reference_kernel(M, n, with_res):
     assert np.array_equal(q.cpu().numpy(), qr.cpu().numpy())
     if with_res:
         assert np.array_equal(_bits(rd), _bits(rr))
+
+
+@pytest.mark.parametrize("M,N,R,off,with_pairs", [(1, 151936, 32, 0, True), (4, 19072, 8, 132864, True),
+                                                   (16, 19072, 1, 19072, False), (3, 8, 32, 5, True),
+                                                   (2, 512, 32, 0, False), (5, 1000, 7, 0, True)])
+def test_row_topk_row_against_oracle(M, N, R, off, with_pairs):
+    """Exact top-R with ties: the values are drawn from few distinct bf16 numbers so every row holds
+    many equal candidates, plus +-inf and signed zeros; slots past the row's width are (-1, -inf)."""
+    rng = np.random.default_rng(M * 7 + N + R)
+    x = gen.f32_to_bf16_bits(np.round(rng.standard_normal((M, N)) * 8).astype(np.float32) / 4)
+    x[0, :4] = [0x7F80, 0xFF80, 0x0000, 0x8000]
+    x[-1, N - 1] = x[-1].view(np.int16).max()                 # a tie with an earlier column at the row's end
+    xd = gu.dev(x).view(torch.bfloat16)
+    idx = torch.full((M, R), -7, dtype=torch.int32, device="cuda")
+    val = torch.zeros((M, R), dtype=torch.float32, device="cuda")
+    pairs = torch.zeros((M, R, 2), dtype=torch.float32, device="cuda") if with_pairs else None
+    r = ops.row_topk(xd, idx, val, pairs, R=R, vocab_off=off)
+    torch.cuda.synchronize()
+    assert r.name == "rowtopk_bf16"
+    want_i, want_v = orc.row_topk(x, R, off)
+    assert np.array_equal(idx.cpu().numpy(), want_i)
+    assert np.array_equal(val.cpu().numpy().view(np.uint32), want_v.view(np.uint32))
+    if with_pairs:
+        p = pairs.cpu().numpy()
+        assert np.array_equal(p[..., 0].copy().view(np.int32), want_i)
+        assert np.array_equal(p[..., 1].view(np.uint32), want_v.view(np.uint32))
+
+
+def test_sharded_row_topk_pairs_merge_to_the_unsharded_answer():
+    """What the column-sharded head does with it: each slab reports its top-R with global ids
+    (vocab_off = the slab's first column); the top-R of the concatenated pairs is the top-R of the row."""
+    M, N, R, G = 4, 4096, 16, 4
+    rng = np.random.default_rng(5)
+    x = gen.f32_to_bf16_bits(np.round(rng.standard_normal((M, N)) * 16).astype(np.float32) / 8)
+    want_i, want_v = orc.row_topk(x, R, 0)
+    got_i, got_v = [], []
+    for g in range(G):
+        sl = np.ascontiguousarray(x[:, g * N // G:(g + 1) * N // G])
+        idx = torch.zeros((M, R), dtype=torch.int32, device="cuda")
+        val = torch.zeros((M, R), dtype=torch.float32, device="cuda")
+        ops.row_topk(gu.dev(sl).view(torch.bfloat16), idx, val, None, R=R, vocab_off=g * N // G)
+        torch.cuda.synchronize()
+        got_i.append(idx.cpu().numpy()); got_v.append(val.cpu().numpy())
+    ci, cv = np.concatenate(got_i, 1), np.concatenate(got_v, 1)
+    for m in range(M):
+        order = np.lexsort((ci[m], -cv[m]))[:R]                # value descending, then id ascending
+        assert np.array_equal(ci[m][order], want_i[m]) and np.array_equal(cv[m][order], want_v[m])
+
+
+@pytest.mark.parametrize("M,N,R,off", [(1, 151936, 32, 0), (4, 19072, 8, 132864), (3, 8, 32, 5), (5, 1000, 7, 0)])
+def test_row_topk_row_against_the_reference_kernel(M, N, R, off):
+    """The reference's own row_topk entry and kernel (src/r3d_more.hip, compiled for sm_100a) on the same
+    rows, ties included: columns, values and the pairs plane must be identical. The rows are positive:
+    in the reference's block reduction a thread that has no candidate left carries (0.0, -1), and its
+    comparison lets that pair win against a real candidate whose value is negative, so on rows whose
+    picks reach below zero it reports holes where its stated contract (exact top-R) has values. This
+    library follows the contract (the oracle test above covers negative rows)."""
+    Rf = orc.ref_more()
+    if Rf is None:
+        pytest.skip("oracle/_ref/libref_more.so not present")
+    rng = np.random.default_rng(M * 11 + N + R)
+    x = gen.f32_to_bf16_bits(np.round(rng.standard_normal((M, N)) * 8).astype(np.float32) / 4 + 16)
+    xd = gu.dev(x).view(torch.bfloat16)
+    out = []
+    for _ in range(2):
+        out.append((torch.full((M, R), -7, dtype=torch.int32, device="cuda"),
+                    torch.zeros((M, R), dtype=torch.float32, device="cuda"),
+                    torch.zeros((M, R, 2), dtype=torch.float32, device="cuda")))
+    ops.row_topk(xd, *out[0], R=R, vocab_off=off)
+    pack = ArgPack([_desc(xd, abi.RAD_BF16), _desc(out[1][0], abi.RAD_I32), _desc(out[1][1], abi.RAD_F32),
+                    _desc(out[1][2], abi.RAD_F32)], dict(M=M, N=N, R=R, vocab_off=off, dtype="bf16"))
+    assert Rf.ref_more_row_topk(C.byref(pack.args), None) == 0
+    torch.cuda.synchronize()
+    for a, b in zip(out[0], out[1]):
+        assert np.array_equal(a.cpu().numpy().view(np.uint32), b.cpu().numpy().view(np.uint32))

@@ -231,3 +231,19 @@ def test_rmsnorm_quant_matches_independent_numpy_walk():
                 assert out["scale"][r, gi] == sc
                 c = np.clip((blk * (np.float32(1) / sc)).astype(np.float32), -448, 448)
                 assert np.array_equal(out["q"][r, gi * 128:gi * 128 + len(blk)], orc.encode_e4m3(c))
+
+
+def test_row_topk_matches_a_sort():
+    """orc_row_topk (src/r3d_more.hip:179-236 of libr3d: R rounds of argmax, each after the previous
+    pick) against a plain sort by (value descending, column ascending); unfillable slots are (-1, -inf)."""
+    rng = np.random.default_rng(13)
+    M, N, R, off = 4, 40, 32, 1000
+    x = gen.f32_to_bf16_bits(np.round(rng.standard_normal((M, N)) * 4).astype(np.float32) / 2)
+    x[0, :3] = [0x7F80, 0xFF80, 0x8000]
+    xf = orc.bf16_bits_to_f32(x)
+    idx, val = orc.row_topk(x, R, off)
+    for m in range(M):
+        order = np.lexsort((np.arange(N), -xf[m]))
+        assert np.array_equal(idx[m], order[:R] + off) and np.array_equal(val[m], xf[m][order[:R]])
+    idx, val = orc.row_topk(x[:, :8], R, 0)
+    assert (idx[:, 8:] == -1).all() and np.isneginf(val[:, 8:]).all() and (idx[:, :8] >= 0).all()

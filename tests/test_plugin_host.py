@@ -65,6 +65,8 @@ def test_schemas_entry_for_entry(plug):
                                                 ("dtype", S, R), ("wadd", F, O)]
     assert s["rmsnorm_quant_fp8"]["operands"] == [("x", IN, 0), ("residual", INOUT, 1), ("w", W, 0),
                                                   ("q", OUT, 0), ("scale", OUT, 0), ("out_bf16", OUT, 1)]
+    assert s["row_topk"]["params"] == [("M", I, R), ("N", I, R), ("R", I, R), ("vocab_off", I, O), ("dtype", S, R)]
+    assert s["row_topk"]["operands"] == [("x", IN, 0), ("idx", OUT, 0), ("val", OUT, 0), ("pairs", OUT, 1)]
     assert plug.lib.rad_kernel_schema_at(-1) is None or not plug.lib.rad_kernel_schema_at(-1)
     assert not plug.lib.rad_kernel_schema_at(99)
 
@@ -74,7 +76,8 @@ def test_rows_names_priorities_constraints(plug):
     want = {"logits_gemm_e4m3": 1000, "gemm_nt_q_mxfp4": 1000, "gemm_nt_q_fp8a8": 1000,
             "gemm_nt_q_fp8a8_decode": 1100, "gemm_nt_q_mxfp4_decode": 1100,
             "gemm_nt_q_mxfp4_decode_q8x": 1200, "gemm_nt_q_gated_fp8a8": 1000,
-            "quant_act_fp8_act": 1000, "gated_quant_fp8_act": 1000, "rmsnorm_quant_fp8": 1000}
+            "quant_act_fp8_act": 1000, "gated_quant_fp8_act": 1000, "rmsnorm_quant_fp8": 1000,
+            "rowtopk_bf16": 1000}
     assert {k: v.priority for k, v in rows.items()} == want
     assert all(r.domain == abi.RAD_DOMAIN_DEVICE and r.launch for r in rows.values())
     assert rows["logits_gemm_e4m3"].has_layout
@@ -82,7 +85,7 @@ def test_rows_names_priorities_constraints(plug):
     assert ("group", abi.RAD_C_EQ, 128, None) in rows["gemm_nt_q_fp8a8"].constraints
     assert ("K", abi.RAD_C_DIV, 128, None) in rows["gemm_nt_q_mxfp4_decode"].constraints
     # never constrain N: the engine may omit it and an absent key fails its constraint
-    assert not any(c[0] == "N" for r in rows.values() for c in r.constraints)
+    assert not any(c[0] == "N" for r in rows.values() for c in r.constraints if r.op == "gemm_nt_q")
     assert not plug.lib.rad_kernel_at(len(rows)) and not plug.lib.rad_kernel_at(-1)
 
 
@@ -117,6 +120,9 @@ def test_band_resolution(plug):
     assert plug.resolve("rmsnorm_quant_fp8", dict(n=5120, group=128, **rq)).name == "rmsnorm_quant_fp8"
     assert plug.resolve("rmsnorm_quant_fp8", dict(n=5122, group=128, **rq)) is None
     assert plug.resolve("rmsnorm_quant_fp8", dict(n=5120, group=64, **rq)) is None
+    assert plug.resolve("row_topk", dict(M=4, N=19072, R=32, dtype="bf16")).name == "rowtopk_bf16"
+    assert plug.resolve("row_topk", dict(M=4, N=19072, R=33, dtype="bf16")) is None
+    assert plug.resolve("row_topk", dict(M=4, N=19071, R=8, dtype="bf16")) is None
 
 
 _DUMP = r"""
@@ -142,7 +148,7 @@ def _rows_under(env):
 
 ALL = {"logits_gemm_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode",
        "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_gated_fp8a8",
-       "quant_act_fp8_act", "gated_quant_fp8_act", "rmsnorm_quant_fp8"}
+       "quant_act_fp8_act", "gated_quant_fp8_act", "rmsnorm_quant_fp8", "rowtopk_bf16"}
 
 
 @pytest.mark.parametrize("env,hidden,mx_row,f8_row", [
@@ -265,6 +271,19 @@ def test_activation_producer_refusals(plug):
     assert rms(n=30724) == SH                                                   # the row must fit shared memory
     assert rms(res=T(z, abi.RAD_BF16, [1, 256])) == SH
     assert rms(w=T(z, abi.RAD_BF16, [1, 256])) == ST                            # w is a rank-1 vector
+
+    def topk(x=None, idx=None, val=None, pairs=None, **p):
+        ts = [x or T(z, abi.RAD_BF16, [2, 256]), idx or T(z, abi.RAD_I32, [2, 4]), val or T(z, abi.RAD_F32, [2, 4]),
+              pairs or T(None, abi.RAD_F32, [])]
+        return plug.entry("r3d_rad_row_topk")(C.byref(ArgPack(ts, dict(dict(M=2, N=256, R=4, dtype="bf16"), **p)).args), None)
+    assert topk(val=T(None, abi.RAD_F32, [2, 4])) == IV
+    assert topk(x=T(z, abi.RAD_F16, [2, 256])) == DT
+    assert topk(idx=T(z, abi.RAD_F32, [2, 4])) == DT
+    assert topk(pairs=T(z, abi.RAD_BF16, [2, 4, 2])) == DT
+    assert topk(R=33) == SH and topk(R=0) == SH
+    assert topk(idx=T(z, abi.RAD_I32, [1, 4])) == SH
+    assert topk(pairs=T(z, abi.RAD_F32, [2, 2, 2])) == SH
+    assert topk(pairs=T(z, abi.RAD_F32, [2, 4, 2], [16, 4, 1])) == ST           # not the dense [M, R, 2] plane
 
 
 def test_fp8_decode_row_band_bound_and_alignment(plug):
