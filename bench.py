@@ -397,7 +397,7 @@ def run_all(args):
         del calls, keep
         torch.cuda.empty_cache()
 
-    want = set(c.strip().upper() for c in args.cfg.split(",")) if args.cfg else {"C1", "C2", "C3", "C4", "C5"}
+    want = set(c.strip().upper() for c in args.cfg.split(",")) if args.cfg else {"C1", "C2", "C3", "C4", "C5", "ROWS"}
     if "C1" in want:
         decode_case("C1", "fp8a8", 1, 4096, 4096)
     if "C2" in want:
@@ -442,6 +442,36 @@ def run_all(args):
         out.append({"cfg": "C5", "band": "logits e4m3", "M": M, "N": NV, "K": K, "us_per_call": round(us, 1),
                     "GBs": round(nbytes / us / 1e3, 1), "hbm_frac_of_measured": round(nbytes / us / 1e3 / peak, 3),
                     "planes": 2, "nonzero_ok": int(torch.count_nonzero(y)) > 0.9 * M * NV})
+    if "ROWS" in want:
+        # the rows either side of the bands, through their row entries: activation producers at the
+        # model's widths and the per-shard top-R over bf16 logits
+        def row_case(name, shape, nbytes, issue):
+            calls = [lambda st, i=i: issue(i) for i in range(4)]
+            us = timed(calls, 50)
+            out.append({"cfg": "ROWS", "row": name, "shape": shape, "us_per_call": round(us, 2),
+                        "GBs": round(nbytes / us / 1e3, 1)})
+        for M in (1, 16):
+            n = 5120
+            xs = [torch.randn((M, n), device=dev, generator=g).to(torch.bfloat16) for _ in range(4)]
+            rs = [torch.randn((M, n), device=dev, generator=g).to(torch.bfloat16) for _ in range(4)]
+            w = torch.ones(n, device=dev, dtype=torch.bfloat16)
+            q = torch.zeros((M, n), dtype=torch.uint8, device=dev)
+            sc = torch.zeros((M, n // 128), dtype=torch.float32, device=dev)
+            ob = torch.zeros((M, n), dtype=torch.bfloat16, device=dev)
+            row_case("quant_act_fp8_act", f"M={M} n={n}", M * n * 3, lambda i: ops.quant_act_fp8_row(xs[i], q, sc))
+            row_case("rmsnorm_quant_fp8 (+residual)", f"M={M} n={n}", M * n * 9,
+                     lambda i: ops.rmsnorm_quant_fp8(xs[i], w, q, sc, eps=1e-6, residual=rs[i], out=ob))
+            n2 = 13824
+            gus = [torch.randn((M, 2 * n2), device=dev, generator=g).to(torch.bfloat16) for _ in range(4)]
+            q2 = torch.zeros((M, n2), dtype=torch.uint8, device=dev)
+            sc2 = torch.zeros((M, n2 // 128), dtype=torch.float32, device=dev)
+            row_case("gated_quant_fp8_act", f"M={M} n={n2}", M * n2 * 5, lambda i: ops.gated_quant_fp8_row(gus[i], q2, sc2))
+        for (M, N, R) in ((1, 151936, 32), (16, 151936, 8), (16, 19072, 32)):
+            ls = [torch.randn((M, N), device=dev, generator=g).to(torch.bfloat16) for _ in range(4)]
+            idx = torch.zeros((M, R), dtype=torch.int32, device=dev)
+            val = torch.zeros((M, R), dtype=torch.float32, device=dev)
+            pairs = torch.zeros((M, R, 2), dtype=torch.float32, device=dev)
+            row_case("rowtopk_bf16", f"M={M} N={N} R={R}", M * N * 2, lambda i: ops.row_topk(ls[i], idx, val, pairs, R=R))
     for r in out:
         sys.stderr.write(json.dumps(r) + "\n")
     print(json.dumps({"workload": "all", "n_gpus": 1, "peak_GBs": peak, "peak_source": "measured", "timed_as":
@@ -458,7 +488,7 @@ def main():
     ap.add_argument("--rot", type=int, default=4, help="distinct weight planes cycled (footprint > L2)")
     ap.add_argument("--row", default="gemm_nt_q_mxfp4_decode")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
-    ap.add_argument("--cfg", default="", help="--workload all: comma list of configurations to run (C1..C5), default all")
+    ap.add_argument("--cfg", default="", help="--workload all: comma list of configurations to run (C1..C5, ROWS), default all")
     ap.add_argument("--tokens", type=int, default=8192, help="--workload all: M of the prefill configuration C4")
     ap.add_argument("--gather", default="push", choices=["push", "nccl"],
                     help="N > 1: all-gather fused into the GEMV epilogue (push) or NCCL after it")

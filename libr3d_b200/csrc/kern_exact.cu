@@ -259,17 +259,20 @@ __global__ __launch_bounds__(128) void k_quant_act_fp8(
 
 /* ------------------------------------------------------------------ gated activation quantiser
  * The epilogue of gemm_nt_q_gated (src/r3d_gemm_fp8a8.hip:700-825 of libr3d, itself
- * src/r3d_band.hip:167-235): one block per row of the bf16 gate_up plane [M, 2n], gate half
+ * src/r3d_band.hip:167-235): one block per (group, row) of the gate_up plane [M, 2n], gate half
  * first; per group of <= g columns the gated value h = bf16((silu ? gt*sg : sg) * up),
  * sg = 1/(1 + (float)exp((double)-gt)), its amax (strict >, NaN never wins), the dequant scale
  * amax/448 and the saturating RTNE e4m3 codes of h/scale. */
-__global__ __launch_bounds__(256) void k_gated_quant_fp8(
+__global__ __launch_bounds__(128) void k_gated_quant_fp8(
     const void* __restrict__ gu, const int gu_dtype, const int64_t gu_pitch, uint8_t* __restrict__ q, const int64_t q_pitch,
     float* __restrict__ scale, const int64_t s_pitch, void* __restrict__ ob, const int ob_dtype,
     const int64_t ob_pitch, const int n, const int g, const int ngrp, const int silu) {
-    __shared__ float red[8];
-    __shared__ float s_sc;
-    const int64_t row = blockIdx.x;
+    /* one block per (group, row): the double-precision exp behind the sigmoid is the cost, so the
+     * groups of a row run side by side and each gated value is computed once (kept in registers
+     * when the group has at most 512 columns, recomputed for the code pass otherwise) */
+    __shared__ float red[4];
+    const int64_t row = blockIdx.y;
+    const int gi = blockIdx.x;
     const uint16_t* gr = (const uint16_t*)gu + row * gu_pitch;
     const float* gf = (const float*)gu + row * gu_pitch;
     auto gated = [&](int i) -> float {
@@ -279,40 +282,55 @@ __global__ __launch_bounds__(256) void k_gated_quant_fp8(
         const float a = silu ? __fmul_rn(gt, sg) : sg;
         return bf16_to_f32(f32_to_bf16(__fmul_rn(a, up)));
     };
-    for (int gi = 0; gi < ngrp; ++gi) {
-        const int k0 = gi * g, k1 = min(k0 + g, n);
-        float amax = 0.0f;
-        for (int i = k0 + threadIdx.x; i < k1; i += 256) {
+    const int k0 = gi * g, k1 = min(k0 + g, n);
+    const bool keep = k1 - k0 <= 512;
+    float hv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float amax = 0.0f;
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = k0 + j * 128 + threadIdx.x;
+            if (i < k1) {
+                hv[j] = gated(i);
+                const float m = fabsf(hv[j]);
+                if (m > amax) amax = m;                 /* strict >: NaN never wins */
+            }
+        }
+    } else {
+        for (int i = k0 + threadIdx.x; i < k1; i += 128) {
             const float m = fabsf(gated(i));
             if (m > amax) amax = m;
         }
-        for (int off = 16; off; off >>= 1) {
-            const float o = __shfl_xor_sync(0xffffffffu, amax, off);
-            if (o > amax) amax = o;
+    }
+    for (int off = 16; off; off >>= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, amax, off);
+        if (o > amax) amax = o;
+    }
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    float r = red[0];
+    for (int w = 1; w < 4; ++w) if (red[w] > r) r = red[w];
+    const float sc = r > 0.0f ? __fmul_rn(r, 1.0f / 448.0f) : 1.0f;
+    if (threadIdx.x == 0) scale[row * s_pitch + gi] = sc;
+    const float inv = __fdiv_rn(1.0f, sc);
+    auto emit = [&](int i, float h) {
+        if (ob) {
+            if (ob_dtype == RAD_F32) ((float*)ob)[row * ob_pitch + i] = h;
+            else ((uint16_t*)ob)[row * ob_pitch + i] = f32_to_bf16(h);
         }
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float r = red[0];
-            for (int w = 1; w < 8; ++w) if (red[w] > r) r = red[w];
-            const float sc = r > 0.0f ? __fmul_rn(r, 1.0f / 448.0f) : 1.0f;
-            s_sc = sc;
-            scale[row * s_pitch + gi] = sc;
+        float c = __fmul_rn(h, inv);
+        if (c > 448.0f) c = 448.0f;
+        if (c < -448.0f) c = -448.0f;
+        q[row * q_pitch + i] = f32_to_e4m3(c);
+    };
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = k0 + j * 128 + threadIdx.x;
+            if (i < k1) emit(i, hv[j]);
         }
-        __syncthreads();
-        const float inv = __fdiv_rn(1.0f, s_sc);
-        for (int i = k0 + threadIdx.x; i < k1; i += 256) {
-            const float h = gated(i);
-            if (ob) {
-                if (ob_dtype == RAD_F32) ((float*)ob)[row * ob_pitch + i] = h;
-                else ((uint16_t*)ob)[row * ob_pitch + i] = f32_to_bf16(h);
-            }
-            float c = __fmul_rn(h, inv);
-            if (c > 448.0f) c = 448.0f;
-            if (c < -448.0f) c = -448.0f;
-            q[row * q_pitch + i] = f32_to_e4m3(c);
-        }
-        __syncthreads();                              /* s_sc is reused by the next group */
+    } else {
+        for (int i = k0 + threadIdx.x; i < k1; i += 128) emit(i, gated(i));
     }
 }
 
@@ -465,7 +483,7 @@ int launch_gated_quant_fp8(const void* gu, int64_t gu_pitch, void* q, int64_t q_
     if (g <= 0 || g > n) g = n;
     const int ngrp = (n + g - 1) / g;
     count_launch();
-    k_gated_quant_fp8<<<(unsigned)rows, 256, 0, st>>>(gu, gu_dtype, gu_pitch, (uint8_t*)q, q_pitch, scale,
+    k_gated_quant_fp8<<<dim3((unsigned)ngrp, (unsigned)rows), 128, 0, st>>>(gu, gu_dtype, gu_pitch, (uint8_t*)q, q_pitch, scale,
                                                       s_pitch, ob, ob_dtype, ob_pitch, n, g, ngrp, silu);
     return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
 }

@@ -4,9 +4,9 @@
  *
  * Here the selection is a tournament, because it serves the column-sharded LM head, whose rows are
  * 19 to 152 thousand columns wide at M = 1..16: a pass gives every warp a tile of 512 items held in
- * registers (16 per lane) and takes the tile's top R with warp shuffles only -- no shared memory, no
- * block barrier -- and passes repeat over the survivors (tiles * R of them) until one tile is left;
- * that last pass writes idx / val / pairs with `vocab_off` added. The order is total on everything
+ * registers (16 per lane, sorted once by each lane) and takes the tile's top R with two warp-wide
+ * integer maxima per pick -- no shared memory, no block barrier -- and passes repeat over the
+ * survivors (tiles * R of them) until one tile is left; that last pass writes idx / val / pairs with `vocab_off` added. The order is total on everything
  * but NaN, so the survivors of the survivors are exactly the R the reference's rounds pick; a slot
  * that cannot be filled reports (-1, -inf) as there. A NaN's place is unspecified (in the reference
  * it depends on which thread meets it first).
@@ -23,18 +23,32 @@ constexpr int kTile = 512;            /* items per warp */
 constexpr int kPer = kTile / 32;      /* items per lane */
 constexpr int kWarps = 4;             /* warps (tiles) per block */
 
-__device__ __forceinline__ bool beats(float av, int ai, float bv, int bi) {
-    return ai >= 0 && (bi < 0 || av > bv || (av == bv && ai < bi));
+/* An item is one 64-bit key whose unsigned order is the selection order: the high word is the
+ * value mapped monotonically onto unsigned integers (-0 first folded onto +0, which the rule
+ * treats as equal), the low word is 0xffffffff - column, so that of two equal values the lower
+ * column is the larger key. 0 is "no item". */
+__device__ __forceinline__ uint32_t ord_of(float v) {
+    uint32_t u = __float_as_uint(v);
+    if (u == 0x80000000u) u = 0u;
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ unsigned long long key_of(float v, int col) {
+    return ((unsigned long long)ord_of(v) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)col);
 }
 
 struct TopkPass {
-    const void* x; int x_dtype; int64_t x_pitch;      /* first pass: the rows themselves */
-    const float* cv; const int* ci; int64_t c_pitch;  /* later passes: the previous survivors */
+    const void* x; int x_dtype; int64_t x_pitch;      /* the rows: items of the first pass, values of the last */
+    const unsigned long long* ck; int64_t c_pitch;    /* later passes: the previous survivors */
     int n;                                            /* items per row in this pass */
-    float* ov; int* oi; int64_t o_pitch;              /* survivors out (tiles * R per row) */
+    unsigned long long* ok; int64_t o_pitch;          /* survivors out (tiles * R per row) */
     int32_t* idx; int64_t idx_pitch; float* val; int64_t val_pitch; float* pairs; int64_t pairs_pitch;
     int R; int64_t off; int last;                     /* last: one tile per row, write the outputs */
 };
+
+__device__ __forceinline__ float load_x(const TopkPass& P, int64_t m, int e) {
+    return P.x_dtype == RAD_F32 ? ((const float*)P.x)[m * P.x_pitch + e]
+                                : bf16_to_f32(((const uint16_t*)P.x)[m * P.x_pitch + e]);
+}
 
 template <bool FIRST>
 __global__ __launch_bounds__(kWarps * 32) void k_topk_pass(const TopkPass P) {
@@ -42,68 +56,62 @@ __global__ __launch_bounds__(kWarps * 32) void k_topk_pass(const TopkPass P) {
     const int tile = blockIdx.x * kWarps + (threadIdx.x >> 5);
     const int64_t m = blockIdx.y;
     const int base = tile * kTile;
-    if (base >= P.n) return;                          /* whole warp: no shuffle is left behind */
-    float v[kPer];
-    int id[kPer];
+    if (base >= P.n) return;                          /* whole warp: no warp-wide step is left behind */
+    unsigned long long k[kPer];
 #pragma unroll
     for (int j = 0; j < kPer; ++j) {
         const int e = base + j * 32 + lane;
-        if (e < P.n) {
-            if (FIRST) {
-                v[j] = P.x_dtype == RAD_F32 ? ((const float*)P.x)[m * P.x_pitch + e]
-                                            : bf16_to_f32(((const uint16_t*)P.x)[m * P.x_pitch + e]);
-                id[j] = e;
-            } else {
-                v[j] = P.cv[m * P.c_pitch + e];
-                id[j] = P.ci[m * P.c_pitch + e];
-            }
-        } else {
-            v[j] = 0.0f;
-            id[j] = -1;
-        }
+        k[j] = 0ull;
+        if (e < P.n) k[j] = FIRST ? key_of(load_x(P, m, e), e) : P.ck[m * P.c_pitch + e];
     }
+    /* each lane sorts its 16 keys, largest first (bitonic network, every index a constant) */
+#pragma unroll
+    for (int kk = 2; kk <= kPer; kk <<= 1)
+#pragma unroll
+        for (int jj = kk >> 1; jj > 0; jj >>= 1)
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const int l = i ^ jj;
+                if (l > i) {
+                    const bool desc = (i & kk) == 0;
+                    const unsigned long long a = k[i], b = k[l];
+                    const bool sw = desc ? a < b : a > b;
+                    k[i] = sw ? b : a;
+                    k[l] = sw ? a : b;
+                }
+            }
+    /* R rounds: the warp's best head (two warp-wide integer maxima), whose lane pops it */
     for (int r = 0; r < P.R; ++r) {
-        float bv = 0.0f;
-        int bi = -1, bj = -1;
+        const uint32_t hi = (uint32_t)(k[0] >> 32), lo = (uint32_t)k[0];
+        const uint32_t vmax = __reduce_max_sync(0xffffffffu, hi);
+        const uint32_t lmax = __reduce_max_sync(0xffffffffu, hi == vmax ? lo : 0u);
+        const bool ok = vmax != 0u;
+        if (ok && hi == vmax && lo == lmax) {
 #pragma unroll
-        for (int j = 0; j < kPer; ++j)
-            if (beats(v[j], id[j], bv, bi)) { bv = v[j]; bi = id[j]; bj = j; }
-        float wv = bv;
-        int wi = bi;
-#pragma unroll
-        for (int sh = 16; sh; sh >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, wv, sh);
-            const int oi = __shfl_xor_sync(0xffffffffu, wi, sh);
-            if (beats(ov, oi, wv, wi)) { wv = ov; wi = oi; }
-        }
-        /* ids are unique inside a row, so exactly one lane owns the winner: it retires the item */
-        if (wi >= 0 && wi == bi) {
-#pragma unroll
-            for (int j = 0; j < kPer; ++j)
-                if (j == bj) id[j] = -1;
+            for (int j = 0; j + 1 < kPer; ++j) k[j] = k[j + 1];
+            k[kPer - 1] = 0ull;
         }
         if (lane == 0) {
-            const bool ok = wi >= 0;
             if (P.last) {
-                const int32_t col = ok ? (int32_t)(wi + P.off) : -1;
-                const float val = ok ? wv : -INFINITY;
-                P.idx[m * P.idx_pitch + r] = col;
-                P.val[m * P.val_pitch + r] = val;
+                const int col = (int)(0xffffffffu - lmax);
+                const int32_t out_col = ok ? (int32_t)(col + P.off) : -1;
+                const float out_val = ok ? load_x(P, m, col) : -INFINITY;     /* the row's own bits (a zero keeps its sign) */
+                P.idx[m * P.idx_pitch + r] = out_col;
+                P.val[m * P.val_pitch + r] = out_val;
                 if (P.pairs) {
                     float* p = P.pairs + m * P.pairs_pitch + 2 * r;
-                    p[0] = __int_as_float(col);
-                    p[1] = val;
+                    p[0] = __int_as_float(out_col);
+                    p[1] = out_val;
                 }
             } else {
-                P.ov[m * P.o_pitch + (int64_t)tile * P.R + r] = ok ? wv : -INFINITY;
-                P.oi[m * P.o_pitch + (int64_t)tile * P.R + r] = ok ? wi : -1;
+                P.ok[m * P.o_pitch + (int64_t)tile * P.R + r] = ok ? (((unsigned long long)vmax << 32) | lmax) : 0ull;
             }
         }
     }
 }
 
 /* plugin-owned survivor planes, two per device (ping-pong), grown on demand and never freed */
-struct Survivors { float* v[2]; int* i[2]; size_t items; };
+struct Survivors { unsigned long long* k[2]; size_t items; };
 Survivors* survivors(size_t items) {
     static Survivors per_dev[64] = {};
     int dev = 0;
@@ -111,9 +119,8 @@ Survivors* survivors(size_t items) {
     Survivors& S = per_dev[dev];
     if (S.items < items) {
         Survivors nw{};
-        for (int k = 0; k < 2; ++k)
-            if (cudaMalloc(&nw.v[k], items * sizeof(float)) != cudaSuccess ||
-                cudaMalloc(&nw.i[k], items * sizeof(int)) != cudaSuccess) {
+        for (int b = 0; b < 2; ++b)
+            if (cudaMalloc(&nw.k[b], items * sizeof(unsigned long long)) != cudaSuccess) {
                 (void)cudaGetLastError();
                 return nullptr;                       /* an earlier, smaller set stays in place */
             }
@@ -141,14 +148,14 @@ int launch_row_topk(const void* x, int x_dtype, int64_t x_pitch, int32_t* idx, i
     int n = N, tiles = tiles0, pass = 0;
     for (;;) {
         P.n = n; P.last = tiles == 1;
-        if (!P.last) { P.ov = S->v[pass & 1]; P.oi = S->i[pass & 1]; P.o_pitch = (int64_t)tiles * R; }
+        if (!P.last) { P.ok = S->k[pass & 1]; P.o_pitch = (int64_t)tiles * R; }
         const dim3 grid((unsigned)((tiles + kWarps - 1) / kWarps), (unsigned)M);
         count_launch();
         if (pass == 0) k_topk_pass<true><<<grid, kWarps * 32, 0, st>>>(P);
         else k_topk_pass<false><<<grid, kWarps * 32, 0, st>>>(P);
         if (cudaGetLastError() != cudaSuccess) return RAD_E_DEVICE;
         if (P.last) break;
-        P.cv = P.ov; P.ci = P.oi; P.c_pitch = P.o_pitch;
+        P.ck = P.ok; P.c_pitch = P.o_pitch;
         n = tiles * R;
         tiles = (n + kTile - 1) / kTile;
         ++pass;
