@@ -335,38 +335,66 @@ __global__ __launch_bounds__(128) void k_gated_quant_fp8(
 }
 
 /* ------------------------------------------------------------------ rmsnorm_quant_fp8
- * src/r3d_more.hip:248-330 of libr3d. One block of 256 threads per row; the sum of squares keeps
- * that kernel's order (thread t adds elements t, t+256, ... ascending; a shuffle-down tree inside
+ * src/r3d_more.hip:248-330 of libr3d. One block of 1024 threads per row; the sum of squares is
+ * taken by the first 256 of them and keeps that kernel's order (thread t adds elements t, t+256, ... ascending; a shuffle-down tree inside
  * each warp; the eight warp sums added ascending by thread 0), so rs = 1/sqrt(ss/n + eps) has the
  * same bits. With a residual the bf16-narrowed sum x + res is stored first and is what the
  * variance and the norm read. h = bf16(src * rs * (w + wadd)) goes to out_bf16 and to the group
  * quantiser (strict-max amax, scale amax/448 or 1, saturating RTNE e4m3 codes of h/scale). */
-__global__ __launch_bounds__(256) void k_rmsnorm_quant_fp8(
+__global__ __launch_bounds__(1024) void k_rmsnorm_quant_fp8(
     const uint16_t* __restrict__ x, const int64_t x_pitch, uint16_t* __restrict__ res, const int64_t r_pitch,
     const void* __restrict__ w, const int w_dtype, uint8_t* __restrict__ q, const int64_t q_pitch,
     float* __restrict__ scale, const int64_t s_pitch, void* __restrict__ ob, const int ob_dtype,
     const int64_t ob_pitch, const int n, const int g, const int ngrp, const float eps, const float wadd) {
     __shared__ float s_part[8];
     __shared__ float s_rs;
-    extern __shared__ uint16_t s_h[];
+    extern __shared__ __align__(16) uint16_t s_h[];
     const int64_t row = blockIdx.x;
     const uint16_t* xr = x + row * x_pitch;
     uint16_t* rr = res ? res + row * r_pitch : nullptr;
-    float ss = 0.0f;
-    for (int i = threadIdx.x; i < n; i += 256) {
-        const float v = bf16_to_f32(xr[i]);
-        if (rr) {
-            const uint16_t h = f32_to_bf16(__fadd_rn(bf16_to_f32(rr[i]), v));
-            rr[i] = h;
+    /* the row (or the bf16-narrowed sum row, which is also stored back) goes to shared memory with
+     * 16-byte accesses where the operands allow; the ordered sums below then read shared memory,
+     * so no global load waits behind a store */
+    const bool vec = (n & 7) == 0 && ((((uintptr_t)xr) | (uintptr_t)(rr ? rr : xr)) & 15u) == 0;
+    if (vec) {
+        for (int c = threadIdx.x; c < (n >> 3); c += 1024) {
+            uint4 xv = ((const uint4*)xr)[c];
+            if (rr) {
+                const uint4 rv = ((const uint4*)rr)[c];
+                const uint32_t xa[4] = {xv.x, xv.y, xv.z, xv.w}, ra[4] = {rv.x, rv.y, rv.z, rv.w};
+                uint32_t ha[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t lo = f32_to_bf16(__fadd_rn(bf16_to_f32((uint16_t)(ra[j] & 0xffffu)), bf16_to_f32((uint16_t)(xa[j] & 0xffffu))));
+                    const uint32_t hi = f32_to_bf16(__fadd_rn(bf16_to_f32((uint16_t)(ra[j] >> 16)), bf16_to_f32((uint16_t)(xa[j] >> 16))));
+                    ha[j] = lo | (hi << 16);
+                }
+                xv = make_uint4(ha[0], ha[1], ha[2], ha[3]);
+                ((uint4*)rr)[c] = xv;
+            }
+            ((uint4*)s_h)[c] = xv;
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += 1024) {
+            uint16_t h = xr[i];
+            if (rr) {
+                h = f32_to_bf16(__fadd_rn(bf16_to_f32(rr[i]), bf16_to_f32(h)));
+                rr[i] = h;
+            }
             s_h[i] = h;
-            const float hv = bf16_to_f32(h);
-            ss = __fadd_rn(ss, __fmul_rn(hv, hv));
-        } else {
-            ss = __fadd_rn(ss, __fmul_rn(v, v));
         }
     }
-    for (int off = 16; off; off >>= 1) ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, off));
-    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    /* the ordered sum is the work of the first 256 threads: the order is the reference block's */
+    if (threadIdx.x < 256) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < n; i += 256) {
+            const float v = bf16_to_f32(s_h[i]);
+            ss = __fadd_rn(ss, __fmul_rn(v, v));
+        }
+        for (int off = 16; off; off >>= 1) ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, off));
+        if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         float r = s_part[0];
@@ -375,8 +403,8 @@ __global__ __launch_bounds__(256) void k_rmsnorm_quant_fp8(
     }
     __syncthreads();
     const float rs = s_rs;
-    for (int i = threadIdx.x; i < n; i += 256) {
-        const float src = rr ? bf16_to_f32(s_h[i]) : bf16_to_f32(xr[i]);
+    for (int i = threadIdx.x; i < n; i += 1024) {
+        const float src = bf16_to_f32(s_h[i]);
         const float wv = __fadd_rn(w_dtype == RAD_F32 ? ((const float*)w)[i] : bf16_to_f32(((const uint16_t*)w)[i]), wadd);
         const uint16_t h = f32_to_bf16(__fmul_rn(__fmul_rn(src, rs), wv));
         if (ob) {
@@ -388,7 +416,7 @@ __global__ __launch_bounds__(256) void k_rmsnorm_quant_fp8(
     __syncthreads();
     /* one warp per group: the group's amax is order-free, the codes are per element */
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int gi = warp; gi < ngrp; gi += 8) {
+    for (int gi = warp; gi < ngrp; gi += 32) {
         const int k0 = gi * g, k1 = min(k0 + g, n);
         float amax = 0.0f;
         for (int i = k0 + lane; i < k1; i += 32) {
@@ -501,7 +529,7 @@ int launch_rmsnorm_quant_fp8(const void* x, int64_t x_pitch, void* res, int64_t 
         attr_set = smem;
     }
     count_launch();
-    k_rmsnorm_quant_fp8<<<(unsigned)rows, 256, smem, st>>>((const uint16_t*)x, x_pitch, (uint16_t*)res, r_pitch, w,
+    k_rmsnorm_quant_fp8<<<(unsigned)rows, 1024, smem, st>>>((const uint16_t*)x, x_pitch, (uint16_t*)res, r_pitch, w,
                                                            w_dtype, (uint8_t*)q, q_pitch, scale, s_pitch, ob,
                                                            ob_dtype, ob_pitch, n, g, ngrp, eps, wadd);
     return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;

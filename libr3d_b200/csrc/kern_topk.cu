@@ -4,8 +4,8 @@
  *
  * Here the selection is a tournament, because it serves the column-sharded LM head, whose rows are
  * 19 to 152 thousand columns wide at M = 1..16: a pass gives every warp a tile of 512 items held in
- * registers (16 per lane, sorted once by each lane) and takes the tile's top R with two warp-wide
- * integer maxima per pick -- no shared memory, no block barrier -- and passes repeat over the
+ * registers (16 per lane, sorted once by each lane) and takes the tile's top R with one warp-wide
+ * integer maximum and one vote per pick -- no shared memory, no block barrier -- and passes repeat over the
  * survivors (tiles * R of them) until one tile is left; that last pass writes idx / val / pairs with `vocab_off` added. The order is total on everything
  * but NaN, so the survivors of the survivors are exactly the R the reference's rounds pick; a slot
  * that cannot be filled reports (-1, -inf) as there. A NaN's place is unspecified (in the reference
@@ -16,6 +16,8 @@
 #include "r3d_numerics.cuh"
 
 namespace r3d {
+
+bool tc_pdl_on();                     /* kern_tc.cu: false under R3D_NO_PDL */
 
 namespace {
 
@@ -56,11 +58,15 @@ __global__ __launch_bounds__(kWarps * 32) void k_topk_pass(const TopkPass P) {
     const int tile = blockIdx.x * kWarps + (threadIdx.x >> 5);
     const int64_t m = blockIdx.y;
     const int base = tile * kTile;
+    /* passes are launched with programmatic stream serialisation: the next pass may take its
+     * place on the machine now, and this one reads nothing before its predecessor has finished */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (base >= P.n) return;                          /* whole warp: no warp-wide step is left behind */
     unsigned long long k[kPer];
 #pragma unroll
     for (int j = 0; j < kPer; ++j) {
-        const int e = base + j * 32 + lane;
+        const int e = base + lane * kPer + j;            /* a lane owns 16 neighbouring items */
         k[j] = 0ull;
         if (e < P.n) k[j] = FIRST ? key_of(load_x(P, m, e), e) : P.ck[m * P.c_pitch + e];
     }
@@ -80,31 +86,47 @@ __global__ __launch_bounds__(kWarps * 32) void k_topk_pass(const TopkPass P) {
                     k[l] = sw ? a : b;
                 }
             }
-    /* R rounds: the warp's best head (two warp-wide integer maxima), whose lane pops it */
-    for (int r = 0; r < P.R; ++r) {
-        const uint32_t hi = (uint32_t)(k[0] >> 32), lo = (uint32_t)k[0];
-        const uint32_t vmax = __reduce_max_sync(0xffffffffu, hi);
-        const uint32_t lmax = __reduce_max_sync(0xffffffffu, hi == vmax ? lo : 0u);
-        const bool ok = vmax != 0u;
-        if (ok && hi == vmax && lo == lmax) {
+    /* the sorted lists go to shared memory ([item][lane]: no bank conflicts); a lane keeps only its
+     * head in a register and fetches the next item when it wins */
+    __shared__ unsigned long long s_k[kWarps][kPer][32];
+    __shared__ int s_col[kWarps][32];
+    const int wib = threadIdx.x >> 5;
 #pragma unroll
-            for (int j = 0; j + 1 < kPer; ++j) k[j] = k[j + 1];
-            k[kPer - 1] = 0ull;
+    for (int j = 0; j < kPer; ++j) s_k[wib][j][lane] = k[j];
+    unsigned long long head = k[0];
+    int h = 0;
+    /* R rounds: the largest head value of the warp (one warp-wide integer maximum); of the lanes
+     * that hold it the lowest wins (one vote), because items lie in the tile in ascending column
+     * order wherever their values are equal -- in the rows themselves by construction, and among
+     * survivors because tiles cover ascending column ranges and each tile lists equal values in
+     * ascending column. The winner records the pick and pops it. */
+    for (int r = 0; r < P.R; ++r) {
+        const uint32_t hi = (uint32_t)(head >> 32);
+        const uint32_t vmax = __reduce_max_sync(0xffffffffu, hi);
+        const bool ok = vmax != 0u;
+        const uint32_t holders = __ballot_sync(0xffffffffu, ok && hi == vmax);
+        if (ok ? lane == __ffs(holders) - 1 : lane == 0) {
+            if (P.last) s_col[wib][r] = ok ? (int)(0xffffffffu - (uint32_t)head) : -1;
+            else P.ok[m * P.o_pitch + (int64_t)tile * P.R + r] = ok ? head : 0ull;
+            if (ok) {
+                ++h;
+                head = h < kPer ? s_k[wib][h][lane] : 0ull;
+            }
         }
-        if (lane == 0) {
-            if (P.last) {
-                const int col = (int)(0xffffffffu - lmax);
-                const int32_t out_col = ok ? (int32_t)(col + P.off) : -1;
-                const float out_val = ok ? load_x(P, m, col) : -INFINITY;     /* the row's own bits (a zero keeps its sign) */
-                P.idx[m * P.idx_pitch + r] = out_col;
-                P.val[m * P.val_pitch + r] = out_val;
-                if (P.pairs) {
-                    float* p = P.pairs + m * P.pairs_pitch + 2 * r;
-                    p[0] = __int_as_float(out_col);
-                    p[1] = out_val;
-                }
-            } else {
-                P.ok[m * P.o_pitch + (int64_t)tile * P.R + r] = ok ? (((unsigned long long)vmax << 32) | lmax) : 0ull;
+    }
+    if (P.last) {
+        /* lane r writes pick r; the value is re-read from the row (a zero keeps its sign) */
+        __syncwarp();
+        if (lane < P.R) {
+            const int col = s_col[wib][lane];
+            const int32_t out_col = col >= 0 ? (int32_t)(col + P.off) : -1;
+            const float out_val = col >= 0 ? load_x(P, m, col) : -INFINITY;
+            P.idx[m * P.idx_pitch + lane] = out_col;
+            P.val[m * P.val_pitch + lane] = out_val;
+            if (P.pairs) {
+                float* p = P.pairs + m * P.pairs_pitch + 2 * lane;
+                p[0] = __int_as_float(out_col);
+                p[1] = out_val;
             }
         }
     }
@@ -151,9 +173,15 @@ int launch_row_topk(const void* x, int x_dtype, int64_t x_pitch, int32_t* idx, i
         if (!P.last) { P.ok = S->k[pass & 1]; P.o_pitch = (int64_t)tiles * R; }
         const dim3 grid((unsigned)((tiles + kWarps - 1) / kWarps), (unsigned)M);
         count_launch();
-        if (pass == 0) k_topk_pass<true><<<grid, kWarps * 32, 0, st>>>(P);
-        else k_topk_pass<false><<<grid, kWarps * 32, 0, st>>>(P);
-        if (cudaGetLastError() != cudaSuccess) return RAD_E_DEVICE;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid; cfg.blockDim = dim3(kWarps * 32); cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = tc_pdl_on() ? 1 : 0;
+        const cudaError_t e = pass == 0 ? cudaLaunchKernelEx(&cfg, k_topk_pass<true>, P)
+                                        : cudaLaunchKernelEx(&cfg, k_topk_pass<false>, P);
+        if (e != cudaSuccess) return RAD_E_DEVICE;
         if (P.last) break;
         P.ck = P.ok; P.c_pitch = P.o_pitch;
         n = tiles * R;
