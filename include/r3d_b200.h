@@ -51,6 +51,9 @@ int r3d_rad_rmsnorm_quant_fp8(const RadArgs* a, RadStream s);
  * (int32 id, f32 value) plane a sharded head gathers instead of its logits. Replaces
  * r3d_rad_row_topk (src/r3d_more.hip:179-236, :438-476). */
 int r3d_rad_row_topk(const RadArgs* a, RadStream s);
+/* sample_argmax (logits, params, token): greedy decode over f32 logits, ties to the lower token
+ * id; `params` is not read. Replaces r3d_rad_sample_argmax (src/r3d_sample.hip:166-173, :607-623). */
+int r3d_rad_sample_argmax(const RadArgs* a, RadStream s);
 /* gemm_nt_q @ mxfp4a8, any M. Replaces r3d_rad_gemm_nt_q
  * (src/r3d_gemm_mxfp4.hip:1587-1691). */
 int r3d_rad_gemm_nt_q(const RadArgs* a, RadStream s);

@@ -10,6 +10,7 @@
  *   rmsnorm_quant_fp8  src/r3d_more.hip:480-541     x, residual?, w, q, scale, out_bf16?
  * and the logits consumer of the column-sharded LM head:
  *   row_topk           src/r3d_more.hip:438-476     x, idx, val, pairs?
+ *   sample_argmax      src/r3d_sample.hip:607-623   logits, params (not read), token
  */
 #include <cuda_runtime.h>
 #include "entry_util.h"
@@ -173,4 +174,24 @@ extern "C" int r3d_rad_row_topk(const RadArgs* a, RadStream s) {
     return launch_row_topk(x->data, (int)x->dtype, xp, (int32_t*)idx->data, ip, (float*)val->data, vp,
                            pairs ? (float*)pairs->data : nullptr, pp, (int)M, (int)N, (int)R, off,
                            (cudaStream_t)(uintptr_t)s);
+}
+
+/* Greedy sampling: token[m] = the column of the row's largest logit, ties to the lower token id --
+ * the top-1 of the same total order, so it is the same tournament with R = 1. The per-row parameter
+ * blob (operand 1) is not read, as in the reference. */
+extern "C" int r3d_rad_sample_argmax(const RadArgs* a, RadStream s) {
+    const RadTensor* lg = rad_arg_in(a, 0);
+    const RadTensor* tok = rad_arg_in(a, 2);
+    if (!lg || !tok) return RAD_E_INVAL;
+    if (lg->dtype != RAD_F32 || tok->dtype != RAD_I32) return RAD_E_DTYPE;
+    long long nv = 0;
+    if (!rad_args_geti(a, "n_vocab", &nv) || nv <= 0) nv = lg->rank >= 2 ? lg->shape[1] : 0;
+    if (nv <= 0 || nv > kMaxExtent) return RAD_E_SHAPE;
+    const int64_t M = rad_tensor_numel(lg) / nv;
+    if (M <= 0 || M > 0xffff) return RAD_E_SHAPE;
+    if (rad_tensor_numel(tok) < M || tok->rank != 1 || tok->stride[0] != 1) return RAD_E_SHAPE;
+    if (lg->rank != 2 || lg->shape[1] != nv || lg->stride[1] != 1) return RAD_E_STRIDE;
+    if (!device_is_sm100()) return RAD_E_UNSUPPORTED;
+    return launch_row_topk(lg->data, RAD_F32, lg->stride[0], (int32_t*)tok->data, 1, nullptr, 0, nullptr, 0, (int)M,
+                           (int)nv, 1, 0, (cudaStream_t)(uintptr_t)s);
 }

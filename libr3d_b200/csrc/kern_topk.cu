@@ -120,9 +120,9 @@ __global__ __launch_bounds__(kWarps * 32) void k_topk_pass(const TopkPass P) {
         if (lane < P.R) {
             const int col = s_col[wib][lane];
             const int32_t out_col = col >= 0 ? (int32_t)(col + P.off) : -1;
-            const float out_val = col >= 0 ? load_x(P, m, col) : -INFINITY;
+            const float out_val = (col >= 0 && (P.val || P.pairs)) ? load_x(P, m, col) : -INFINITY;
             P.idx[m * P.idx_pitch + lane] = out_col;
-            P.val[m * P.val_pitch + lane] = out_val;
+            if (P.val) P.val[m * P.val_pitch + lane] = out_val;
             if (P.pairs) {
                 float* p = P.pairs + m * P.pairs_pitch + 2 * lane;
                 p[0] = __int_as_float(out_col);

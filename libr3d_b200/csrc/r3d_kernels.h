@@ -31,7 +31,7 @@ int launch_rmsnorm_quant_fp8(const void* x, int64_t x_pitch, void* res, int64_t 
                              void* q, int64_t q_pitch, float* scale, int64_t s_pitch, void* ob, int ob_dtype,
                              int64_t ob_pitch, int rows, int n, int g, float eps, float wadd, cudaStream_t st);
 
-/* exact per-row top-R (kern_topk.cu); pitches in elements (pairs: floats), pairs may be null */
+/* exact per-row top-R (kern_topk.cu); pitches in elements (pairs: floats); val and pairs may be null */
 int launch_row_topk(const void* x, int x_dtype, int64_t x_pitch, int32_t* idx, int64_t idx_pitch, float* val,
                     int64_t val_pitch, float* pairs, int64_t pairs_pitch, int M, int N, int R, int64_t off,
                     cudaStream_t st);

@@ -95,7 +95,17 @@ const RadOperandSpec kRowTopkOperands[] = {
     { "x", RAD_OPD_IN, 0 }, { "idx", RAD_OPD_OUT, 0 }, { "val", RAD_OPD_OUT, 0 }, { "pairs", RAD_OPD_OUT, 1 },
 };
 
+/* sample_argmax: src/r3d_rows.cpp:285-288, :655-659 */
+const RadParamSpec kArgmaxParams[] = {
+    { "M", RAD_P_INT, RAD_REQUIRED, 0 }, { "n_vocab", RAD_P_INT, RAD_REQUIRED, 0 },
+};
+const RadOperandSpec kArgmaxOperands[] = {
+    { "logits", RAD_OPD_IN, 0 }, { "params", RAD_OPD_IN, 0 }, { "token", RAD_OPD_OUT, 0 },
+};
+
 const RadOpSchema kSchemas[] = {
+    { "sample_argmax", kArgmaxParams, COUNT_OF(kArgmaxParams), kArgmaxOperands, COUNT_OF(kArgmaxOperands),
+      "greedy: the token of the largest logit, ties to the lower token id." },
     { "row_topk", kRowTopkParams, COUNT_OF(kRowTopkParams), kRowTopkOperands, COUNT_OF(kRowTopkOperands),
       "exact per-row top-R, descending, ties to the lower column; `vocab_off` shifts the reported "
       "columns to global ids and `pairs` is the [M, R, 2] (int32 id, f32 value) plane a sharded "
@@ -161,6 +171,8 @@ const RadConstraint kCRmsQuant[] = {
     { "dtype", RAD_C_IN, 0, "bf16" },
 };
 
+/* src/r3d_rows.cpp:1255 */
+const RadConstraint kCArgmax[] = { { "n_vocab", RAD_C_GE, 1, nullptr } };
 /* src/r3d_rows.cpp:1412-1418 */
 const RadConstraint kCRowTopk[] = {
     { "N", RAD_C_DIV, 8, nullptr }, { "M", RAD_C_GE, 1, nullptr }, { "R", RAD_C_GE, 1, nullptr },
@@ -265,6 +277,14 @@ const RadKernelInfo kRows[] = {
         "any M, N a multiple of 8, R <= 32",
         "bf16 in, f32 values + i32 columns out, optional f32 pairs plane",
         kPrioPlain, kCRowTopk, r3d_rad_row_topk),
+
+    /* greedy decode directly behind logits_gemm's f32 logits (src/r3d_rows.cpp:1791-1798) */
+    ROW("sample_argmax_f32", "sample_argmax", "sample",
+        "greedy, ties to the lower token id: the top-1 of the (value descending, id ascending) "
+        "tournament that row_topk runs, so greedy and top-1 agree",
+        "any vocabulary",
+        "f32 logits, i32 token; the parameter blob is not read",
+        kPrioPlain, kCArgmax, r3d_rad_sample_argmax),
 };
 
 /* ------------------------------------------------------------------ registration gate */

@@ -202,6 +202,14 @@ def row_topk(x: torch.Tensor, idx: torch.Tensor, val: torch.Tensor, pairs: torch
                                       _desc(pairs, abi.RAD_F32)])
 
 
+def sample_argmax(logits: torch.Tensor, token: torch.Tensor, params: torch.Tensor | None = None) -> Row:
+    """The sample_argmax op through its row: logits f32 [M, n_vocab] -> token i32 [M] (greedy, ties to the
+    lower id). `params` is the engine's per-row parameter blob; the row does not read it."""
+    query = dict(M=logits.shape[0], n_vocab=logits.shape[1])
+    return _issue("sample_argmax", query, [_desc(logits, abi.RAD_F32), _desc(params, abi.RAD_U8),
+                                           _desc(token, abi.RAD_I32)])
+
+
 class BoundGemm:
     """A gemm_nt_q band declared once and issued many times, the way the engine uses a row:
     the row is resolved and the RadArgs built at declare time over fixed device buffers; each

@@ -24,7 +24,7 @@ EXPORTS = [
     "r3d_rad_gemm_nt_q_fp8", "r3d_rad_gemm_nt_q_fp8_decode", "r3d_rad_gemm_nt_q",
     "r3d_rad_gemm_nt_q_mxfp4_decode", "r3d_rad_gemm_nt_q_mxfp4_decode_q8x",
     "r3d_rad_gemm_nt_q_gated_fp8", "r3d_rad_gemm_nt_q_gated_fp8_scratch", "r3d_b200_gated_quant_fp8",
-    "r3d_rad_quant_act_fp8", "r3d_rad_gated_quant_fp8", "r3d_rad_rmsnorm_quant_fp8", "r3d_rad_row_topk",
+    "r3d_rad_quant_act_fp8", "r3d_rad_gated_quant_fp8", "r3d_rad_rmsnorm_quant_fp8", "r3d_rad_row_topk", "r3d_rad_sample_argmax",
     "r3d_mxfp4_q8x_off", "r3d_rad_logits_gemm_e4m3", "r3d_layout_head", "r3d_relayout_head",
     "r3d_unrelayout_head",
     "r3d_b200_gemm_fp8a8", "r3d_b200_gemm_mxfp4a8", "r3d_b200_gemm_mxfp4a8_q8x",

@@ -236,6 +236,15 @@ def row_topk(x_bits: np.ndarray, R: int, vocab_off: int = 0):
     return idx, val
 
 
+def sample_argmax(logits: np.ndarray) -> np.ndarray:
+    """f32 logits [M, n_vocab] -> int32 token [M]: the largest logit, ties to the lower token id."""
+    lg = _c(logits, np.float32)
+    M, nv = lg.shape
+    tok = np.empty(M, np.int32)
+    lib().orc_sample_argmax(_p(lg), I64(M), I64(nv), _p(tok))
+    return tok
+
+
 def quant_act_mx8(x: np.ndarray):
     x = _c(x, np.float32)
     M, n = x.shape

@@ -309,6 +309,22 @@ ORC_API void orc_row_topk(const uint16_t* x, int64_t M, int64_t N, int64_t R, in
     }
 }
 
+/* ------------------------------------------------------------------ sample_argmax
+ * src/r3d_sample.hip:166-173 of libr3d (argmax_kernel over r3d_block_argmax): the column of the
+ * row's largest f32 logit under the same total order as row_topk (value descending, ties to the
+ * lower token id), walked here serially in ascending column. */
+ORC_API void orc_sample_argmax(const float* lg, int64_t M, int64_t n_vocab, int32_t* tok) {
+    for (int64_t m = 0; m < M; ++m) {
+        float bv = 0.0f;
+        int64_t bi = -1;
+        for (int64_t i = 0; i < n_vocab; ++i) {
+            const float v = lg[m * n_vocab + i];
+            if (bi < 0 || v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+        }
+        tok[m] = (int32_t)bi;
+    }
+}
+
 /* ------------------------------------------------------------------ OCP-MX activation
  * quantiser (e4m3 elements, one E8M0 scale per 32 columns). PARITY UNPINNED: the
  * reference has no such quantiser. Rule: shared exponent = floor(log2(amax)) - 8 (8 is

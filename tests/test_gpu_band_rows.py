@@ -207,3 +207,36 @@ def test_row_topk_row_against_the_reference_kernel(M, N, R, off):
     torch.cuda.synchronize()
     for a, b in zip(out[0], out[1]):
         assert np.array_equal(a.cpu().numpy().view(np.uint32), b.cpu().numpy().view(np.uint32))
+
+
+@pytest.mark.parametrize("M,nv", [(1, 151936), (16, 151936), (4, 19072), (3, 7), (2, 513)])
+def test_sample_argmax_row_against_oracle(M, nv):
+    """Greedy over f32 logits with many ties (few distinct values), a row of all -inf and signed zeros;
+    it must also be row_topk's first pick on the same values."""
+    rng = np.random.default_rng(M + nv)
+    lg = (np.round(rng.standard_normal((M, nv)) * 3) / 2).astype(np.float32)
+    lg[0, :] = np.minimum(lg[0, :], 2.0)                       # the row's maximum occurs many times
+    if M > 1:
+        lg[1, :] = -np.inf
+    if M > 2:
+        lg[2, :] = np.where(rng.random(nv) < 0.5, np.float32(-0.0), np.float32(0.0))
+    ld = gu.dev(lg)
+    tok = torch.full((M,), -9, dtype=torch.int32, device="cuda")
+    r = ops.sample_argmax(ld, tok)
+    torch.cuda.synchronize()
+    assert r.name == "sample_argmax_f32"
+    want = orc.sample_argmax(lg)
+    assert np.array_equal(tok.cpu().numpy(), want)
+    assert np.array_equal(want, np.argmax(lg, axis=1).astype(np.int32))
+
+
+def test_greedy_decode_tail_logits_then_argmax():
+    """The end of a decode step as the engine issues it: logits_gemm (f32) then sample_argmax, against
+    the oracle's logits and the oracle's argmax over them."""
+    c = gen.case_logits(77, 4, 1024, 512, 128, 0)
+    got = gu.logits_launch(c, abi.R3D_ARM_AUTO)
+    ld = gu.dev(got)
+    tok = torch.zeros((4,), dtype=torch.int32, device="cuda")
+    ops.sample_argmax(ld, tok)
+    torch.cuda.synchronize()
+    assert np.array_equal(tok.cpu().numpy(), orc.sample_argmax(got))

@@ -66,6 +66,8 @@ def test_schemas_entry_for_entry(plug):
     assert s["rmsnorm_quant_fp8"]["operands"] == [("x", IN, 0), ("residual", INOUT, 1), ("w", W, 0),
                                                   ("q", OUT, 0), ("scale", OUT, 0), ("out_bf16", OUT, 1)]
     assert s["row_topk"]["params"] == [("M", I, R), ("N", I, R), ("R", I, R), ("vocab_off", I, O), ("dtype", S, R)]
+    assert s["sample_argmax"]["params"] == [("M", I, R), ("n_vocab", I, R)]
+    assert s["sample_argmax"]["operands"] == [("logits", IN, 0), ("params", IN, 0), ("token", OUT, 0)]
     assert s["row_topk"]["operands"] == [("x", IN, 0), ("idx", OUT, 0), ("val", OUT, 0), ("pairs", OUT, 1)]
     assert plug.lib.rad_kernel_schema_at(-1) is None or not plug.lib.rad_kernel_schema_at(-1)
     assert not plug.lib.rad_kernel_schema_at(99)
@@ -77,7 +79,7 @@ def test_rows_names_priorities_constraints(plug):
             "gemm_nt_q_fp8a8_decode": 1100, "gemm_nt_q_mxfp4_decode": 1100,
             "gemm_nt_q_mxfp4_decode_q8x": 1200, "gemm_nt_q_gated_fp8a8": 1000,
             "quant_act_fp8_act": 1000, "gated_quant_fp8_act": 1000, "rmsnorm_quant_fp8": 1000,
-            "rowtopk_bf16": 1000}
+            "rowtopk_bf16": 1000, "sample_argmax_f32": 1000}
     assert {k: v.priority for k, v in rows.items()} == want
     assert all(r.domain == abi.RAD_DOMAIN_DEVICE and r.launch for r in rows.values())
     assert rows["logits_gemm_e4m3"].has_layout
@@ -148,7 +150,7 @@ def _rows_under(env):
 
 ALL = {"logits_gemm_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode",
        "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_gated_fp8a8",
-       "quant_act_fp8_act", "gated_quant_fp8_act", "rmsnorm_quant_fp8", "rowtopk_bf16"}
+       "quant_act_fp8_act", "gated_quant_fp8_act", "rmsnorm_quant_fp8", "rowtopk_bf16", "sample_argmax_f32"}
 
 
 @pytest.mark.parametrize("env,hidden,mx_row,f8_row", [
@@ -276,6 +278,16 @@ def test_activation_producer_refusals(plug):
         ts = [x or T(z, abi.RAD_BF16, [2, 256]), idx or T(z, abi.RAD_I32, [2, 4]), val or T(z, abi.RAD_F32, [2, 4]),
               pairs or T(None, abi.RAD_F32, [])]
         return plug.entry("r3d_rad_row_topk")(C.byref(ArgPack(ts, dict(dict(M=2, N=256, R=4, dtype="bf16"), **p)).args), None)
+    def argmax(lg=None, tok=None, **p):
+        ts = [lg or T(z, abi.RAD_F32, [2, 256]), T(None, abi.RAD_U8, []), tok or T(z, abi.RAD_I32, [2])]
+        return plug.entry("r3d_rad_sample_argmax")(C.byref(ArgPack(ts, dict(dict(M=2, n_vocab=256), **p)).args), None)
+    assert argmax(tok=T(None, abi.RAD_I32, [2])) == IV
+    assert argmax(lg=T(z, abi.RAD_BF16, [2, 256])) == DT
+    assert argmax(tok=T(z, abi.RAD_F32, [2])) == DT
+    assert argmax(tok=T(z, abi.RAD_I32, [1])) == SH and argmax(tok=T(z, abi.RAD_I32, [2, 1])) == SH
+    assert argmax(lg=T(z, abi.RAD_F32, [512])) == ST                            # logits are a rank-2 plane
+    assert argmax(lg=T(z, abi.RAD_F32, [2, 256], [512, 2])) == ST
+    assert plug.resolve("sample_argmax", dict(M=2, n_vocab=151936)).name == "sample_argmax_f32"
     assert topk(val=T(None, abi.RAD_F32, [2, 4])) == IV
     assert topk(x=T(z, abi.RAD_F16, [2, 256])) == DT
     assert topk(idx=T(z, abi.RAD_F32, [2, 4])) == DT
