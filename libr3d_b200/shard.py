@@ -52,6 +52,34 @@ def gather_columns(y_local: torch.Tensor, n_rows: int, granule: int = 128,
     return buf.permute(1, 0, 2).reshape(M, world * padded)[:, :n_rows]
 
 
+def gather_topk(pairs_local: torch.Tensor, group: dist.ProcessGroup | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """The exchange behind a column-sharded head that samples: every rank ran row_topk over its own
+    slab with `vocab_off` = the slab's first column and hands in its pairs plane [M, R, 2] (f32 words:
+    the bits of the int32 global id, the value; a hole is id -1 / -inf). The planes are all-gathered
+    (M * R * 8 bytes per rank instead of the logits) and merged under the same order the rows use --
+    value descending, ties to the lower id, holes last -- into idx int32 [M, R], val f32 [M, R] on
+    every rank: the unsharded row_topk's answer. The merge is tiny (world * R candidates per row) and
+    runs as tensor ops on whatever device holds the planes."""
+    world = dist.get_world_size(group)
+    M, R, _ = pairs_local.shape
+    flat = pairs_local.contiguous().view(M, 2 * R)
+    if world > 1:
+        buf = torch.empty((world * M, 2 * R), dtype=flat.dtype, device=flat.device)
+        dist.all_gather_into_tensor(buf, flat, group=group)
+        cand = buf.view(world, M, R, 2).permute(1, 0, 2, 3).reshape(M, world * R, 2)
+    else:
+        cand = flat.view(M, R, 2)
+    ids = cand[..., 0].contiguous().view(torch.int32)
+    vals = cand[..., 1].contiguous()
+    big = torch.iinfo(torch.int32).max
+    key_id = torch.where(ids < 0, torch.full_like(ids, big), ids)
+    order = torch.sort(key_id, dim=1, stable=True).indices                    # ids ascending, holes last
+    v1 = torch.gather(vals, 1, order)
+    order2 = torch.sort(v1, dim=1, descending=True, stable=True).indices      # then values descending, stably
+    pick = torch.gather(order, 1, order2)[:, :R]
+    return torch.gather(ids, 1, pick), torch.gather(vals, 1, pick)
+
+
 class PushGather:
     """The fused form of the gather: the serving kernel's epilogue stores this rank's columns
     into every rank's [M, world * n_pad] buffer over NVLink (CUDA IPC peer mappings) and raises

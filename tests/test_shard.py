@@ -9,7 +9,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from libr3d_b200.shard import gather_columns, slab_of
+from libr3d_b200.shard import gather_columns, gather_topk, slab_of
+from oracle import oracle as orc
 
 
 @pytest.mark.parametrize("n,world", [(151936, 1), (151936, 2), (151936, 4), (151936, 8), (27648, 8),
@@ -55,4 +56,33 @@ def test_gather_equals_unsharded_two_ranks(n, M):
     out = mgr.dict()
     port = _free_port()
     mp.spawn(_rank, args=(2, port, n, M, out), nprocs=2, join=True)
+    assert dict(out) == {0: True, 1: True}
+
+
+def _rank_topk(rank, world, port, n, M, R, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(3)
+        # few distinct bf16 values: ties inside a slab and across slabs; one row with a single finite value
+        bits = orc.f32_to_bf16_bits((np.round(rng.standard_normal((M, n)) * 4) / 2).astype(np.float32))
+        bits[-1, :] = 0xFF80
+        bits[-1, n // 2 + 3] = 0x3F80
+        s = slab_of(n, world, rank)
+        # what this rank's row_topk row would write (the CPU oracle stands in for the GPU kernel here)
+        idx, val = orc.row_topk(np.ascontiguousarray(bits[:, s.start:s.start + s.rows]), R, s.start)
+        pairs = np.stack([idx.view(np.float32), val], axis=-1)
+        gi, gv = gather_topk(torch.from_numpy(pairs))
+        wi, wv = orc.row_topk(bits, R, 0)
+        out[rank] = bool(np.array_equal(gi.numpy(), wi) and np.array_equal(gv.numpy().view(np.uint32), wv.view(np.uint32)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n,M,R", [(1024, 3, 8), (4096, 2, 32), (256, 4, 32)])
+def test_sharded_topk_pairs_merge_two_ranks(n, M, R):
+    mgr = mp.Manager()
+    out = mgr.dict()
+    port = _free_port()
+    mp.spawn(_rank_topk, args=(2, port, n, M, R, out), nprocs=2, join=True)
     assert dict(out) == {0: True, 1: True}
