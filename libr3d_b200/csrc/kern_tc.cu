@@ -401,14 +401,16 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
                                    (int)cudaSharedmemCarveoutMaxShared);
         attr_set = smem;
     }
-    /* K shares per row tile: enough CTAs to put two on every SM (their stage rings are the
-     * bytes in flight), never more shares than whole stages, at most 8 (portable cluster) */
+    /* K shares per row tile (CTAs of one cluster): never more shares than whole stages, at most 8
+     * (portable cluster) */
     const int tiles = (P.n + kTileRows - 1) / kTileRows;
     static const int forced = [] { const char* e = getenv("R3D_TC_KSPLIT"); return e ? atoi(e) : 0; }();
-    /* measured: a CTA costs ~3 us of fill and drain and a cluster's reduction more per member, so K
-     * is split only when the row tiles alone cannot occupy the machine, and at most four ways
-     * (six to eight shares of the same shapes ran 40 % slower than four) */
-    int ks = forced > 0 ? forced : (tiles >= sm_count() / 2 ? 1 : tiles >= sm_count() / 4 ? 2 : 4);
+    /* measured over 16 to 216 row tiles (M = 1..16, K = 4096..13824): the best share count keeps
+     * the grid near 190-250 CTAs and never past five shares -- tiles * shares of 288 and more ran up
+     * to 70 % slower (a cluster must sit inside one GPC, so the last clusters of such a grid wait
+     * for a second wave), and six to eight shares cost more in the reduction than they stream */
+    int ks = forced > 0 ? forced : (5 * sm_count() / 3) / (tiles > 0 ? tiles : 1);
+    if (forced <= 0 && ks > 5) ks = 5;
     if (ks > 8) ks = 8;
     if (ks > P.k / kStageK) ks = P.k / kStageK;
     if (ks < 1) ks = 1;

@@ -470,12 +470,13 @@ int launch_s(const CUtensorMap* tw, const CUtensorMap* ts, const CUtensorMap* tp
                                    (int)cudaSharedmemCarveoutMaxShared);
         attr_set = smem;
     }
-    /* K shares per row tile: split K over a cluster only when the row tiles alone cannot occupy the
-     * machine, at most four ways (measured); shares are whole scale tiles (4 stages) */
+    /* K shares per row tile (CTAs of one cluster), the rule measured for the other tcgen05 walk:
+     * a grid near 190-250 CTAs, at most five shares; shares are whole scale tiles (4 stages) */
     P4 Q = P;
     const int tiles = (P.n + kRows - 1) / kRows, nk_all = P.k / kStageK;
     static const int forced = [] { const char* e = getenv("R3D_TC_KSPLIT"); return e ? atoi(e) : 0; }();
-    int ks = forced > 0 ? forced : (tiles >= tc_sm_count() / 2 ? 1 : tiles >= tc_sm_count() / 4 ? 2 : 4);
+    int ks = forced > 0 ? forced : (5 * tc_sm_count() / 3) / (tiles > 0 ? tiles : 1);
+    if (forced <= 0 && ks > 5) ks = 5;
     if (ks > 8) ks = 8;
     int per = nk_all;
     for (; ks > 1; --ks) {
