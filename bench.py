@@ -442,6 +442,29 @@ def run_all(args):
         out.append({"cfg": "C5", "band": "logits e4m3", "M": M, "N": NV, "K": K, "us_per_call": round(us, 1),
                     "GBs": round(nbytes / us / 1e3, 1), "hbm_frac_of_measured": round(nbytes / us / 1e3 / peak, 3),
                     "planes": 2, "nonzero_ok": int(torch.count_nonzero(y)) > 0.9 * M * NV})
+    # C5, mxfp4 head (e2m1 nibbles + one E8M0 byte per 32 columns; not a reference format), f32 logits
+    heads4 = []
+    for _ in range(2 if "C5" in want else 0):
+        heads4.append((torch.randint(0, 256, (NV, K // 2), dtype=torch.uint8, device=dev, generator=g),
+                       torch.randint(119, 124, (NV, K // 32), dtype=torch.uint8, device=dev, generator=g)))
+    for M in ((1, 4, 16) if "C5" in want else ()):
+        x = torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
+        y = torch.zeros((M, NV), dtype=torch.float32, device=dev)
+        ls = []
+        for codes, scale in heads4:
+            l = abi.R3dLogits()
+            l.x, l.codes, l.scale, l.y = x.data_ptr(), codes.data_ptr(), scale.data_ptr(), y.data_ptr()
+            l.m, l.n, l.k, l.br = M, NV, K, 1
+            l.scale_dtype, l.y_dtype, l.head_fmt, l.arm = abi.RAD_E8M0, abi.RAD_F32, 1, abi.R3D_ARM_AUTO
+            l.x_pitch, l.code_pitch, l.y_pitch, l.scale_pitch = K, K // 2, NV, K // 32
+            ls.append(l)
+        calls = [lambda st, l=l: P.lib.r3d_b200_logits(C.byref(l), st) for l in ls]
+        us = timed(calls, 20)
+        nbytes = NV * K // 2 + NV * K // 32 + M * K * 2 + M * NV * 4
+        out.append({"cfg": "C5", "band": "logits mxfp4", "M": M, "N": NV, "K": K, "us_per_call": round(us, 1),
+                    "GBs": round(nbytes / us / 1e3, 1), "hbm_frac_of_measured": round(nbytes / us / 1e3 / peak, 3),
+                    "planes": 2, "nonzero_ok": int(torch.count_nonzero(y)) > 0.9 * M * NV})
+    del heads4
     if "ROWS" in want:
         # the rows either side of the bands, through their row entries: activation producers at the
         # model's widths and the per-shard top-R over bf16 logits

@@ -601,6 +601,10 @@ int tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push) {
 }
 
 bool tc_logits_ok(const R3dLogits& l) {
+    if (l.head_fmt == 1)                      /* mxfp4 head: e2m1 nibbles + one E8M0 byte per 32 columns */
+        return l.m >= 1 && l.m <= 16 && l.k >= 128 && (l.k % 128) == 0 && l.k <= kLgMaxK && al(l.codes, 32) &&
+               (l.code_pitch % 32) == 0 && al(l.scale, 4) && (l.scale_pitch % 4) == 0 && al(l.x, 8) &&
+               (l.x_pitch % 4) == 0 && (l.y_dtype == RAD_F32 || l.y_dtype == RAD_BF16) && encode_fn() != nullptr;
     return l.head_fmt == 0 && l.m >= 1 && l.m <= kLgMaxTok && l.k >= 128 && (l.k % 128) == 0 &&
            l.k <= kLgMaxK && (l.br == 1 || l.br == 128) && al(l.codes, 16) && (l.code_pitch % 16) == 0 &&
            al(l.x, 8) && (l.x_pitch % 4) == 0 &&
@@ -628,8 +632,10 @@ int tc_logits(const R3dLogits& l, cudaStream_t st, const PushCfg* push) {
                                sc.pieces, sc.scale) != cudaSuccess) return RAD_E_DEVICE;
     }
     const int ntok = 2 * mp <= 16 ? 16 : 2 * mp;
+    const bool fp4 = l.head_fmt == 1;
     const CUtensorMap* tw = tensor_map(l.codes, (uint64_t)l.k, (uint64_t)l.n, (uint64_t)l.code_pitch,
-                                       CU_TENSOR_MAP_DATA_TYPE_UINT8, kTileRows);
+                                       fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+                                       kTileRows);
     const CUtensorMap* ta = tensor_map(sc.pieces, (uint64_t)l.k, (uint64_t)(2 * mp), (uint64_t)l.k,
                                        CU_TENSOR_MAP_DATA_TYPE_UINT8, (uint32_t)ntok);
     if (!tw || !ta) return RAD_E_UNSUPPORTED;
@@ -640,6 +646,18 @@ int tc_logits(const R3dLogits& l, cudaStream_t st, const PushCfg* push) {
     P.m = 2 * mp; P.mlive = l.m; P.n = l.n; P.k = l.k;
     P.as_cols = n128; P.ws_cols = n128; P.rblk = l.br; P.ws_dtype = l.scale_dtype;
     if (push) P.push = *push;
+    if (fp4) {
+        /* the mxfp4 head: the tensor core applies the E8M0 group scales (one byte per 32 columns),
+         * the epilogue only the pieces' power-of-two scales */
+        P.ws_cols = l.k / 32; P.rblk = 1; P.ws_dtype = RAD_E8M0;
+        switch (mp) {
+        case 1:  return launch_tc<TC_MXFP4, 16, 2, 1>(tw, ta, P, st);
+        case 2:  return launch_tc<TC_MXFP4, 16, 4, 1>(tw, ta, P, st);
+        case 4:  return launch_tc<TC_MXFP4, 16, 8, 1>(tw, ta, P, st);
+        case 8:  return launch_tc<TC_MXFP4, 16, 16, 1>(tw, ta, P, st);
+        default: return launch_tc<TC_MXFP4, 32, 32, 1>(tw, ta, P, st);
+        }
+    }
     switch (mp) {
     case 1:  return launch_tc<TC_FP8, 16, 2, 1>(tw, ta, P, st);
     case 2:  return launch_tc<TC_FP8, 16, 4, 1>(tw, ta, P, st);

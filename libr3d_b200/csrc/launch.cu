@@ -170,7 +170,8 @@ extern "C" int r3d_b200_logits(const R3dLogits* l, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     int arm = l->arm;
     if (arm == R3D_ARM_AUTO) {
-        R3dLogits probe = *l; if (probe.m > 32) probe.m = 32;
+        const int tile_step = l->head_fmt == 1 ? 16 : 32;
+        R3dLogits probe = *l; if (probe.m > tile_step) probe.m = tile_step;
         if (tc_logits_ok(probe)) arm = R3D_ARM_TILE;
         else {
             probe = *l; if (probe.m > 64) probe.m = 64;
@@ -182,7 +183,7 @@ extern "C" int r3d_b200_logits(const R3dLogits* l, void* stream) {
     const bool tile = arm == R3D_ARM_TILE;
     debug_arm("logits", tile ? "tcgen05" : "stream", l->m);
     const int ysz = l->y_dtype == RAD_F32 ? 4 : 2;
-    const int step = tile ? 32 : 64;
+    const int step = tile ? (l->head_fmt == 1 ? 16 : 32) : 64;
     for (int m0 = 0; m0 < l->m; m0 += step) {
         R3dLogits c = *l;
         c.m = l->m - m0 < step ? l->m - m0 : step;

@@ -1,4 +1,6 @@
 """GPU parity of logits_gemm over the joined e4m3 + block-scale head."""
+import ctypes as C
+
 import numpy as np
 import pytest
 import torch
@@ -113,3 +115,40 @@ def test_vocab_size_head_sampled_rows():
         got = gu.logits_launch(c, arm)
         assert _rel(got[:, rows], want.astype(np.float64)) < tol, arm
         assert np.count_nonzero(got) > got.size * 0.99
+
+
+def _mxfp4_head_launch(Xb, B, BS, arm, y_dtype=abi.RAD_F32):
+    P = ops.plugin()
+    X, codes, scale = gu.dev(Xb), gu.dev(B), gu.dev(BS)
+    M, K = Xb.shape
+    N = B.shape[0]
+    out = gu.GuardedOut((M, N), np.float32 if y_dtype == abi.RAD_F32 else np.uint16)
+    l = abi.R3dLogits()
+    l.x, l.codes, l.scale, l.y = X.data_ptr(), codes.data_ptr(), scale.data_ptr(), out.ptr
+    l.m, l.n, l.k, l.br = M, N, K, 1
+    l.scale_dtype, l.y_dtype, l.head_fmt, l.arm = abi.RAD_E8M0, y_dtype, 1, arm
+    l.x_pitch, l.code_pitch, l.y_pitch, l.scale_pitch = K, K // 2, N, K // 32
+    rc = P.lib.r3d_b200_logits(C.byref(l), None)
+    assert rc == abi.RAD_OK, abi.STATUS_NAMES[rc]
+    return out.get()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (4, 1000, 5120), (16, 384, 2560), (20, 256, 512)])
+def test_mxfp4_head_tcgen05_arm_against_oracle_and_exact_arm(M, N, K):
+    """The mxfp4 LM head (e2m1 nibbles, one E8M0 byte per 32 columns; not a reference format: the
+    oracle fixes y = sum f32(x) * (e2m1 * 2^(s-127)) as one fp32 fma chain). The exact arm must match
+    the oracle bit for bit; the tcgen05 arm (hardware group scales, two exact e4m3 pieces per bf16
+    activation) within the logits tolerance. M = 20 takes two passes of 16."""
+    c = gen.case_mxfp4(4400 + M, 1, N, K)
+    rng = np.random.default_rng(M + N)
+    Xb = gen.f32_to_bf16_bits(rng.uniform(-2, 2, (M, K)).astype(np.float32))
+    want = orc.logits_mxfp4(Xb, c["B"], c["BS"]).astype(np.float64)
+    exact = _mxfp4_head_launch(Xb, c["B"], c["BS"], abi.R3D_ARM_EXACT)
+    assert np.array_equal(exact.view(np.uint32), orc.logits_mxfp4(Xb, c["B"], c["BS"]).view(np.uint32))
+    rel = lambda a, b: np.abs(a - b).max() / max(np.abs(b).max(), 1e-6)
+    for arm in (abi.R3D_ARM_TILE, abi.R3D_ARM_AUTO):
+        got = _mxfp4_head_launch(Xb, c["B"], c["BS"], arm).astype(np.float64)
+        assert rel(got, want) < 2e-5, (arm, rel(got, want))
+    gb = _mxfp4_head_launch(Xb, c["B"], c["BS"], abi.R3D_ARM_TILE, abi.RAD_BF16)
+    d = orc.bf16_ulp_distance(gb, orc.f32_to_bf16_bits(want.astype(np.float32)))
+    assert (d <= 2).mean() > 0.999
