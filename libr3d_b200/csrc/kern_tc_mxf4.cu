@@ -394,37 +394,48 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 /* ------------------------------------------------------------------ activation split */
 constexpr int kMaxK = 32768;
 __device__ __align__(256) uint8_t g_p4_pieces[kMaxTok * kPieces * (kMaxK / 2)];
-__device__ uint32_t g_p4_nan[kMaxTok * (kMaxK / 1024)];
+__device__ uint32_t g_p4_nan[kMaxTok * (kMaxK / 256)];       /* one flag per split block (128 threads x >= 2 elements) */
 
-/* one thread per 8 consecutive K elements of one token (blockIdx.y): 8 e4m3 bytes in, one 32-bit
- * word of packed e2m1 out to each of the token's twelve piece rows; every block also writes its
- * "saw a NaN code" flag, set or clear, so no flag outlives the call that wrote it */
+/* one thread per EPT (2, 4 or 8) consecutive K elements of one token (blockIdx.y): EPT e4m3 bytes in,
+ * EPT packed e2m1 nibbles out to each of the token's twelve piece rows; every block also writes its
+ * "saw a NaN code" flag, set or clear, so no flag outlives the call that wrote it. The kernel sits on
+ * the critical path of every call (the weight-streaming kernel waits for it), so the work per thread
+ * is kept short: fewer elements per thread, more threads. */
+template <int EPT>
 __global__ void __launch_bounds__(128)
 k_mxf4_split(const uint8_t* __restrict__ a, int64_t a_pitch, int k,
              uint8_t* __restrict__ pieces, uint32_t* __restrict__ nanflag) {
     dep_launch();
     dep_wait();                    /* the activation is the previous kernel's output, and the
                                       previous reader of the piece rows must have finished */
-    const int per = k / 8;
-    const int c8 = blockIdx.x * 128 + threadIdx.x, t = blockIdx.y;
+    const int per = k / EPT;
+    const int c = blockIdx.x * 128 + threadIdx.x, t = blockIdx.y;
     bool nan = false;
-    if (c8 < per) {
-        const uint2 raw = __ldg((const uint2*)(a + (int64_t)t * a_pitch + c8 * 8));
+    if (c < per) {
+        const uint8_t* src = a + (int64_t)t * a_pitch + c * EPT;
+        uint32_t raw[2] = {0u, 0u};
+        if (EPT == 8) { const uint2 r = __ldg((const uint2*)src); raw[0] = r.x; raw[1] = r.y; }
+        else if (EPT == 4) raw[0] = __ldg((const uint32_t*)src);
+        else raw[0] = __ldg((const uint16_t*)src);
         uint32_t out[kPieces];
 #pragma unroll
         for (int p = 0; p < kPieces; ++p) out[p] = 0u;
 #pragma unroll
-        for (int e8 = 0; e8 < 8; ++e8) {
-            const uint32_t b = ((e8 < 4 ? raw.x : raw.y) >> (8 * (e8 & 3))) & 0xffu;
+        for (int e = 0; e < EPT; ++e) {
+            const uint32_t b = (raw[e >> 2] >> (8 * (e & 3))) & 0xffu;
             if ((b & 0x7fu) == 0x7fu) nan = true;
             const uint64_t L = piece_codes(b);
 #pragma unroll
-            for (int p = 0; p < kPieces; ++p) out[p] |= (uint32_t)((L >> (4 * p)) & 0xfull) << (4 * e8);
+            for (int p = 0; p < kPieces; ++p) out[p] |= (uint32_t)((L >> (4 * p)) & 0xfull) << (4 * e);
         }
         const int64_t rowb = k / 2;
 #pragma unroll
-        for (int p = 0; p < kPieces; ++p)
-            *(uint32_t*)(pieces + (int64_t)(t * kPieces + p) * rowb + c8 * 4) = out[p];
+        for (int p = 0; p < kPieces; ++p) {
+            uint8_t* dst = pieces + (int64_t)(t * kPieces + p) * rowb + c * (EPT / 2);
+            if (EPT == 8) *(uint32_t*)dst = out[p];
+            else if (EPT == 4) *(uint16_t*)dst = (uint16_t)out[p];
+            else *dst = (uint8_t)out[p];
+        }
     }
     const int any = __syncthreads_or(nan ? 1 : 0);
     if (threadIdx.x == 0) nanflag[t * gridDim.x + blockIdx.x] = any ? 1u : 0u;
@@ -534,10 +545,16 @@ bool tc_mxf4_ok(const R3dGemmQ& p) {
 int tc_mxf4(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push) {
     Scratch sc;
     if (!scratch(&sc)) return RAD_E_DEVICE;
-    const int nb = (p.k / 8 + 127) / 128;
+    static const int ept = [] { const char* e = getenv("R3D_SPLIT_EPT"); const int v = e ? atoi(e) : 2;
+                                return v == 8 || v == 4 ? v : 2; }();
+    const int nb = (p.k / ept + 127) / 128;
     count_launch();
-    if (launch_pdl(k_mxf4_split, dim3((unsigned)nb, (unsigned)p.m), dim3(128), 0, st, (const uint8_t*)p.a,
-                   (int64_t)p.a_pitch, (int)p.k, sc.pieces, sc.nan) != cudaSuccess) return RAD_E_DEVICE;
+    const dim3 sgrid((unsigned)nb, (unsigned)p.m);
+    cudaError_t se;
+    if (ept == 8) se = launch_pdl(k_mxf4_split<8>, sgrid, dim3(128), 0, st, (const uint8_t*)p.a, (int64_t)p.a_pitch, (int)p.k, sc.pieces, sc.nan);
+    else if (ept == 4) se = launch_pdl(k_mxf4_split<4>, sgrid, dim3(128), 0, st, (const uint8_t*)p.a, (int64_t)p.a_pitch, (int)p.k, sc.pieces, sc.nan);
+    else se = launch_pdl(k_mxf4_split<2>, sgrid, dim3(128), 0, st, (const uint8_t*)p.a, (int64_t)p.a_pitch, (int)p.k, sc.pieces, sc.nan);
+    if (se != cudaSuccess) return RAD_E_DEVICE;
     const int np = p.m == 1 ? 16 : (p.m == 2 ? 32 : (p.m <= 4 ? 48 : 96));
     const CUtensorMap* tw = tc_tensor_map(p.b, (uint64_t)(p.k / 2), (uint64_t)p.n, (uint64_t)p.b_pitch,
                                           CU_TENSOR_MAP_DATA_TYPE_UINT8, kRows);
