@@ -741,7 +741,7 @@ def main():
         traffic = None
         tf = ROOT / "profiles" / "traffic.json"
         if tf.exists():
-            traffic = json.loads(tf.read_text()).get("k_tc_mxf4_c2_bytes_per_call")
+            traffic = None if args.row.endswith("_q8x") else json.loads(tf.read_text()).get("k_tc_mxf4_c2_bytes_per_call")
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -757,7 +757,9 @@ def main():
                                        + (f" [{gather_note}]" if gather_note else ""))},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": which, "traffic": traffic,
-                         "kernel": "k_tc_mxf4<NP,MT> (one per call, after its k_mxf4_split)", "bytes_per_launch": STEP_BYTES / 3,
+                         "kernel": ("k_q8x_gemv<MT,WALK> (one per call, after its k_q8x_requant)" if args.row.endswith("_q8x")
+                                    else "k_tc_mxf4<NP,MT> (one per call, after its k_mxf4_split)"),
+                         "bytes_per_launch": STEP_BYTES / 3,
                          "us_per_launch": per_launch_s * 1e6},
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "timed_as": e2e_how,
                     "steps": e2e_steps},

@@ -76,25 +76,44 @@ __global__ __launch_bounds__(128) void k_q8x_gemv(
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m] = 0.0f;
 
-    for (int g0 = 0; g0 < K32; g0 += 32) {
+    /* The weight words and scale bytes of W sweeps (W * 32 groups of 32 codes) are requested back
+     * to back before any of them is consumed: a lane then has W 16-byte loads in flight instead of
+     * one, which is what a stream of 2.5 KB rows needs to keep HBM busy. Only the order of the loads
+     * changes; every float operation keeps its place. */
+    constexpr int W = 4;
+    for (int gw = 0; gw < K32; gw += 32 * W) {
+        uint4 wv[W];
+        uint8_t sbv[W];
+#pragma unroll
+        for (int d = 0; d < W; ++d) {
+            const int g = gw + d * 32 + lane;
+            wv[d] = make_uint4(0u, 0u, 0u, 0u);
+            sbv[d] = 0;
+            if (g < K32) {
+                if (al16) wv[d] = *(const uint4*)(brow + ((int64_t)g << 4));
+                else {
+                    const uint8_t* bp = brow + ((int64_t)g << 4);
+                    wv[d] = make_uint4(*(const uint32_t*)bp, *(const uint32_t*)(bp + 4), *(const uint32_t*)(bp + 8),
+                                       *(const uint32_t*)(bp + 12));
+                }
+                sbv[d] = srow[g];
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < W; ++d) {
+        const int g0 = gw + d * 32;
+        if (g0 >= K32) break;
         const int g = g0 + lane;
         const bool on = g < K32;
         float c[MT];
 #pragma unroll
         for (int m = 0; m < MT; ++m) c[m] = 0.0f;
         if (on) {
-            uint32_t w[4];
-            if (al16) {
-                const uint4 v = *(const uint4*)(brow + ((int64_t)g << 4));
-                w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) w[i] = *(const uint32_t*)(brow + ((int64_t)g << 4) + 4 * i);
-            }
+            const uint32_t w[4] = {wv[d].x, wv[d].y, wv[d].z, wv[d].w};
             uint32_t s8[8];
 #pragma unroll
             for (int i = 0; i < 4; ++i) e2m1x8_to_s8(w[i], s8[2 * i], s8[2 * i + 1]);
-            const float sc = e8m0_to_f32(srow[g]);
+            const float sc = e8m0_to_f32(sbv[d]);
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 if (m < live) {
@@ -135,6 +154,7 @@ __global__ __launch_bounds__(128) void k_q8x_gemv(
             for (int m = 0; m < MT; ++m)
                 if (on) acc[m] = __fadd_rn(acc[m], c[m]);
         }
+    }
     }
     if (WALK == 1) {
 #pragma unroll
