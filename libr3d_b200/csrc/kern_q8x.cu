@@ -73,8 +73,9 @@ __global__ __launch_bounds__(128) void k_q8x_gemv(
     const bool al16 = ((((uintptr_t)p.b) | (uintptr_t)p.b_pitch) & 15) == 0;
 
     float acc[MT];
+    const float* as_row[MT];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) acc[m] = 0.0f;
+    for (int m = 0; m < MT; ++m) { acc[m] = 0.0f; as_row[m] = p.a_scale + (int64_t)m * p.as_pitch; }
 
     /* The weight words and scale bytes of W sweeps (W * 32 groups of 32 codes) are requested back
      * to back before any of them is consumed: a lane then has W 16-byte loads in flight instead of
@@ -117,8 +118,9 @@ __global__ __launch_bounds__(128) void k_q8x_gemv(
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 if (m < live) {
-                    const uint4* xp = (const uint4*)(X8 + (int64_t)m * K + ((int64_t)g << 5));
-                    const uint4 xa = xp[0], xb = xp[1];
+                    /* offsets fit 32 bits: M <= 8 rows of at most 2^20 columns */
+                    const uint4* xp = (const uint4*)(X8 + (m * K + (g << 5)));
+                    const uint4 xa = __ldg(xp), xb = __ldg(xp + 1);
                     int pp = __dp4a((int)xa.x, (int)s8[0], 0);
                     pp = __dp4a((int)xa.y, (int)s8[1], pp);
                     pp = __dp4a((int)xa.z, (int)s8[2], pp);
@@ -127,8 +129,8 @@ __global__ __launch_bounds__(128) void k_q8x_gemv(
                     pp = __dp4a((int)xb.y, (int)s8[5], pp);
                     pp = __dp4a((int)xb.z, (int)s8[6], pp);
                     pp = __dp4a((int)xb.w, (int)s8[7], pp);
-                    float v = __fmul_rn((float)pp, SG[(int64_t)m * K32 + g]);
-                    v = __fmul_rn(v, p.a_scale[(int64_t)m * p.as_pitch + (g >> 2)]);
+                    float v = __fmul_rn((float)pp, __ldg(SG + (m * K32 + g)));
+                    v = __fmul_rn(v, __ldg(as_row[m] + (g >> 2)));
                     v = __fmul_rn(v, sc);
                     c[m] = __fmul_rn(v, 0.5f);
                 }
@@ -182,7 +184,7 @@ int q8x_requant(const R3dGemmQ& p, int8_t* x8, float* sg, cudaStream_t st) {
 }
 
 int q8x_gemv(const R3dGemmQ& p, const int8_t* x8, const float* sg, int walk, cudaStream_t st) {
-    if (p.m < 1 || p.m > 8 || (p.k & 255)) return RAD_E_UNSUPPORTED;
+    if (p.m < 1 || p.m > 8 || (p.k & 255) || p.k > (1 << 20)) return RAD_E_UNSUPPORTED;   /* 32-bit offsets in the kernel */
     if ((((uintptr_t)p.b) | (uintptr_t)p.b_pitch) & 3) return RAD_E_UNSUPPORTED;
     const int mt = p.m <= 1 ? 1 : p.m <= 2 ? 2 : p.m <= 4 ? 4 : 8;
     const dim3 grid((unsigned)((p.n + 3) / 4));

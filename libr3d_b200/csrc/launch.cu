@@ -157,7 +157,7 @@ extern "C" int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream) {
 extern "C" int r3d_b200_gemm_mxfp4a8_q8x(const R3dGemmQ* q, int8_t* x8, float* sg, int walk,
                                          void* stream) {
     if (!q || !x8 || !sg || !device_is_sm100()) return RAD_E_UNSUPPORTED;
-    if (q->m < 1 || q->m > 8 || (q->k & 255)) return RAD_E_UNSUPPORTED;
+    if (q->m < 1 || q->m > 8 || (q->k & 255) || q->k > (1 << 20)) return RAD_E_UNSUPPORTED;   /* the kernel's 32-bit offsets */
     cudaStream_t st = (cudaStream_t)stream;
     int rc = q8x_requant(*q, x8, sg, st);
     if (rc != RAD_OK) return rc;
