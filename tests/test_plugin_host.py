@@ -206,6 +206,23 @@ def _mx_args(M=2, N=64, K=256, drop=(), **over):
     return ArgPack(list(t.values()), p), z
 
 
+def _both(plug, sym, lib, ref_sym, pack):
+    """This library's entry and, where it was built, the reference's own compiled entry on the same
+    operands: the status must be the same; returns it."""
+    from oracle import oracle as orc
+    rc = plug.entry(sym)(C.byref(pack.args), None)
+    R = orc.ref_band() if lib == "band" else orc.ref_more()
+    if R is not None:
+        assert getattr(R, ref_sym)(C.byref(pack.args), None) == rc, (sym, rc)
+    return rc
+
+
+def _ref_entries(which):
+    """The reference's band file compiled by oracle/Makefile, or None where it was not built."""
+    from oracle import oracle as orc
+    return orc.ref_gemm(which)
+
+
 Z = np.zeros(16, np.uint8)
 U, SH, ST = abi.RAD_E_UNSUPPORTED, abi.RAD_E_SHAPE, abi.RAD_E_STRIDE
 
@@ -232,6 +249,12 @@ def test_fp8_entry_refusals(plug, over, code):
     pack, _ = _fp8_args(**over)
     for sym in ("r3d_rad_gemm_nt_q_fp8", "r3d_rad_gemm_nt_q_fp8_decode"):
         assert plug.entry(sym)(C.byref(pack.args), None) == code, sym
+    # the reference's own entries (src/r3d_gemm_fp8a8.hip of libr3d, compiled where it lay) refuse the
+    # same operands with the same status: every case here stops before any device work
+    R = _ref_entries("fp8a8")
+    if R is not None:
+        for sym in ("ref_fp8a8_gemm_nt_q", "ref_fp8a8_gemm_nt_q_decode"):
+            assert getattr(R, sym)(C.byref(pack.args), None) == code, sym
 
 
 def test_activation_producer_refusals(plug):
@@ -243,7 +266,7 @@ def test_activation_producer_refusals(plug):
 
     def quant(x=None, q=None, sc=None, **p):
         ts = [x or T(z, abi.RAD_BF16, [2, 256]), q or T(z, abi.RAD_F8E4M3, [2, 256]), sc or T(z, abi.RAD_F32, [2, 2])]
-        return plug.entry("r3d_rad_quant_act_fp8")(C.byref(ArgPack(ts, dict(dict(M=2, n=256, group=128, dtype="bf16"), **p)).args), None)
+        return _both(plug, "r3d_rad_quant_act_fp8", "band", "ref_band_quant_act_fp8", ArgPack(ts, dict(dict(M=2, n=256, group=128, dtype="bf16"), **p)))
     assert quant(x=T(None, abi.RAD_BF16, [2, 256])) == IV
     assert quant(x=T(z, abi.RAD_F16, [2, 256])) == DT
     assert quant(q=T(z, abi.RAD_U8, [2, 256])) == DT
@@ -256,7 +279,7 @@ def test_activation_producer_refusals(plug):
     def gated(gu=None, ob=None, **p):
         ts = [gu or T(z, abi.RAD_BF16, [2, 512]), T(z, abi.RAD_F8E4M3, [2, 256]), T(z, abi.RAD_F32, [2, 2]),
               ob or T(None, abi.RAD_BF16, [])]
-        return plug.entry("r3d_rad_gated_quant_fp8")(C.byref(ArgPack(ts, dict(dict(M=2, n=256, group=128, dtype="bf16"), **p)).args), None)
+        return _both(plug, "r3d_rad_gated_quant_fp8", "band", "ref_band_gated_quant_fp8", ArgPack(ts, dict(dict(M=2, n=256, group=128, dtype="bf16"), **p)))
     assert gated(gu=T(z, abi.RAD_F16, [2, 512])) == DT
     assert gated(ob=T(z, abi.RAD_F16, [2, 256])) == DT
     assert gated(ob=T(z, abi.RAD_BF16, [1, 256])) == SH
@@ -265,7 +288,7 @@ def test_activation_producer_refusals(plug):
     def rms(x=None, res=None, w=None, n_t=6, **p):
         ts = [x or T(z, abi.RAD_BF16, [2, 256]), res or T(None, abi.RAD_BF16, []), w or T(z, abi.RAD_BF16, [256]),
               T(z, abi.RAD_F8E4M3, [2, 256]), T(z, abi.RAD_F32, [2, 2]), T(None, abi.RAD_BF16, [])][:n_t]
-        return plug.entry("r3d_rad_rmsnorm_quant_fp8")(C.byref(ArgPack(ts, dict(dict(M=2, n=256, eps=1e-6, group=128, dtype="bf16"), **p)).args), None)
+        return _both(plug, "r3d_rad_rmsnorm_quant_fp8", "more", "ref_more_rmsnorm_quant_fp8", ArgPack(ts, dict(dict(M=2, n=256, eps=1e-6, group=128, dtype="bf16"), **p)))
     assert rms(n_t=4) == IV
     assert rms(x=T(z, abi.RAD_F32, [2, 256])) == DT                             # the published row is bf16
     assert rms(res=T(z, abi.RAD_F32, [2, 256])) == DT
@@ -277,7 +300,7 @@ def test_activation_producer_refusals(plug):
     def topk(x=None, idx=None, val=None, pairs=None, **p):
         ts = [x or T(z, abi.RAD_BF16, [2, 256]), idx or T(z, abi.RAD_I32, [2, 4]), val or T(z, abi.RAD_F32, [2, 4]),
               pairs or T(None, abi.RAD_F32, [])]
-        return plug.entry("r3d_rad_row_topk")(C.byref(ArgPack(ts, dict(dict(M=2, N=256, R=4, dtype="bf16"), **p)).args), None)
+        return _both(plug, "r3d_rad_row_topk", "more", "ref_more_row_topk", ArgPack(ts, dict(dict(M=2, N=256, R=4, dtype="bf16"), **p)))
     def argmax(lg=None, tok=None, **p):
         ts = [lg or T(z, abi.RAD_F32, [2, 256]), T(None, abi.RAD_U8, []), tok or T(z, abi.RAD_I32, [2])]
         return plug.entry("r3d_rad_sample_argmax")(C.byref(ArgPack(ts, dict(dict(M=2, n_vocab=256), **p)).args), None)
@@ -321,6 +344,10 @@ def test_mxfp4_entry_refusals(plug, over, code):
     pack, _ = _mx_args(**over)
     for sym in ("r3d_rad_gemm_nt_q", "r3d_rad_gemm_nt_q_mxfp4_decode", "r3d_rad_gemm_nt_q_mxfp4_decode_q8x"):
         assert plug.entry(sym)(C.byref(pack.args), None) == code, sym
+    R = _ref_entries("mxfp4")                      # src/r3d_gemm_mxfp4.hip's own entries: same status
+    if R is not None:
+        for sym in ("ref_mxfp4_gemm_nt_q", "ref_mxfp4_gemm_nt_q_decode", "ref_mxfp4_gemm_nt_q_decode_q8x"):
+            assert getattr(R, sym)(C.byref(pack.args), None) == code, sym
 
 
 def test_mxfp4_b_ref_is_accepted_and_ignored(plug):
@@ -374,9 +401,15 @@ def test_logits_entry_refusals(plug):
     f = plug.entry("r3d_rad_logits_gemm_e4m3")
     D = abi.RAD_E_DTYPE
 
+    from oracle import oracle as orc
+    Rl = orc.ref_logits()                      # the reference's own entry (src/r3d_gemm_logits.hip), where built
+
     def rc(blob=good, **over):
         pack, keep = _logits_args(blob, **over)
-        return f(C.byref(pack.args), None)
+        got = f(C.byref(pack.args), None)
+        if Rl is not None:
+            assert Rl.ref_logits_gemm_e4m3(C.byref(pack.args), None) == got, over
+        return got
 
     assert rc(dtype="f16") == U and rc(n_vocab=None) == SH and rc(n_vocab=7) == SH
     assert rc(n_embd=510, x=tensor_desc(Z.ctypes.data, abi.RAD_BF16, [2, 510])) == U    # K % 4
