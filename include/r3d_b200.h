@@ -125,9 +125,16 @@ int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream);
 /* The int8-per-32 arm: requantise the activation into x8/sg (caller-owned scratch,
  * x8 >= m*k bytes, sg >= m*k/32 floats), then the dot. walk 0 = per-256 tree, 1 = lane
  * map. Replaces m4_act_i8_kernel + gemm_nt_mxfp4_gemv_q8x[_lm]_kernel
- * (src/r3d_gemm_mxfp4.hip:1150-1166, :1217-1458); needs no repacked weight plane. */
+ * (src/r3d_gemm_mxfp4.hip:1150-1166, :1217-1458); needs no repacked weight plane. The exact
+ * integer dots run on the tensor core (tcgen05.mma kind::mxf4 over e2m1 digit rows of the int8
+ * activation, which live in a device array owned by the library: order calls on one stream) when
+ * K <= 32768, the weight and scale planes are 16-byte aligned with pitches that are multiples of
+ * 16 bytes; otherwise on dp4a. Both give the reference arm's bits. */
 int r3d_b200_gemm_mxfp4a8_q8x(const R3dGemmQ* q, int8_t* x8, float* sg, int walk,
                               void* stream);
+/* 1 when the call above would run its dots on the tensor core, 0 when on dp4a (no launch): for
+ * tests and debug prints, like r3d_b200_pick_arm_*. No counterpart in the reference. */
+int r3d_b200_q8x_on_tensor_core(const R3dGemmQ* q);
 
 /* The same arm with no allocation anywhere: the requantised-activation scratch is a fixed
  * array inside the library (288 KiB per GPU, held until the process exits) instead of

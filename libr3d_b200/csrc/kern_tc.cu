@@ -684,6 +684,8 @@ int tc_status() {
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
     if (v) return v;
     v = tc_mxf4_status();
+    if (v) return v;
+    v = tc_q8x_status();
     return v ? v : tc_gemm_status();
 }
 

@@ -154,15 +154,28 @@ extern "C" int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream) {
     return RAD_E_UNSUPPORTED;
 }
 
+namespace r3d {
+int q8x_run(const R3dGemmQ& q, int8_t* x8, float* sg, int walk, cudaStream_t st) {
+    if (tc_q8x_ok(q)) {
+        debug_arm("mxfp4a8", walk ? "q8x lane-map on tcgen05" : "q8x dot4 on tcgen05", q.m);
+        return tc_q8x(q, x8, sg, walk, st);
+    }
+    const int rc = q8x_requant(q, x8, sg, st);
+    if (rc != RAD_OK) return rc;
+    debug_arm("mxfp4a8", walk ? "q8x lane-map" : "q8x dot4", q.m);
+    return q8x_gemv(q, x8, sg, walk, st);
+}
+} /* namespace r3d */
+
+extern "C" int r3d_b200_q8x_on_tensor_core(const R3dGemmQ* q) {
+    return q && q->m >= 1 && q->m <= 8 && tc_q8x_ok(*q) ? 1 : 0;
+}
+
 extern "C" int r3d_b200_gemm_mxfp4a8_q8x(const R3dGemmQ* q, int8_t* x8, float* sg, int walk,
                                          void* stream) {
     if (!q || !x8 || !sg || !device_is_sm100()) return RAD_E_UNSUPPORTED;
-    if (q->m < 1 || q->m > 8 || (q->k & 255) || q->k > (1 << 20)) return RAD_E_UNSUPPORTED;   /* the kernel's 32-bit offsets */
-    cudaStream_t st = (cudaStream_t)stream;
-    int rc = q8x_requant(*q, x8, sg, st);
-    if (rc != RAD_OK) return rc;
-    debug_arm("mxfp4a8", walk ? "q8x lane-map" : "q8x dot4", q->m);
-    return q8x_gemv(*q, x8, sg, walk, st);
+    if (q->m < 1 || q->m > 8 || (q->k & 255) || q->k > (1 << 20)) return RAD_E_UNSUPPORTED;   /* the kernels' 32-bit offsets */
+    return q8x_run(*q, x8, sg, walk ? 1 : 0, (cudaStream_t)stream);
 }
 
 extern "C" int r3d_b200_logits(const R3dLogits* l, void* stream) {

@@ -71,7 +71,5 @@ extern "C" int r3d_b200_gemm_mxfp4a8_q8x_static(const R3dGemmQ* q, int walk, voi
     int8_t* x8 = (int8_t*)base;
     float* sg = (float*)(base + kCodeBytes);
     cudaStream_t st = (cudaStream_t)stream;
-    const int rc = r3d::q8x_requant(*q, x8, sg, st);
-    if (rc != RAD_OK) return rc;
-    return r3d::q8x_gemv(*q, x8, sg, walk ? 1 : 0, st);
+    return r3d::q8x_run(*q, x8, sg, walk ? 1 : 0, st);
 }

@@ -67,5 +67,13 @@ int  tc_status();                      /* 0, or the code of a bounded wait that 
 /* int8-per-32 activation arm (kern_q8x.cu) */
 int q8x_requant(const R3dGemmQ& p, int8_t* x8, float* sg, cudaStream_t st);
 int q8x_gemv(const R3dGemmQ& p, const int8_t* x8, const float* sg, int walk, cudaStream_t st);
+/* the same arm on the tensor core (kern_tc_q8x.cu): packed nibbles by TMA, the exact integer dots by
+ * tcgen05.mma kind::mxf4 over e2m1 digit rows of the int8 activation, the float chain in the epilogue;
+ * writes x8 and sg like q8x_requant does */
+bool tc_q8x_ok(const R3dGemmQ& p);
+int  tc_q8x(const R3dGemmQ& p, int8_t* x8, float* sg, int walk, cudaStream_t st);
+int  tc_q8x_status();
+/* requantise + dot, on the tensor core when the operands allow it, else the dp4a kernels */
+int  q8x_run(const R3dGemmQ& p, int8_t* x8, float* sg, int walk, cudaStream_t st);
 
 } /* namespace r3d */

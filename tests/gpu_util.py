@@ -69,8 +69,9 @@ def gemm_launch(kind: str, case: dict, arm: int, a_dev=None) -> np.ndarray:
     return out.get()
 
 
-def q8x_launch(case: dict, walk: int):
-    """The int8 arm through the launch layer with caller scratch; returns (Y bits, x8, sg)."""
+def q8x_launch(case: dict, walk: int, want_tc: bool | None = None):
+    """The int8 arm through the launch layer with caller scratch; returns (Y bits, x8, sg).
+    want_tc: assert that the dots run on the tensor core (True) or on dp4a (False)."""
     P = ops.plugin()
     A, AS, B, BS = dev(case["A"]), dev(case["AS"]), dev(case["B"]), dev(case["BS"])
     M, K = case["A"].shape
@@ -84,9 +85,13 @@ def q8x_launch(case: dict, walk: int):
     q.as_cols, q.bs_cols = K // 128, K // 32
     q.a_pitch, q.b_pitch, q.y_pitch, q.as_pitch, q.bs_pitch = K, K // 2, N, K // 128, K // 32
     q.rblk, q.bs_dtype = 1, abi.RAD_E8M0
+    if want_tc is not None:
+        assert bool(P.lib.r3d_b200_q8x_on_tensor_core(C.byref(q))) == want_tc
     rc = P.lib.r3d_b200_gemm_mxfp4a8_q8x(C.byref(q), x8.data_ptr(), sg.data_ptr(), walk, None)
     assert rc == abi.RAD_OK, abi.STATUS_NAMES[rc]
-    return out.get(), x8.cpu().numpy(), sg.cpu().numpy()
+    y = out.get()
+    assert P.lib.r3d_b200_stream_status() == 0
+    return y, x8.cpu().numpy(), sg.cpu().numpy()
 
 
 def logits_launch(case: dict, arm: int, y_dtype: int = abi.RAD_F32) -> np.ndarray:

@@ -178,6 +178,73 @@ def test_q8x_arm_bit_identical_to_its_chain(walk, M):
     assert np.array_equal(y, orc.gemm_mxfp4_q8x(case["A"], case["AS"], case["B"], case["BS"], walk))
 
 
+@pytest.mark.parametrize("walk", [0, 1])
+@pytest.mark.parametrize("M,N,K", [(1, 203, 512), (2, 128, 1024), (3, 300, 1536), (4, 257, 2560), (5, 77, 3072),
+                                   (7, 640, 5120), (8, 203, 1536), (8, 129, 13824), (4, 64, 8192)])
+def test_q8x_arm_on_the_tensor_core_bit_identical_to_its_chain(walk, M, N, K):
+    # K % 512 == 0 keeps the scale plane's pitch a multiple of 16 bytes: the tcgen05 kernel serves.
+    # 512 leaves two of the lane map's four stage classes empty, 1536 and 3072 fill them unevenly,
+    # 13824 is the down projection (27 scale tiles, the last one half outside the plane).
+    case = gen.case_mxfp4(5100 + M, M, N, K)
+    y, x8, sg = gu.q8x_launch(case, walk, want_tc=True)
+    x8_ref, sg_ref = orc.q8x_requant(case["A"])
+    assert np.array_equal(x8, x8_ref) and np.array_equal(sg.view(np.uint32), sg_ref.view(np.uint32))
+    assert np.array_equal(y, orc.gemm_mxfp4_q8x(case["A"], case["AS"], case["B"], case["BS"], walk))
+
+
+def _groups_covering_every_int8():
+    """e4m3 code groups (max code first, probe code second) whose requantised probe element takes
+    every int8 value a ratio of two e4m3 numbers can round to (100 of 1..127; e.g. 126 is not
+    one): searched over all (max, probe) pairs with the CPU checker."""
+    pairs = [(i, j) for i in range(1, 0x7F) for j in range(1, i + 1)]
+    cand = np.zeros((1, len(pairs) * 32), np.uint8)
+    cand[0, 0::32] = [p[0] for p in pairs]
+    cand[0, 1::32] = [p[1] for p in pairs]
+    x8, _ = orc.q8x_requant(cand)
+    probe = x8[0, 1::32]
+    pick = {}
+    for idx, v in enumerate(probe):
+        if v > 0:
+            pick.setdefault(int(v), pairs[idx])
+    assert len(pick) == 100 and 127 in pick and 1 in pick
+    return [pick[v] for v in sorted(pick)]
+
+
+def test_q8x_arm_on_the_tensor_core_every_int8_value_and_the_largest_dots():
+    # every x8 the requantiser can produce occurs as an activation, against random weight codes and
+    # against +-6; two more groups hold +-448 against +-6 weights: |p| = 32 * 127 * 12, the largest dot
+    M, N, K = 2, 128, 8192
+    case = gen.case_mxfp4(5200, M, N, K)
+    A = np.zeros((M, K), np.uint8)
+    groups = _groups_covering_every_int8()
+    for g, (mx, pr) in enumerate(groups):
+        A[0, 32 * g] = mx; A[0, 32 * g + 1:32 * g + 17] = pr                       # positive probes
+        A[0, 32 * (127 + g)] = mx; A[0, 32 * (127 + g) + 1:32 * (127 + g) + 17] = pr | 0x80
+    A[0, 254 * 32:] = np.array([0x7E, 0xFE] * 32, np.uint8)
+    A[1] = np.roll(A[0], 32)
+    case["A"] = A
+    case["B"][:64, :127 * 16] = 0x77                                                # codes 7: +6
+    case["B"][:8, 254 * 16:] = 0x7F                                                 # +6, -6 alternating
+    x8_ref, _ = orc.q8x_requant(A)
+    assert len(set(np.unique(x8_ref))) >= 2 * len(groups)
+    for walk in (0, 1):
+        y, x8, _ = gu.q8x_launch(case, walk, want_tc=True)
+        assert np.array_equal(x8, x8_ref)
+        assert np.array_equal(y, orc.gemm_mxfp4_q8x(case["A"], case["AS"], case["B"], case["BS"], walk))
+
+
+def test_q8x_arm_on_the_tensor_core_after_a_wider_call():
+    # the digit rows live in one array shared by all calls: what an 8-token call leaves behind must
+    # not reach a 1-token call with other operands, and a shorter K must not see a longer one's rows
+    big = gen.case_mxfp4(5300, 8, 128, 4096)
+    gu.q8x_launch(big, 1, want_tc=True)
+    for M, K in ((1, 512), (2, 2048), (5, 1024)):
+        case = gen.case_mxfp4(5301 + M, M, 130, K)
+        for walk in (0, 1):
+            y, _, _ = gu.q8x_launch(case, walk, want_tc=True)
+            assert np.array_equal(y, orc.gemm_mxfp4_q8x(case["A"], case["AS"], case["B"], case["BS"], walk))
+
+
 def test_q8x_arm_torture_bytes():
     g = np.load(GOLD / "mxfp4a8_torture.npz")
     case = dict(A=g["A"], AS=g["AS"], B=g["B"], BS=g["BS"])
