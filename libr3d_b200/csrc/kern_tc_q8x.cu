@@ -64,9 +64,10 @@ constexpr int kTmemCols = 256;
 constexpr int kMaxStages = 8;
 constexpr int kScTile = kRows * 32;                /* E8M0 bytes of 128 rows x 1024 K */
 
-template <int MT, bool HW>
+/* MT tokens (1, 2, 4, 8; M rounds up), HW digit sum by the tensor core, EW epilogue warp sets (each
+ * set = four warps = the 128 weight rows; the sets share the tokens) */
+template <int MT, bool HW, int EW>
 struct Shape {
-    static constexpr int EW = MT >= 2 ? 2 : 1;                         /* epilogue warp sets */
     static constexpr int TPS = MT / EW;                                /* tokens per set */
     static constexpr int CPT = HW ? 2 : 6;                             /* columns per token per K=64 slab */
     static constexpr int SB = HW ? TPS * 2 : (TPS == 1 ? 8 : (TPS == 2 ? 16 : 24));   /* columns of one set */
@@ -76,15 +77,33 @@ struct Shape {
     static constexpr int kPBytes = (HW ? 48 : NP) * 128;               /* digit tile bytes per stage */
     static constexpr int kStage = kWBytes + kPBytes;
     static constexpr int kThreads = 64 + 128 * EW;
+    static_assert(MT % EW == 0 && TPS >= 1 && TPS <= 4 && EW * SB <= 48, "token split");
 };
 
 /* digit row of (token t, parity, digit j) inside the 48-row digit plane. In every form the
  * parity is the row's lowest bit: a row is only ever written at groups of its own parity, whatever
  * M the calls of a process bring, so its other half stays zero for good. */
-template <int MT, bool HW>
-__host__ __device__ constexpr int digit_row(int t, int par, int j) {
-    using S = Shape<MT, HW>;
-    return HW ? j * 16 + t * 2 + par : (t / S::TPS) * S::SB + (t % S::TPS) * 6 + j * 2 + par;
+__host__ __device__ inline int digit_row(bool hw, int tps, int sb, int t, int par, int j) {
+    return hw ? j * 16 + t * 2 + par : (t / tps) * sb + (t % tps) * 6 + j * 2 + par;
+}
+
+/* two f32 in one 64-bit register pair and the packed arithmetic on them (each half is an IEEE
+ * round-to-nearest f32 operation, the same bits as the scalar instruction): half the issue slots */
+typedef uint64_t f32x2;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) {
+    f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r;
+}
+__device__ __forceinline__ void upk2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r;
 }
 
 struct PQ {
@@ -116,19 +135,19 @@ __device__ __forceinline__ void ld_cols(uint32_t ta, float* v) {
     else tmem_ld<N>(ta, v);
 }
 
-template <int MT, int WALK, bool HW>
-__global__ void __launch_bounds__(Shape<MT, HW>::kThreads, 2)
+template <int MT, int WALK, bool HW, int EW>
+__global__ void __launch_bounds__(Shape<MT, HW, EW>::kThreads, 2)
 k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
          const __grid_constant__ CUtensorMap tmP, const PQ P) {
-    using S = Shape<MT, HW>;
-    constexpr int EW = S::EW, TPS = S::TPS, SB = S::SB, NP = S::NP, UC = S::UC, kBufs = S::kBufs;
+    using S = Shape<MT, HW, EW>;
+    constexpr int TPS = S::TPS, SB = S::SB, NP = S::NP, UC = S::UC, kBufs = S::kBufs;
     static_assert(kSfCols + kBufs * UC <= kTmemCols && kBufs >= 2, "TMEM columns");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int kStages = P.stages;
     const int nk = P.k / kStageK;
-    const int k32 = P.k / 32, n128 = P.k / 128;
+    const int n128 = P.k / 128;
     const int ntile = (nk + 3) / 4;
     uint8_t* sc = smem + kStages * S::kStage;                       /* [ntile][128 rows][32 bytes] */
     uint64_t* full = (uint64_t*)(sc + ntile * kScTile);             /* weights of a stage have landed */
@@ -139,11 +158,15 @@ k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
     uint64_t* sc_full = acc_empty + 4;
     uint64_t* sf_ready = sc_full + 1;
     uint32_t* tmem_slot = (uint32_t*)(sf_ready + 1);
-    float* sg_s = (float*)(tmem_slot + 4);                          /* [MT][k32] */
-    float* as_s = sg_s + MT * k32;                                  /* [MT][n128] */
+    float* rec_s = (float*)(tmem_slot + 4);                         /* [MT][n128] records of 8 floats: SG of the
+                                                                       unit's four groups, AS twice, two unused */
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r0 = blockIdx.x * kRows;
+    /* walk 1 visits the four stage classes in a rotated order, a different start per CTA: classes 2c
+     * and 2c+1 share 256-byte blocks of a weight row, so a class is either all first touches (DRAM)
+     * or all second touches (L2); mixing the phases across CTAs keeps DRAM busy throughout */
+    const int rs = WALK ? (int)(blockIdx.x & 3u) : 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&pfull[s], 1); mbar_init(&empty[s], 1); }
@@ -192,8 +215,8 @@ k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
             int v = 0;
             Ring rg(kStages);
             bool ok = true;
-            for (int r = 0; r < (WALK ? 4 : 1) && ok; ++r) {
-                for (int st = r; st < nk; st += (WALK ? 4 : 1)) {
+            for (int ri = 0; ri < (WALK ? 4 : 1) && ok; ++ri) {
+                for (int st = WALK ? ((rs + ri) & 3) : 0; st < nk; st += (WALK ? 4 : 1)) {
                     if (!mbar_wait(&empty[rg.i], rg.ph ^ 1u, 22)) { ok = false; break; }
                     mbar_expect_tx(&full[rg.i], (uint32_t)kWBytes);
                     tma_load_2d(smem + rg.i * S::kStage, &tmW, st * 128, r0, &full[rg.i]);
@@ -219,8 +242,8 @@ k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
                                    ((uint32_t)(kRows >> 4) << 24);
             Ring rg(kStages), ab(kBufs);
             bool ok = mbar_wait(sf_ready, 0, 23);
-            for (int r = 0; r < (WALK ? 4 : 1) && ok; ++r) {
-                for (int st = r; st < nk && ok; st += (WALK ? 4 : 1)) {
+            for (int ri = 0; ri < (WALK ? 4 : 1) && ok; ++ri) {
+                for (int st = WALK ? ((rs + ri) & 3) : 0; st < nk && ok; st += (WALK ? 4 : 1)) {
                     if (!mbar_wait(&full[rg.i], rg.ph, 25) || !mbar_wait(&pfull[rg.i], rg.ph, 29)) { ok = false; break; }
                     const uint32_t a0 = smem_u32(smem + rg.i * S::kStage), b0 = a0 + kWBytes;
 #pragma unroll
@@ -271,86 +294,130 @@ k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
         /* the requantised activation's scales are the previous kernels' output */
         dep_wait();
         const int et = threadIdx.x - 64;
-        for (int i = et; i < MT * k32; i += 128 * EW) {
-            const int t = i / k32;
-            sg_s[i] = t < P.m ? __ldg(P.sg + i) : 0.0f;
-        }
         for (int i = et; i < MT * n128; i += 128 * EW) {
             const int t = i / n128, c = i - t * n128;
-            as_s[i] = t < P.m ? __ldg(P.as + (int64_t)t * P.as_pitch + c) : 0.0f;
+            float4 sg4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            float as = 0.0f;
+            if (t < P.m) {
+                sg4 = __ldg((const float4*)(P.sg + (int64_t)t * (4 * n128) + 4 * c));
+                as = __ldg(P.as + (int64_t)t * P.as_pitch + c);
+            }
+            *(float4*)(rec_s + 8 * i) = sg4;
+            *(float2*)(rec_s + 8 * i + 4) = make_float2(as, as);
         }
         asm volatile("bar.sync 3, %0;" ::"n"(128 * EW) : "memory");
         alive = mbar_wait(sc_full, 0, 26);
 
-        float acc[TPS], hold[TPS], la[TPS][8], fold[TPS][2];
+        /* Groups travel in pairs (g, g+1) = the two halves of a 64-bit register pair: adjacent
+         * accumulator columns, adjacent SG values, one packed instruction per step of both chains. */
+        float acc[TPS], half[TPS], sub[TPS][4];        /* sub: subtree of the ri-th class visited */
+        f32x2 la[TPS][4];                                /* walk 1: lane sums (8r+2i, 8r+2i+1) of the current class */
 #pragma unroll
-        for (int t = 0; t < TPS; ++t) { acc[t] = 0.0f; hold[t] = 0.0f; fold[t][0] = fold[t][1] = 0.0f; }
+        for (int t = 0; t < TPS; ++t) {
+            acc[t] = 0.0f; half[t] = 0.0f; sub[t][0] = sub[t][1] = sub[t][2] = sub[t][3] = 0.0f;
+#pragma unroll
+            for (int l = 0; l < 4; ++l) la[t][l] = 0ull;
+        }
         const uint8_t* sc_row = sc + (q * 32 + lane) * 32;
         const uint32_t tset = tlane + kSfCols + set * SB;
-        Ring ab(kBufs);
-        for (int r = 0; r < (WALK ? 4 : 1) && alive; ++r) {
-            if (WALK) {
+        const float* rec_t = rec_s + (size_t)(set * TPS) * n128 * 8;
+        const f32x2 k_half = pk2(0.5f, 0.5f), k_four = pk2(4.0f, 4.0f), k_sixteen = pk2(16.0f, 16.0f);
+        /* The walk is a sequence of steps of one 128-of-K unit (two K=64 slabs, four 32-groups), two
+         * per stage. The tensor-memory loads of step i+1 are issued before step i is computed and
+         * waited for after it, so their latency hides behind the float chains; R[i & 1] holds step i. */
+        float R[2][2][SB];
+        Ring ab(kBufs);                                  /* accumulator unit of the step being fetched */
+        auto fetch = [&](float (*dst)[SB]) -> bool {
+            if (!mbar_wait(&acc_full[ab.i], ab.ph, 28)) return false;
+            tc_fence_after();
+            ld_cols<SB>(tset + ab.i * UC, dst[0]);
+            ld_cols<SB>(tset + ab.i * UC + NP, dst[1]);
+            return true;
+        };
+        auto landed = [&](float (*dst)[SB]) {
+            tmem_ld_wait();
+            tmem_pin<SB>(dst[0]);
+            tmem_pin<SB>(dst[1]);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[ab.i]);
+            ab.next();
+        };
+        constexpr int kStep = WALK ? 4 : 1;
+        /* (ri, st): ri-th class visited (class (rs + ri) & 3) and the stage within it; classes
+         * without a stage (K < 1024) are skipped: their lanes hold +0 and so does their subtree */
+        int ri = 0, st = rs;
+        while (WALK && ri < 4 && st >= nk) { ++ri; st = (rs + ri) & 3; }
+        if (ri >= 4) alive = false;                      /* cannot happen: nk >= 1 */
+        if (alive) { alive = fetch(R[0]); if (alive) landed(R[0]); }
+        while (alive) {
+            int nst = st + kStep, nri = ri;
+            if (WALK) while (nst >= nk && nri < 4) { ++nri; nst = (rs + nri) & 3; }
+            const bool has_next = nst < nk && nri < 4;
+            const uint2 sw = *(const uint2*)(sc_row + (st >> 2) * kScTile + (st & 3) * 8);
+            /* bytes 0x00 (2^-127, a subnormal) and 0xFF (NaN) are not "byte << 23": rare, so one test per stage */
+            const uint32_t any = (((sw.x - 0x01010101u) & ~sw.x) | ((sw.y - 0x01010101u) & ~sw.y) |
+                                  ((~sw.x - 0x01010101u) & sw.x) | ((~sw.y - 0x01010101u) & sw.y)) & 0x80808080u;
 #pragma unroll
-                for (int t = 0; t < TPS; ++t)
+            for (int u = 0; u < 2; ++u) {
+                bool fetched = false;
+                if (u == 0 || has_next) { alive = fetch(R[u ^ 1]); fetched = alive; }
+                if (!alive) break;
+                const uint32_t word = u ? sw.y : sw.x;
+                f32x2 sc01, sc23;
+                if (any) {
+                    sc01 = pk2(e8m0_to_f32((uint8_t)word), e8m0_to_f32((uint8_t)(word >> 8)));
+                    sc23 = pk2(e8m0_to_f32((uint8_t)(word >> 16)), e8m0_to_f32((uint8_t)(word >> 24)));
+                } else {
+                    sc01 = pk2(__uint_as_float((word << 23) & 0x7f800000u), __uint_as_float((word << 15) & 0x7f800000u));
+                    sc23 = pk2(__uint_as_float((word << 7) & 0x7f800000u), __uint_as_float((word >> 1) & 0x7f800000u));
+                }
+                const float* rec_u = rec_t + (2 * st + u) * 8;
 #pragma unroll
-                    for (int l = 0; l < 8; ++l) la[t][l] = 0.0f;
-            }
-            for (int st = r; st < nk && alive; st += (WALK ? 4 : 1)) {
-                const uint2 sw = *(const uint2*)(sc_row + (st >> 2) * kScTile + (st & 3) * 8);
+                for (int tl = 0; tl < TPS; ++tl) {
+                    const float* rec = rec_u + (size_t)tl * n128 * 8;
+                    const ulonglong2 sg = *(const ulonglong2*)rec;          /* (SG0, SG1), (SG2, SG3) */
+                    const f32x2 as2 = *(const f32x2*)(rec + 4);              /* (AS, AS) */
+                    f32x2 c[2];
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    if (!mbar_wait(&acc_full[ab.i], ab.ph, 28)) { alive = false; break; }
-                    tc_fence_after();
-                    float d[2][SB];
-                    ld_cols<SB>(tset + ab.i * UC, d[0]);
-                    ld_cols<SB>(tset + ab.i * UC + NP, d[1]);
-                    tmem_ld_wait();
-                    tmem_pin<SB>(d[0]);
-                    tmem_pin<SB>(d[1]);
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[ab.i]);
-                    ab.next();
-                    const uint32_t word = u ? sw.y : sw.x;
-                    float scv[4];
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) scv[g] = e8m0_to_f32((uint8_t)(word >> (8 * g)));
-#pragma unroll
-                    for (int tl = 0; tl < TPS; ++tl) {
-                        const int t = set * TPS + tl;
-                        const float4 sg4 = *(const float4*)(sg_s + t * k32 + 8 * st + 4 * u);
-                        const float sgv[4] = {sg4.x, sg4.y, sg4.z, sg4.w};
-                        const float asv = as_s[t * n128 + 2 * st + u];
-                        float c[4];
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            const float* col = d[g >> 1] + tl * S::CPT + (g & 1);
-                            const float pf = HW ? col[0] : fmaf(col[4], 16.0f, fmaf(col[2], 4.0f, col[0]));
-                            float v = __fmul_rn(pf, sgv[g]);
-                            v = __fmul_rn(v, asv);
-                            v = __fmul_rn(v, scv[g]);
-                            c[g] = __fmul_rn(v, 0.5f);
-                        }
-                        if (WALK == 0) {
-                            const float h = __fadd_rn(__fadd_rn(c[0], c[1]), __fadd_rn(c[2], c[3]));
-                            if (u == 0) hold[tl] = h;
-                            else acc[tl] = __fadd_rn(acc[tl], __fadd_rn(hold[tl], h));
-                        } else {
-#pragma unroll
-                            for (int g = 0; g < 4; ++g) la[tl][4 * u + g] = __fadd_rn(la[tl][4 * u + g], c[g]);
-                        }
+                    for (int h = 0; h < 2; ++h) {                            /* slab h: groups 2h, 2h+1 */
+                        const float* col = R[u][h] + tl * S::CPT;
+                        f32x2 pf = pk2(col[0], col[1]);
+                        if (!HW) pf = fma2(pk2(col[4], col[5]), k_sixteen, fma2(pk2(col[2], col[3]), k_four, pf));
+                        f32x2 v = mul2(pf, h ? sg.y : sg.x);
+                        v = mul2(v, as2);
+                        v = mul2(v, h ? sc23 : sc01);
+                        c[h] = mul2(v, k_half);
+                    }
+                    if (WALK == 0) {
+                        float c0, c1, c2, c3;
+                        upk2(c[0], c0, c1); upk2(c[1], c2, c3);
+                        const float hsum = __fadd_rn(__fadd_rn(c0, c1), __fadd_rn(c2, c3));
+                        if (u == 0) half[tl] = hsum;
+                        else acc[tl] = __fadd_rn(acc[tl], __fadd_rn(half[tl], hsum));
+                    } else {
+                        la[tl][2 * u] = add2(la[tl][2 * u], c[0]);
+                        la[tl][2 * u + 1] = add2(la[tl][2 * u + 1], c[1]);
                     }
                 }
+                if (fetched) landed(R[u ^ 1]);
             }
-            if (WALK) {
+            if (!alive) break;
+            if (WALK && (!has_next || nri != ri)) {
+                /* the class is complete: its eight lanes of the butterfly fold to their subtree */
 #pragma unroll
                 for (int t = 0; t < TPS; ++t) {
-                    const float p = __fadd_rn(__fadd_rn(__fadd_rn(la[t][0], la[t][1]), __fadd_rn(la[t][2], la[t][3])),
-                                              __fadd_rn(__fadd_rn(la[t][4], la[t][5]), __fadd_rn(la[t][6], la[t][7])));
-                    if ((r & 1) == 0) fold[t][r >> 1] = p;
-                    else fold[t][r >> 1] = __fadd_rn(fold[t][r >> 1], p);
+                    float a[8];
+#pragma unroll
+                    for (int l = 0; l < 4; ++l) { upk2(la[t][l], a[2 * l], a[2 * l + 1]); la[t][l] = 0ull; }
+                    const float p = __fadd_rn(__fadd_rn(__fadd_rn(a[0], a[1]), __fadd_rn(a[2], a[3])),
+                                              __fadd_rn(__fadd_rn(a[4], a[5]), __fadd_rn(a[6], a[7])));
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) if (ri == c) sub[t][c] = p;
                 }
             }
+            if (!has_next) break;
+            st = nst; ri = nri;
         }
         const int row = r0 + q * 32 + lane;
         if (alive && row < P.n) {
@@ -358,7 +425,15 @@ k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
             for (int tl = 0; tl < TPS; ++tl) {
                 const int t = set * TPS + tl;
                 if (t >= P.m) break;
-                const float v = WALK ? __fadd_rn(fold[tl][0], fold[tl][1]) : acc[tl];
+                float v = acc[tl];
+                if (WALK) {
+                    /* class c was visited as number (c - rs) & 3: (P0 + P1) + (P2 + P3) */
+                    const float* s4 = sub[tl];
+                    v = rs == 0 ? __fadd_rn(__fadd_rn(s4[0], s4[1]), __fadd_rn(s4[2], s4[3]))
+                      : rs == 1 ? __fadd_rn(__fadd_rn(s4[3], s4[0]), __fadd_rn(s4[1], s4[2]))
+                      : rs == 2 ? __fadd_rn(__fadd_rn(s4[2], s4[3]), __fadd_rn(s4[0], s4[1]))
+                                : __fadd_rn(__fadd_rn(s4[1], s4[2]), __fadd_rn(s4[3], s4[0]));
+                }
                 P.y[(int64_t)t * P.y_pitch + row] = f32_to_bf16(v);
             }
         }
@@ -380,10 +455,10 @@ __device__ __align__(256) uint8_t g_q8x_digits[kDigitRows * kPitch];
  * byte (low nibble = even k) into the digit rows of the group's parity. The rows of the other
  * parity are never written at this group's offset: they stay zero from the array's
  * initialisation, because the row pitch is fixed. */
-template <int MT, bool HW>
 __global__ void __launch_bounds__(256)
 k_q8x_split(const uint8_t* __restrict__ a, int64_t a_pitch, int m, int k,
-            int8_t* __restrict__ x8o, float* __restrict__ sgo, uint8_t* __restrict__ digits) {
+            int8_t* __restrict__ x8o, float* __restrict__ sgo, uint8_t* __restrict__ digits,
+            int hw, int tps, int sb) {
     dep_launch();
     dep_wait();                    /* the activation is the previous kernel's output, and the
                                       previous reader of the digit rows must have finished */
@@ -420,7 +495,7 @@ k_q8x_split(const uint8_t* __restrict__ a, int64_t a_pitch, int m, int k,
         word |= ((v >> (4 * (j < 3 ? j : 0))) & 0xfu) << (4 * i);
     }
     if (lane < 12) {
-        const int row = digit_row<MT, HW>(t, g & 1, j);
+        const int row = digit_row(hw != 0, tps, sb, t, g & 1, j);
         *(uint32_t*)(digits + (int64_t)row * kPitch + g * 16 + w * 4) = word;
     }
 }
@@ -437,19 +512,19 @@ uint8_t* digit_plane() {
     return per_dev[dev];
 }
 
-template <int MT, bool HW>
+template <int MT, bool HW, int EW>
 size_t smem_bytes(int k, int stages) {
     const int nk = k / kStageK;
-    return 1024 + (size_t)stages * Shape<MT, HW>::kStage + (size_t)((nk + 3) / 4) * kScTile +
-           (3 * kMaxStages + 10) * sizeof(uint64_t) + 16 + (size_t)MT * (k / 32 + k / 128) * sizeof(float);
+    return 1024 + (size_t)stages * Shape<MT, HW, EW>::kStage + (size_t)((nk + 3) / 4) * kScTile +
+           (3 * kMaxStages + 10) * sizeof(uint64_t) + 16 + (size_t)MT * (k / 128) * 8 * sizeof(float);
 }
 
 /* the deepest ring (3..6 stages) that lets two CTAs share an SM, else the deepest that fits one */
-template <int MT, bool HW>
+template <int MT, bool HW, int EW>
 int pick_stages(int k) {
     const size_t half = 233472 / 2 - 1024, whole = 227 * 1024;
-    for (int s = 6; s >= 3; --s) if (smem_bytes<MT, HW>(k, s) <= half) return s;
-    for (int s = 6; s >= 3; --s) if (smem_bytes<MT, HW>(k, s) <= whole) return s;
+    for (int s = 6; s >= 3; --s) if (smem_bytes<MT, HW, EW>(k, s) <= half) return s;
+    for (int s = 6; s >= 3; --s) if (smem_bytes<MT, HW, EW>(k, s) <= whole) return s;
     return 0;
 }
 
@@ -464,21 +539,23 @@ cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
     return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
-template <int MT, int WALK, bool HW>
+template <int MT, int WALK, bool HW, int EW>
 int run(const R3dGemmQ& p, int8_t* x8, float* sg, cudaStream_t st) {
-    using S = Shape<MT, HW>;
+    using S = Shape<MT, HW, EW>;
     uint8_t* plane = digit_plane();
     if (!plane) return RAD_E_DEVICE;
-    const int stages = pick_stages<MT, HW>(p.k);
+    int stages = pick_stages<MT, HW, EW>(p.k);
     if (!stages) return RAD_E_UNSUPPORTED;
-    const size_t smem = smem_bytes<MT, HW>(p.k, stages);
+    static const int forced = [] { const char* e = getenv("R3D_Q8X_STAGES"); return e ? atoi(e) : 0; }();
+    if (forced >= 3 && forced <= 6 && smem_bytes<MT, HW, EW>(p.k, forced) <= 227 * 1024) stages = forced;
+    const size_t smem = smem_bytes<MT, HW, EW>(p.k, stages);
     static size_t attr_set[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return RAD_E_DEVICE;
     if (smem > attr_set[dev]) {
-        if (cudaFuncSetAttribute(k_tc_q8x<MT, WALK, HW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(k_tc_q8x<MT, WALK, HW, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) return RAD_E_DEVICE;
-        (void)cudaFuncSetAttribute(k_tc_q8x<MT, WALK, HW>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        (void)cudaFuncSetAttribute(k_tc_q8x<MT, WALK, HW, EW>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                    (int)cudaSharedmemCarveoutMaxShared);
         attr_set[dev] = smem;
     }
@@ -492,31 +569,34 @@ int run(const R3dGemmQ& p, int8_t* x8, float* sg, cudaStream_t st) {
 
     count_launch();
     const unsigned sgrid = (unsigned)(((int64_t)p.m * (p.k >> 5) + 7) / 8);
-    if (launch_pdl(k_q8x_split<MT, HW>, dim3(sgrid), dim3(256), 0, st, (const uint8_t*)p.a, (int64_t)p.a_pitch,
-                   (int)p.m, (int)p.k, x8, sg, plane) != cudaSuccess) return RAD_E_DEVICE;
+    if (launch_pdl(k_q8x_split, dim3(sgrid), dim3(256), 0, st, (const uint8_t*)p.a, (int64_t)p.a_pitch,
+                   (int)p.m, (int)p.k, x8, sg, plane, (int)HW, (int)S::TPS, (int)S::SB) != cudaSuccess) return RAD_E_DEVICE;
     PQ P{};
     P.as = p.a_scale; P.as_pitch = p.as_pitch; P.sg = sg;
     P.y = (uint16_t*)p.y; P.y_pitch = p.y_pitch;
     P.m = p.m; P.n = p.n; P.k = p.k; P.stages = stages;
     const int tiles = (p.n + kRows - 1) / kRows;
     count_launch();
-    const cudaError_t e = launch_pdl(k_tc_q8x<MT, WALK, HW>, dim3((unsigned)tiles), dim3(S::kThreads), smem, st,
+    const cudaError_t e = launch_pdl(k_tc_q8x<MT, WALK, HW, EW>, dim3((unsigned)tiles), dim3(S::kThreads), smem, st,
                                      *tw, *ts, *tp, P);
     return e == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
 }
 
-template <int MT>
-int run_mt(const R3dGemmQ& p, int8_t* x8, float* sg, int walk, bool hw, cudaStream_t st) {
-    if (hw) return walk ? run<MT, 1, true>(p, x8, sg, st) : run<MT, 0, true>(p, x8, sg, st);
-    return walk ? run<MT, 1, false>(p, x8, sg, st) : run<MT, 0, false>(p, x8, sg, st);
+int env_int(const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; }
+
+/* form per token count: digit sum by the tensor core (HW) and epilogue warp sets (EW); the
+ * R3D_Q8X_HWSUM / R3D_Q8X_EW levers override the measured defaults */
+template <int MT, int EW_A, int EW_B>
+int run_mt(const R3dGemmQ& p, int8_t* x8, float* sg, int walk, bool hw, int ew, cudaStream_t st) {
+    if (ew == EW_B && EW_B != EW_A) {
+        if (hw) return walk ? run<MT, 1, true, EW_B>(p, x8, sg, st) : run<MT, 0, true, EW_B>(p, x8, sg, st);
+        return walk ? run<MT, 1, false, EW_B>(p, x8, sg, st) : run<MT, 0, false, EW_B>(p, x8, sg, st);
+    }
+    if (hw) return walk ? run<MT, 1, true, EW_A>(p, x8, sg, st) : run<MT, 0, true, EW_A>(p, x8, sg, st);
+    return walk ? run<MT, 1, false, EW_A>(p, x8, sg, st) : run<MT, 0, false, EW_A>(p, x8, sg, st);
 }
 
 bool al(const void* p, int a) { return (((uintptr_t)p) & (uintptr_t)(a - 1)) == 0; }
-
-bool hw_sum() {
-    static const bool on = [] { const char* e = getenv("R3D_Q8X_HWSUM"); return e && *e && *e != '0'; }();
-    return on;
-}
 
 } /* anonymous namespace */
 
@@ -526,17 +606,19 @@ bool tc_q8x_ok(const R3dGemmQ& p) {
     if (!(p.m >= 1 && p.m <= kMaxTok && p.k >= 256 && (p.k % 256) == 0 && p.k <= kMaxK && p.as_cols == p.k / 128 &&
           al(p.b, 16) && (p.b_pitch % 16) == 0 && al(p.b_scale, 16) && (p.bs_pitch % 16) == 0 &&
           p.bs_cols == p.k / 32 && tc_have_encoder())) return false;
-    return (hw_sum() ? pick_stages<8, true>(p.k) : pick_stages<8, false>(p.k)) != 0;
+    return pick_stages<8, true, 2>(p.k) != 0 && pick_stages<8, false, 2>(p.k) != 0;
 }
 
 /* Two launches: the split (requantisation + digit rows; the digit plane is a file-scope device
  * array, so calls on one device must be ordered on one stream), then the weight-streaming kernel. */
 int tc_q8x(const R3dGemmQ& p, int8_t* x8, float* sg, int walk, cudaStream_t st) {
-    const bool hw = hw_sum();
-    if (p.m == 1) return run_mt<1>(p, x8, sg, walk, hw, st);
-    if (p.m == 2) return run_mt<2>(p, x8, sg, walk, hw, st);
-    if (p.m <= 4) return run_mt<4>(p, x8, sg, walk, hw, st);
-    return run_mt<8>(p, x8, sg, walk, hw, st);
+    static const int hw_env = env_int("R3D_Q8X_HWSUM", -1), ew_env = env_int("R3D_Q8X_EW", 0);
+    const int mt = p.m == 1 ? 1 : (p.m == 2 ? 2 : (p.m <= 4 ? 4 : 8));
+    const bool hw = hw_env >= 0 ? hw_env != 0 : false;
+    if (mt == 1) return run_mt<1, 1, 1>(p, x8, sg, walk, hw, 1, st);
+    if (mt == 2) return run_mt<2, 1, 2>(p, x8, sg, walk, hw, ew_env ? ew_env : 1, st);
+    if (mt == 4) return run_mt<4, 1, 2>(p, x8, sg, walk, hw, ew_env ? ew_env : 1, st);
+    return walk ? run<8, 1, true, 2>(p, x8, sg, st) : run<8, 0, true, 2>(p, x8, sg, st);
 }
 
 int tc_q8x_status() {
