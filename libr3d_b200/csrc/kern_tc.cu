@@ -29,6 +29,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <unordered_map>
 #include <vector>
 #define R3D_TC_STATUS_WORD ::r3d::g_tc_status
 namespace r3d { __device__ int g_tc_status = 0; }   /* nonzero = code of the bounded wait that expired */
@@ -353,35 +354,56 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-struct MapKey { const void* ptr; uint64_t d0, d1, pitch; int dtype; uint32_t box1, box0; };
-struct MapEnt { MapKey k; CUtensorMap m; };
+struct MapKey {
+    const void* ptr; uint64_t d0, d1, pitch; int dtype; uint32_t box1, box0; int dev, promo;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && pitch == o.pitch && dtype == o.dtype &&
+               box1 == o.box1 && box0 == o.box0 && dev == o.dev && promo == o.promo;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        uint64_t h = (uint64_t)(uintptr_t)k.ptr * 0x9E3779B97F4A7C15ull;
+        h ^= (k.d0 + 0x632BE59BD9B4E019ull) * 0xD6E8FEB86659FD93ull;
+        h ^= (k.d1 * 0xFF51AFD7ED558CCDull) ^ (k.pitch << 17) ^ ((uint64_t)k.box1 << 40) ^ ((uint64_t)k.box0 << 52) ^
+             ((uint64_t)k.dtype << 8) ^ ((uint64_t)k.dev << 3) ^ (uint64_t)k.promo;
+        return (size_t)(h ^ (h >> 29));
+    }
+};
 
-/* Tensor maps are remembered per (pointer, geometry): the engine's buffers are long-lived and
- * a launch must not do driver work in steady state. Single dispatch thread, like the
- * reference's plane cache (src/r3d_gemm_mxfp4.hip:1879-1880). */
+/* Tensor maps are remembered per (device, pointer, geometry): the engine's buffers are long-lived and
+ * a launch must not do driver work in steady state. Single dispatch thread, like the reference's
+ * plane cache (src/r3d_gemm_mxfp4.hip:1879-1880). A lookup hands out a copy in a small ring, so the
+ * maps of one launch (at most four lookups) stay valid whatever the table does in between; when the
+ * table is full (activation buffers that keep moving) it is emptied and refills with what is live. */
 const CUtensorMap* tensor_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_t pitch_bytes,
-                              CUtensorMapDataType dt, uint32_t box1, uint32_t box0 = 128u) {
-    static std::vector<MapEnt*> cache;
-    for (const MapEnt* e : cache)
-        if (e->k.ptr == ptr && e->k.d0 == d0 && e->k.d1 == d1 && e->k.pitch == pitch_bytes &&
-            e->k.dtype == (int)dt && e->k.box1 == box1 && e->k.box0 == box0)
-            return &e->m;
+                              CUtensorMapDataType dt, uint32_t box1, uint32_t box0 = 128u, int promo128 = 0) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static CUtensorMap ring[16];
+    static unsigned ring_at = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    const MapKey key{ptr, d0, d1, pitch_bytes, (int)dt, box1, box0, dev, promo128};
+    CUtensorMap* slot = &ring[ring_at++ & 15u];
+    auto it = cache.find(key);
+    if (it != cache.end()) { *slot = it->second; return slot; }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return nullptr;
-    MapEnt* e = new MapEnt;
-    e->k = MapKey{ptr, d0, d1, pitch_bytes, (int)dt, box1, box0};
     const cuuint64_t dims[2] = {d0, d1};
     const cuuint64_t strides[1] = {pitch_bytes};
     const cuuint32_t box[2] = {box0, box1};
     const cuuint32_t estr[2] = {1u, 1u};
-    const CUresult rc = fn(&e->m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+    CUtensorMap m;
+    const CUresult rc = fn(&m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE,
                            box0 == 128u ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (rc != CUDA_SUCCESS) { delete e; return nullptr; }
-    if (cache.size() >= 4096) { delete cache.front(); cache.erase(cache.begin()); }
-    cache.push_back(e);
-    return &e->m;
+                           promo128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return nullptr;
+    if (cache.size() >= 16384) cache.clear();
+    cache.emplace(key, m);
+    *slot = m;
+    return slot;
 }
 
 int sm_count();
@@ -392,7 +414,10 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
                         (3 * kTcStages + 8) * sizeof(uint64_t) + 16 +
                         (size_t)(P.k / kStageK) * NTOK * sizeof(float);
     if (smem > 220 * 1024) return RAD_E_UNSUPPORTED;
-    static size_t attr_set = 0;
+    static size_t attr_set_dev[kTcMaxDevices] = {};
+    const int adev = tc_device();
+    if (adev < 0) return RAD_E_DEVICE;
+    size_t& attr_set = attr_set_dev[adev];
     if (smem > attr_set) {
         if (cudaFuncSetAttribute(k_tc_decode<FMT, NTOK, ML, kTcStages, LG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) return RAD_E_DEVICE;
@@ -445,12 +470,15 @@ int launch_tc(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaStre
 }
 
 int sm_count() {
-    static int n = [] {
-        int dev = 0, v = 148;
-        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-        return v > 0 ? v : 148;
-    }();
-    return n;
+    static int per_dev[kTcMaxDevices] = {};
+    const int dev = tc_device();
+    if (dev < 0) return 148;
+    if (!per_dev[dev]) {
+        int v = 148;
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        per_dev[dev] = v > 0 ? v : 148;
+    }
+    return per_dev[dev];
 }
 
 
@@ -669,8 +697,13 @@ int tc_logits(const R3dLogits& l, cudaStream_t st, const PushCfg* push) {
 }
 
 const CUtensorMap* tc_tensor_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_t pitch_bytes,
-                                 CUtensorMapDataType dt, uint32_t box1, uint32_t box0) {
-    return tensor_map(ptr, d0, d1, pitch_bytes, dt, box1, box0);
+                                 CUtensorMapDataType dt, uint32_t box1, uint32_t box0, int promo128) {
+    return tensor_map(ptr, d0, d1, pitch_bytes, dt, box1, box0, promo128);
+}
+int tc_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kTcMaxDevices) return -1;
+    return dev;
 }
 bool tc_have_encoder() { return encode_fn() != nullptr; }
 int tc_sm_count() { return sm_count(); }

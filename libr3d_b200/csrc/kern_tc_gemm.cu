@@ -334,11 +334,13 @@ template <int FMT>
 int launch(const CUtensorMap* tw, const CUtensorMap* ta, const CUtensorMap* ts, PG P, cudaStream_t st) {
     const size_t smem = 1024 + (size_t)kStages * kStage + kScTiles * kScBytes + kFs * kTok * sizeof(float) +
                         (2 * kStages + 4 + kSfSlots + 2 * kScTiles + 2 * kFs) * sizeof(uint64_t) + 64;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[kTcMaxDevices] = {};
+    const int adev = tc_device();
+    if (adev < 0) return RAD_E_DEVICE;
+    if (!attr_set[adev]) {
         if (cudaFuncSetAttribute(k_tc_gemm<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return RAD_E_DEVICE;
-        attr_set = true;
+        attr_set[adev] = true;
     }
     const int wtiles = (P.n + kRows - 1) / kRows;
     P.tok_tiles = (P.m + kTok - 1) / kTok;

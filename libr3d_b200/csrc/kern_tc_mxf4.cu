@@ -473,7 +473,10 @@ template <int NP, int MT, int kStages, bool SR>
 int launch_s(const CUtensorMap* tw, const CUtensorMap* ts, const CUtensorMap* tp, const P4& P, cudaStream_t st) {
     const size_t smem = smem_fixed<kStages>() + (size_t)kStages * (kWBytes + NP * 128) +
                         (size_t)(P.k / 128) * MT * sizeof(float);
-    static size_t attr_set = 0;
+    static size_t attr_set_dev[kTcMaxDevices] = {};
+    const int adev = tc_device();
+    if (adev < 0) return RAD_E_DEVICE;
+    size_t& attr_set = attr_set_dev[adev];
     if (smem > attr_set) {
         if (cudaFuncSetAttribute(k_tc_mxf4<NP, MT, kStages, SR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) return RAD_E_DEVICE;

@@ -21,21 +21,26 @@
  * float chain at its own place) and 2^2 for the digits, so an accumulator column holds
  * sum (w8/2) * (digit/2) * 4 = sum w8 * digit exactly (small integers in f32). Two forms:
  *   HW = false  digit rows are separate MMA columns; the epilogue forms p = D0 + 4 D1 + 16 D2
+ *               (up to four tokens)
  *   HW = true   three MMAs accumulate into one column with digit scales 2^2, 2^4, 2^6: the
- *               column holds p itself
+ *               column holds p itself (eight tokens: fewer columns, fewer registers)
+ * Both were checked bit for bit against the CPU checker on the full 27648 x 5120 plane, on the
+ * largest dots there are (|p| = 32 * 127 * 12) and on every int8 value the requantiser can produce.
  * Every accumulator is fresh per 64 of K (no accumulation across groups), the epilogue thread of
- * a weight row reads its columns from tensor memory and runs the float chain above in the
- * reference's order. For walk 1 the K stages are visited class by class (stage index mod 4 =
- * lane index / 8), so that only eight lane sums per token are live at a time: class r finishes
- * lanes 8r..8r+7, their subtree ((a0+a1)+(a2+a3))+((a4+a5)+(a6+a7)) is final and the four
- * subtrees fold as (P0+P1)+(P2+P3) -- the butterfly's tree.
+ * a weight row reads its columns from tensor memory one 128-of-K unit ahead of the unit it is
+ * computing, and runs the float chain above in the reference's order, two groups per packed
+ * f32x2 instruction (each half an IEEE f32 operation). For walk 1 the K stages are visited class by
+ * class (stage index mod 4 = lane index / 8), so that only eight lane sums per token are live at
+ * a time: class r finishes lanes 8r..8r+7, their subtree ((a0+a1)+(a2+a3))+((a4+a5)+(a6+a7)) is
+ * final and the four subtrees fold as (P0+P1)+(P2+P3) -- the butterfly's tree. The class order is
+ * rotated per CTA (the subtrees are independent).
  *
  * Data path: weights by TMA (plain byte tensor map, 128-byte row segments, 256 K per stage), all
  * E8M0 bytes of the CTA's 128 rows resident in shared memory (one TMA tile per 1024 K), digit
  * rows by TMA from a file-scope device array a small split kernel fills once per call (it also
  * writes x8 and SG into the caller's scratch, the arm's contract). Warp 0 TMA producer, warp 1 MMA
- * issuer and TMEM owner, warps 2.. epilogue (thread = weight row; two warp sets share the
- * tokens from M = 2). Programmatic dependent launch: weights and their scales are requested
+ * issuer and TMEM owner, warps 2.. epilogue (thread = weight row; at eight tokens two warp sets
+ * share the tokens). Programmatic dependent launch: weights and their scales are requested
  * before griddepcontrol.wait, everything the previous kernel may have written after it. Every
  * wait is bounded; on expiry a status word is set and the CTA drains, frees its TMEM and leaves
  * without storing.
@@ -324,24 +329,41 @@ k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
         const f32x2 k_half = pk2(0.5f, 0.5f), k_four = pk2(4.0f, 4.0f), k_sixteen = pk2(16.0f, 16.0f);
         /* The walk is a sequence of steps of one 128-of-K unit (two K=64 slabs, four 32-groups), two
          * per stage. The tensor-memory loads of step i+1 are issued before step i is computed and
-         * waited for after it, so their latency hides behind the float chains; R[i & 1] holds step i. */
-        float R[2][2][SB];
+         * waited for after it, so their latency hides behind the float chains. What a step keeps of
+         * its loads is the integer dot of every (token, group) as a float, two groups per register
+         * pair: PF; the raw columns (three digit columns per dot when the digits are summed here) are
+         * live only while the load is in flight. */
+        float raw[2][SB];
+        f32x2 PF[TPS][2];
         Ring ab(kBufs);                                  /* accumulator unit of the step being fetched */
-        auto fetch = [&](float (*dst)[SB]) -> bool {
+        auto fetch = [&]() -> bool {
             if (!mbar_wait(&acc_full[ab.i], ab.ph, 28)) return false;
             tc_fence_after();
-            ld_cols<SB>(tset + ab.i * UC, dst[0]);
-            ld_cols<SB>(tset + ab.i * UC + NP, dst[1]);
+            ld_cols<SB>(tset + ab.i * UC, raw[0]);
+            ld_cols<SB>(tset + ab.i * UC + NP, raw[1]);
             return true;
         };
-        auto landed = [&](float (*dst)[SB]) {
+        auto landed = [&]() {
             tmem_ld_wait();
-            tmem_pin<SB>(dst[0]);
-            tmem_pin<SB>(dst[1]);
+            tmem_pin<SB>(raw[0]);
+            tmem_pin<SB>(raw[1]);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[ab.i]);
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "setp.eq.u32 p, %1, 0;\n\t"
+                "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}"
+                ::"r"(smem_u32(&acc_empty[ab.i])), "r"((uint32_t)lane) : "memory");
             ab.next();
+#pragma unroll
+            for (int tl = 0; tl < TPS; ++tl)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float* col = raw[h] + tl * S::CPT;
+                    f32x2 pf = pk2(col[0], col[1]);
+                    if (!HW) pf = fma2(pk2(col[4], col[5]), k_sixteen, fma2(pk2(col[2], col[3]), k_four, pf));
+                    PF[tl][h] = pf;
+                }
         };
         constexpr int kStep = WALK ? 4 : 1;
         /* (ri, st): ri-th class visited (class (rs + ri) & 3) and the stage within it; classes
@@ -349,7 +371,7 @@ k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
         int ri = 0, st = rs;
         while (WALK && ri < 4 && st >= nk) { ++ri; st = (rs + ri) & 3; }
         if (ri >= 4) alive = false;                      /* cannot happen: nk >= 1 */
-        if (alive) { alive = fetch(R[0]); if (alive) landed(R[0]); }
+        if (alive) { alive = fetch(); if (alive) landed(); }
         while (alive) {
             int nst = st + kStep, nri = ri;
             if (WALK) while (nst >= nk && nri < 4) { ++nri; nst = (rs + nri) & 3; }
@@ -361,7 +383,7 @@ k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
                 bool fetched = false;
-                if (u == 0 || has_next) { alive = fetch(R[u ^ 1]); fetched = alive; }
+                if (u == 0 || has_next) { alive = fetch(); fetched = alive; }
                 if (!alive) break;
                 const uint32_t word = u ? sw.y : sw.x;
                 f32x2 sc01, sc23;
@@ -381,10 +403,7 @@ k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
                     f32x2 c[2];
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {                            /* slab h: groups 2h, 2h+1 */
-                        const float* col = R[u][h] + tl * S::CPT;
-                        f32x2 pf = pk2(col[0], col[1]);
-                        if (!HW) pf = fma2(pk2(col[4], col[5]), k_sixteen, fma2(pk2(col[2], col[3]), k_four, pf));
-                        f32x2 v = mul2(pf, h ? sg.y : sg.x);
+                        f32x2 v = mul2(PF[tl][h], h ? sg.y : sg.x);
                         v = mul2(v, as2);
                         v = mul2(v, h ? sc23 : sc01);
                         c[h] = mul2(v, k_half);
@@ -400,7 +419,7 @@ k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
                         la[tl][2 * u + 1] = add2(la[tl][2 * u + 1], c[1]);
                     }
                 }
-                if (fetched) landed(R[u ^ 1]);
+                if (fetched) landed();
             }
             if (!alive) break;
             if (WALK && (!has_next || nri != ri)) {
@@ -544,14 +563,12 @@ int run(const R3dGemmQ& p, int8_t* x8, float* sg, cudaStream_t st) {
     using S = Shape<MT, HW, EW>;
     uint8_t* plane = digit_plane();
     if (!plane) return RAD_E_DEVICE;
-    int stages = pick_stages<MT, HW, EW>(p.k);
+    const int stages = pick_stages<MT, HW, EW>(p.k);
     if (!stages) return RAD_E_UNSUPPORTED;
-    static const int forced = [] { const char* e = getenv("R3D_Q8X_STAGES"); return e ? atoi(e) : 0; }();
-    if (forced >= 3 && forced <= 6 && smem_bytes<MT, HW, EW>(p.k, forced) <= 227 * 1024) stages = forced;
     const size_t smem = smem_bytes<MT, HW, EW>(p.k, stages);
-    static size_t attr_set[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return RAD_E_DEVICE;
+    static size_t attr_set[kTcMaxDevices] = {};
+    const int dev = tc_device();
+    if (dev < 0) return RAD_E_DEVICE;
     if (smem > attr_set[dev]) {
         if (cudaFuncSetAttribute(k_tc_q8x<MT, WALK, HW, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) return RAD_E_DEVICE;
@@ -559,8 +576,10 @@ int run(const R3dGemmQ& p, int8_t* x8, float* sg, cudaStream_t st) {
                                    (int)cudaSharedmemCarveoutMaxShared);
         attr_set[dev] = smem;
     }
+    /* walk 1 touches the two 128-byte halves of a 256-byte block of a weight row a quarter of the kernel
+     * apart: its weight map promotes L2 fills to 128 bytes, not 256 (measured: 17.6 -> 16.5 us at M = 1) */
     const CUtensorMap* tw = tc_tensor_map(p.b, (uint64_t)(p.k / 2), (uint64_t)p.n, (uint64_t)p.b_pitch,
-                                          CU_TENSOR_MAP_DATA_TYPE_UINT8, kRows);
+                                          CU_TENSOR_MAP_DATA_TYPE_UINT8, kRows, 128u, WALK ? 1 : 0);
     const CUtensorMap* ts = tc_tensor_map(p.b_scale, (uint64_t)(p.k / 32), (uint64_t)p.n, (uint64_t)p.bs_pitch,
                                           CU_TENSOR_MAP_DATA_TYPE_UINT8, kRows, 32u);
     const CUtensorMap* tp = tc_tensor_map(plane, (uint64_t)(p.k / 2), (uint64_t)kDigitRows, (uint64_t)kPitch,
@@ -582,20 +601,6 @@ int run(const R3dGemmQ& p, int8_t* x8, float* sg, cudaStream_t st) {
     return e == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
 }
 
-int env_int(const char* name, int dflt) { const char* e = getenv(name); return e && *e ? atoi(e) : dflt; }
-
-/* form per token count: digit sum by the tensor core (HW) and epilogue warp sets (EW); the
- * R3D_Q8X_HWSUM / R3D_Q8X_EW levers override the measured defaults */
-template <int MT, int EW_A, int EW_B>
-int run_mt(const R3dGemmQ& p, int8_t* x8, float* sg, int walk, bool hw, int ew, cudaStream_t st) {
-    if (ew == EW_B && EW_B != EW_A) {
-        if (hw) return walk ? run<MT, 1, true, EW_B>(p, x8, sg, st) : run<MT, 0, true, EW_B>(p, x8, sg, st);
-        return walk ? run<MT, 1, false, EW_B>(p, x8, sg, st) : run<MT, 0, false, EW_B>(p, x8, sg, st);
-    }
-    if (hw) return walk ? run<MT, 1, true, EW_A>(p, x8, sg, st) : run<MT, 0, true, EW_A>(p, x8, sg, st);
-    return walk ? run<MT, 1, false, EW_A>(p, x8, sg, st) : run<MT, 0, false, EW_A>(p, x8, sg, st);
-}
-
 bool al(const void* p, int a) { return (((uintptr_t)p) & (uintptr_t)(a - 1)) == 0; }
 
 } /* anonymous namespace */
@@ -606,18 +611,18 @@ bool tc_q8x_ok(const R3dGemmQ& p) {
     if (!(p.m >= 1 && p.m <= kMaxTok && p.k >= 256 && (p.k % 256) == 0 && p.k <= kMaxK && p.as_cols == p.k / 128 &&
           al(p.b, 16) && (p.b_pitch % 16) == 0 && al(p.b_scale, 16) && (p.bs_pitch % 16) == 0 &&
           p.bs_cols == p.k / 32 && tc_have_encoder())) return false;
-    return pick_stages<8, true, 2>(p.k) != 0 && pick_stages<8, false, 2>(p.k) != 0;
+    return pick_stages<8, true, 2>(p.k) != 0 && pick_stages<4, false, 1>(p.k) != 0;
 }
 
 /* Two launches: the split (requantisation + digit rows; the digit plane is a file-scope device
- * array, so calls on one device must be ordered on one stream), then the weight-streaming kernel. */
+ * array, so calls on one device must be ordered on one stream), then the weight-streaming kernel.
+ * Forms (measured on 27648 x 5120): up to four tokens the epilogue sums the digit columns itself and
+ * one warp set serves all tokens (two sets, or the tensor core summing the digits with three times
+ * the MMAs, were 1 to 6 us slower); eight tokens need the tensor core's sum to fit the registers. */
 int tc_q8x(const R3dGemmQ& p, int8_t* x8, float* sg, int walk, cudaStream_t st) {
-    static const int hw_env = env_int("R3D_Q8X_HWSUM", -1), ew_env = env_int("R3D_Q8X_EW", 0);
-    const int mt = p.m == 1 ? 1 : (p.m == 2 ? 2 : (p.m <= 4 ? 4 : 8));
-    const bool hw = hw_env >= 0 ? hw_env != 0 : false;
-    if (mt == 1) return run_mt<1, 1, 1>(p, x8, sg, walk, hw, 1, st);
-    if (mt == 2) return run_mt<2, 1, 2>(p, x8, sg, walk, hw, ew_env ? ew_env : 1, st);
-    if (mt == 4) return run_mt<4, 1, 2>(p, x8, sg, walk, hw, ew_env ? ew_env : 1, st);
+    if (p.m == 1) return walk ? run<1, 1, false, 1>(p, x8, sg, st) : run<1, 0, false, 1>(p, x8, sg, st);
+    if (p.m == 2) return walk ? run<2, 1, false, 1>(p, x8, sg, st) : run<2, 0, false, 1>(p, x8, sg, st);
+    if (p.m <= 4) return walk ? run<4, 1, false, 1>(p, x8, sg, st) : run<4, 0, false, 1>(p, x8, sg, st);
     return walk ? run<8, 1, true, 2>(p, x8, sg, st) : run<8, 0, true, 2>(p, x8, sg, st);
 }
 

@@ -14,25 +14,33 @@ namespace r3d {
 static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
-/* The kernels are compiled for sm_100a only. Checked once per process (the reference's
- * chip gate: src/r3d_gemm_fp8a8.hip:903-913). */
+/* The kernels are compiled for sm_100a only. Checked once per device (the reference's chip gate:
+ * src/r3d_gemm_fp8a8.hip:903-913); one process may drive several GPUs. */
 bool device_is_sm100() {
-    static int ok = -1;
-    if (ok < 0) {
-        int dev = 0;
-        cudaDeviceProp pr{};
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaGetDeviceProperties(&pr, dev) != cudaSuccess) {
-            fprintf(stderr, "libr3d_b200: no usable CUDA device -- every row refuses\n");
-            ok = 0;
+    static signed char ok[64] = {};                       /* 0 unknown, 1 yes, -1 no */
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        static bool said = false;
+        if (!said) fprintf(stderr, "libr3d_b200: no usable CUDA device -- every row refuses\n");
+        said = true;
+        (void)cudaGetLastError();
+        return false;
+    }
+    if (!ok[dev]) {
+        int major = 0, minor = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess) {
+            fprintf(stderr, "libr3d_b200: device %d cannot be queried -- every row refuses\n", dev);
+            (void)cudaGetLastError();
+            ok[dev] = -1;
         } else {
-            ok = (pr.major == 10) ? 1 : 0;
-            if (!ok)
-                fprintf(stderr, "libr3d_b200: device '%s' is sm_%d%d; this library holds sm_100a "
-                                "code only -- every row refuses\n", pr.name, pr.major, pr.minor);
+            ok[dev] = major == 10 ? 1 : -1;
+            if (major != 10)
+                fprintf(stderr, "libr3d_b200: device %d is sm_%d%d; this library holds sm_100a code only -- "
+                                "every row refuses\n", dev, major, minor);
         }
     }
-    return ok == 1;
+    return ok[dev] == 1;
 }
 
 static void debug_arm(const char* band, const char* arm, int m) {

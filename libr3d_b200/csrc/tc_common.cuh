@@ -216,7 +216,11 @@ bool tc_pdl_on();
 /* host side (kern_tc.cu): cached 2-D tensor maps, box = box0 x box1 elements; an inner box of 128
  * elements gets the 128-byte swizzle, any other none */
 const CUtensorMap* tc_tensor_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_t pitch_bytes,
-                                 CUtensorMapDataType dt, uint32_t box1, uint32_t box0 = 128u);
+                                 CUtensorMapDataType dt, uint32_t box1, uint32_t box0 = 128u, int promo128 = 0);
+/* the current device's ordinal, or -1 (no device, or beyond kTcMaxDevices): function attributes and
+ * device properties are remembered per device, one process may drive several GPUs */
+constexpr int kTcMaxDevices = 64;
+int  tc_device();
 bool tc_have_encoder();
 int  tc_sm_count();
 
