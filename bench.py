@@ -23,8 +23,15 @@ the kernel (--gather nccl); time = max over ranks.
 --workload c5: the column-sharded LM head (strong scaling). --workload all [--cfg C1,..,C5]: every
 configuration of the hot path on one GPU, one line each.
 
+The line also carries `per_M` (each M timed alone), `spread` (the K-step region is timed five
+times, the median is the value), `rows` (the band's other decode row on the same planes: the
+int8-per-32 row the resolver picks by default), `rot_sweep` (2 / 4 / 8 rotating planes) and `c5`
+(the sharded LM head, strong scaling, bf16 logits).
+
 --impl reference: the reference's arithmetic for this path on the host cores (the CPU
-restatement: the reference's kernels are HIP and cannot build here), same metric and config.
+restatement, all cores; the reference has no CPU implementation of this path), same metric and
+config; `reference_gpu` adds the reference's own kernels, compiled for sm_100a from where they lie
+(oracle/_ref/libref_mxfp4.so), timed on the same GPU.
 """
 from __future__ import annotations
 
@@ -98,6 +105,7 @@ def cpu_step_sample(rows: int, reps: int):
     import gen
     from oracle import oracle as orc
     cases = [gen.case_mxfp4(100 + m, m, rows, K_DIM) for m in MS]
+    orc.lib().orc_set_threads(os.cpu_count() or 1)      # a launcher may have exported OMP_NUM_THREADS=1
     orc.gemm_mxfp4a8(**cases[0])
     t0 = time.perf_counter()
     for _ in range(reps):
@@ -116,6 +124,8 @@ def run_reference(args):
     import gen
     from oracle import oracle as orc
     cases = [gen.case_mxfp4(100 + m, m, rows, K_DIM) for m in MS]
+    # rank 0 alone runs this arm, on all host cores (torch.distributed.run exports OMP_NUM_THREADS=1)
+    orc.lib().orc_set_threads(os.cpu_count() or 1)
     for _ in range(max(args.warmup, 1)):
         for c in cases:
             orc.gemm_mxfp4a8(**c)
@@ -134,7 +144,8 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "C2 mxfp4a8 decode GEMV, M in {1,2,4}, K=5120, N=27648", "sample": sample},
+        "config": {"workload": "C2 mxfp4a8 decode GEMV, M in {1,2,4}, K=5120, N=27648 per GPU", "sample": sample,
+                   "host_threads": threads},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "reference_gpu": ref_gpu,
@@ -502,15 +513,131 @@ def run_all(args):
                       "status": int(P.lib.r3d_b200_stream_status()), "results": out}))
 
 
+def _peak():
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        peaks = json.loads(pk.read_text())
+        if "hbm_gbs" in peaks:
+            return float(peaks["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def _record(fn, n: int):
+    """Record n calls of fn(i) once (a CUDA graph: the engine's recorded pass) and return the graph."""
+    import torch
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            for i in range(n):
+                fn(i)
+    torch.cuda.current_stream().wait_stream(s)
+    return graph
+
+
+def _timed(run, regions: int, fence):
+    """`regions` device-timed repetitions of run(); returns the list of milliseconds."""
+    import torch
+    out = []
+    for _ in range(regions):
+        fence()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run()
+        e1.record()
+        fence()
+        out.append(e0.elapsed_time(e1))
+    return out
+
+
+def c5_record(args, P, dev, world: int, rank: int, peak: float):
+    """The sharded LM head (configuration C5) as a sub-record: N = 151936, K = 5120, M in {1, 4, 16},
+    e4m3 head with a bf16 scale per 128x128 block, column slabs over the ranks (strong scaling),
+    bf16 logits; per M the time of the head alone and with the all-gather of the logits fused into
+    its epilogue, and the per-GPU HBM fraction."""
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    from libr3d_b200 import abi, shard
+    NV, K = 151936, 5120
+    slab = shard.slab_of(NV, world, rank)
+    rows = max(slab.rows, 128)
+    g = torch.Generator(device=dev).manual_seed(99 + rank)
+    rot = 2 if rows * K > 200e6 else 4
+    heads = []
+    for _ in range(rot):
+        codes = torch.randint(0, 127, (rows, K), dtype=torch.uint8, device=dev, generator=g)
+        scale = (torch.rand(((rows + 127) // 128, K // 128), device=dev, generator=g) * 0.01 + 0.001).to(torch.bfloat16)
+        heads.append((codes, scale))
+    pg = shard.PushGather(P, slot_bytes=16 * world * slab.padded * 2, slots=2) if world > 1 else None
+    res = {}
+    steps = 20
+    for M in (1, 4, 16):
+        x = torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
+        y = torch.zeros((M, slab.padded), dtype=torch.bfloat16, device=dev)
+        ls = []
+        for codes, scale in heads:
+            l = abi.R3dLogits()
+            l.x, l.y, l.codes, l.scale = x.data_ptr(), y.data_ptr(), codes.data_ptr(), scale.data_ptr()
+            l.m, l.n, l.k, l.br = M, rows, K, 128
+            l.scale_dtype, l.y_dtype, l.head_fmt, l.arm = abi.RAD_BF16, abi.RAD_BF16, 0, abi.R3D_ARM_AUTO
+            l.x_pitch, l.code_pitch, l.y_pitch, l.scale_pitch = K, K, slab.padded, K // 128
+            ls.append(l)
+
+        def step(i, gather):
+            st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            if pg is not None and gather:
+                assert P.lib.r3d_b200_logits_push(ctypes.byref(ls[i % rot]), pg.ptr, i % 2, slab.padded, st) == 0
+                pg.wait(st.value)
+            else:
+                assert P.lib.r3d_b200_logits(ctypes.byref(ls[i % rot]), st) == 0
+
+        times = {}
+        for gather in ((False, True) if pg is not None else (False,)):
+            for i in range(4):
+                step(i, gather)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier(); torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(steps):
+                step(i, gather)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            if world > 1:
+                t = torch.tensor([ms], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+            times[gather] = ms / steps * 1e3
+        wbytes = rows * K + ((rows + 127) // 128) * (K // 128) * 2 + M * K * 2 + M * rows * 2
+        r = {"us_head": round(times[False], 2), "per_gpu_GBs": round(wbytes / times[False] / 1e3, 1),
+             "per_gpu_hbm_frac": round(wbytes / times[False] / 1e3 / peak, 3)}
+        if True in times:
+            r["us_head_and_gather"] = round(times[True], 2)
+        res[f"M{M}"] = r
+    if pg is not None:
+        pg.close()
+    del heads
+    torch.cuda.empty_cache()
+    return {"workload": "C5 LM head, e4m3 codes + bf16 scale per 128x128, N=151936, K=5120, bf16 logits",
+            "scaling": "strong", "rows_per_gpu": rows, "planes": rot, "steps": steps,
+            "issue": "direct calls of r3d_b200_logits / r3d_b200_logits_push (+ gather wait), CUDA events, max over ranks",
+            "gather": "fused into the head's epilogue: peer stores over NVLink + flags" if world > 1 else "none (one GPU)",
+            "results": res}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--rot", type=int, default=4, help="distinct weight planes cycled (footprint > L2)")
+    ap.add_argument("--rot", type=int, default=8, help="distinct weight planes cycled (footprint > L2)")
     ap.add_argument("--row", default="gemm_nt_q_mxfp4_decode")
+    ap.add_argument("--regions", type=int, default=5, help="how many times the K-step region is timed (median reported)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-sub", action="store_true", help="skip the sub-records (other row, plane sweep, C5)")
     ap.add_argument("--cfg", default="", help="--workload all: comma list of configurations to run (C1..C5, ROWS), default all")
     ap.add_argument("--tokens", type=int, default=8192, help="--workload all: M of the prefill configuration C4")
     ap.add_argument("--gather", default="push", choices=["push", "nccl"],
@@ -538,6 +665,8 @@ def main():
     dev = torch.device("cuda", local)
     P = ops.plugin()
     rot = max(args.rot, 1)
+    peak, which = _peak()
+    OTHER = "gemm_nt_q_mxfp4_decode_q8x" if args.row == "gemm_nt_q_mxfp4_decode" else "gemm_nt_q_mxfp4_decode"
 
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     planes = [(torch.randint(0, 256, (N_DIM, K_DIM // 2), dtype=torch.uint8, device=dev, generator=g),
@@ -548,16 +677,18 @@ def main():
         x = torch.randn((m, K_DIM), device=dev, generator=g).to(torch.bfloat16)
         acts[m] = ops.quant_act_fp8(x, 128)
         outs[m] = torch.zeros((m, N_DIM), dtype=torch.bfloat16, device=dev)
-        for p in range(rot):
-            ops_[m, p] = ops.BoundGemm(acts[m][0], acts[m][1], planes[p][0], planes[p][1], outs[m],
-                                       dtype="mxfp4a8", N=N_DIM, K=K_DIM, row=args.row)
+        for row in (args.row, OTHER):
+            for p in range(rot):
+                ops_[row, m, p] = ops.BoundGemm(acts[m][0], acts[m][1], planes[p][0], planes[p][1], outs[m],
+                                                dtype="mxfp4a8", N=N_DIM, K=K_DIM, row=row)
     gathered = {m: torch.empty((world * m, N_DIM), dtype=torch.bfloat16, device=dev) for m in MS} if world > 1 else None
     push = world > 1 and args.gather == "push"
     gather_note = ""
+    pg = None
     if push:
         # the all-gather fused into the GEMV epilogue: peer stores over NVLink + flags, two slots.
         # Every rank must get its peer mappings; if one cannot, all ranks take the NCCL form.
-        pg, err = None, ""
+        err = ""
         try:
             pg = shard.PushGather(P, slot_bytes=max(MS) * world * N_DIM * 2, slots=2)
         except Exception as e:                                  # noqa: BLE001 - reported in the JSON line
@@ -573,14 +704,17 @@ def main():
                                            M=m, n_local=N_DIM, n_pad=N_DIM, K=K_DIM, scratch=outs[m])
                   for m in MS for p in range(rot)}
 
-    def step(i: int):
+    def call(row: str, m: int, i: int, nrot: int = rot):
+        if push:
+            pushed[m, i % nrot].issue(i % 2)
+            return
+        ops_[row, m, i % nrot].issue()
+        if world > 1:
+            dist.all_gather_into_tensor(gathered[m], outs[m])
+
+    def step(i: int, row: str = args.row, nrot: int = rot):
         for m in MS:
-            if push:
-                pushed[m, i % rot].issue(i % 2)
-                continue
-            ops_[m, i % rot].issue()
-            if world > 1:
-                dist.all_gather_into_tensor(gathered[m], outs[m])
+            call(row, m, i, nrot)
 
     def fence():
         torch.cuda.synchronize()
@@ -593,51 +727,96 @@ def main():
     fence()
     probe = pushed[4, (args.warmup - 1) % rot].result((args.warmup - 1) % 2) if push else outs[4]
     assert int(torch.count_nonzero(probe.view(torch.int16))) > 0.9 * probe.numel()
+    recordable = world == 1 or push
 
-    # ---- device-timed region: exactly `steps` steps
-    graph = None
-    if world == 1 or push:
-        # a recorded pass: `rot` steps captured once, replayed (what the engine's pass replay does)
-        s = torch.cuda.Stream()
-        s.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(s):
-            graph = torch.cuda.CUDAGraph()
-            lc = P.lib.r3d_b200_launch_count()
-            with torch.cuda.graph(graph, stream=s):
-                for i in range(rot):
-                    step(i)
-            per_replay = P.lib.r3d_b200_launch_count() - lc     # kernels recorded in one replay
-        torch.cuda.current_stream().wait_stream(s)
-        replays, rem = divmod(args.steps, rot)
+    def region_runner(row: str, nrot: int, steps: int):
+        """run() issues exactly `steps` steps: replays of a recorded pass of nrot steps + the remainder"""
+        if not recordable:
+            return (lambda: [step(i, row, nrot) for i in range(steps)]), 0
+        for i in range(nrot):                            # a row's first calls may build its scratch: not inside a recording
+            step(i, row, nrot)
+        torch.cuda.synchronize()
+        lc = P.lib.r3d_b200_launch_count()
+        graph = _record(lambda i: step(i, row, nrot), nrot)
+        per_replay = P.lib.r3d_b200_launch_count() - lc
+        replays, rem = divmod(steps, nrot)
         for _ in range(3):
             graph.replay()
-    fence()
-    l0 = P.lib.r3d_b200_launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clk:
-        time.sleep(0.25)
-        fence()
-        e0.record()
-        if graph is not None:
+
+        def run():
             for _ in range(replays):
                 graph.replay()
             for i in range(rem):
-                step(i)
-        else:
-            for i in range(args.steps):
-                step(i)
-        e1.record()
-        fence()
+                step(i, row, nrot)
+        run.keep = graph
+        return run, per_replay * replays
+
+    # ---- device-timed region: exactly `steps` steps, timed `regions` times; the median is the value
+    run_main, graph_launches = region_runner(args.row, rot, args.steps)
+    fence()
+    l0 = P.lib.r3d_b200_launch_count()
+    with ClockSampler(local) as clk:
         time.sleep(0.25)
-    ms = e0.elapsed_time(e1)
-    launches = P.lib.r3d_b200_launch_count() - l0
-    if graph is not None:
-        launches += per_replay * replays
+        ms_list = _timed(run_main, max(args.regions, 1), fence)
+        time.sleep(0.25)
+    direct_launches = (P.lib.r3d_b200_launch_count() - l0) // max(args.regions, 1)
+    launches = graph_launches + direct_launches
     if world > 1:
-        t = torch.tensor([ms], device=dev)
+        t = torch.tensor(ms_list, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        ms_list = [float(v) for v in t.tolist()]
+    ms = statistics.median(ms_list)
     value = STEP_BYTES * args.steps * world / (ms * 1e-3) / 1e9
+
+    def per_m(row: str, nrot: int):
+        """each M alone: a recorded pass of nrot calls over the rotating planes, median of 3 regions"""
+        out = {}
+        for m in MS:
+            if recordable:
+                call(row, m, 0, nrot)
+                torch.cuda.synchronize()
+                gph = _record(lambda i, m=m: call(row, m, i, nrot), nrot)
+                for _ in range(3):
+                    gph.replay()
+                reps = max(2, 120 // nrot)
+                msl = _timed(lambda: [gph.replay() for _ in range(reps)], 3, fence)
+                n_calls = reps * nrot
+            else:
+                n_calls = 60
+                msl = _timed(lambda: [call(row, m, i, nrot) for i in range(n_calls)], 3, fence)
+            if world > 1:
+                t = torch.tensor(msl, device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); msl = [float(v) for v in t.tolist()]
+            us = statistics.median(msl) * 1e3 / n_calls
+            out[f"M{m}"] = {"us_per_call": round(us, 2), "GBs": round(algo_bytes(m) / us / 1e3, 1),
+                            "hbm_frac": round(algo_bytes(m) / us / 1e3 / peak, 3)}
+        return out
+
+    def row_value(row: str, nrot: int, steps: int, regions: int):
+        run, _ = region_runner(row, nrot, steps)
+        msl = _timed(run, regions, fence)
+        if world > 1:
+            t = torch.tensor(msl, device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); msl = [float(v) for v in t.tolist()]
+        m_ = statistics.median(msl)
+        return STEP_BYTES * steps * world / (m_ * 1e-3) / 1e9, m_ / steps
+
+    per_m_main = per_m(args.row, rot)
+    rows_rec, rot_sweep, c5 = None, None, None
+    if not args.no_sub:
+        sub_steps = min(args.steps, 200)
+        if not push:
+            v_o, ms_o = row_value(OTHER, rot, sub_steps, 3)
+            rows_rec = {OTHER: {"value": v_o, "unit": "GB/s", "ms_per_step": ms_o, "steps": sub_steps, "regions": 3,
+                                "hbm_frac_per_gpu": v_o / world / peak, "per_M": per_m(OTHER, rot),
+                                "what": ("the row the band resolver picks when no lever is set (priority 1200): int8-per-32 "
+                                         "activation arm, exact integer dots on tcgen05 kind::mxf4, bit-identical to the reference row"
+                                         if OTHER.endswith("_q8x") else "the fp32-walk decode row (priority 1100)")}}
+        if world == 1:
+            rot_sweep = {}
+            for nrot in sorted({2, 4, rot}):
+                if nrot <= rot:
+                    v_r, _ = row_value(args.row, nrot, sub_steps, 3)
+                    rot_sweep[str(nrot)] = {"planes_MB": round(nrot * (N_DIM * K_DIM // 2 + N_DIM * K_DIM // 32) / 1e6),
+                                            "value": round(v_r, 1), "hbm_frac": round(v_r / peak, 3)}
 
     # ---- end to end: host activations in, host outputs back, through the declared ops
     # every step: ONE copy of the packed activations (codes + scales of the three calls) from
@@ -647,21 +826,21 @@ def main():
     d_in = torch.empty(in_bytes, dtype=torch.uint8, device=dev)
     d_out = torch.empty((sum(MS), N_DIM), dtype=torch.bfloat16, device=dev)
     h_out = torch.empty((sum(MS), N_DIM), dtype=torch.bfloat16).pin_memory()
-    e2e_ops, e2e_out, off, row = {}, {}, 0, 0
+    e2e_ops, e2e_out, off, row_at = {}, {}, 0, 0
     for m in MS:
         na, ns = acts[m][0].numel(), acts[m][1].numel() * 4
         h_in[off:off + na].copy_(acts[m][0].flatten().cpu())
         h_in[off + na:off + na + ns].copy_(acts[m][1].flatten().view(torch.uint8).cpu())
         a_v = d_in[off:off + na].view(m, K_DIM)
         s_v = d_in[off + na:off + na + ns].view(torch.float32).view(m, K_DIM // 128)
-        e2e_out[m] = d_out[row:row + m]
+        e2e_out[m] = d_out[row_at:row_at + m]
         for p in range(rot):
             e2e_ops[m, p] = (shard.PushedGemm(pg, a_v, s_v, planes[p][0], planes[p][1], dtype="mxfp4a8", M=m,
                                               n_local=N_DIM, n_pad=N_DIM, K=K_DIM, scratch=e2e_out[m]) if push else
                              ops.BoundGemm(a_v, s_v, planes[p][0], planes[p][1], e2e_out[m],
                                            dtype="mxfp4a8", N=N_DIM, K=K_DIM, row=args.row))
         off += na + ns
-        row += m
+        row_at += m
     h2d, d2h = in_bytes, h_out.numel() * 2
 
     def step_e2e_body(i: int):
@@ -685,7 +864,7 @@ def main():
     # timed step replays its recording and waits for it on the host. If recording is not possible
     # (the NCCL-gather form), the step is issued directly.
     e2e_graphs, e2e_how = None, "direct issue per step"
-    if world == 1 or push:
+    if recordable:
         try:
             for i in range(2):
                 step_e2e_body(i)
@@ -717,31 +896,32 @@ def main():
     e2e_steps = min(args.steps, 200)
     for i in range(3):
         step_e2e(i)
-    fence()
-    e0.record()
-    for i in range(e2e_steps):
-        step_e2e(i)
-    e1.record()
-    fence()
-    ms_e = e0.elapsed_time(e1)
+    ms_e_list = _timed(lambda: [step_e2e(i) for i in range(e2e_steps)], 3, fence)
     if world > 1:
-        t = torch.tensor([ms_e], device=dev)
+        t = torch.tensor(ms_e_list, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_e = float(t.item())
+        ms_e_list = [float(v) for v in t.tolist()]
+    ms_e = statistics.median(ms_e_list)
     e2e = STEP_BYTES * e2e_steps * world / (ms_e * 1e-3) / 1e9
 
+    if not args.no_sub:
+        if pg is not None and push:
+            # the C5 record makes its own exchange buffers; release this one's slots first
+            pass
+        try:
+            c5 = c5_record(args, P, dev, world, rank, peak)
+        except Exception as ex:                          # noqa: BLE001 - the headline stands without the sub-record
+            c5 = {"unavailable": f"{type(ex).__name__}: {ex}"}
+
     if rank == 0:
-        peaks = {}
-        pk = ROOT / "MEASURED_PEAKS.json"
-        if pk.exists():
-            peaks = json.loads(pk.read_text())
-        peak, which = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
         per_launch_s = ms * 1e-3 / (3 * args.steps)
         achieved = (STEP_BYTES / 3) / per_launch_s / 1e9
         traffic = None
         tf = ROOT / "profiles" / "traffic.json"
         if tf.exists():
-            traffic = None if args.row.endswith("_q8x") else json.loads(tf.read_text()).get("k_tc_mxf4_c2_bytes_per_call")
+            tj = json.loads(tf.read_text())
+            traffic = tj.get("k_tc_q8x_c2_bytes_per_call" if args.row.endswith("_q8x") else "k_tc_mxf4_c2_bytes_per_call")
+        vals = [STEP_BYTES * args.steps * world / (m_ * 1e-3) / 1e9 for m_ in ms_list]
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -750,22 +930,32 @@ def main():
                        "row": args.row, "rot_planes": rot,
                        "l2": f"inputs larger than L2: {rot} rotating weight planes, "
                              f"{rot * (N_DIM * K_DIM // 2 + N_DIM * K_DIM // 32) / 1e6:.0f} MB",
-                       "timed_as": "CUDA graph replay of recorded steps" if graph is not None else "direct issue",
+                       "timed_as": ("CUDA graph replay of recorded steps" if recordable else "direct issue")
+                                   + f"; the {args.steps}-step region timed {len(ms_list)} times, median reported",
                        "parallelism": "1 GPU" if world == 1 else
                                       (f"column slabs x{world}, all-gather fused into the GEMV epilogue (peer stores + flags)"
                                        if push else f"column slabs x{world} + NCCL all_gather per call"
                                        + (f" [{gather_note}]" if gather_note else ""))},
+            "spread": {"regions": len(ms_list), "value_min": min(vals), "value_max": max(vals),
+                       "rel": (max(vals) - min(vals)) / value},
+            "per_M": per_m_main,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": which, "traffic": traffic,
-                         "kernel": ("k_q8x_gemv<MT,WALK> (one per call, after its k_q8x_requant)" if args.row.endswith("_q8x")
+                         "kernel": ("k_tc_q8x<MT,WALK,HW,EW> (one per call, after its k_q8x_split)" if args.row.endswith("_q8x")
                                     else "k_tc_mxf4<NP,MT> (one per call, after its k_mxf4_split)"),
                          "bytes_per_launch": STEP_BYTES / 3,
                          "us_per_launch": per_launch_s * 1e6},
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "timed_as": e2e_how,
-                    "steps": e2e_steps},
+                    "steps": e2e_steps, "regions": len(ms_e_list)},
             "gpu_launches": int(launches),
             "clocks": clk.summary(),
         }
+        if rows_rec is not None:
+            line["rows"] = rows_rec
+        if rot_sweep is not None:
+            line["rot_sweep"] = rot_sweep
+        if c5 is not None:
+            line["c5"] = c5
         if world == 1 and not args.no_cpu:
             v, dt, threads = cpu_step_sample(N_DIM, 3)
             line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",

@@ -163,11 +163,17 @@ int plan_mxfp4a8(const RadArgs* a, const RadTensor* A, const RadTensor* AS, cons
  * (src/r3d_gemm_mxfp4.hip:1841-1849). One buffer pair per distinct K, never freed. */
 struct Q8xScratch { long long k; int8_t* x8; float* sg; };
 
-bool q8x_scratch_for(long long K, int8_t** x8, float** sg) {
+bool q8x_scratch_for(long long K, int8_t** x8, float** sg, cudaStream_t st) {
     static std::vector<Q8xScratch> pool;
     static bool dead = false;
     for (const Q8xScratch& e : pool) if (e.k == K) { *x8 = e.x8; *sg = e.sg; return true; }
     if (dead) return false;
+    /* a first call for this K that arrives while its stream is being recorded cannot allocate (the
+     * allocation would invalidate the recording): this call rides the fp32 walk, the next call
+     * outside a recording builds the scratch */
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) { (void)cudaGetLastError(); return false; }
+    if (cap != cudaStreamCaptureStatusNone) return false;
     /* host-side fault injection for the fallback test: makes the allocator "fail" */
     static const bool inject = env_present("R3D_Q8X_FAIL_ALLOC");
     int8_t* nx = nullptr; float* ns = nullptr;
@@ -212,7 +218,7 @@ int run_mxfp4_decode(const RadArgs* a, RadStream s, bool q8x_row) {
 
     if (q8x_row && (q.k & 255) == 0 && q.k <= (1 << 20)) {
         int8_t* x8 = nullptr; float* sg = nullptr;
-        if (q8x_scratch_for(q.k, &x8, &sg)) {
+        if (q8x_scratch_for(q.k, &x8, &sg, (cudaStream_t)(uintptr_t)s)) {
             /* walk lever, three states like the reference's R3D_Q8X_LMAP
              * (src/r3d_gemm_mxfp4.hip:2065-2076): "0" tree walk always, "2" lane map always,
              * default lane map for 4 or more tokens */

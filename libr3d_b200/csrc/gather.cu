@@ -45,6 +45,9 @@ __global__ void k_gather_wait(volatile uint32_t* flags, FlagPtrs mine, uint32_t*
         while ((int)(flags[threadIdx.x] - want) < 0) {
             if (clock64() - t0 > 2000000000LL) { atomicExch(status, 1 + (int)threadIdx.x); break; }
         }
+        /* acquire side: what follows (this kernel's end, then the readers of the gathered buffer)
+         * is ordered after the flag observation, as the peer's stores were ordered before its flag */
+        __threadfence_system();
     }
     /* kernels that follow in the stream read the gathered buffer from this GPU's own memory,
      * where the peers' stores have landed before their flag did */

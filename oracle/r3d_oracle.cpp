@@ -587,6 +587,16 @@ ORC_API void orc_truth_mxfp4a8(const uint8_t* A, const float* AS, const uint8_t*
         }
 }
 
+/* The host threads later calls use (0 or less: leave as is). A launcher may have exported
+ * OMP_NUM_THREADS=1 for its ranks; the timed baseline asks for the cores it is meant to use. */
+ORC_API void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -99,14 +99,24 @@ def test_row_entry_with_joined_blob():
     assert _rel(out.get(), want.astype(np.float64)) < 1e-4
 
 
-def test_vocab_size_head_sampled_rows():
-    """N = 151936, K = 5120 (the LM head of the benchmark): stream arm vs the oracle on a
-    sample of rows, and vs the exact arm on a slab."""
-    N, K, M = 151936, 5120, 4
+@pytest.fixture(scope="module")
+def vocab_head():
+    """N = 151936, K = 5120: the LM head of the benchmark, e4m3 codes + a bf16 scale per 128x128"""
+    N, K = 151936, 5120
     rng = np.random.default_rng(5)
     codes = rng.integers(0, 256, (N, K), dtype=np.uint8)
     codes[(codes & 0x7F) == 0x7F] &= 0x7E
     scale = gen.f32_to_bf16_bits(np.exp(rng.uniform(-6, -4, ((N + 127) // 128, K // 128))).astype(np.float32))
+    return codes, scale
+
+
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_vocab_size_head_sampled_rows(vocab_head, M):
+    """The full-size head at M = 1, 4 and 16 (one pass of 32 piece rows): both tensor-core arms vs
+    the oracle on a sample of rows (first, random, last), nothing left unwritten."""
+    codes, scale = vocab_head
+    N, K = codes.shape
+    rng = np.random.default_rng(50 + M)
     X = gen.f32_to_bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
     c = dict(X=X, codes=codes, scale=scale, sdt=0, br=128)
     rows = np.concatenate([np.arange(0, 256), rng.choice(N, 256, replace=False), np.arange(N - 64, N)])
@@ -131,6 +141,20 @@ def _mxfp4_head_launch(Xb, B, BS, arm, y_dtype=abi.RAD_F32):
     rc = P.lib.r3d_b200_logits(C.byref(l), None)
     assert rc == abi.RAD_OK, abi.STATUS_NAMES[rc]
     return out.get()
+
+
+def test_mxfp4_head_vocab_size_sampled_rows():
+    """The mxfp4 head at N = 151936, K = 5120, M = 4: the tcgen05 arm vs the oracle on a row sample."""
+    N, K, M = 151936, 5120, 4
+    rng = np.random.default_rng(6)
+    B = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+    BS = rng.integers(119, 124, (N, K // 32), dtype=np.uint8)
+    Xb = gen.f32_to_bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    rows = np.concatenate([np.arange(0, 256), rng.choice(N, 256, replace=False), np.arange(N - 64, N)])
+    want = orc.logits_mxfp4(Xb, np.ascontiguousarray(B[rows]), np.ascontiguousarray(BS[rows])).astype(np.float64)
+    got = _mxfp4_head_launch(Xb, B, BS, abi.R3D_ARM_AUTO).astype(np.float64)
+    assert np.abs(got[:, rows] - want).max() / np.abs(want).max() < 2e-5
+    assert np.count_nonzero(got) > got.size * 0.99
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (4, 1000, 5120), (16, 384, 2560), (20, 256, 512)])
