@@ -368,24 +368,34 @@ def run_all(args):
         return e0.elapsed_time(e1) * 1e3 / (reps * len(calls))
 
     def gemm(kind, M, N, K, rot):
+        """kind: mxfp4a8, fp8a8 (the reference's grids: bf16 scale per 128x128, f32 per token and 128 of K)
+        or fp8a8/channel (one f32 scale per token, one per output channel: the benchmark's prefill contract)"""
+        channel = kind == "fp8a8/channel"
         x = torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
-        A, AS = ops.quant_act_fp8(x, 128)
+        A, AS = ops.quant_act_fp8(x, K if channel else 128)
+        acols = 1 if channel else K // 128
         keep, calls = [], []
         for _ in range(rot):
             if kind == "mxfp4a8":
                 B = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=g)
                 BS = torch.randint(119, 124, (N, K // 32), dtype=torch.uint8, device=dev, generator=g)
+            elif channel:
+                B = torch.randint(0, 127, (N, K), dtype=torch.uint8, device=dev, generator=g)
+                BS = torch.rand((N, 1), device=dev, generator=g) * 0.01 + 0.001
             else:
                 B = torch.randint(0, 127, (N, K), dtype=torch.uint8, device=dev, generator=g)
                 BS = (torch.rand(((N + 127) // 128, K // 128), device=dev, generator=g) * 0.01 + 0.001).to(torch.bfloat16)
             Y = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
             q = abi.R3dGemmQ()
             q.a, q.a_scale, q.b, q.b_scale, q.y = A.data_ptr(), AS.data_ptr(), B.data_ptr(), BS.data_ptr(), Y.data_ptr()
-            q.m, q.n, q.k, q.as_cols = M, N, K, K // 128
-            q.a_pitch, q.y_pitch, q.as_pitch, q.arm = K, N, K // 128, abi.R3D_ARM_AUTO
+            q.m, q.n, q.k, q.as_cols = M, N, K, acols
+            q.a_pitch, q.y_pitch, q.as_pitch, q.arm = K, N, acols, abi.R3D_ARM_AUTO
             if kind == "mxfp4a8":
                 q.bs_cols, q.rblk, q.bs_dtype, q.b_pitch, q.bs_pitch = K // 32, 1, abi.RAD_E8M0, K // 2, K // 32
                 fn = P.lib.r3d_b200_gemm_mxfp4a8
+            elif channel:
+                q.bs_cols, q.rblk, q.bs_dtype, q.b_pitch, q.bs_pitch = 1, 1, abi.RAD_F32, K, 1
+                fn = P.lib.r3d_b200_gemm_fp8a8
             else:
                 q.bs_cols, q.rblk, q.bs_dtype, q.b_pitch, q.bs_pitch = K // 128, 128, abi.RAD_BF16, K, K // 128
                 fn = P.lib.r3d_b200_gemm_fp8a8
@@ -420,10 +430,10 @@ def run_all(args):
                 decode_case("C3", kind, 16, N, K)
     if "C4" in want:
         MT = args.tokens
-        for kind in ("fp8a8", "mxfp4a8"):
+        for kind in ("fp8a8/channel", "fp8a8", "mxfp4a8"):
             for (K, N) in ((5120, 27648), (13824, 5120)):
                 calls, keep, _ = gemm(kind, MT, N, K, 1)
-                us = timed(calls, 5)
+                us = timed(calls, 10)
                 out.append({"cfg": "C4", "band": kind, "M": MT, "N": N, "K": K, "us_per_call": round(us, 1),
                             "TFLOPs": round(2 * MT * N * K / us / 1e6, 1),
                             "nonzero_ok": int(torch.count_nonzero(keep[0][2].view(torch.int16))) > 0.9 * MT * N})

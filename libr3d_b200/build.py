@@ -32,7 +32,7 @@ SOURCES = [
     "kern_q8x.cu",
     "q8x_static.cu",
     "kern_stream.cu",
-    "kern_tc.cu", "kern_tc_mxf4.cu", "kern_tc_q8x.cu", "kern_tc_gemm.cu", "gather.cu",
+    "kern_tc.cu", "kern_tc_mxf4.cu", "kern_tc_q8x.cu", "kern_tc_gemm.cu", "kern_tc_gemm2.cu", "gather.cu",
 ]
 
 NVCC_FLAGS = [

@@ -719,6 +719,8 @@ int tc_status() {
     v = tc_mxf4_status();
     if (v) return v;
     v = tc_q8x_status();
+    if (v) return v;
+    v = tc_gemm2_status();
     return v ? v : tc_gemm_status();
 }
 

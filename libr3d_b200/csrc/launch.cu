@@ -126,6 +126,10 @@ extern "C" int r3d_b200_gemm_fp8a8(const R3dGemmQ* q, void* stream) {
     }
     if (arm == R3D_ARM_EXACT) { debug_arm("fp8a8", "exact", q->m); return exact_fp8a8(*q, st); }
     if (arm == R3D_ARM_TILE) {
+        if (q->m > 64 && !no_gemm() && tc_gemm_ws_fp8a8_ok(*q)) {
+            debug_arm("fp8a8", "tcgen05 pair tile, one accumulation over K", q->m);
+            return tc_gemm_ws_fp8a8(*q, st);
+        }
         if (q->m > 64 && !no_gemm() && tc_gemm_fp8a8_ok(*q)) {
             debug_arm("fp8a8", "tcgen05 tile", q->m);
             return tc_gemm_fp8a8(*q, st);

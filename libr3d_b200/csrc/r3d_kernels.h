@@ -62,6 +62,11 @@ bool tc_gemm_fp8a8_ok(const R3dGemmQ& p);
 bool tc_gemm_mxfp4a8_ok(const R3dGemmQ& p);
 int  tc_gemm_fp8a8(const R3dGemmQ& p, cudaStream_t st);
 int  tc_gemm_mxfp4a8(const R3dGemmQ& p, cudaStream_t st);
+/* prefill kernel for scales that are constant along K (kern_tc_gemm2.cu): CTA pairs on
+ * tcgen05 cta_group::2, [256 weight rows x 256 tokens] per pair, persistent, one accumulation over K */
+bool tc_gemm_ws_fp8a8_ok(const R3dGemmQ& p);
+int  tc_gemm_ws_fp8a8(const R3dGemmQ& p, cudaStream_t st);
+int  tc_gemm2_status();
 int  tc_status();                      /* 0, or the code of a bounded wait that expired */
 
 /* int8-per-32 activation arm (kern_q8x.cu) */

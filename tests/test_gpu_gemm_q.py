@@ -411,6 +411,44 @@ def test_prefill_tile_kernel_within_2ulp(kind, M, N, K, grid):
     assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 5e-3, g
 
 
+@pytest.mark.parametrize("M,N,K", [(65, 130, 256), (100, 128, 512), (256, 256, 128), (300, 520, 1024), (481, 384, 1536),
+                                   (722, 1000, 2560), (1100, 777, 640), (513, 2048, 5120)])
+def test_prefill_pair_kernel_whole_k_scales_within_2ulp(M, N, K):
+    """fp8a8 with one f32 scale per token and one per output channel (the benchmark's prefill
+    contract): CTA pairs, [256 rows x 256 tokens] tiles, one accumulation over K, persistent over
+    ragged tile lists (1 to 15 tiles, odd row and token tails)."""
+    case = gen.case_fp8(5400 + M, M, N, K, "channel")
+    _, acc = orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], case["rblk"], want_acc=True)
+    _, ab = orc.truth_fp8a8(case["A"], case["AS"], case["B"], case["BS"], case["rblk"])
+    got = gu.gemm_launch("fp8a8", case, TILE)
+    assert ops.plugin().lib.r3d_b200_stream_status() == 0
+    g = gu.grade_bf16(got, acc, ab)
+    assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 5e-3, g
+    assert np.array_equal(gu.gemm_launch("fp8a8", case, EX), orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], 1))
+
+
+@pytest.mark.parametrize("N,K", [(27648, 5120), (5120, 13824)])
+def test_config_c4_prefill_channel_scales_full_size_sampled(N, K):
+    """M = 8192 with per-token / per-channel f32 scales at the benchmark's layer geometry: the pair
+    kernel against the CPU oracle on 48 token rows x 384 weight rows, nothing left unwritten."""
+    M = 8192
+    rng = np.random.default_rng(78)
+    case = gen.case_fp8(43, 256, N, K, "channel")
+    reps = M // 256
+    case["A"] = np.ascontiguousarray(np.tile(case["A"], (reps, 1))); case["AS"] = np.ascontiguousarray(np.tile(case["AS"], (reps, 1)))
+    perm = rng.permutation(M)
+    case["A"], case["AS"] = case["A"][perm], case["AS"][perm]
+    got = gu.gemm_launch("fp8a8", case, TILE)
+    assert ops.plugin().lib.r3d_b200_stream_status() == 0
+    assert np.count_nonzero(got & 0x7FFF) > got.size * 0.99
+    ts = np.concatenate([np.arange(8), np.arange(M - 8, M), rng.choice(M, 32, replace=False)])
+    ns = np.concatenate([np.arange(128), np.arange(N - 128, N), rng.choice(N, 128, replace=False)])
+    _, acc = orc.gemm_fp8a8(case["A"][ts], case["AS"][ts], case["B"][ns], case["BS"][ns], 1, want_acc=True)
+    _, ab = orc.truth_fp8a8(case["A"][ts], case["AS"][ts], case["B"][ns], case["BS"][ns], 1)
+    g = gu.grade_bf16(got[np.ix_(ts, ns)], acc, ab)
+    assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 5e-3, g
+
+
 @pytest.mark.parametrize("kind,N,K", [("mxfp4a8", 27648, 5120), ("fp8a8", 5120, 13824),
                                       ("fp8a8", 27648, 5120), ("mxfp4a8", 5120, 13824)])
 def test_config_c4_prefill_full_size_sampled(kind, N, K):
