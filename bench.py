@@ -370,13 +370,18 @@ def run_all(args):
     def gemm(kind, M, N, K, rot):
         """kind: mxfp4a8, fp8a8 (the reference's grids: bf16 scale per 128x128, f32 per token and 128 of K)
         or fp8a8/channel (one f32 scale per token, one per output channel: the benchmark's prefill contract)"""
-        channel = kind == "fp8a8/channel"
+        channel, mx8 = kind == "fp8a8/channel", kind == "mxfp4mx8"
         x = torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
         A, AS = ops.quant_act_fp8(x, K if channel else 128)
         acols = 1 if channel else K // 128
+        if mx8:
+            # timing operands: e4m3 codes as above with an E8M0 byte per 32 columns (the values the
+            # OCP-MX quantiser would store for N(0,1) activations lie around 127 - 8 + 1)
+            AS = torch.randint(118, 122, (M, K // 32), dtype=torch.uint8, device=dev, generator=g)
+            acols = K // 32
         keep, calls = [], []
         for _ in range(rot):
-            if kind == "mxfp4a8":
+            if kind in ("mxfp4a8", "mxfp4mx8"):
                 B = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=g)
                 BS = torch.randint(119, 124, (N, K // 32), dtype=torch.uint8, device=dev, generator=g)
             elif channel:
@@ -390,9 +395,9 @@ def run_all(args):
             q.a, q.a_scale, q.b, q.b_scale, q.y = A.data_ptr(), AS.data_ptr(), B.data_ptr(), BS.data_ptr(), Y.data_ptr()
             q.m, q.n, q.k, q.as_cols = M, N, K, acols
             q.a_pitch, q.y_pitch, q.as_pitch, q.arm = K, N, acols, abi.R3D_ARM_AUTO
-            if kind == "mxfp4a8":
+            if kind in ("mxfp4a8", "mxfp4mx8"):
                 q.bs_cols, q.rblk, q.bs_dtype, q.b_pitch, q.bs_pitch = K // 32, 1, abi.RAD_E8M0, K // 2, K // 32
-                fn = P.lib.r3d_b200_gemm_mxfp4a8
+                fn = P.lib.r3d_b200_gemm_mxfp4mx8 if mx8 else P.lib.r3d_b200_gemm_mxfp4a8
             elif channel:
                 q.bs_cols, q.rblk, q.bs_dtype, q.b_pitch, q.bs_pitch = 1, 1, abi.RAD_F32, K, 1
                 fn = P.lib.r3d_b200_gemm_fp8a8
@@ -401,7 +406,7 @@ def run_all(args):
                 fn = P.lib.r3d_b200_gemm_fp8a8
             keep.append((B, BS, Y, q))
             calls.append(lambda st, q=q, fn=fn: fn(C.byref(q), st))
-        wbytes = N * K // 2 + N * K // 32 if kind == "mxfp4a8" else N * K + ((N + 127) // 128) * (K // 128) * 2
+        wbytes = N * K // 2 + N * K // 32 if kind in ("mxfp4a8", "mxfp4mx8") else N * K + ((N + 127) // 128) * (K // 128) * 2
         return calls, keep, wbytes + M * (K + K // 128 * 4) + M * N * 2
 
     out = []
@@ -430,7 +435,7 @@ def run_all(args):
                 decode_case("C3", kind, 16, N, K)
     if "C4" in want:
         MT = args.tokens
-        for kind in ("fp8a8/channel", "fp8a8", "mxfp4a8"):
+        for kind in ("fp8a8/channel", "mxfp4mx8", "fp8a8", "mxfp4a8"):
             for (K, N) in ((5120, 27648), (13824, 5120)):
                 calls, keep, _ = gemm(kind, MT, N, K, 1)
                 us = timed(calls, 10)

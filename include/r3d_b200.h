@@ -57,6 +57,9 @@ int r3d_rad_sample_argmax(const RadArgs* a, RadStream s);
 /* gemm_nt_q @ mxfp4a8, any M. Replaces r3d_rad_gemm_nt_q
  * (src/r3d_gemm_mxfp4.hip:1587-1691). */
 int r3d_rad_gemm_nt_q(const RadArgs* a, RadStream s);
+/* gemm_nt_q @ mxfp4mx8, any M (row gemm_nt_q_mxfp4mx8): a_scale is an E8M0 plane [M, K/32]. No
+ * counterpart in the reference; see r3d_b200_gemm_mxfp4mx8. */
+int r3d_rad_gemm_nt_q_mx8(const RadArgs* a, RadStream s);
 /* gemm_nt_q @ mxfp4a8, decode band M <= 8, fp32 walk. Replaces
  * r3d_rad_gemm_nt_q_mxfp4_decode (src/r3d_gemm_mxfp4.hip:1715-1716). */
 int r3d_rad_gemm_nt_q_mxfp4_decode(const RadArgs* a, RadStream s);
@@ -122,6 +125,13 @@ int r3d_b200_gemm_fp8a8(const R3dGemmQ* q, void* stream);
 /* Replaces the kernel dispatch of r3d_gemm_nt_q_impl and the fp32 decode walk
  * (src/r3d_gemm_mxfp4.hip:1613-1690, :2125-2169). */
 int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream);
+/* gemm_nt_q @ mxfp4mx8 -- a dtype spelling the reference does not have (its mxfp4 band takes e4m3
+ * activations with an f32 scale per 128 of K): e2m1 weights [N, K/2 bytes] + E8M0 [N, K/32] and e4m3
+ * activations [M, K] + E8M0 [M, K/32], the OCP-MX pair whose scales the tensor core applies itself.
+ * `a_scale` carries the activations' E8M0 bytes (as_cols = K/32, as_pitch in bytes). Rule (fixed by
+ * this library's CPU checker, no reference pin): per 32 of K  acc += (sum a*w * 2^(xa-127)) * 2^(xw-127).
+ * Arms: AUTO / TILE (M > 64: CTA-pair tcgen05 kernel, one accumulation over K) and EXACT. */
+int r3d_b200_gemm_mxfp4mx8(const R3dGemmQ* q, void* stream);
 /* The int8-per-32 arm: requantise the activation into x8/sg (caller-owned scratch,
  * x8 >= m*k bytes, sg >= m*k/32 floats), then the dot. walk 0 = per-256 tree, 1 = lane
  * map. Replaces m4_act_i8_kernel + gemm_nt_mxfp4_gemv_q8x[_lm]_kernel

@@ -158,6 +158,45 @@ int plan_mxfp4a8(const RadArgs* a, const RadTensor* A, const RadTensor* AS, cons
     return RAD_OK;
 }
 
+/* ------------------------------------------------------------------ mxfp4mx8 plan
+ * The mxfp4a8 plan with the activation's scale grid changed: E8M0 bytes, one per 32 of K. The
+ * same refusal order as the mxfp4a8 entry (src/r3d_gemm_mxfp4.hip:1521-1582 of libr3d), which has no
+ * such spelling itself. */
+int plan_mxfp4mx8(const RadArgs* a, const RadTensor* A, const RadTensor* AS, const RadTensor* B,
+                  const RadTensor* BS, const RadTensor* Y, long long M, long long N, R3dGemmQ* q) {
+    const char* enc = rad_args_gets(a, "dtype");
+    if (!enc || strcmp(enc, "mxfp4mx8") != 0) return RAD_E_UNSUPPORTED;
+    long long part = 0;
+    if (rad_args_geti(a, "pb1", &part) && part > 0) return RAD_E_UNSUPPORTED;
+    if (rad_args_geti(a, "pb2", &part) && part > 0) return RAD_E_UNSUPPORTED;
+    if (A->dtype != RAD_F8E4M3 || B->dtype != RAD_FP4E2M1 || Y->dtype != RAD_BF16 ||
+        (AS->dtype != RAD_E8M0 && AS->dtype != RAD_U8) || (BS->dtype != RAD_E8M0 && BS->dtype != RAD_U8))
+        return RAD_E_UNSUPPORTED;
+    long long K = 0;
+    if (!rad_args_geti(a, "K", &K)) return RAD_E_SHAPE;
+    if (N <= 0 || K <= 0 || M <= 0) return RAD_E_SHAPE;
+    if (M > kMaxExtent || N > kMaxExtent || K > kMaxExtent) return RAD_E_SHAPE;
+    if (rad_tensor_numel(A) < M * K || rad_tensor_numel(B) < N * K) return RAD_E_SHAPE;
+    if (BS->rank != 2 || BS->stride[1] != 1 || (long long)BS->shape[0] < N) return RAD_E_UNSUPPORTED;
+    if (AS->rank != 2 || AS->stride[1] != 1 || (long long)AS->shape[0] < M) return RAD_E_UNSUPPORTED;
+    const int64_t bs_cols = BS->shape[1], as_cols = AS->shape[1];
+    if (grid_block(K, bs_cols) != 32 || grid_block(K, as_cols) != 32) return RAD_E_UNSUPPORTED;
+    if (bs_cols != (K + 31) / 32 || as_cols != (K + 31) / 32) return RAD_E_UNSUPPORTED;
+    if (rad_tensor_numel(AS) < M * as_cols) return RAD_E_SHAPE;
+    if (!inner_contiguous(A) || !inner_contiguous(B) || !inner_contiguous(Y)) return RAD_E_STRIDE;
+    if ((K & 1) || row_pitch(B, K) != K) return RAD_E_STRIDE;
+    q->a = A->data; q->a_scale = (const float*)AS->data; q->b = B->data; q->b_scale = BS->data;
+    q->y = Y->data;
+    q->m = (int32_t)M; q->n = (int32_t)N; q->k = (int32_t)K;
+    q->as_cols = (int32_t)as_cols; q->bs_cols = (int32_t)bs_cols;
+    q->rblk = 1; q->bs_dtype = RAD_E8M0;
+    q->a_pitch = row_pitch(A, K); q->b_pitch = K / 2;
+    q->y_pitch = row_pitch(Y, N);
+    q->as_pitch = row_pitch(AS, as_cols); q->bs_pitch = row_pitch(BS, bs_cols);
+    q->arm = R3D_ARM_AUTO;
+    return RAD_OK;
+}
+
 /* Immortal per-K scratch of the int8 arm: pointers must never move once handed to a
  * launch, because the engine may record a pass and replay it with the recorded arguments
  * (src/r3d_gemm_mxfp4.hip:1841-1849). One buffer pair per distinct K, never freed. */
@@ -262,6 +301,27 @@ int r3d_rad_gemm_nt_q(const RadArgs* a, RadStream s) {
     const int rc = plan_mxfp4a8(a, A, AS, B, BS, Y, Yn / N, N, &q);
     if (rc != RAD_OK) return rc;
     return r3d_b200_gemm_mxfp4a8(&q, (void*)s);
+}
+
+int r3d_rad_gemm_nt_q_mx8(const RadArgs* a, RadStream s) {
+    static const bool off = env_present("R3D_NO_MXFP4");
+    if (off) return RAD_E_UNSUPPORTED;
+    const RadTensor* A = rad_arg_in(a, 0);
+    const RadTensor* AS = rad_arg_in(a, 1);
+    const RadTensor* B = rad_arg_in(a, 2);
+    const RadTensor* BS = rad_arg_in(a, 3);
+    const RadTensor* Y = rad_arg_in(a, 4);
+    if (!A || !AS || !B || !BS || !Y) return RAD_E_UNSUPPORTED;
+    if (rad_arg_in(a, 5)) return RAD_E_UNSUPPORTED;                 /* a_sum; b_ref is ignored */
+    if (Y->dtype != RAD_BF16) return RAD_E_UNSUPPORTED;
+    long long N = 0;
+    if (!rad_args_geti(a, "N", &N) || N <= 0) return RAD_E_SHAPE;
+    const long long Yn = rad_tensor_numel(Y);
+    if (Yn <= 0 || Yn % N) return RAD_E_SHAPE;
+    R3dGemmQ q{};
+    const int rc = plan_mxfp4mx8(a, A, AS, B, BS, Y, Yn / N, N, &q);
+    if (rc != RAD_OK) return rc;
+    return r3d_b200_gemm_mxfp4mx8(&q, (void*)s);
 }
 
 int r3d_rad_gemm_nt_q_mxfp4_decode(const RadArgs* a, RadStream s) {

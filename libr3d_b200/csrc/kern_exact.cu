@@ -104,7 +104,9 @@ __global__ __launch_bounds__(128) void k_fp8a8_exact(const R3dGemmQ p, const int
 }
 
 /* ------------------------------------------------------------------ mxfp4a8 */
-template <int MT>
+/* MX8: the activation's scale is one E8M0 byte per 32 of K (a_scale holds bytes, as_pitch in bytes)
+ * instead of one f32 per 128 */
+template <int MT, bool MX8>
 __global__ __launch_bounds__(128) void k_mxfp4a8_exact(const R3dGemmQ p, const int m0) {
     __shared__ float lut[256];
     for (int i = threadIdx.x; i < 256; i += 128) lut[i] = e4m3_to_f32((uint8_t)i);
@@ -148,8 +150,9 @@ __global__ __launch_bounds__(128) void k_mxfp4a8_exact(const R3dGemmQ p, const i
 #pragma unroll
             for (int m = 0; m < MT; ++m)
                 if (m < live) {
-                    const float sa = p.a_scale[(int64_t)(m0 + m) * p.as_pitch +
-                                               scale_col(g >> 2, p.as_cols, n128)];
+                    const float sa = MX8 ? e8m0_to_f32(((const uint8_t*)p.a_scale)[(int64_t)(m0 + m) * p.as_pitch + g])
+                                         : p.a_scale[(int64_t)(m0 + m) * p.as_pitch +
+                                                     scale_col(g >> 2, p.as_cols, n128)];
                     term[m] = __fmul_rn(__fmul_rn(part[m], sa), sc);
                 }
         }
@@ -472,10 +475,24 @@ int exact_mxfp4a8(const R3dGemmQ& p, cudaStream_t st) {
         [&](int mt, int m0) {
             count_launch();
             switch (mt) {
-                case 1: k_mxfp4a8_exact<1><<<grid, 128, 0, st>>>(p, m0); break;
-                case 2: k_mxfp4a8_exact<2><<<grid, 128, 0, st>>>(p, m0); break;
-                case 4: k_mxfp4a8_exact<4><<<grid, 128, 0, st>>>(p, m0); break;
-                default: k_mxfp4a8_exact<8><<<grid, 128, 0, st>>>(p, m0); break;
+                case 1: k_mxfp4a8_exact<1, false><<<grid, 128, 0, st>>>(p, m0); break;
+                case 2: k_mxfp4a8_exact<2, false><<<grid, 128, 0, st>>>(p, m0); break;
+                case 4: k_mxfp4a8_exact<4, false><<<grid, 128, 0, st>>>(p, m0); break;
+                default: k_mxfp4a8_exact<8, false><<<grid, 128, 0, st>>>(p, m0); break;
+            }
+        }, p);
+}
+
+int exact_mxfp4mx8(const R3dGemmQ& p, cudaStream_t st) {
+    const dim3 grid((unsigned)((p.n + 3) / 4));
+    return launch_mt(
+        [&](int mt, int m0) {
+            count_launch();
+            switch (mt) {
+                case 1: k_mxfp4a8_exact<1, true><<<grid, 128, 0, st>>>(p, m0); break;
+                case 2: k_mxfp4a8_exact<2, true><<<grid, 128, 0, st>>>(p, m0); break;
+                case 4: k_mxfp4a8_exact<4, true><<<grid, 128, 0, st>>>(p, m0); break;
+                default: k_mxfp4a8_exact<8, true><<<grid, 128, 0, st>>>(p, m0); break;
             }
         }, p);
 }

@@ -79,8 +79,11 @@ __device__ __forceinline__ void umma2_f8f6f4(uint32_t d_tmem, uint64_t adesc, ui
 __device__ __forceinline__ void umma2_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+/* arrive on a barrier of either CTA of the pair. What the arrival publishes lives in tensor memory and
+ * is ordered by the tcgen05 fences on both sides, so the arrive itself needs no cluster-scope release
+ * of generic memory (which cost about a microsecond per arrival when the scale warps did one per stage) */
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
@@ -220,6 +223,224 @@ k_tc_gemm_ws(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
     }
 }
 
+/* ------------------------------------------------------------------ mxfp4 weights x mxfp8 activations
+ * The OCP-MX pair: e2m1 weights and e4m3 activations, each with one E8M0 scale per 32 of K. Both
+ * scale sets are applied by the tensor core (kind::mxf8f6f4.block_scale, one scale byte per operand
+ * row per K=32 instruction, read from tensor memory), so the whole K sum is one accumulation and the
+ * epilogue only narrows to bf16. Same pair structure as above with [256 weight rows x 192 tokens]
+ * tiles (two accumulators plus the scale-factor columns fill tensor memory). Four more warps per CTA
+ * move the scale bytes: the weights' and the activations' E8M0 bytes arrive as TMA tiles of
+ * [rows x 32 bytes] (eight stages each); per stage a scale warp stores its lane quarter's words --
+ * weight row r at lane r, column r / 32; token n at lane n % 32 of every lane quarter, column n / 32
+ * (every CTA of the pair holds the scales of all 192 tokens). */
+constexpr int kTokMC = 96;                         /* tokens loaded per CTA */
+constexpr int kTokM = 2 * kTokMC;                  /* tokens per pair tile */
+constexpr int kABytesM = kTokMC * kStageK;         /* 12 KiB */
+constexpr int kStageM = kWBytes + kABytesM;
+constexpr int kStagesM = 6;
+constexpr int kScRing = 2;
+constexpr int kScW = kRows * 32, kScA = kTokM * 32;
+constexpr int kScTileB = kScW + kScA;              /* 10 KiB: weight-scale tile + activation-scale tile of eight stages */
+constexpr int kSfBaseM = 2 * kTokM;                /* 384: scale-factor columns behind the two accumulators */
+constexpr int kSfSlot = 16;                        /* per stage: 4 columns for the weights, 6 (of 8) for the tokens */
+constexpr int kThreadsM = 32 * 10;
+
+struct PGM {
+    uint16_t* y; int64_t y_pitch;
+    int m, n, k;
+    int tok_tiles, tiles, pairs;
+};
+
+__device__ __forceinline__ void umma2_mxf8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsM, 1)
+k_tc_gemm_mx(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
+             const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmE, const PGM P) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sc = smem + kStagesM * kStageM;                      /* [kScRing][weights 128x32 | tokens 192x32] */
+    uint64_t* full = (uint64_t*)(sc + kScRing * kScTileB);
+    uint64_t* empty = full + kStagesM;
+    uint64_t* prep = empty + kStagesM;                            /* scale factors of a stage are in both CTAs' tensor memory */
+    uint64_t* acc_full = prep + kStagesM;
+    uint64_t* acc_empty = acc_full + 2;
+    uint64_t* sc_full = acc_empty + 2;
+    uint64_t* sc_empty = sc_full + kScRing;
+    uint32_t* tmem_slot = (uint32_t*)(sc_empty + kScRing);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t crank = cluster_rank();
+    const bool leader = crank == 0;
+    const int pair = blockIdx.x >> 1;
+    const int nk = P.k / kStageK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStagesM; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&prep[s], 8); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+        for (int b = 0; b < kScRing; ++b) { mbar_init(&sc_full[b], 1); mbar_init(&sc_empty[b], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool alive = true;
+
+    if (warp == 0) {
+        /* ---------------- TMA producer ---------------- */
+        if (elect_one()) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmS) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmE) : "memory");
+            int s = 0; uint32_t ph = 0;
+            int r = 0; uint32_t rph = 0;
+            for (int tile = pair; tile < P.tiles && alive; tile += P.pairs) {
+                const int wt = tile / P.tok_tiles, tt = tile - wt * P.tok_tiles;
+                const int r0 = wt * 2 * kRows + (int)crank * kRows, tp = tt * kTokM, t0 = tp + (int)crank * kTokMC;
+                for (int it = 0; it < nk; ++it) {
+                    if ((it & 7) == 0) {
+                        /* the scale bytes of the next eight stages: this CTA's 128 weight rows, the pair's 192 tokens */
+                        if (!mbar_wait(&sc_empty[r], rph ^ 1u, 71)) { alive = false; break; }
+                        mbar_expect_tx(&sc_full[r], (uint32_t)kScTileB);
+                        tma_load_2d(sc + r * kScTileB, &tmS, (it >> 3) * 32, r0, &sc_full[r]);
+                        tma_load_2d(sc + r * kScTileB + kScW, &tmE, (it >> 3) * 32, tp, &sc_full[r]);
+                        if (++r == kScRing) { r = 0; rph ^= 1u; }
+                    }
+                    if (!mbar_wait(&empty[s], ph ^ 1u, 72)) { alive = false; break; }
+                    const uint32_t bar = mapa_u32(smem_u32(&full[s]), 0u);
+                    /* the unpacking tensor map counts the packed bytes it read */
+                    if (leader) mbar_expect_tx(&full[s], (uint32_t)(2 * (kWBytes / 2 + kABytesM)));
+                    uint8_t* st = smem + s * kStageM;
+                    tma_load_2d_pair(st, &tmW, it * kStageK, r0, bar);
+                    tma_load_2d_pair(st + kWBytes, &tmA, it * kStageK, t0, bar);
+                    if (++s == kStagesM) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        /* ---------------- MMA issuer (the pair's leader only) ---------------- */
+        if (leader && elect_one()) {
+            /* block-scaled kinds: a format e2m1 (5) at bit 7, b format e4m3 (0), N >> 3 at bit 17, scale format
+             * ue8m0 at bit 23, M >> 4 at bit 24; which byte of a row's scale word this K=32 step uses:
+             * b_sf_id at bit 4, a_sf_id at bit 29 */
+            const uint32_t idesc = (5u << 7) | ((uint32_t)(kTokM >> 3) << 17) | (1u << 23) | ((uint32_t)((2 * kRows) >> 4) << 24);
+            int s = 0; uint32_t ph = 0;
+            int ab = 0; uint32_t aph = 0;
+            for (int tile = pair; tile < P.tiles && alive; tile += P.pairs) {
+                if (!mbar_wait(&acc_empty[ab], aph ^ 1u, 74)) { alive = false; break; }
+                for (int it = 0; it < nk; ++it) {
+                    if (!mbar_wait(&prep[s], ph, 73) || !mbar_wait(&full[s], ph, 75)) { alive = false; break; }
+                    tc_fence_after();
+                    const uint32_t a0 = smem_u32(smem + s * kStageM), b0 = a0 + kWBytes;
+                    const uint32_t sf = tmem_base + kSfBaseM + s * kSfSlot;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma2_mxf8(tmem_base + ab * kTokM, smem_desc_sw128(a0 + k * 32), smem_desc_sw128(b0 + k * 32),
+                                   idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4), sf, sf + 4, (it | k) ? 1u : 0u);
+                    umma2_commit(smem_u32(&empty[s]));
+                    umma2_commit(mapa_u32(smem_u32(&empty[s]), 1u));
+                    if (++s == kStagesM) { s = 0; ph ^= 1u; }
+                }
+                if (!alive) break;
+                umma2_commit(smem_u32(&acc_full[ab]));
+                umma2_commit(mapa_u32(smem_u32(&acc_full[ab]), 1u));
+                if (++ab == 2) { ab = 0; aph ^= 1u; }
+            }
+        }
+    } else if (warp >= 6) {
+        /* ---------------- scale warps: lane quarter q of this CTA's tensor memory ---------------- */
+        const int q = warp & 3;                                   /* warps 6..9 -> quarters 2, 3, 0, 1 */
+        const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
+        const uint32_t prep_leader0 = mapa_u32(smem_u32(&prep[0]), 0u);
+        int s = 0; uint32_t ph = 0;
+        int r = 0; uint32_t rph = 0;
+        for (int tile = pair; tile < P.tiles && alive; tile += P.pairs) {
+            for (int it = 0; it < nk; ++it) {
+                if ((it & 7) == 0 && !mbar_wait(&sc_full[r], rph, 76)) { alive = false; break; }
+                const uint8_t* tw = sc + r * kScTileB + (it & 7) * 4;
+                const uint32_t ww = *(const uint32_t*)(tw + (q * 32 + lane) * 32);
+                uint32_t wa[6];
+#pragma unroll
+                for (int c = 0; c < 6; ++c) wa[c] = *(const uint32_t*)(tw + kScW + (c * 32 + lane) * 32);
+                if ((it & 7) == 7 || it == nk - 1) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sc_empty[r]);
+                    if (++r == kScRing) { r = 0; rph ^= 1u; }
+                }
+                /* the slot was last read by the MMAs that also released shared-memory stage s */
+                if (!mbar_wait(&empty[s], ph ^ 1u, 77)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t sf = tlane + kSfBaseM + s * kSfSlot;
+                tmem_st1(sf + q, ww);
+#pragma unroll
+                for (int c = 0; c < 6; ++c) tmem_st1(sf + 4 + c, wa[c]);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(prep_leader0 + (uint32_t)(s * sizeof(uint64_t)));
+                if (++s == kStagesM) { s = 0; ph ^= 1u; }
+            }
+        }
+    } else {
+        /* ---------------- epilogue: thread = weight row of this CTA ---------------- */
+        const int q = warp & 3;
+        const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
+        const uint32_t acc_empty_leader[2] = {mapa_u32(smem_u32(&acc_empty[0]), 0u), mapa_u32(smem_u32(&acc_empty[1]), 0u)};
+        int ab = 0; uint32_t aph = 0;
+        for (int tile = pair; tile < P.tiles && alive; tile += P.pairs) {
+            const int wt = tile / P.tok_tiles, tt = tile - wt * P.tok_tiles;
+            const int row = wt * 2 * kRows + (int)crank * kRows + q * 32 + lane;
+            const int t0 = tt * kTokM;
+            if (!mbar_wait(&acc_full[ab], aph, 78)) { alive = false; break; }
+            tc_fence_after();
+            const uint32_t ta = tlane + ab * kTokM;
+            float c[2][16];
+            tmem_ld16(ta, c[0]);
+#pragma unroll 1
+            for (int ch = 0; ch < kTokM / 16; ch += 2) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    tmem_ld_wait();
+                    tmem_pin16(c[h]);
+                    if (ch + h + 1 < kTokM / 16) tmem_ld16(ta + (ch + h + 1) * 16, c[h ^ 1]);
+                    if (row < P.n) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = t0 + (ch + h) * 16 + j;
+                            if (t < P.m) P.y[(int64_t)t * P.y_pitch + row] = f32_to_bf16(c[h][j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty_leader[ab]);
+            if (++ab == 2) { ab = 0; aph ^= 1u; }
+        }
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
+    }
+}
+
 bool al(const void* p, int a) { return (((uintptr_t)p) & (uintptr_t)(a - 1)) == 0; }
 
 } /* anonymous namespace */
@@ -258,6 +479,48 @@ int tc_gemm_ws_fp8a8(const R3dGemmQ& p, cudaStream_t st) {
     P.pairs = P.tiles < max_pairs ? P.tiles : max_pairs;
     count_launch();
     k_tc_gemm_ws<<<(unsigned)(2 * P.pairs), kThreads, smem, st>>>(*tw, *ta, P);
+    return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+}
+
+/* mxfp4 weights x mxfp8 activations: R3dGemmQ.a_scale carries the activations' E8M0 bytes [M, K/32]
+ * (as_cols = K/32, as_pitch in bytes) */
+bool tc_gemm_mx_ok(const R3dGemmQ& p) {
+    return p.m > 64 && (p.k % 128) == 0 && p.k >= 128 && al(p.b, 32) && (p.b_pitch % 32) == 0 &&
+           al(p.b_scale, 16) && (p.bs_pitch % 16) == 0 && p.bs_cols == p.k / 32 &&
+           al(p.a_scale, 16) && (p.as_pitch % 16) == 0 && p.as_cols == p.k / 32 &&
+           al(p.a, 16) && (p.a_pitch % 16) == 0 &&
+           (long long)((p.n + 255) / 256) * ((p.m + kTokM - 1) / kTokM) < (1ll << 30) && tc_have_encoder();
+}
+
+int tc_gemm_mx(const R3dGemmQ& p, cudaStream_t st) {
+    const CUtensorMap* tw = tc_tensor_map(p.b, (uint64_t)p.k, (uint64_t)p.n, (uint64_t)p.b_pitch,
+                                          CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, kRows);
+    const CUtensorMap* ta = tc_tensor_map(p.a, (uint64_t)p.k, (uint64_t)p.m, (uint64_t)p.a_pitch,
+                                          CU_TENSOR_MAP_DATA_TYPE_UINT8, kTokMC);
+    const CUtensorMap* ts = tc_tensor_map(p.b_scale, (uint64_t)(p.k / 32), (uint64_t)p.n, (uint64_t)p.bs_pitch,
+                                          CU_TENSOR_MAP_DATA_TYPE_UINT8, kRows, 32u);
+    const CUtensorMap* te = tc_tensor_map(p.a_scale, (uint64_t)(p.k / 32), (uint64_t)p.m, (uint64_t)p.as_pitch,
+                                          CU_TENSOR_MAP_DATA_TYPE_UINT8, kTokM, 32u);
+    if (!tw || !ta || !ts || !te) return RAD_E_UNSUPPORTED;
+    const size_t smem = 1024 + (size_t)kStagesM * kStageM + kScRing * kScTileB +
+                        (3 * kStagesM + 4 + 2 * kScRing) * sizeof(uint64_t) + 64;
+    static bool attr_set[kTcMaxDevices] = {};
+    const int dev = tc_device();
+    if (dev < 0) return RAD_E_DEVICE;
+    if (!attr_set[dev]) {
+        if (cudaFuncSetAttribute(k_tc_gemm_mx, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return RAD_E_DEVICE;
+        attr_set[dev] = true;
+    }
+    PGM P{};
+    P.y = (uint16_t*)p.y; P.y_pitch = p.y_pitch;
+    P.m = p.m; P.n = p.n; P.k = p.k;
+    P.tok_tiles = (p.m + kTokM - 1) / kTokM;
+    P.tiles = ((p.n + 2 * kRows - 1) / (2 * kRows)) * P.tok_tiles;
+    const int max_pairs = tc_sm_count() / 2;
+    P.pairs = P.tiles < max_pairs ? P.tiles : max_pairs;
+    count_launch();
+    k_tc_gemm_mx<<<(unsigned)(2 * P.pairs), kThreadsM, smem, st>>>(*tw, *ta, *ts, *te, P);
     return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
 }
 

@@ -166,6 +166,22 @@ extern "C" int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream) {
     return RAD_E_UNSUPPORTED;
 }
 
+/* gemm_nt_q @ mxfp4mx8: e2m1 weights and e4m3 activations, each with E8M0 scales per 32 of K.
+ * AUTO: the CTA-pair tcgen05 kernel for M > 64 when TMA's alignment rules are met, else the
+ * oracle-order kernel (any shape). */
+extern "C" int r3d_b200_gemm_mxfp4mx8(const R3dGemmQ* q, void* stream) {
+    if (!q || !device_is_sm100()) return RAD_E_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (q->arm != R3D_ARM_AUTO && q->arm != R3D_ARM_TILE && q->arm != R3D_ARM_EXACT) return RAD_E_UNSUPPORTED;
+    if (q->arm != R3D_ARM_EXACT && q->m > 64 && !no_gemm() && tc_gemm_mx_ok(*q)) {
+        debug_arm("mxfp4mx8", "tcgen05 pair tile, hardware scales on both operands", q->m);
+        return tc_gemm_mx(*q, st);
+    }
+    if (q->arm == R3D_ARM_TILE) return RAD_E_UNSUPPORTED;
+    debug_arm("mxfp4mx8", "exact", q->m);
+    return exact_mxfp4mx8(*q, st);
+}
+
 namespace r3d {
 int q8x_run(const R3dGemmQ& q, int8_t* x8, float* sg, int walk, cudaStream_t st) {
     if (tc_q8x_ok(q)) {

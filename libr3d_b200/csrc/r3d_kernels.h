@@ -18,6 +18,7 @@ bool device_is_sm100();                /* chip gate: these kernels are built for
 /* oracle-order arm (kern_exact.cu) */
 int exact_fp8a8(const R3dGemmQ& p, cudaStream_t st);
 int exact_mxfp4a8(const R3dGemmQ& p, cudaStream_t st);
+int exact_mxfp4mx8(const R3dGemmQ& p, cudaStream_t st);   /* a_scale = E8M0 bytes [M, K/32] */
 int exact_logits(const R3dLogits& p, cudaStream_t st);
 int launch_quant_act_fp8(const void* x, int x_dtype, int64_t x_pitch, void* q, int64_t q_pitch,
                          float* scale, int64_t s_pitch, int rows, int n, int group,
@@ -66,6 +67,10 @@ int  tc_gemm_mxfp4a8(const R3dGemmQ& p, cudaStream_t st);
  * tcgen05 cta_group::2, [256 weight rows x 256 tokens] per pair, persistent, one accumulation over K */
 bool tc_gemm_ws_fp8a8_ok(const R3dGemmQ& p);
 int  tc_gemm_ws_fp8a8(const R3dGemmQ& p, cudaStream_t st);
+/* ... and for mxfp4 weights x mxfp8 activations (both E8M0 scale sets applied by the tensor core),
+ * [256 x 192] per pair */
+bool tc_gemm_mx_ok(const R3dGemmQ& p);
+int  tc_gemm_mx(const R3dGemmQ& p, cudaStream_t st);
 int  tc_gemm2_status();
 int  tc_status();                      /* 0, or the code of a bounded wait that expired */
 

@@ -140,6 +140,7 @@ const RadConstraint kCLogits[] = {
     { "dtype", RAD_C_IN, 0, "bf16" },
 };
 const RadConstraint kCMxfp4[] = { { "dtype", RAD_C_IN, 0, "mxfp4a8" } };
+const RadConstraint kCMxfp4Mx8[] = { { "dtype", RAD_C_IN, 0, "mxfp4mx8" }, { "K", RAD_C_DIV, 32, nullptr } };
 const RadConstraint kCFp8[] = {
     { "dtype", RAD_C_IN, 0, "fp8a8" }, { "K", RAD_C_DIV, 128, nullptr },
     { "group", RAD_C_EQ, 128, nullptr },
@@ -204,6 +205,14 @@ const RadKernelInfo kRows[] = {
         "b:32 / a:128 scale grids; nibble rows byte-packed; M from numel(y)/N",
         "e4m3 a + f32 a_scale, e2m1 b + E8M0 b_scale, bf16 y; b_ref ignored; a_sum refused",
         kPrioPlain, kCMxfp4, r3d_rad_gemm_nt_q),
+
+    /* not a reference row: the OCP-MX activation spelling of the mxfp4 band (weights as above) */
+    ROW("gemm_nt_q_mxfp4mx8", "gemm_nt_q", "gemm",
+        "mxfp4 weights x mxfp8 activations, any M: both E8M0 scale sets are applied by the tensor core "
+        "(kind::mxf8f6f4 block scaling); M > 64 on CTA-pair 256x192 tiles with one accumulation over K",
+        "b:32 / a:32 scale grids; nibble rows byte-packed; M from numel(y)/N",
+        "e4m3 a + E8M0 a_scale, e2m1 b + E8M0 b_scale, bf16 y; b_ref ignored; a_sum refused",
+        kPrioPlain, kCMxfp4Mx8, r3d_rad_gemm_nt_q_mx8),
 
     ROW("gemm_nt_q_fp8a8", "gemm_nt_q", "gemm",
         "fp8a8, any M: e4m3 codes feed tcgen05 untouched (swap-AB weight streaming up to M = 64, "
@@ -298,6 +307,7 @@ bool row_hidden(const RadKernelInfo& k) {
     if (!strcmp(k.name, "gemm_nt_q_fp8a8_decode")) return no_fp8 || no_fp8_dec;
     if (!strcmp(k.name, "gemm_nt_q_gated_fp8a8")) return no_fp8;       /* src/r3d_rows.cpp:2235 */
     if (!strcmp(k.name, "gemm_nt_q_mxfp4")) return no_mx;
+    if (!strcmp(k.name, "gemm_nt_q_mxfp4mx8")) return no_mx;
     if (!strcmp(k.name, "gemm_nt_q_mxfp4_decode")) return no_mx || no_mx_dec;
     /* the q8x sibling rides every lever of its band, plus its own */
     if (!strcmp(k.name, "gemm_nt_q_mxfp4_decode_q8x")) return no_mx || no_mx_dec || q8x_off;

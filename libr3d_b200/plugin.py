@@ -28,7 +28,8 @@ EXPORTS = [
     "r3d_mxfp4_q8x_off", "r3d_rad_logits_gemm_e4m3", "r3d_layout_head", "r3d_relayout_head",
     "r3d_unrelayout_head",
     "r3d_b200_gemm_fp8a8", "r3d_b200_gemm_mxfp4a8", "r3d_b200_gemm_mxfp4a8_q8x",
-    "r3d_b200_gemm_mxfp4a8_q8x_static", "r3d_b200_q8x_on_tensor_core",
+    "r3d_b200_gemm_mxfp4a8_q8x_static", "r3d_b200_q8x_on_tensor_core", "r3d_b200_gemm_mxfp4mx8",
+    "r3d_rad_gemm_nt_q_mx8",
     "r3d_b200_logits", "r3d_b200_quant_act_fp8", "r3d_b200_pick_arm_fp8a8",
     "r3d_b200_pick_arm_mxfp4a8", "r3d_b200_launch_count", "r3d_b200_stream_status",
     "r3d_b200_gather_create", "r3d_b200_gather_connect", "r3d_b200_gather_buffer", "r3d_b200_gather_wait",
@@ -87,7 +88,7 @@ class Plugin:
         L.rad_kernel_at.argtypes = [C.c_int]
         L.r3d_mxfp4_q8x_off.restype = C.c_bool
         L.r3d_b200_launch_count.restype = C.c_longlong
-        for f in ("r3d_b200_gemm_fp8a8", "r3d_b200_gemm_mxfp4a8"):
+        for f in ("r3d_b200_gemm_fp8a8", "r3d_b200_gemm_mxfp4a8", "r3d_b200_gemm_mxfp4mx8"):
             getattr(L, f).argtypes = [C.POINTER(abi.R3dGemmQ), C.c_void_p]
         L.r3d_b200_gemm_mxfp4a8_q8x.argtypes = [C.POINTER(abi.R3dGemmQ), C.c_void_p, C.c_void_p,
                                                 C.c_int, C.c_void_p]

@@ -347,6 +347,28 @@ def truth_mxfp4a8(A, AS, B, BS):
     return Yt, Ya
 
 
+def gemm_mxfp4mx8(A, AE, B, BS, want_acc: bool = False):
+    """mxfp4 weights x mxfp8 activations (A e4m3 [M,K], AE E8M0 [M,K/32]); parity unpinned."""
+    A, B, AE, BS = _c(A, np.uint8), _c(B, np.uint8), _c(AE, np.uint8), _c(BS, np.uint8)
+    M, K = A.shape
+    N = B.shape[0]
+    Y = np.empty((M, N), np.uint16)
+    acc = np.empty((M, N), np.float32) if want_acc else None
+    lib().orc_gemm_mxfp4mx8(_p(A), _p(AE), _p(B), _p(BS), I64(M), I64(N), I64(K), _p(Y),
+                            _p(acc) if want_acc else None)
+    return (Y, acc) if want_acc else Y
+
+
+def truth_mxfp4mx8(A, AE, B, BS):
+    A, B, AE, BS = _c(A, np.uint8), _c(B, np.uint8), _c(AE, np.uint8), _c(BS, np.uint8)
+    M, K = A.shape
+    N = B.shape[0]
+    Yt = np.empty((M, N), np.float64)
+    Ya = np.empty((M, N), np.float64)
+    lib().orc_truth_mxfp4mx8(_p(A), _p(AE), _p(B), _p(BS), I64(M), I64(N), I64(K), _p(Yt), _p(Ya))
+    return Yt, Ya
+
+
 # ---- numpy helpers shared by the graders ----
 def bf16_bits_to_f32(h: np.ndarray) -> np.ndarray:
     return (h.astype(np.uint32) << 16).view(np.float32)

@@ -587,6 +587,54 @@ ORC_API void orc_truth_mxfp4a8(const uint8_t* A, const float* AS, const uint8_t*
         }
 }
 
+/* ------------------------------------------------------------------ mxfp4 weights x mxfp8 activations
+ * (dtype spelling "mxfp4mx8": e2m1 + E8M0/32 weights, e4m3 + E8M0/32 activations -- the OCP-MX pair
+ * the tensor core scales by itself). PARITY UNPINNED: the reference has no such band; the rule is the
+ * mxfp4a8 rule (src/r3d_gemm_mxfp4.hip:14-15 of libr3d) with the activation's f32 scale per 128
+ * replaced by its E8M0 scale per 32:
+ *   per 32-of-K group ascending: s = sum a_k * w_k (f32); acc += (s * 2^(xa-127)) * 2^(xw-127) */
+ORC_API void orc_gemm_mxfp4mx8(const uint8_t* A, const uint8_t* AE, const uint8_t* B,
+                               const uint8_t* BS, int64_t M, int64_t N, int64_t K,
+                               uint16_t* Y, float* Yacc) {
+    const int64_t K32 = (K + 31) / 32;
+    float lut[256];
+    for (int i = 0; i < 256; ++i) lut[i] = e4m3_to_f32((uint8_t)i);
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+        const uint8_t* brow = B + n * (K / 2);
+        for (int64_t m = 0; m < M; ++m) {
+            float acc = 0.0f;
+            for (int64_t g = 0; g < K32; ++g) {
+                float s = 0.0f;
+                const int64_t kend = (g * 32 + 32 < K) ? g * 32 + 32 : K;
+                for (int64_t kk = g * 32; kk < kend; ++kk)
+                    s += lut[A[m * K + kk]] * e2m1_to_f32(nib_at(brow, kk));
+                acc += (s * e8m0_to_f32(AE[m * K32 + g])) * e8m0_to_f32(BS[n * K32 + g]);
+            }
+            if (Y) Y[m * N + n] = f32_to_bf16(acc);
+            if (Yacc) Yacc[m * N + n] = acc;
+        }
+    }
+}
+
+ORC_API void orc_truth_mxfp4mx8(const uint8_t* A, const uint8_t* AE, const uint8_t* B,
+                                const uint8_t* BS, int64_t M, int64_t N, int64_t K,
+                                double* Yt, double* Yabs) {
+    const int64_t K32 = (K + 31) / 32;
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n)
+        for (int64_t m = 0; m < M; ++m) {
+            double acc = 0.0, ab = 0.0;
+            for (int64_t k = 0; k < K; ++k) {
+                const double sc = (double)e8m0_to_f32(AE[m * K32 + (k >> 5)]) * (double)e8m0_to_f32(BS[n * K32 + (k >> 5)]);
+                const double p = (double)e4m3_to_f32(A[m * K + k]) *
+                                 (double)e2m1_to_f32(nib_at(B + n * (K / 2), k)) * sc;
+                acc += p; ab += std::fabs(p);
+            }
+            Yt[m * N + n] = acc; if (Yabs) Yabs[m * N + n] = ab;
+        }
+}
+
 /* The host threads later calls use (0 or less: leave as is). A launcher may have exported
  * OMP_NUM_THREADS=1 for its ranks; the timed baseline asks for the cores it is meant to use. */
 ORC_API void orc_set_threads(int n) {

@@ -86,6 +86,19 @@ def case_mxfp4(seed: int, M: int, N: int, K: int, scale_lo: int = 119, scale_hi:
     return dict(A=A, AS=AS, B=B, BS=BS)
 
 
+def case_mxfp4mx8(seed: int, M: int, N: int, K: int, spread: int = 0):
+    """mxfp4 weights as in case_mxfp4; activations bf16 N(0,1) (optionally with per-block magnitudes
+    spread over 2^+-spread) through the OCP-MX quantiser of the CPU checker: e4m3 codes A and one
+    E8M0 byte per 32 columns AE. Parity unpinned (the reference has no such activation format)."""
+    w = case_mxfp4(seed, 1, N, K)
+    rng = np.random.default_rng(seed + 7)
+    x = act_bf16(rng, M, K)
+    if spread:
+        x = bf16_round(x * np.exp2(rng.integers(-spread, spread + 1, (M, K // 32))).repeat(32, axis=1).astype(np.float32))
+    A, AE = orc.quant_act_mx8(x)
+    return dict(A=A, AE=AE, B=w["B"], BS=w["BS"])
+
+
 def case_logits(seed: int, M: int, N: int, K: int, br: int, sdt: int):
     """LM head in the reference test's distributions (tools/test_logits_e4m3.cpp:55-95):
     random e4m3 bytes (NaN codes excluded here), x uniform(-2,2) in bf16, scales exp(U(-2,2))

@@ -69,6 +69,26 @@ def gemm_launch(kind: str, case: dict, arm: int, a_dev=None) -> np.ndarray:
     return out.get()
 
 
+def mx8_launch(case: dict, arm: int) -> np.ndarray:
+    """gemm_nt_q @ mxfp4mx8 through the launch layer: case has A (e4m3), AE (E8M0 [M, K/32]), B, BS."""
+    P = ops.plugin()
+    A, AE, B, BS = dev(case["A"]), dev(case["AE"]), dev(case["B"]), dev(case["BS"])
+    M, K = case["A"].shape
+    N = case["B"].shape[0]
+    out = GuardedOut((M, N), np.uint16)
+    q = abi.R3dGemmQ()
+    q.a, q.a_scale, q.b, q.b_scale, q.y = A.data_ptr(), AE.data_ptr(), B.data_ptr(), BS.data_ptr(), out.ptr
+    q.m, q.n, q.k = M, N, K
+    q.as_cols, q.bs_cols = K // 32, K // 32
+    q.a_pitch, q.b_pitch, q.y_pitch, q.as_pitch, q.bs_pitch = K, K // 2, N, K // 32, K // 32
+    q.rblk, q.bs_dtype, q.arm = 1, abi.RAD_E8M0, arm
+    rc = P.lib.r3d_b200_gemm_mxfp4mx8(C.byref(q), None)
+    assert rc == abi.RAD_OK, abi.STATUS_NAMES[rc]
+    y = out.get()
+    assert P.lib.r3d_b200_stream_status() == 0
+    return y
+
+
 def q8x_launch(case: dict, walk: int, want_tc: bool | None = None):
     """The int8 arm through the launch layer with caller scratch; returns (Y bits, x8, sg).
     want_tc: assert that the dots run on the tensor core (True) or on dp4a (False)."""

@@ -427,6 +427,48 @@ def test_prefill_pair_kernel_whole_k_scales_within_2ulp(M, N, K):
     assert np.array_equal(gu.gemm_launch("fp8a8", case, EX), orc.gemm_fp8a8(case["A"], case["AS"], case["B"], case["BS"], 1))
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 130, 256), (5, 200, 512), (16, 128, 1024), (70, 64, 384)])
+def test_mxfp4mx8_exact_arm_bit_identical_to_oracle(M, N, K):
+    """mxfp4 weights x mxfp8 activations (E8M0 per 32 on both sides; no reference row: the CPU
+    checker fixes the rule): the oracle-order kernel, any M, K a multiple of 32."""
+    case = gen.case_mxfp4mx8(5500 + M, M, N, K, spread=6)
+    assert np.array_equal(gu.mx8_launch(case, EX), orc.gemm_mxfp4mx8(case["A"], case["AE"], case["B"], case["BS"]))
+
+
+@pytest.mark.parametrize("M,N,K", [(65, 130, 512), (100, 128, 512), (192, 256, 1024), (300, 520, 1536), (481, 384, 2560),
+                                   (722, 1000, 2560), (1100, 777, 1024), (513, 2048, 5120)])
+def test_mxfp4mx8_pair_kernel_within_2ulp(M, N, K):
+    """The CTA-pair kernel with both scale sets applied by the tensor core from tensor memory:
+    ragged tile lists, scale tiles that end inside a tile (K = 1536, 2560: 12 and 20 stages),
+    activation block magnitudes spread over 2^+-6 so that a misplaced scale byte cannot hide."""
+    case = gen.case_mxfp4mx8(5600 + M, M, N, K, spread=6)
+    _, acc = orc.gemm_mxfp4mx8(case["A"], case["AE"], case["B"], case["BS"], want_acc=True)
+    _, ab = orc.truth_mxfp4mx8(case["A"], case["AE"], case["B"], case["BS"])
+    g = gu.grade_bf16(gu.mx8_launch(case, TILE), acc, ab)
+    assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 5e-3, g
+
+
+@pytest.mark.parametrize("N,K", [(27648, 5120), (5120, 13824)])
+def test_config_c4_prefill_mxfp4mx8_full_size_sampled(N, K):
+    """M = 8192, mxfp4 weights x mxfp8 activations at the benchmark's layer geometry: the pair kernel
+    against the CPU oracle on 48 token rows x 384 weight rows, nothing left unwritten."""
+    M = 8192
+    rng = np.random.default_rng(79)
+    case = gen.case_mxfp4mx8(44, 256, N, K, spread=3)
+    reps = M // 256
+    perm = rng.permutation(M)
+    case["A"] = np.ascontiguousarray(np.tile(case["A"], (reps, 1))[perm])
+    case["AE"] = np.ascontiguousarray(np.tile(case["AE"], (reps, 1))[perm])
+    got = gu.mx8_launch(case, TILE)
+    assert np.count_nonzero(got & 0x7FFF) > got.size * 0.99
+    ts = np.concatenate([np.arange(8), np.arange(M - 8, M), rng.choice(M, 32, replace=False)])
+    ns = np.concatenate([np.arange(128), np.arange(N - 128, N), rng.choice(N, 128, replace=False)])
+    _, acc = orc.gemm_mxfp4mx8(case["A"][ts], case["AE"][ts], case["B"][ns], case["BS"][ns], want_acc=True)
+    _, ab = orc.truth_mxfp4mx8(case["A"][ts], case["AE"][ts], case["B"][ns], case["BS"][ns])
+    g = gu.grade_bf16(got[np.ix_(ts, ns)], acc, ab)
+    assert g["floored_bad"] == 0 and g["frac_le2"] > 0.999 and g["rel_l2"] < 5e-3, g
+
+
 @pytest.mark.parametrize("N,K", [(27648, 5120), (5120, 13824)])
 def test_config_c4_prefill_channel_scales_full_size_sampled(N, K):
     """M = 8192 with per-token / per-channel f32 scales at the benchmark's layer geometry: the pair

@@ -75,7 +75,7 @@ def test_schemas_entry_for_entry(plug):
 
 def test_rows_names_priorities_constraints(plug):
     rows = {r.name: r for r in plug.rows()}
-    want = {"logits_gemm_e4m3": 1000, "gemm_nt_q_mxfp4": 1000, "gemm_nt_q_fp8a8": 1000,
+    want = {"logits_gemm_e4m3": 1000, "gemm_nt_q_mxfp4": 1000, "gemm_nt_q_mxfp4mx8": 1000, "gemm_nt_q_fp8a8": 1000,
             "gemm_nt_q_fp8a8_decode": 1100, "gemm_nt_q_mxfp4_decode": 1100,
             "gemm_nt_q_mxfp4_decode_q8x": 1200, "gemm_nt_q_gated_fp8a8": 1000,
             "quant_act_fp8_act": 1000, "gated_quant_fp8_act": 1000, "rmsnorm_quant_fp8": 1000,
@@ -97,6 +97,8 @@ def test_band_resolution(plug):
     assert name(M=1, group=32, dtype="mxfp4a8") == "gemm_nt_q_mxfp4_decode_q8x"
     assert name(M=8, group=32, dtype="mxfp4a8") == "gemm_nt_q_mxfp4_decode_q8x"
     assert name(M=16, group=32, dtype="mxfp4a8") == "gemm_nt_q_mxfp4"
+    assert name(M=8192, group=32, dtype="mxfp4mx8") == "gemm_nt_q_mxfp4mx8"
+    assert name(M=1, group=32, dtype="mxfp4mx8") == "gemm_nt_q_mxfp4mx8"
     assert name(M=4, group=128, dtype="fp8a8") == "gemm_nt_q_fp8a8_decode"
     assert name(M=9, group=128, dtype="fp8a8") == "gemm_nt_q_fp8a8"
     assert plug.resolve("gemm_nt_q", dict(M=1, N=8, K=200, group=128, dtype="fp8a8")) is None
@@ -148,7 +150,7 @@ def _rows_under(env):
     return set(out[0].split(",")), out[1], out[2]
 
 
-ALL = {"logits_gemm_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode",
+ALL = {"logits_gemm_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_mxfp4mx8", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode",
        "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_gated_fp8a8",
        "quant_act_fp8_act", "gated_quant_fp8_act", "rmsnorm_quant_fp8", "rowtopk_bf16", "sample_argmax_f32"}
 
@@ -158,7 +160,7 @@ ALL = {"logits_gemm_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a
     ({"R3D_MXFP4_Q8X": "0"}, {"gemm_nt_q_mxfp4_decode_q8x"}, "gemm_nt_q_mxfp4_decode", "gemm_nt_q_fp8a8_decode"),
     ({"R3D_MXFP4_Q8X": "1"}, set(), "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_fp8a8_decode"),
     ({"R3D_NO_FP4_DEC": "1"}, {"gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x"}, "gemm_nt_q_mxfp4", "gemm_nt_q_fp8a8_decode"),
-    ({"R3D_NO_MXFP4": ""}, {"gemm_nt_q_mxfp4", "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x"}, "-", "gemm_nt_q_fp8a8_decode"),
+    ({"R3D_NO_MXFP4": ""}, {"gemm_nt_q_mxfp4", "gemm_nt_q_mxfp4mx8", "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x"}, "-", "gemm_nt_q_fp8a8_decode"),
     ({"R3D_NO_FP8_DEC": "1"}, {"gemm_nt_q_fp8a8_decode"}, "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_fp8a8"),
     ({"R3D_NO_FP8A8": "1"}, {"gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode", "gemm_nt_q_gated_fp8a8"}, "gemm_nt_q_mxfp4_decode_q8x", "-"),
 ])
