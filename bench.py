@@ -26,7 +26,8 @@ configuration of the hot path on one GPU, one line each.
 The line also carries `per_M` (each M timed alone), `spread` (the K-step region is timed five
 times, the median is the value), `rows` (the band's other decode row on the same planes: the
 int8-per-32 row the resolver picks by default), `rot_sweep` (2 / 4 / 8 rotating planes) and `c5`
-(the sharded LM head, strong scaling, bf16 logits).
+(the sharded LM head, strong scaling, bf16 logits) and, on one GPU, `c4` (the prefill band at
+M = 8192 in TFLOP/s against the measured MMA-issue rate).
 
 --impl reference: the reference's arithmetic for this path on the host cores (the CPU
 restatement, all cores; the reference has no CPU implementation of this path), same metric and
@@ -566,6 +567,82 @@ def _timed(run, regions: int, fence):
     return out
 
 
+def mma_peak(P, kind: int) -> float:
+    """TFLOP/s of the MMA-issue kernel (operands resident in shared memory, nothing loaded or stored):
+    the measured tensor-pipe rate the prefill fractions divide by. kind 0 e4m3 x e4m3, 1 block-scaled
+    e2m1 x e4m3."""
+    import torch
+    iters = 4000
+    vals = []
+    for rep in range(4):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        flops = P.lib.r3d_b200_mma_peak(kind, iters, None)
+        e1.record()
+        torch.cuda.synchronize()
+        if flops <= 0:
+            return float("nan")
+        if rep:
+            vals.append(flops / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    return statistics.median(vals)
+
+
+def c4_record(P, dev):
+    """The prefill band (configuration C4) as a sub-record: M = 8192 tokens over (K=5120, N=27648) and
+    (K=13824, N=5120), fp8 W8A8 with per-channel / per-token f32 scales and mxfp4 weights x mxfp8
+    activations; TFLOP/s and the fraction of the measured MMA-issue rate of the same tensor-core kind."""
+    import ctypes as C
+    import torch
+    from libr3d_b200 import abi, ops
+    g = torch.Generator(device=dev).manual_seed(4)
+    peaks = {"fp8a8/channel": mma_peak(P, 0), "mxfp4mx8": mma_peak(P, 1)}
+    M, res = 8192, []
+    for kind in ("fp8a8/channel", "mxfp4mx8"):
+        for (K, N) in ((5120, 27648), (13824, 5120)):
+            x = torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
+            q = abi.R3dGemmQ()
+            if kind == "mxfp4mx8":
+                A, _ = ops.quant_act_fp8(x, 128)
+                AS = torch.randint(118, 122, (M, K // 32), dtype=torch.uint8, device=dev, generator=g)
+                B = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=g)
+                BS = torch.randint(119, 124, (N, K // 32), dtype=torch.uint8, device=dev, generator=g)
+                q.as_cols, q.as_pitch, q.bs_cols, q.bs_pitch, q.b_pitch = K // 32, K // 32, K // 32, K // 32, K // 2
+                q.rblk, q.bs_dtype, fn = 1, abi.RAD_E8M0, P.lib.r3d_b200_gemm_mxfp4mx8
+            else:
+                A, AS = ops.quant_act_fp8(x, K)
+                B = torch.randint(0, 127, (N, K), dtype=torch.uint8, device=dev, generator=g)
+                BS = torch.rand((N, 1), device=dev, generator=g) * 0.01 + 0.001
+                q.as_cols, q.as_pitch, q.bs_cols, q.bs_pitch, q.b_pitch = 1, 1, 1, 1, K
+                q.rblk, q.bs_dtype, fn = 1, abi.RAD_F32, P.lib.r3d_b200_gemm_fp8a8
+            Y = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
+            q.a, q.a_scale, q.b, q.b_scale, q.y = A.data_ptr(), AS.data_ptr(), B.data_ptr(), BS.data_ptr(), Y.data_ptr()
+            q.m, q.n, q.k, q.a_pitch, q.y_pitch, q.arm = M, N, K, K, N, abi.R3D_ARM_AUTO
+            for _ in range(2):
+                assert fn(C.byref(q), None) == 0
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(5):
+                    fn(C.byref(q), None)
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) / 5)
+            ms = statistics.median(ts)
+            tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+            ok = int(torch.count_nonzero(Y.view(torch.int16))) > 0.9 * M * N
+            res.append({"contract": kind, "M": M, "N": N, "K": K, "ms_per_call": round(ms, 4), "TFLOPs": round(tf, 1),
+                        "frac_of_measured_mma_rate": round(tf / peaks[kind], 3), "frac_of_nominal_dense_fp8": round(tf / 4500.0, 3),
+                        "nonzero_ok": ok})
+            del x, A, AS, B, BS, Y
+            torch.cuda.empty_cache()
+    return {"workload": "C4 prefill, M=8192 (weights and activations larger than L2 together; 5 calls per region, median of 3)",
+            "mma_issue_rate_TFLOPs": {k: round(v, 1) for k, v in peaks.items()},
+            "mma_issue_rate_how": "r3d_b200_mma_peak: every CTA pair issues 16000 cta_group::2 MMAs from resident shared-memory tiles, CUDA events",
+            "results": res, "status": int(P.lib.r3d_b200_stream_status())}
+
+
 def c5_record(args, P, dev, world: int, rank: int, peak: float):
     """The sharded LM head (configuration C5) as a sub-record: N = 151936, K = 5120, M in {1, 4, 16},
     e4m3 head with a bf16 scale per 128x128 block, column slabs over the ranks (strong scaling),
@@ -815,7 +892,7 @@ def main():
         return STEP_BYTES * steps * world / (m_ * 1e-3) / 1e9, m_ / steps
 
     per_m_main = per_m(args.row, rot)
-    rows_rec, rot_sweep, c5 = None, None, None
+    rows_rec, rot_sweep, c5, c4 = None, None, None, None
     if not args.no_sub:
         sub_steps = min(args.steps, 200)
         if not push:
@@ -927,6 +1004,11 @@ def main():
             c5 = c5_record(args, P, dev, world, rank, peak)
         except Exception as ex:                          # noqa: BLE001 - the headline stands without the sub-record
             c5 = {"unavailable": f"{type(ex).__name__}: {ex}"}
+        if world == 1:
+            try:
+                c4 = c4_record(P, dev)
+            except Exception as ex:                      # noqa: BLE001
+                c4 = {"unavailable": f"{type(ex).__name__}: {ex}"}
 
     if rank == 0:
         per_launch_s = ms * 1e-3 / (3 * args.steps)
@@ -971,6 +1053,8 @@ def main():
             line["rot_sweep"] = rot_sweep
         if c5 is not None:
             line["c5"] = c5
+        if c4 is not None:
+            line["c4"] = c4
         if world == 1 and not args.no_cpu:
             v, dt, threads = cpu_step_sample(N_DIM, 3)
             line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",

@@ -195,6 +195,13 @@ int r3d_b200_gated_quant_fp8(const void* gu, int64_t gu_pitch, void* q, int64_t 
                              int32_t n, int32_t group, int32_t silu, void* stream);
 int r3d_b200_stream_status(void);
 
+/* The tensor pipe's issue rate, the denominator of the prefill band's fraction: one launch in which
+ * every CTA pair issues `iters` stages of four K=32 cta_group::2 MMAs from operand tiles resident in
+ * shared memory (kind 0: e4m3 x e4m3, 256 x 256 per instruction; kind 1: block-scaled e2m1 x e4m3,
+ * 256 x 192). Returns the FLOPs of the launch for the caller to divide by its event time, negative
+ * on failure. No counterpart in the reference. */
+double r3d_b200_mma_peak(int kind, int iters, void* stream);
+
 /* Kernels this library launched since load (all arms): bench bookkeeping. */
 long long r3d_b200_launch_count(void);
 

@@ -441,6 +441,78 @@ k_tc_gemm_mx(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
     }
 }
 
+/* ------------------------------------------------------------------ MMA-issue rate
+ * The denominator for the prefill band's tensor-pipe fraction: one kernel, every CTA pair's operand
+ * tiles resident in shared memory (filled once with hashed bytes), the pair's leader issues `iters`
+ * stages of four K=32 MMAs back to back into two alternating accumulators, nothing is loaded or
+ * stored in the timed part. kind 0: f8f6f4 e4m3 x e4m3, 256 x 256 per instruction; kind 1:
+ * mxf8f6f4 block-scaled e2m1 x e4m3, 256 x 192, scale factors in tensor memory. */
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
+k_mma_peak(const int kind, const int iters) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t done;
+    __shared__ uint32_t tmem_slot;
+    const int warp = threadIdx.x >> 5;
+    const uint32_t crank = cluster_rank();
+    /* four stages of operand tiles; e4m3 bytes with the exponent kept small so that no NaN code occurs */
+    for (int i = threadIdx.x; i < 4 * kStage / 4; i += blockDim.x) {
+        uint32_t h = (uint32_t)i * 2654435761u + blockIdx.x * 40503u;
+        h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+        ((uint32_t*)smem)[i] = kind == 1 ? (h & 0x0f0f0f0fu) | ((h >> 3) & 0x30303030u) & 0x3f3f3f3fu : h & 0x3f3f3f3fu;
+    }
+    if (threadIdx.x == 0) {
+        mbar_init(&done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    if (kind == 1) {
+        /* scale factors 2^0 in the sixteen columns behind the accumulators, every lane */
+        const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
+        for (int c = 0; c < 16; ++c) tmem_st1(tlane + kSfBaseM + c, 0x7f7f7f7fu);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    if (warp == 1 && crank == 0 && elect_one()) {
+        const uint32_t idesc_f8 = (1u << 4) | ((uint32_t)(kTok >> 3) << 17) | ((uint32_t)((2 * kRows) >> 4) << 24);
+        const uint32_t idesc_mx = (5u << 7) | ((uint32_t)(kTokM >> 3) << 17) | (1u << 23) | ((uint32_t)((2 * kRows) >> 4) << 24);
+        for (int it = 0; it < iters; ++it) {
+            const uint32_t a0 = smem_u32(smem + (it & 3) * kStage), b0 = a0 + kWBytes;
+            const uint32_t d = tmem_base + (uint32_t)((it >> 3) & 1) * (kind == 1 ? kTokM : kTok);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (kind == 1)
+                    umma2_mxf8(d, smem_desc_sw128(a0 + k * 32), smem_desc_sw128(b0 + k * 32),
+                               idesc_mx | ((uint32_t)k << 29) | ((uint32_t)k << 4), tmem_base + kSfBaseM, tmem_base + kSfBaseM + 4,
+                               (it & 7) | k ? 1u : 0u);
+                else
+                    umma2_f8f6f4(d, smem_desc_sw128(a0 + k * 32), smem_desc_sw128(b0 + k * 32), idesc_f8, (it & 7) | k ? 1u : 0u);
+            }
+        }
+        umma2_commit(smem_u32(&done));
+        (void)mbar_wait(&done, 0, 79);
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
+    }
+}
+
 bool al(const void* p, int a) { return (((uintptr_t)p) & (uintptr_t)(a - 1)) == 0; }
 
 } /* anonymous namespace */
@@ -522,6 +594,25 @@ int tc_gemm_mx(const R3dGemmQ& p, cudaStream_t st) {
     count_launch();
     k_tc_gemm_mx<<<(unsigned)(2 * P.pairs), kThreadsM, smem, st>>>(*tw, *ta, *ts, *te, P);
     return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+}
+
+/* One launch of the MMA-issue kernel on every CTA pair of the device; returns the FLOPs it issues
+ * (the caller times the launch with events), or a negative status. */
+extern "C" double r3d_b200_mma_peak(int kind, int iters, void* stream) {
+    if (!device_is_sm100() || iters < 1 || (kind != 0 && kind != 1)) return -1.0;
+    const size_t smem = 1024 + 4 * (size_t)kStage;
+    static bool attr_set[kTcMaxDevices] = {};
+    const int dev = tc_device();
+    if (dev < 0) return -1.0;
+    if (!attr_set[dev]) {
+        if (cudaFuncSetAttribute(k_mma_peak, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1.0;
+        attr_set[dev] = true;
+    }
+    const int pairs = tc_sm_count() / 2;
+    count_launch();
+    k_mma_peak<<<(unsigned)(2 * pairs), 128, smem, (cudaStream_t)stream>>>(kind, iters);
+    if (cudaGetLastError() != cudaSuccess) return -1.0;
+    return 2.0 * 256.0 * (kind == 1 ? (double)kTokM : (double)kTok) * 128.0 * (double)iters * (double)pairs;
 }
 
 int tc_gemm2_status() {

@@ -29,7 +29,7 @@ EXPORTS = [
     "r3d_unrelayout_head",
     "r3d_b200_gemm_fp8a8", "r3d_b200_gemm_mxfp4a8", "r3d_b200_gemm_mxfp4a8_q8x",
     "r3d_b200_gemm_mxfp4a8_q8x_static", "r3d_b200_q8x_on_tensor_core", "r3d_b200_gemm_mxfp4mx8",
-    "r3d_rad_gemm_nt_q_mx8",
+    "r3d_rad_gemm_nt_q_mx8", "r3d_b200_mma_peak",
     "r3d_b200_logits", "r3d_b200_quant_act_fp8", "r3d_b200_pick_arm_fp8a8",
     "r3d_b200_pick_arm_mxfp4a8", "r3d_b200_launch_count", "r3d_b200_stream_status",
     "r3d_b200_gather_create", "r3d_b200_gather_connect", "r3d_b200_gather_buffer", "r3d_b200_gather_wait",
@@ -94,6 +94,8 @@ class Plugin:
                                                 C.c_int, C.c_void_p]
         L.r3d_b200_gemm_mxfp4a8_q8x_static.argtypes = [C.POINTER(abi.R3dGemmQ), C.c_int, C.c_void_p]
         L.r3d_b200_q8x_on_tensor_core.argtypes = [C.POINTER(abi.R3dGemmQ)]
+        L.r3d_b200_mma_peak.argtypes = [C.c_int, C.c_int, C.c_void_p]
+        L.r3d_b200_mma_peak.restype = C.c_double
         L.r3d_b200_logits.argtypes = [C.POINTER(abi.R3dLogits), C.c_void_p]
         L.r3d_rad_gemm_nt_q_gated_fp8_scratch.restype = C.c_int64
         L.r3d_rad_gemm_nt_q_gated_fp8_scratch.argtypes = [C.POINTER(abi.RadArgs)]
