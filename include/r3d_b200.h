@@ -72,6 +72,15 @@ bool r3d_mxfp4_q8x_off(void);
 /* logits_gemm over the joined e4m3 + block-scale head, f32 logits. Replaces
  * r3d_rad_logits_gemm_e4m3 (src/r3d_gemm_logits.hip:145-226). */
 int r3d_rad_logits_gemm_e4m3(const RadArgs* a, RadStream s);
+/* logit_rerank over the same joined head: R <= 32 candidate ids a row rescored by a double-precision
+ * chain in ascending k and re-sorted (larger value, ties to the lower id, pads last). Replaces
+ * r3d_rad_logit_rerank_e4m3 (src/r3d_logit_rerank_e4m3.hip:146-345). */
+int r3d_rad_logit_rerank_e4m3(const RadArgs* a, RadStream s);
+/* Forget the remembered header of a head blob (the rows above copy a device-resident blob's
+ * rad.planes header to the host on first sight of its address): call it when the blob's memory is
+ * released or rewritten. No counterpart in the reference, which reads the header through the
+ * operand pointer on every call. */
+void r3d_b200_forget_head(const void* blob);
 /* Layout hooks of that row. Replace r3d_layout_head / r3d_relayout_head /
  * r3d_unrelayout_head (src/r3d_gemm_logits.hip:233-272). */
 int r3d_layout_head(const RadParam* p, int n_p, int operand, const RadEncoding* enc,

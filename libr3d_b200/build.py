@@ -29,6 +29,7 @@ SOURCES = [
     "launch.cu",
     "kern_exact.cu",
     "kern_topk.cu",
+    "kern_rerank.cu",
     "kern_q8x.cu",
     "q8x_static.cu",
     "kern_stream.cu",

@@ -18,6 +18,7 @@
 #include "entry_util.h"
 #include "rad_planes.h"
 #include "r3d_b200.h"
+#include "r3d_kernels.h"
 
 using namespace r3d;
 
@@ -29,31 +30,68 @@ struct HeadView {
                                    RAD_ENC_MAX_PLANES * sizeof(RadPlanesEntry)];
 };
 
-/* Host-readable copy of the blob's header + entry table, or nullptr. */
-const unsigned char* head_of(const void* blob) {
-    static std::vector<HeadView*> seen;
-    for (const HeadView* v : seen) if (v->blob == blob) return v->head;
+std::vector<HeadView*>& seen_heads() { static std::vector<HeadView*> v; return v; }
+
+bool read_head(HeadView* v) {
     cudaPointerAttributes at{};
-    const bool have = cudaPointerGetAttributes(&at, blob) == cudaSuccess;
+    const bool have = cudaPointerGetAttributes(&at, v->blob) == cudaSuccess;
     if (!have) (void)cudaGetLastError();
-    HeadView* v = new HeadView;
-    v->blob = blob;
     if (have && at.type == cudaMemoryTypeDevice) {
-        if (cudaMemcpy(v->head, blob, sizeof v->head, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        if (cudaMemcpy(v->head, v->blob, sizeof v->head, cudaMemcpyDeviceToHost) != cudaSuccess) {
             (void)cudaGetLastError();
-            delete v;
-            return nullptr;
+            return false;
         }
     } else {
-        memcpy(v->head, blob, sizeof v->head);      /* host, pinned or managed memory */
+        memcpy(v->head, v->blob, sizeof v->head);   /* host, pinned or managed memory */
     }
-    seen.push_back(v);
+    return true;
+}
+
+/* Host-readable copy of the blob's header + entry table, or nullptr. `*cached` says whether the
+ * copy was taken by an earlier call: the engine may have put another head at the same device
+ * address since (model reload, a caching allocator), so a caller whose validation of a cached
+ * copy fails calls refresh_head() and validates once more before it refuses. */
+const unsigned char* head_of(const void* blob, bool* cached) {
+    for (const HeadView* v : seen_heads()) if (v->blob == blob) { *cached = true; return v->head; }
+    *cached = false;
+    HeadView* v = new HeadView;
+    v->blob = blob;
+    if (!read_head(v)) { delete v; return nullptr; }
+    seen_heads().push_back(v);
     return v->head;
+}
+const unsigned char* refresh_head(const void* blob) {
+    for (HeadView* v : seen_heads()) if (v->blob == blob) return read_head(v) ? v->head : nullptr;
+    return nullptr;
+}
+
+struct HeadPlanes { const RadPlanesHeader* h; const RadPlanesEntry* ec; const RadPlanesEntry* es; };
+
+/* the checks of src/r3d_gemm_logits.hip:176-194 of libr3d on a host copy of the header */
+int check_head(const unsigned char* hv, long long N, long long K, HeadPlanes* out, int not_joined) {
+    const RadPlanesHeader* h = hv ? rad_planes_header(hv) : nullptr;
+    if (!h || h->n_planes != 2) return h ? RAD_E_DTYPE : not_joined;
+    if (h->transform[0]) return RAD_E_UNSUPPORTED;
+    const RadPlanesEntry* ec = nullptr;
+    const RadPlanesEntry* es = nullptr;
+    if (!rad_planes_find(hv, "codes", &ec) || !rad_planes_find(hv, "scale", &es) || !ec || !es)
+        return RAD_E_DTYPE;
+    if (ec->dtype != RAD_F8E4M3 || ec->block[0] != 1 || ec->block[1] != 1 ||
+        ec->rows != N || ec->cols != K) return RAD_E_SHAPE;
+    out->h = h; out->ec = ec; out->es = es;
+    return RAD_OK;
 }
 
 } /* namespace */
 
 extern "C" {
+
+/* Drop the remembered header of a head blob (call when the blob's memory is released or rewritten). */
+void r3d_b200_forget_head(const void* blob) {
+    std::vector<HeadView*>& v = seen_heads();
+    for (size_t i = 0; i < v.size(); ++i)
+        if (v[i]->blob == blob) { delete v[i]; v.erase(v.begin() + (long)i); return; }
+}
 
 int r3d_rad_logits_gemm_e4m3(const RadArgs* a, RadStream s) {
     const RadTensor* X = rad_arg_in(a, 0);
@@ -79,16 +117,15 @@ int r3d_rad_logits_gemm_e4m3(const RadArgs* a, RadStream s) {
     const int64_t y_pitch = Y->rank >= 2 ? Y->stride[Y->rank - 2] : N;
     if (x_pitch < K || y_pitch < N) return RAD_E_STRIDE;
 
-    const unsigned char* hv = head_of(W->data);
-    const RadPlanesHeader* h = hv ? rad_planes_header(hv) : nullptr;
-    if (!h || h->n_planes != 2) return RAD_E_DTYPE;
-    if (h->transform[0]) return RAD_E_UNSUPPORTED;
-    const RadPlanesEntry* ec = nullptr;
-    const RadPlanesEntry* es = nullptr;
-    if (!rad_planes_find(hv, "codes", &ec) || !rad_planes_find(hv, "scale", &es) || !ec || !es)
-        return RAD_E_DTYPE;
-    if (ec->dtype != RAD_F8E4M3 || ec->block[0] != 1 || ec->block[1] != 1 ||
-        ec->rows != N || ec->cols != K) return RAD_E_SHAPE;
+    bool cached = false;
+    const unsigned char* hv = head_of(W->data, &cached);
+    HeadPlanes hp{};
+    int hst = check_head(hv, N, K, &hp, RAD_E_DTYPE);
+    if (hst != RAD_OK && cached) hst = check_head(refresh_head(W->data), N, K, &hp, RAD_E_DTYPE);
+    if (hst != RAD_OK) return hst;
+    const RadPlanesHeader* h = hp.h;
+    const RadPlanesEntry* ec = hp.ec;
+    const RadPlanesEntry* es = hp.es;
     if (es->dtype != RAD_BF16 && es->dtype != RAD_F16 && es->dtype != RAD_F32)
         return RAD_E_UNSUPPORTED;
     if (es->block[1] != 128 || (es->block[0] != 1 && es->block[0] != 128)) return RAD_E_UNSUPPORTED;
@@ -112,6 +149,75 @@ int r3d_rad_logits_gemm_e4m3(const RadArgs* a, RadStream s) {
     l.x_pitch = x_pitch; l.code_pitch = ec->row_bytes; l.y_pitch = y_pitch;
     l.scale_pitch = es->row_bytes / (es->dtype == RAD_F32 ? 4 : 2);
     return r3d_b200_logits(&l, (void*)s);
+}
+
+/* logit_rerank over the joined e4m3 head (src/r3d_logit_rerank_e4m3.hip:226-345 of libr3d): operands
+ * x, head, idx_in, idx, val, pairs?; R <= 32; M = numel(x) / n_embd, never the M parameter; the same
+ * refusal order and codes as the reference's entry. */
+int r3d_rad_logit_rerank_e4m3(const RadArgs* a, RadStream s) {
+    static const bool off = env_present("R3D_NO_DFLASH");
+    if (off) return RAD_E_UNSUPPORTED;
+    if (a->n_t < 5) return RAD_E_INVAL;
+    const RadTensor* x = rad_arg_in(a, 0);
+    const RadTensor* w = rad_arg_in(a, 1);
+    const RadTensor* in = rad_arg_in(a, 2);
+    const RadTensor* idx = rad_arg_in(a, 3);
+    const RadTensor* val = rad_arg_in(a, 4);
+    const RadTensor* pairs = (a->n_t > 5 && a->t[5].data) ? &a->t[5] : nullptr;
+    if (!x || !w || !in || !idx || !val) return RAD_E_INVAL;
+    long long R = 1, K = 0, NV = 0, voff = 0, v = 0;
+    if (rad_args_geti(a, "R", &v)) R = v;
+    if (rad_args_geti(a, "n_embd", &v)) K = v;
+    if (rad_args_geti(a, "n_vocab", &v)) NV = v;
+    if (rad_args_geti(a, "vocab_off", &v)) voff = v;
+    if (R <= 0 || K <= 0 || NV <= 0) return RAD_E_SHAPE;
+    if (R > 32) return RAD_E_UNSUPPORTED;
+    const long long M = rad_tensor_numel(x) / K;
+    if (M <= 0 || M > 0xffff) return RAD_E_SHAPE;
+    if (rad_tensor_numel(in) < M * R || rad_tensor_numel(idx) < M * R || rad_tensor_numel(val) < M * R)
+        return RAD_E_SHAPE;
+    if (x->dtype != RAD_F32 && x->dtype != RAD_BF16) return RAD_E_DTYPE;
+    if (in->dtype != RAD_I32 || idx->dtype != RAD_I32 || val->dtype != RAD_F32) return RAD_E_DTYPE;
+
+    bool cached = false;
+    const unsigned char* hv = head_of(w->data, &cached);
+    HeadPlanes hp{};
+    int hst = check_head(hv, NV, K, &hp, RAD_E_UNSUPPORTED);
+    if (hst != RAD_OK && cached) hst = check_head(refresh_head(w->data), NV, K, &hp, RAD_E_UNSUPPORTED);
+    if (hst != RAD_OK) return hst;
+    const RadPlanesEntry* ec = hp.ec;
+    const RadPlanesEntry* es = hp.es;
+    if (ec->row_bytes != K) return RAD_E_STRIDE;
+    if (es->dtype != RAD_BF16 && es->dtype != RAD_F16 && es->dtype != RAD_F32) return RAD_E_DTYPE;
+    if (es->block[1] != 128 || (es->block[0] != 1 && es->block[0] != 128)) return RAD_E_DTYPE;
+    const int64_t srows = (NV + es->block[0] - 1) / es->block[0];
+    const int64_t scols = (K + 127) / 128;
+    if (es->rows != srows || es->cols != scols) return RAD_E_SHAPE;
+    if ((int64_t)hp.h->bytes < es->offset + es->rows * es->row_bytes) return RAD_E_SHAPE;
+    const int64_t sbytes = es->dtype == RAD_F32 ? 4 : 2;
+    if (es->row_bytes < scols * sbytes) return RAD_E_STRIDE;
+    const int64_t scale_rs = es->row_bytes / sbytes;
+
+    if (pairs && (pairs->dtype != RAD_F32 || rad_tensor_numel(pairs) < M * R * 2)) return RAD_E_SHAPE;
+    if (pairs) {
+        if (pairs->rank == 3) {
+            if (pairs->stride[2] != 1 || pairs->stride[1] != 2 || pairs->stride[0] != 2 * R) return RAD_E_STRIDE;
+        } else if (pairs->rank != 2 || pairs->stride[1] != 1 || pairs->stride[0] < 2 * R) return RAD_E_STRIDE;
+    }
+    auto row2 = [](const RadTensor* t, int64_t cols, int64_t* pitch) {
+        if (!t || t->rank != 2 || t->stride[1] != 1) return false;
+        *pitch = (t->shape[1] == cols) ? t->stride[0] : cols;
+        return true;
+    };
+    int64_t xp = 0, ip = 0, op = 0, vp = 0;
+    if (!row2(x, K, &xp) || !row2(in, R, &ip) || !row2(idx, R, &op) || !row2(val, R, &vp)) return RAD_E_STRIDE;
+    if (!r3d::device_is_sm100()) return RAD_E_UNSUPPORTED;
+    return r3d::launch_logit_rerank_e4m3(x->data, (int)x->dtype, xp, (const unsigned char*)w->data + ec->offset,
+                                         ec->row_bytes, (const unsigned char*)w->data + es->offset, scale_rs,
+                                         (int)es->block[0], (int)es->dtype, (const int32_t*)in->data, ip,
+                                         (int32_t*)idx->data, op, (float*)val->data, vp,
+                                         pairs ? (float*)pairs->data : nullptr, (int)M, (int)R, (int)K, NV, voff,
+                                         (cudaStream_t)(uintptr_t)s);
 }
 
 /* Admit exactly "codes, then one scale", affine, untransformed -- and only e4m3 codes.

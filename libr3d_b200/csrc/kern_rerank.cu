@@ -1,0 +1,138 @@
+/* kern_rerank.cu -- logit_rerank over the joined e4m3 LM head: R candidate ids a row rescored
+ * exactly and re-sorted.
+ *
+ * Contract (src/r3d_logit_rerank_e4m3.hip:22-39, :146-206 of libr3d), bit for bit: for row m and
+ * candidate r with global id g (local = g - vocab_off; g < 0 or local outside [0, n_vocab) is a pad:
+ * id -1, value -inf)
+ *     acc (double) = 0; for k ascending: hv = f32(code[local][k]) * scale[local / br][k / 128]  (ONE f32
+ *     rounding); acc += (double) f32(x[m][k]) * (double) hv   (the product of two floats is exact
+ *     in double, the add rounds); score = (float) acc
+ * then R rounds of selection under (larger value; ties to the LOWER id; pads last), ids / values /
+ * the optional (id bits, value) pairs plane written in that order.
+ *
+ * The double chain is serial by definition, so the work is laid out for its latency, not for a
+ * tensor core: one block of eight warps per row; the row's activations are widened to f32 once
+ * into shared memory by the whole block; every warp serves four candidates at once, eight lanes
+ * each: per step a lane fetches four consecutive codes of its candidate's head row (one 32-byte
+ * sector per candidate, against the reference's one thread per candidate striding its own row),
+ * forms the four exact products, and the segment's accumulator takes the 32 products of the step
+ * in ascending k through width-8 shuffles -- the same adds in the same order, four chains per
+ * FP64 instruction. Thread 0 runs the selection over shared memory.
+ */
+#include "r3d_kernels.h"
+#include "r3d_numerics.cuh"
+#include <cmath>
+
+namespace r3d {
+
+namespace {
+constexpr int kMaxR = 32;
+constexpr int kWarps = 8;
+
+__device__ __forceinline__ float ld_scale_any(const void* base, int64_t idx, int dt) {
+    if (dt == RAD_F32) return ((const float*)base)[idx];
+    if (dt == RAD_F16) return f16_to_f32(((const uint16_t*)base)[idx]);
+    return bf16_to_f32(((const uint16_t*)base)[idx]);
+}
+
+__global__ void __launch_bounds__(32 * kWarps)
+k_logit_rerank_e4m3(const uint8_t* __restrict__ x, int xdt, int64_t x_rs,
+                    const uint8_t* __restrict__ codes, int64_t code_rs,
+                    const void* __restrict__ scale, int64_t scale_rs, int br, int sdt,
+                    const int32_t* __restrict__ in, int64_t in_rs,
+                    int32_t* __restrict__ idx, int64_t idx_rs, float* __restrict__ val, int64_t val_rs,
+                    float* __restrict__ pairs, int R, int K, int64_t NV, int64_t voff, int x_in_smem) {
+    extern __shared__ float xs[];                         /* [K] when it fits */
+    __shared__ int32_t sid[kMaxR];
+    __shared__ float ssc[kMaxR];
+    const int64_t m = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    static_assert(kWarps * 4 >= kMaxR, "one pass over the candidates");
+    if (x_in_smem) {
+        for (int k = threadIdx.x; k < K; k += blockDim.x)
+            xs[k] = xdt == RAD_F32 ? ((const float*)x)[m * x_rs + k] : bf16_to_f32(((const uint16_t*)x)[m * x_rs + k]);
+        __syncthreads();
+    }
+    {
+        const int r = warp * 4 + (lane >> 3), j = lane & 7;      /* candidate slot of this 8-lane segment */
+        const int64_t g = r < R ? (int64_t)in[m * in_rs + r] : -1;
+        const int64_t local = g - voff;
+        const bool pad = r >= R || g < 0 || local < 0 || local >= NV;
+        const uint8_t* crow = codes + (pad ? 0 : local) * code_rs;
+        const int64_t sbase = pad ? 0 : (local / br) * scale_rs;
+        const bool al4 = ((((uintptr_t)codes) | (uintptr_t)code_rs) & 3) == 0;
+        double acc = 0.0;
+        for (int k0 = 0; k0 < K; k0 += 32) {
+            const int k = k0 + 4 * j;
+            double p[4] = {0.0, 0.0, 0.0, 0.0};
+            if (!pad && k < K) {
+                uint32_t cw;
+                if (al4 && k + 4 <= K) cw = *(const uint32_t*)(crow + k);
+                else {
+                    cw = 0u;
+                    for (int i = 0; i < 4; ++i) if (k + i < K) cw |= (uint32_t)crow[k + i] << (8 * i);
+                }
+                const float s = ld_scale_any(scale, sbase + (k >> 7), sdt);      /* k % 4 == 0: one block for all four */
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (k + i >= K) break;
+                    const float hv = __fmul_rn(e4m3_to_f32((uint8_t)(cw >> (8 * i))), s);
+                    const float xv = x_in_smem ? xs[k + i]
+                                               : (xdt == RAD_F32 ? ((const float*)x)[m * x_rs + k + i]
+                                                                 : bf16_to_f32(((const uint16_t*)x)[m * x_rs + k + i]));
+                    p[i] = __dmul_rn((double)xv, (double)hv);
+                }
+            }
+            const int n = min(32, K - k0);
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const double pj = __shfl_sync(0xffffffffu, p[i], jj, 8);
+                    if (jj * 4 + i < n) acc = __dadd_rn(acc, pj);
+                }
+        }
+        if (j == 0 && r < R) {
+            sid[r] = pad ? -1 : (int32_t)g;
+            ssc[r] = pad ? -INFINITY : (float)acc;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t used = 0u;
+        for (int o = 0; o < R; ++o) {
+            int best = -1;
+            for (int c = 0; c < R; ++c) {
+                if (((used >> c) & 1u) || sid[c] < 0) continue;
+                if (best < 0 || ssc[c] > ssc[best] || (ssc[c] == ssc[best] && sid[c] < sid[best])) best = c;
+            }
+            const int32_t oid = best >= 0 ? sid[best] : -1;
+            const float ov = best >= 0 ? ssc[best] : -INFINITY;
+            if (best >= 0) used |= 1u << best;
+            idx[m * idx_rs + o] = oid;
+            val[m * val_rs + o] = ov;
+            if (pairs) {
+                float* p = pairs + (m * R + o) * 2;
+                p[0] = __int_as_float(oid);
+                p[1] = ov;
+            }
+        }
+    }
+}
+} /* namespace */
+
+int launch_logit_rerank_e4m3(const void* x, int xdt, int64_t x_rs, const void* codes, int64_t code_rs,
+                             const void* scale, int64_t scale_rs, int br, int sdt, const int32_t* in, int64_t in_rs,
+                             int32_t* idx, int64_t idx_rs, float* val, int64_t val_rs, float* pairs, int M, int R,
+                             int K, int64_t NV, int64_t voff, cudaStream_t st) {
+    if (R < 1 || R > kMaxR || M < 1) return RAD_E_UNSUPPORTED;
+    const size_t want = (size_t)K * sizeof(float);
+    const int in_smem = want <= 48 * 1024 ? 1 : 0;       /* larger rows are read through the caches */
+    count_launch();
+    k_logit_rerank_e4m3<<<(unsigned)M, 32 * kWarps, in_smem ? want : 0, st>>>(
+        (const uint8_t*)x, xdt, x_rs, (const uint8_t*)codes, code_rs, scale, scale_rs, br, sdt, in, in_rs, idx, idx_rs,
+        val, val_rs, pairs, R, K, NV, voff, in_smem);
+    return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+}
+
+} /* namespace r3d */

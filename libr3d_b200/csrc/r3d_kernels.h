@@ -37,6 +37,12 @@ int launch_row_topk(const void* x, int x_dtype, int64_t x_pitch, int32_t* idx, i
                     int64_t val_pitch, float* pairs, int64_t pairs_pitch, int M, int N, int R, int64_t off,
                     cudaStream_t st);
 
+/* logit_rerank over the joined e4m3 head (kern_rerank.cu): pitches in elements; pairs may be null */
+int launch_logit_rerank_e4m3(const void* x, int xdt, int64_t x_rs, const void* codes, int64_t code_rs,
+                             const void* scale, int64_t scale_rs, int br, int sdt, const int32_t* in, int64_t in_rs,
+                             int32_t* idx, int64_t idx_rs, float* val, int64_t val_rs, float* pairs, int M, int R,
+                             int K, int64_t NV, int64_t voff, cudaStream_t st);
+
 /* weight-streaming tensor-core arm (kern_stream.cu); *_ok say whether the arm can take
  * the call's shape and alignment */
 bool stream_fp8a8_ok(const R3dGemmQ& p);

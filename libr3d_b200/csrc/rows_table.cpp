@@ -95,6 +95,17 @@ const RadOperandSpec kRowTopkOperands[] = {
     { "x", RAD_OPD_IN, 0 }, { "idx", RAD_OPD_OUT, 0 }, { "val", RAD_OPD_OUT, 0 }, { "pairs", RAD_OPD_OUT, 1 },
 };
 
+/* logit_rerank: src/r3d_rows.cpp:768-791, :1022-1030 */
+const RadParamSpec kRerankParams[] = {
+    { "M", RAD_P_INT, RAD_REQUIRED, 0 },         { "R", RAD_P_INT, RAD_REQUIRED, 0 },
+    { "n_vocab", RAD_P_INT, RAD_REQUIRED, 0 },   { "n_embd", RAD_P_INT, RAD_REQUIRED, 0 },
+    { "vocab_off", RAD_P_INT, RAD_OPTIONAL, 0 }, { "dtype", RAD_P_STR, RAD_REQUIRED, 0 },
+};
+const RadOperandSpec kRerankOperands[] = {
+    { "x", RAD_OPD_IN, 0 },    { "head", RAD_OPD_WEIGHT, 0 }, { "idx_in", RAD_OPD_IN, 0 },
+    { "idx", RAD_OPD_OUT, 0 }, { "val", RAD_OPD_OUT, 0 },     { "pairs", RAD_OPD_OUT, 1 },
+};
+
 /* sample_argmax: src/r3d_rows.cpp:285-288, :655-659 */
 const RadParamSpec kArgmaxParams[] = {
     { "M", RAD_P_INT, RAD_REQUIRED, 0 }, { "n_vocab", RAD_P_INT, RAD_REQUIRED, 0 },
@@ -104,6 +115,10 @@ const RadOperandSpec kArgmaxOperands[] = {
 };
 
 const RadOpSchema kSchemas[] = {
+    { "logit_rerank", kRerankParams, COUNT_OF(kRerankParams), kRerankOperands, COUNT_OF(kRerankOperands),
+      "R candidate ids a row rescored exactly against the full-precision head and re-sorted on those "
+      "values; `idx_in` carries global ids as row_topk reports them, `vocab_off` is this rank's first "
+      "column, an id outside its rows becomes a pad; ties break on the lower id." },
     { "sample_argmax", kArgmaxParams, COUNT_OF(kArgmaxParams), kArgmaxOperands, COUNT_OF(kArgmaxOperands),
       "greedy: the token of the largest logit, ties to the lower token id." },
     { "row_topk", kRowTopkParams, COUNT_OF(kRowTopkParams), kRowTopkOperands, COUNT_OF(kRowTopkOperands),
@@ -172,6 +187,11 @@ const RadConstraint kCRmsQuant[] = {
     { "dtype", RAD_C_IN, 0, "bf16" },
 };
 
+/* src/r3d_rows.cpp:784-791 */
+const RadConstraint kCRerank[] = {
+    { "M", RAD_C_GE, 1, nullptr },       { "R", RAD_C_GE, 1, nullptr },      { "R", RAD_C_LE, 32, nullptr },
+    { "n_vocab", RAD_C_GE, 1, nullptr }, { "n_embd", RAD_C_GE, 1, nullptr }, { "dtype", RAD_C_IN, 0, "bf16" },
+};
 /* src/r3d_rows.cpp:1255 */
 const RadConstraint kCArgmax[] = { { "n_vocab", RAD_C_GE, 1, nullptr } };
 /* src/r3d_rows.cpp:1412-1418 */
@@ -197,6 +217,18 @@ const RadKernelInfo kRows[] = {
       "bf16 x, joined e4m3 + bf16/f16/f32 head, f32 logits",
       RAD_DOMAIN_DEVICE, kPrioPlain, kCLogits, COUNT_OF(kCLogits), nullptr, 0, nullptr,
       nullptr, nullptr, r3d_rad_logits_gemm_e4m3, nullptr, r3d_layout_head,
+      r3d_relayout_head, nullptr, r3d_unrelayout_head, nullptr },
+
+    /* src/r3d_rows.cpp:2145-2162: the joined-e4m3 sibling of the plain-head rerank row, with the head's hooks */
+    { "logit_rerank_e4m3", "logit_rerank", "select",
+      "R candidates a row rescored exactly against the joined e4m3 lm_head: a double-precision chain in "
+      "ascending k per candidate (four candidates per warp, the products formed in parallel, the adds "
+      "in the oracle's order), then the oracle's selection sort",
+      "any M, R <= 32; the joined e4m3 head r3d_layout_head admits; M derives from numel(x)/n_embd; "
+      "idx_in/idx/val at their own row pitches, pairs only densely packed",
+      "bf16/f32 x, joined e4m3 + bf16/f16/f32 head, f32 values + i32 ids out, optional f32 pairs plane",
+      RAD_DOMAIN_DEVICE, kPrioPlain, kCRerank, COUNT_OF(kCRerank), nullptr, 0, nullptr,
+      nullptr, nullptr, r3d_rad_logit_rerank_e4m3, nullptr, r3d_layout_head,
       r3d_relayout_head, nullptr, r3d_unrelayout_head, nullptr },
 
     ROW("gemm_nt_q_mxfp4", "gemm_nt_q", "gemm",
@@ -303,6 +335,8 @@ bool row_hidden(const RadKernelInfo& k) {
     static const bool no_mx = getenv("R3D_NO_MXFP4") != nullptr;
     static const bool no_mx_dec = getenv("R3D_NO_FP4_DEC") != nullptr;
     static const bool q8x_off = r3d_mxfp4_q8x_off();
+    static const bool no_df = getenv("R3D_NO_DFLASH") != nullptr;      /* the drafter family's lever, src/r3d_rows.cpp:2224-2227 */
+    if (no_df && !strcmp(k.op, "logit_rerank")) return true;
     if (!strcmp(k.name, "gemm_nt_q_fp8a8")) return no_fp8;
     if (!strcmp(k.name, "gemm_nt_q_fp8a8_decode")) return no_fp8 || no_fp8_dec;
     if (!strcmp(k.name, "gemm_nt_q_gated_fp8a8")) return no_fp8;       /* src/r3d_rows.cpp:2235 */

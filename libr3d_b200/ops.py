@@ -127,6 +127,27 @@ def logits_gemm(x: torch.Tensor, head_blob: torch.Tensor, logits: torch.Tensor, 
     return r
 
 
+def logit_rerank(x: torch.Tensor, head_blob: torch.Tensor, idx_in: torch.Tensor, idx: torch.Tensor,
+                 val: torch.Tensor, pairs: torch.Tensor | None = None, *, n_vocab: int, n_embd: int,
+                 vocab_off: int = 0) -> Row:
+    """R candidate ids a row (idx_in int32 [M, R], global ids) rescored exactly against the joined e4m3
+    head and re-sorted: idx int32 [M, R], val f32 [M, R], optional pairs f32 [M, R, 2] (id bits, value).
+    x is bf16 or f32 [M, n_embd]."""
+    P = plugin()
+    M, R = idx_in.shape
+    query = dict(M=M, R=R, n_vocab=n_vocab, n_embd=n_embd, vocab_off=vocab_off, dtype="bf16")
+    r = P.resolve("logit_rerank", query)
+    if r is None:
+        raise RuntimeError(f"no row serves logit_rerank {query}")
+    xdt = abi.RAD_F32 if x.dtype == torch.float32 else abi.RAD_BF16
+    tensors = [_desc(x, xdt), _desc(head_blob, abi.RAD_U8), _desc(idx_in, abi.RAD_I32), _desc(idx, abi.RAD_I32),
+               _desc(val, abi.RAD_F32), _desc(pairs, abi.RAD_F32)]
+    rc = P.launch_row(r, ArgPack(tensors, query), _stream())
+    if rc != abi.RAD_OK:
+        raise RowRefused(r.name, rc)
+    return r
+
+
 def quant_act_fp8(x: torch.Tensor, group: int = 128) -> tuple[torch.Tensor, torch.Tensor]:
     """bf16/f32 activations [rows, n] -> (e4m3 codes uint8 [rows, n], f32 scale [rows, n/group])."""
     P = plugin()

@@ -29,7 +29,7 @@ EXPORTS = [
     "r3d_unrelayout_head",
     "r3d_b200_gemm_fp8a8", "r3d_b200_gemm_mxfp4a8", "r3d_b200_gemm_mxfp4a8_q8x",
     "r3d_b200_gemm_mxfp4a8_q8x_static", "r3d_b200_q8x_on_tensor_core", "r3d_b200_gemm_mxfp4mx8",
-    "r3d_rad_gemm_nt_q_mx8", "r3d_b200_mma_peak",
+    "r3d_rad_gemm_nt_q_mx8", "r3d_b200_mma_peak", "r3d_rad_logit_rerank_e4m3", "r3d_b200_forget_head",
     "r3d_b200_logits", "r3d_b200_quant_act_fp8", "r3d_b200_pick_arm_fp8a8",
     "r3d_b200_pick_arm_mxfp4a8", "r3d_b200_launch_count", "r3d_b200_stream_status",
     "r3d_b200_gather_create", "r3d_b200_gather_connect", "r3d_b200_gather_buffer", "r3d_b200_gather_wait",

@@ -119,6 +119,29 @@ def ref_logits() -> C.CDLL | None:
     return _ref_logits
 
 
+_ref_rerank: list = []
+
+
+def ref_rerank() -> C.CDLL | None:
+    """src/r3d_logit_rerank_e4m3.hip of libr3d compiled as it lies for sm_100a
+    (oracle/_ref/libref_rerank.so): entry ref_logit_rerank_e4m3(const RadArgs*, stream) plus a managed
+    allocator for the head blob. None when the library was not built."""
+    if not _ref_rerank:
+        so, R = HERE / "_ref" / "libref_rerank.so", None
+        if so.exists():
+            try:
+                R = C.CDLL(str(so))
+                R.ref_logit_rerank_e4m3.argtypes = [C.c_void_p, C.c_void_p]
+                R.ref_rerank_alloc.restype = C.c_void_p
+                R.ref_rerank_alloc.argtypes = [C.c_longlong]
+                R.ref_rerank_free.argtypes = [C.c_void_p]
+                R.ref_rerank_free.restype = None
+            except OSError:
+                R = None
+        _ref_rerank.append(R)
+    return _ref_rerank[0]
+
+
 _ref_gemm: dict = {}
 
 
@@ -345,6 +368,27 @@ def truth_mxfp4a8(A, AS, B, BS):
     lib().orc_truth_mxfp4a8(_p(A), _p(AS), _p(B), _p(BS), I64(M), I64(N), I64(K),
                             I64(AS.shape[1]), _p(Yt), _p(Ya))
     return Yt, Ya
+
+
+def logit_rerank_e4m3(X_bits, codes, scale, sdt: int, br: int, idx_in, vocab_off: int = 0):
+    """X_bits: bf16 bit patterns [M,K] (or float32 values); scale in its stored dtype (sdt 0 bf16 bits,
+    1 f16 bits, 2 f32). Returns (idx int32 [M,R], val f32 [M,R], pairs f32 [M,R,2])."""
+    X = X_bits if X_bits.dtype == np.float32 else bf16_bits_to_f32(X_bits)
+    X = _c(X, np.float32)
+    if sdt == 0:
+        sc = bf16_bits_to_f32(scale)
+    elif sdt == 1:
+        sc = scale.view(np.float16).astype(np.float32)
+    else:
+        sc = scale
+    sc, codes, idx_in = _c(sc, np.float32), _c(codes, np.uint8), _c(idx_in, np.int32)
+    M, K = X.shape
+    R = idx_in.shape[1]
+    NV = codes.shape[0]
+    idx = np.empty((M, R), np.int32); val = np.empty((M, R), np.float32); pairs = np.empty((M, R, 2), np.float32)
+    lib().orc_logit_rerank_e4m3(_p(X), _p(codes), _p(sc), I64(sc.shape[1]), C.c_int(br), _p(idx_in), I64(M), I64(R),
+                                I64(K), I64(NV), I64(vocab_off), _p(idx), _p(val), _p(pairs))
+    return idx, val, pairs
 
 
 def gemm_mxfp4mx8(A, AE, B, BS, want_acc: bool = False):

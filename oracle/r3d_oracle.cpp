@@ -587,6 +587,47 @@ ORC_API void orc_truth_mxfp4a8(const uint8_t* A, const float* AS, const uint8_t*
         }
 }
 
+/* ------------------------------------------------------------------ logit_rerank, joined e4m3 head
+ * src/r3d_logit_rerank_e4m3.hip:22-39 of libr3d (its statement of libref's ref_logit_rerank): per row
+ * m and candidate r with global id g, local = g - vocab_off; g < 0 or local outside [0, n_vocab) is
+ * a pad (id -1, value -inf); else acc (double) over k ascending, no FMA:
+ *   hv = f32(code[local][k]) * scale[local/br][k/128]  (one f32 rounding)
+ *   acc += (double) x[m][k] * (double) hv;   score = (float) acc
+ * then R rounds of selection: largest value, ties to the LOWER id, pads last. x is given widened
+ * to f32 (bf16 widens exactly), scale widened to f32. */
+ORC_API void orc_logit_rerank_e4m3(const float* X, const uint8_t* codes, const float* scale,
+                                   int64_t scale_cols, int br, const int32_t* in, int64_t M, int64_t R,
+                                   int64_t K, int64_t NV, int64_t voff, int32_t* idx, float* val,
+                                   float* pairs) {
+#pragma omp parallel for schedule(static)
+    for (int64_t m = 0; m < M; ++m) {
+        int32_t sid[64]; float ssc[64]; bool used[64];
+        for (int64_t r = 0; r < R; ++r) {
+            const int64_t g = in[m * R + r], local = g - voff;
+            used[r] = false;
+            if (g < 0 || local < 0 || local >= NV) { sid[r] = -1; ssc[r] = -INFINITY; continue; }
+            double acc = 0.0;
+            for (int64_t k = 0; k < K; ++k) {
+                const float hv = e4m3_to_f32(codes[local * K + k]) * scale[(local / br) * scale_cols + (k >> 7)];
+                acc += (double)X[m * K + k] * (double)hv;
+            }
+            sid[r] = (int32_t)g; ssc[r] = (float)acc;
+        }
+        for (int64_t o = 0; o < R; ++o) {
+            int best = -1;
+            for (int c = 0; c < R; ++c) {
+                if (used[c] || sid[c] < 0) continue;
+                if (best < 0 || ssc[c] > ssc[best] || (ssc[c] == ssc[best] && sid[c] < sid[best])) best = c;
+            }
+            const int32_t oid = best >= 0 ? sid[best] : -1;
+            const float ov = best >= 0 ? ssc[best] : -INFINITY;
+            if (best >= 0) used[best] = true;
+            idx[m * R + o] = oid; val[m * R + o] = ov;
+            if (pairs) { memcpy(&pairs[(m * R + o) * 2], &oid, 4); pairs[(m * R + o) * 2 + 1] = ov; }
+        }
+    }
+}
+
 /* ------------------------------------------------------------------ mxfp4 weights x mxfp8 activations
  * (dtype spelling "mxfp4mx8": e2m1 + E8M0/32 weights, e4m3 + E8M0/32 activations -- the OCP-MX pair
  * the tensor core scales by itself). PARITY UNPINNED: the reference has no such band; the rule is the

@@ -66,6 +66,10 @@ def test_schemas_entry_for_entry(plug):
     assert s["rmsnorm_quant_fp8"]["operands"] == [("x", IN, 0), ("residual", INOUT, 1), ("w", W, 0),
                                                   ("q", OUT, 0), ("scale", OUT, 0), ("out_bf16", OUT, 1)]
     assert s["row_topk"]["params"] == [("M", I, R), ("N", I, R), ("R", I, R), ("vocab_off", I, O), ("dtype", S, R)]
+    assert s["logit_rerank"]["params"] == [("M", I, R), ("R", I, R), ("n_vocab", I, R), ("n_embd", I, R),
+                                           ("vocab_off", I, O), ("dtype", S, R)]
+    assert s["logit_rerank"]["operands"] == [("x", IN, 0), ("head", W, 0), ("idx_in", IN, 0), ("idx", OUT, 0),
+                                             ("val", OUT, 0), ("pairs", OUT, 1)]
     assert s["sample_argmax"]["params"] == [("M", I, R), ("n_vocab", I, R)]
     assert s["sample_argmax"]["operands"] == [("logits", IN, 0), ("params", IN, 0), ("token", OUT, 0)]
     assert s["row_topk"]["operands"] == [("x", IN, 0), ("idx", OUT, 0), ("val", OUT, 0), ("pairs", OUT, 1)]
@@ -75,7 +79,7 @@ def test_schemas_entry_for_entry(plug):
 
 def test_rows_names_priorities_constraints(plug):
     rows = {r.name: r for r in plug.rows()}
-    want = {"logits_gemm_e4m3": 1000, "gemm_nt_q_mxfp4": 1000, "gemm_nt_q_mxfp4mx8": 1000, "gemm_nt_q_fp8a8": 1000,
+    want = {"logits_gemm_e4m3": 1000, "logit_rerank_e4m3": 1000, "gemm_nt_q_mxfp4": 1000, "gemm_nt_q_mxfp4mx8": 1000, "gemm_nt_q_fp8a8": 1000,
             "gemm_nt_q_fp8a8_decode": 1100, "gemm_nt_q_mxfp4_decode": 1100,
             "gemm_nt_q_mxfp4_decode_q8x": 1200, "gemm_nt_q_gated_fp8a8": 1000,
             "quant_act_fp8_act": 1000, "gated_quant_fp8_act": 1000, "rmsnorm_quant_fp8": 1000,
@@ -150,7 +154,7 @@ def _rows_under(env):
     return set(out[0].split(",")), out[1], out[2]
 
 
-ALL = {"logits_gemm_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_mxfp4mx8", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode",
+ALL = {"logits_gemm_e4m3", "logit_rerank_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_mxfp4mx8", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode",
        "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_gated_fp8a8",
        "quant_act_fp8_act", "gated_quant_fp8_act", "rmsnorm_quant_fp8", "rowtopk_bf16", "sample_argmax_f32"}
 
@@ -163,6 +167,7 @@ ALL = {"logits_gemm_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_mxfp4mx8", "gemm_nt_q_f
     ({"R3D_NO_MXFP4": ""}, {"gemm_nt_q_mxfp4", "gemm_nt_q_mxfp4mx8", "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x"}, "-", "gemm_nt_q_fp8a8_decode"),
     ({"R3D_NO_FP8_DEC": "1"}, {"gemm_nt_q_fp8a8_decode"}, "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_fp8a8"),
     ({"R3D_NO_FP8A8": "1"}, {"gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode", "gemm_nt_q_gated_fp8a8"}, "gemm_nt_q_mxfp4_decode_q8x", "-"),
+    ({"R3D_NO_DFLASH": "1"}, {"logit_rerank_e4m3"}, "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_fp8a8_decode"),
 ])
 def test_kill_switch_matrix(env, hidden, mx_row, f8_row):
     # levers act at registration: a hidden row is not enumerated and the band re-resolves
@@ -431,6 +436,67 @@ def test_logits_entry_refusals(plug):
     wrongn = np.frombuffer(planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), codes[:200]),
                                         ("scale", abi.RAD_BF16, (128, 128), scale)]), np.uint8).copy()
     assert rc(blob=wrongn) == SH
+
+
+def test_logit_rerank_entry_refusals(plug):
+    """every refusal of the rerank entry, status for status against the reference's own compiled entry
+    (src/r3d_logit_rerank_e4m3.hip:226-345), which reads the head's header on the host like this one"""
+    codes, scale = _head()
+    N, K = codes.shape
+    good = np.frombuffer(planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), codes),
+                                      ("scale", abi.RAD_BF16, (128, 128), scale)]), np.uint8).copy()
+    f = plug.entry("r3d_rad_logit_rerank_e4m3")
+    from oracle import oracle as orc
+    Rr = orc.ref_rerank()
+    M, R = 2, 4
+    buf = np.zeros(1 << 16, np.uint8)
+    IV, D = abi.RAD_E_INVAL, abi.RAD_E_DTYPE
+
+    def rc(blob=good, drop=None, **over):
+        t = dict(x=tensor_desc(buf.ctypes.data, abi.RAD_BF16, [M, K]),
+                 head=tensor_desc(blob.ctypes.data, abi.RAD_U8, [blob.size]),
+                 idx_in=tensor_desc(buf.ctypes.data, abi.RAD_I32, [M, R]),
+                 idx=tensor_desc(buf.ctypes.data, abi.RAD_I32, [M, R]),
+                 val=tensor_desc(buf.ctypes.data, abi.RAD_F32, [M, R]),
+                 pairs=tensor_desc(buf.ctypes.data, abi.RAD_F32, [M, R, 2]))
+        p = dict(M=M, R=R, n_vocab=N, n_embd=K, vocab_off=0, dtype="bf16")
+        for k, v in over.items():
+            if k in t:
+                t[k] = v
+            elif v is None:
+                p.pop(k)
+            else:
+                p[k] = v
+        ts = list(t.values())
+        if drop is not None:
+            ts = ts[:drop]
+        pack = ArgPack(ts, p)
+        got = f(C.byref(pack.args), None)
+        if Rr is not None:
+            assert Rr.ref_logit_rerank_e4m3(C.byref(pack.args), None) == got, (over, drop)
+        return got
+
+    assert rc(drop=4) == IV                                                               # fewer than five operands
+    assert rc(val=tensor_desc(None, abi.RAD_F32, [])) == IV
+    assert rc(n_vocab=None) == SH and rc(n_embd=None) == SH and rc(R=0) == SH
+    assert rc(R=33, idx_in=tensor_desc(buf.ctypes.data, abi.RAD_I32, [M, 33]), idx=tensor_desc(buf.ctypes.data, abi.RAD_I32, [M, 33]),
+              val=tensor_desc(buf.ctypes.data, abi.RAD_F32, [M, 33])) == U                 # R beyond the band
+    assert rc(idx=tensor_desc(buf.ctypes.data, abi.RAD_I32, [M, 3])) == SH
+    assert rc(x=tensor_desc(buf.ctypes.data, abi.RAD_F16, [M, K])) == D
+    assert rc(idx_in=tensor_desc(buf.ctypes.data, abi.RAD_F32, [M, R])) == D
+    bad = good.copy(); bad[0] ^= 0xFF
+    assert rc(blob=bad) == U                                                              # a plain head: not this row's
+    one = np.frombuffer(planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), codes)]), np.uint8).copy()
+    assert rc(blob=one) == D
+    i8 = np.frombuffer(planes_blob([("codes", abi.RAD_I8, (1, 1), codes),
+                                    ("scale", abi.RAD_BF16, (128, 128), scale)]), np.uint8).copy()
+    assert rc(blob=i8) == SH
+    g64 = np.frombuffer(planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), codes),
+                                     ("scale", abi.RAD_BF16, (128, 64), scale)]), np.uint8).copy()
+    assert rc(blob=g64) == D
+    assert rc(pairs=tensor_desc(buf.ctypes.data, abi.RAD_F32, [M, R])) == SH              # too small
+    assert rc(pairs=tensor_desc(buf.ctypes.data, abi.RAD_F32, [M, R, 2], [4 * R, 2, 1])) == ST   # not densely packed
+    assert rc(x=tensor_desc(buf.ctypes.data, abi.RAD_BF16, [M, K], [2 * K, 2])) == ST
 
 
 def _enc(roles=("codes", "scale"), dtypes=(abi.RAD_F8E4M3, abi.RAD_BF16), scheme=b"affine",
