@@ -60,6 +60,17 @@ int r3d_rad_gemm_nt_q(const RadArgs* a, RadStream s);
 /* gemm_nt_q @ mxfp4mx8, any M (row gemm_nt_q_mxfp4mx8): a_scale is an E8M0 plane [M, K/32]. No
  * counterpart in the reference; see r3d_b200_gemm_mxfp4mx8. */
 int r3d_rad_gemm_nt_q_mx8(const RadArgs* a, RadStream s);
+/* gemm_nt_q @ w2a8, the draft head's decode band (M <= 16), and its layout hooks: operand 3 (b_scale) is
+ * the canonical rad.planes join of the f16 scale and the u8 / u4 zero plane, operand 2 (the codes) is
+ * stored as it is. Replace r3d_rad_gemm_nt_q_w2a8_decode, r3d_layout_gemm_w2a8, r3d_relayout_gemm_w2a8,
+ * r3d_unrelayout_gemm_w2a8 (src/r3d_gemm_w2a8.hip:1317-1349, :1362-1436). */
+int r3d_rad_gemm_nt_q_w2a8_decode(const RadArgs* a, RadStream s);
+int r3d_layout_gemm_w2a8(const RadParam* p, int n_p, int operand, const RadEncoding* enc, const int* sel,
+                         const RadTensor* planes, int n, RadLayout* out);
+int r3d_relayout_gemm_w2a8(const RadParam* p, int n_p, int operand, const RadEncoding* enc, const int* sel,
+                           const RadTensor* planes, int n, void* dst, int64_t dst_bytes);
+int r3d_unrelayout_gemm_w2a8(const RadParam* p, int n_p, int operand, const RadEncoding* enc, const int* sel,
+                             const void* src, int64_t src_bytes, const RadTensor* planes, int n);
 /* gemm_nt_q @ mxfp4a8, decode band M <= 8, fp32 walk. Replaces
  * r3d_rad_gemm_nt_q_mxfp4_decode (src/r3d_gemm_mxfp4.hip:1715-1716). */
 int r3d_rad_gemm_nt_q_mxfp4_decode(const RadArgs* a, RadStream s);
@@ -164,6 +175,25 @@ int r3d_b200_q8x_on_tensor_core(const R3dGemmQ* q);
  * stream. The first call on a device resolves the array's address; make it before any
  * stream capture. This entry point has no counterpart in the reference. */
 int r3d_b200_gemm_mxfp4a8_q8x_static(const R3dGemmQ* q, int walk, void* stream);
+
+/* Operands of one gemm_nt_q @ w2a8 call (the draft head's decode band, M <= 16). */
+typedef struct R3dW2A8 {
+    const void*  a;         /* i8 codes [M, K] in quant_act_i8's step order (column k at index k with bits 2 and 3 swapped) */
+    const float* a_scale;   /* f32, one a row */
+    const void*  b;         /* u2 codes [N, K/4 bytes], code k of a row in byte k>>2 at bit 2*(k&3) */
+    const void*  scale;     /* f16 [N, K/128] */
+    const void*  zero;      /* u8 [N, K/128], or u4 (two a byte, low nibble first) when zero_u4 */
+    const float* a_sum;     /* f32 [K/128, mpad], group-major: the row's code sums per 128 of K */
+    void*        y;         /* bf16 [M, N] */
+    int32_t      m, n, k, mpad, zero_u4, reserved;
+    int64_t      a_pitch, as_pitch, y_pitch;   /* elements */
+    int64_t      b_pitch, zp_pitch;            /* bytes */
+    int64_t      sc_pitch;                     /* f16 elements */
+} R3dW2A8;
+
+/* Replaces the kernel dispatch of w2_launch (src/r3d_gemm_w2a8.hip:1058-1315): one thread per weight
+ * row, dp4a over byte-quads cut from the 2-bit plane, the oracle's flush per 128 of K; exact. */
+int r3d_b200_gemm_w2a8(const R3dW2A8* q, void* stream);
 
 typedef struct R3dLogits {
     const void* x;          /* bf16 [M, K] */

@@ -26,10 +26,13 @@ SOURCES = [
     "entries_gemm_q.cpp",
     "entries_band.cpp",
     "entries_logits.cpp",
+    "entries_w2a8.cpp",
+    "planes_cache.cpp",
     "launch.cu",
     "kern_exact.cu",
     "kern_topk.cu",
     "kern_rerank.cu",
+    "kern_w2a8.cu",
     "kern_q8x.cu",
     "q8x_static.cu",
     "kern_stream.cu",

@@ -24,47 +24,6 @@ using namespace r3d;
 
 namespace {
 
-struct HeadView {
-    const void* blob;               /* key: the operand's data pointer */
-    alignas(16) unsigned char head[sizeof(RadPlanesHeader) +
-                                   RAD_ENC_MAX_PLANES * sizeof(RadPlanesEntry)];
-};
-
-std::vector<HeadView*>& seen_heads() { static std::vector<HeadView*> v; return v; }
-
-bool read_head(HeadView* v) {
-    cudaPointerAttributes at{};
-    const bool have = cudaPointerGetAttributes(&at, v->blob) == cudaSuccess;
-    if (!have) (void)cudaGetLastError();
-    if (have && at.type == cudaMemoryTypeDevice) {
-        if (cudaMemcpy(v->head, v->blob, sizeof v->head, cudaMemcpyDeviceToHost) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return false;
-        }
-    } else {
-        memcpy(v->head, v->blob, sizeof v->head);   /* host, pinned or managed memory */
-    }
-    return true;
-}
-
-/* Host-readable copy of the blob's header + entry table, or nullptr. `*cached` says whether the
- * copy was taken by an earlier call: the engine may have put another head at the same device
- * address since (model reload, a caching allocator), so a caller whose validation of a cached
- * copy fails calls refresh_head() and validates once more before it refuses. */
-const unsigned char* head_of(const void* blob, bool* cached) {
-    for (const HeadView* v : seen_heads()) if (v->blob == blob) { *cached = true; return v->head; }
-    *cached = false;
-    HeadView* v = new HeadView;
-    v->blob = blob;
-    if (!read_head(v)) { delete v; return nullptr; }
-    seen_heads().push_back(v);
-    return v->head;
-}
-const unsigned char* refresh_head(const void* blob) {
-    for (HeadView* v : seen_heads()) if (v->blob == blob) return read_head(v) ? v->head : nullptr;
-    return nullptr;
-}
-
 struct HeadPlanes { const RadPlanesHeader* h; const RadPlanesEntry* ec; const RadPlanesEntry* es; };
 
 /* the checks of src/r3d_gemm_logits.hip:176-194 of libr3d on a host copy of the header */
@@ -85,13 +44,6 @@ int check_head(const unsigned char* hv, long long N, long long K, HeadPlanes* ou
 } /* namespace */
 
 extern "C" {
-
-/* Drop the remembered header of a head blob (call when the blob's memory is released or rewritten). */
-void r3d_b200_forget_head(const void* blob) {
-    std::vector<HeadView*>& v = seen_heads();
-    for (size_t i = 0; i < v.size(); ++i)
-        if (v[i]->blob == blob) { delete v[i]; v.erase(v.begin() + (long)i); return; }
-}
 
 int r3d_rad_logits_gemm_e4m3(const RadArgs* a, RadStream s) {
     const RadTensor* X = rad_arg_in(a, 0);
@@ -118,10 +70,10 @@ int r3d_rad_logits_gemm_e4m3(const RadArgs* a, RadStream s) {
     if (x_pitch < K || y_pitch < N) return RAD_E_STRIDE;
 
     bool cached = false;
-    const unsigned char* hv = head_of(W->data, &cached);
+    const unsigned char* hv = planes_head_of(W->data, &cached);
     HeadPlanes hp{};
     int hst = check_head(hv, N, K, &hp, RAD_E_DTYPE);
-    if (hst != RAD_OK && cached) hst = check_head(refresh_head(W->data), N, K, &hp, RAD_E_DTYPE);
+    if (hst != RAD_OK && cached) hst = check_head(planes_head_refresh(W->data), N, K, &hp, RAD_E_DTYPE);
     if (hst != RAD_OK) return hst;
     const RadPlanesHeader* h = hp.h;
     const RadPlanesEntry* ec = hp.ec;
@@ -180,10 +132,10 @@ int r3d_rad_logit_rerank_e4m3(const RadArgs* a, RadStream s) {
     if (in->dtype != RAD_I32 || idx->dtype != RAD_I32 || val->dtype != RAD_F32) return RAD_E_DTYPE;
 
     bool cached = false;
-    const unsigned char* hv = head_of(w->data, &cached);
+    const unsigned char* hv = planes_head_of(w->data, &cached);
     HeadPlanes hp{};
     int hst = check_head(hv, NV, K, &hp, RAD_E_UNSUPPORTED);
-    if (hst != RAD_OK && cached) hst = check_head(refresh_head(w->data), NV, K, &hp, RAD_E_UNSUPPORTED);
+    if (hst != RAD_OK && cached) hst = check_head(planes_head_refresh(w->data), NV, K, &hp, RAD_E_UNSUPPORTED);
     if (hst != RAD_OK) return hst;
     const RadPlanesEntry* ec = hp.ec;
     const RadPlanesEntry* es = hp.es;

@@ -48,6 +48,11 @@ inline bool env_is_zero(const char* name) {
     return e && !strcmp(e, "0");
 }
 
+/* Host-readable copy of a rad.planes blob's header + entry table (planes_cache.cpp), or nullptr.
+ * `*cached` says whether the copy was taken by an earlier call; planes_head_refresh re-reads it. */
+const unsigned char* planes_head_of(const void* blob, bool* cached);
+const unsigned char* planes_head_refresh(const void* blob);
+
 constexpr long long kMaxExtent = 0x7ffffffLL;   /* extents must fit the kernels' int math */
 
 } /* namespace r3d */

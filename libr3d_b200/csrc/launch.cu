@@ -182,6 +182,12 @@ extern "C" int r3d_b200_gemm_mxfp4mx8(const R3dGemmQ* q, void* stream) {
     return exact_mxfp4mx8(*q, st);
 }
 
+extern "C" int r3d_b200_gemm_w2a8(const R3dW2A8* q, void* stream) {
+    if (!q || !device_is_sm100()) return RAD_E_UNSUPPORTED;
+    debug_arm("w2a8", "dp4a row walk", q->m);
+    return launch_gemm_w2a8(*q, (cudaStream_t)stream);
+}
+
 namespace r3d {
 int q8x_run(const R3dGemmQ& q, int8_t* x8, float* sg, int walk, cudaStream_t st) {
     if (tc_q8x_ok(q)) {

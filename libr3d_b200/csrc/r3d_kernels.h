@@ -43,6 +43,9 @@ int launch_logit_rerank_e4m3(const void* x, int xdt, int64_t x_rs, const void* c
                              int32_t* idx, int64_t idx_rs, float* val, int64_t val_rs, float* pairs, int M, int R,
                              int K, int64_t NV, int64_t voff, cudaStream_t st);
 
+/* gemm_nt_q @ w2a8 (kern_w2a8.cu) */
+int launch_gemm_w2a8(const R3dW2A8& q, cudaStream_t st);
+
 /* weight-streaming tensor-core arm (kern_stream.cu); *_ok say whether the arm can take
  * the call's shape and alignment */
 bool stream_fp8a8_ok(const R3dGemmQ& p);

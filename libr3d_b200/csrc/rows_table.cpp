@@ -155,6 +155,11 @@ const RadConstraint kCLogits[] = {
     { "dtype", RAD_C_IN, 0, "bf16" },
 };
 const RadConstraint kCMxfp4[] = { { "dtype", RAD_C_IN, 0, "mxfp4a8" } };
+/* src/r3d_rows.cpp:1101-1112: no M and no N constraint (the drafter's op carries no N at issue; the entry
+ * re-checks M <= 16 and N % 16) */
+const RadConstraint kCW2A8[] = {
+    { "dtype", RAD_C_IN, 0, "w2a8" }, { "K", RAD_C_DIV, 128, nullptr }, { "group", RAD_C_EQ, 128, nullptr },
+};
 const RadConstraint kCMxfp4Mx8[] = { { "dtype", RAD_C_IN, 0, "mxfp4mx8" }, { "K", RAD_C_DIV, 32, nullptr } };
 const RadConstraint kCFp8[] = {
     { "dtype", RAD_C_IN, 0, "fp8a8" }, { "K", RAD_C_DIV, 128, nullptr },
@@ -237,6 +242,20 @@ const RadKernelInfo kRows[] = {
         "b:32 / a:128 scale grids; nibble rows byte-packed; M from numel(y)/N",
         "e4m3 a + f32 a_scale, e2m1 b + E8M0 b_scale, bf16 y; b_ref ignored; a_sum refused",
         kPrioPlain, kCMxfp4, r3d_rad_gemm_nt_q),
+
+    /* src/r3d_rows.cpp:1677-1703 */
+    { "gemm_nt_q_w2a8_decode", "gemm_nt_q", "gemm",
+      "w2a8 decode-band GEMV (the draft head): one thread per weight row walks the 2-bit plane 64 bytes at a "
+      "time, byte-quads cut from each dword meet the int8 activation (de-permuted from step order in "
+      "shared memory) in dp4a, each group flushes as (sub * a_scale) * b_scale with sub = is - zero * a_sum "
+      "in the oracle's order: every value before the scales is an exact integer, so the row is bit-exact",
+      "M <= 16; K a multiple of 128; N a multiple of 16; group exactly 128; M derives from numel(y)/N",
+      "int8 a with an f32 per-row scale (quant_act_i8's step order), u2 b (stored as it is) with an f16 scale "
+      "and a u8/u4 zero per 128 K in the canonical rad.planes join, f32 a_sum [K/128][Mpad] (required), bf16 y; "
+      "b_ref refused; pb1/pb2 refused; an encoding transform declines at declare",
+      RAD_DOMAIN_DEVICE, kPrioDecode, kCW2A8, COUNT_OF(kCW2A8), nullptr, 0, nullptr,
+      nullptr, nullptr, r3d_rad_gemm_nt_q_w2a8_decode, nullptr, r3d_layout_gemm_w2a8,
+      r3d_relayout_gemm_w2a8, nullptr, r3d_unrelayout_gemm_w2a8, nullptr },
 
     /* not a reference row: the OCP-MX activation spelling of the mxfp4 band (weights as above) */
     ROW("gemm_nt_q_mxfp4mx8", "gemm_nt_q", "gemm",
@@ -336,7 +355,7 @@ bool row_hidden(const RadKernelInfo& k) {
     static const bool no_mx_dec = getenv("R3D_NO_FP4_DEC") != nullptr;
     static const bool q8x_off = r3d_mxfp4_q8x_off();
     static const bool no_df = getenv("R3D_NO_DFLASH") != nullptr;      /* the drafter family's lever, src/r3d_rows.cpp:2224-2227 */
-    if (no_df && !strcmp(k.op, "logit_rerank")) return true;
+    if (no_df && (!strcmp(k.op, "logit_rerank") || !strcmp(k.name, "gemm_nt_q_w2a8_decode"))) return true;
     if (!strcmp(k.name, "gemm_nt_q_fp8a8")) return no_fp8;
     if (!strcmp(k.name, "gemm_nt_q_fp8a8_decode")) return no_fp8 || no_fp8_dec;
     if (!strcmp(k.name, "gemm_nt_q_gated_fp8a8")) return no_fp8;       /* src/r3d_rows.cpp:2235 */

@@ -127,6 +127,25 @@ def logits_gemm(x: torch.Tensor, head_blob: torch.Tensor, logits: torch.Tensor, 
     return r
 
 
+def gemm_w2a8(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, bs_blob: torch.Tensor, y: torch.Tensor,
+              a_sum: torch.Tensor, *, N: int, K: int, M_param: int | None = None) -> Row:
+    """y[M,N] bf16 = a[M,K] (int8, quant_act_i8's step order, f32 scale a row) @ dequant(b)[N,K]^T for the
+    draft head's 2-bit weight: b uint8 [N, K/4] (four codes a byte), bs_blob the joined rad.planes blob of
+    its f16 scale and u8/u4 zero per (row, 128 of K), a_sum f32 [K/128, mpad] the activation's group sums."""
+    P = plugin()
+    M = y.numel() // N
+    query: dict[str, Any] = dict(M=M_param if M_param is not None else M, N=N, K=K, group=128, dtype="w2a8")
+    r = P.resolve("gemm_nt_q", query)
+    if r is None:
+        raise RuntimeError(f"no row serves gemm_nt_q {query}")
+    tensors = [_desc(a, abi.RAD_I8), _desc(a_scale, abi.RAD_F32), _desc(b, abi.RAD_U2, shape=[N, K], stride=[K, 1]),
+               _desc(bs_blob, abi.RAD_U8), _desc(y, abi.RAD_BF16), _desc(a_sum, abi.RAD_F32), _desc(None, abi.RAD_BF16)]
+    rc = P.launch_row(r, ArgPack(tensors, query), _stream())
+    if rc != abi.RAD_OK:
+        raise RowRefused(r.name, rc)
+    return r
+
+
 def logit_rerank(x: torch.Tensor, head_blob: torch.Tensor, idx_in: torch.Tensor, idx: torch.Tensor,
                  val: torch.Tensor, pairs: torch.Tensor | None = None, *, n_vocab: int, n_embd: int,
                  vocab_off: int = 0) -> Row:

@@ -30,6 +30,8 @@ EXPORTS = [
     "r3d_b200_gemm_fp8a8", "r3d_b200_gemm_mxfp4a8", "r3d_b200_gemm_mxfp4a8_q8x",
     "r3d_b200_gemm_mxfp4a8_q8x_static", "r3d_b200_q8x_on_tensor_core", "r3d_b200_gemm_mxfp4mx8",
     "r3d_rad_gemm_nt_q_mx8", "r3d_b200_mma_peak", "r3d_rad_logit_rerank_e4m3", "r3d_b200_forget_head",
+    "r3d_rad_gemm_nt_q_w2a8_decode", "r3d_layout_gemm_w2a8", "r3d_relayout_gemm_w2a8", "r3d_unrelayout_gemm_w2a8",
+    "r3d_b200_gemm_w2a8",
     "r3d_b200_logits", "r3d_b200_quant_act_fp8", "r3d_b200_pick_arm_fp8a8",
     "r3d_b200_pick_arm_mxfp4a8", "r3d_b200_launch_count", "r3d_b200_stream_status",
     "r3d_b200_gather_create", "r3d_b200_gather_connect", "r3d_b200_gather_buffer", "r3d_b200_gather_wait",
@@ -226,20 +228,22 @@ class ArgPack:
 
 def planes_blob(planes: list[tuple[str, int, tuple[int, int], "Any"]]) -> bytes:
     """Join weight planes into one rad.planes blob (the recipe of tools/bench_w2a8.cpp:84-105
-    of libr3d). `planes` = [(role, rad_dtype, (block_rows, block_cols), 2-D numpy array)]."""
+    of libr3d). `planes` = [(role, rad_dtype, (block_rows, block_cols), 2-D numpy array[, logical columns])]."""
     import numpy as np
 
     n = len(planes)
     head = C.sizeof(abi.RadPlanesHeader) + n * C.sizeof(abi.RadPlanesEntry)
     off = abi.planes_round(head)
     entries, payloads = [], []
-    for role, dt, block, arr in planes:
+    for role, dt, block, arr, *rest in planes:
         arr = np.ascontiguousarray(arr)
         e = abi.RadPlanesEntry()
         e.role = role.encode()
         e.dtype, e.kind = dt, abi.RAD_PLANE_TILED
         e.block[0], e.block[1] = block
         e.rows, e.cols = arr.shape
+        if rest:                              # logical columns of a sub-byte plane (u4: two a byte)
+            e.cols = rest[0]
         e.row_bytes = arr.strides[0]
         e.offset = off
         entries.append(e)

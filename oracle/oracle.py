@@ -119,6 +119,24 @@ def ref_logits() -> C.CDLL | None:
     return _ref_logits
 
 
+_ref_w2a8: list = []
+
+
+def ref_w2a8_host() -> C.CDLL | None:
+    """The host-only layout hook of src/r3d_gemm_w2a8.hip of libr3d compiled as it lies
+    (oracle/_ref/libref_w2a8_host.so): ref_layout_gemm_w2a8 with the hook's own signature. None when
+    the library was not built."""
+    if not _ref_w2a8:
+        so, R = HERE / "_ref" / "libref_w2a8_host.so", None
+        if so.exists():
+            try:
+                R = C.CDLL(str(so))
+            except OSError:
+                R = None
+        _ref_w2a8.append(R)
+    return _ref_w2a8[0]
+
+
 _ref_rerank: list = []
 
 
@@ -368,6 +386,28 @@ def truth_mxfp4a8(A, AS, B, BS):
     lib().orc_truth_mxfp4a8(_p(A), _p(AS), _p(B), _p(BS), I64(M), I64(N), I64(K),
                             I64(AS.shape[1]), _p(Yt), _p(Ya))
     return Yt, Ya
+
+
+def gemm_w2a8(A, AS, B, SC, ZP, ASUM, zp_u4: bool = False, want_acc: bool = False):
+    """gemm_nt_q @ w2a8: A int8 [M,K] in quant_act_i8's step order, AS f32 [M], B u2 codes [N, K/4] bytes,
+    SC f16 bits [N, K/128], ZP u8 [N, K/128] (or u4 [N, ceil(K/256)] bytes), ASUM f32 [K/128, mpad]."""
+    A, AS, B = _c(A, np.int8), _c(AS, np.float32), _c(B, np.uint8)
+    SC, ZP, ASUM = _c(SC, np.uint16), _c(ZP, np.uint8), _c(ASUM, np.float32)
+    M, K = A.shape
+    N = B.shape[0]
+    Y = np.empty((M, N), np.uint16)
+    acc = np.empty((M, N), np.float32) if want_acc else None
+    lib().orc_gemm_w2a8(_p(A), _p(AS), _p(B), _p(SC), _p(ZP), C.c_int(1 if zp_u4 else 0), _p(ASUM), I64(M), I64(N),
+                        I64(K), _p(Y), _p(acc) if want_acc else None)
+    return (Y, acc) if want_acc else Y
+
+
+def w2a8_group_sums(A):
+    A = _c(A, np.int8)
+    M, K = A.shape
+    out = np.empty((K // 128, (M + 15) // 16 * 16), np.float32)
+    lib().orc_w2a8_group_sums(_p(A), I64(M), I64(K), _p(out))
+    return out
 
 
 def logit_rerank_e4m3(X_bits, codes, scale, sdt: int, br: int, idx_in, vocab_off: int = 0):

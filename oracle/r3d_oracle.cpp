@@ -587,6 +587,57 @@ ORC_API void orc_truth_mxfp4a8(const uint8_t* A, const float* AS, const uint8_t*
         }
 }
 
+/* ------------------------------------------------------------------ gemm_nt_q @ w2a8 (the draft head)
+ * src/r3d_gemm_w2a8.hip:32-51 of libr3d (its transcription of libref's gemm_zp, ZP_I8_ROW arm):
+ *   G = K / 128; mpad = ceil(M/16)*16; q[n][k] = (B[n][k>>2] >> (2*(k&3))) & 3   (raw 0..3)
+ *   A[m][k] = a[m][step_pos(k)], step_pos swaps bits 2 and 3 of k (quant_act_i8's storage order)
+ *   per (m, n): acc = 0; for g ascending: is = sum_{k in g} A[m][k] * q[n][k]  (exact integer)
+ *       sub = (float)is - ((float)z[n][g] * a_sum[g*mpad + m]);  acc += (sub * sa[m]) * sb[n][g]
+ *   y = bf16(acc).  z is u8 (or u4, low nibble first), sb f16 widened exactly. */
+static inline int w2_step_pos(int64_t k) { return (int)((k & ~12) | ((k & 4) << 1) | ((k & 8) >> 1)); }
+
+ORC_API void orc_gemm_w2a8(const int8_t* A, const float* AS, const uint8_t* B, const uint16_t* SC_f16,
+                           const uint8_t* ZP, int zp_u4, const float* ASUM, int64_t M, int64_t N, int64_t K,
+                           uint16_t* Y, float* Yacc) {
+    const int64_t G = K / 128, mpad = (M + 15) / 16 * 16;
+    const int64_t zp_pitch = zp_u4 ? (G + 1) / 2 : G;
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+        const uint8_t* crow = B + n * (K / 4);
+        for (int64_t m = 0; m < M; ++m) {
+            float acc = 0.0f;
+            for (int64_t g = 0; g < G; ++g) {
+                int64_t is = 0;
+                for (int64_t k = g * 128; k < g * 128 + 128; ++k) {
+                    const int q = (crow[k >> 2] >> (2 * (k & 3))) & 3;
+                    is += (int64_t)A[m * K + w2_step_pos(k)] * q;
+                }
+                const uint8_t zb = ZP[n * zp_pitch + (zp_u4 ? g >> 1 : g)];
+                const int z = zp_u4 ? ((zb >> (4 * (g & 1))) & 15) : zb;
+                const float zs = (float)z * ASUM[g * mpad + m];
+                const float sub = (float)is - zs;
+                const float t = sub * AS[m];
+                acc += t * f16_to_f32(SC_f16[n * G + g]);
+            }
+            if (Y) Y[m * N + n] = f32_to_bf16(acc);
+            if (Yacc) Yacc[m * N + n] = acc;
+        }
+    }
+}
+
+/* quant_act_i8's group sums as the band's a_sum operand: [K/128][mpad] f32, group-major, the sum of the
+ * row's int8 codes over each 128 of K in COLUMN order (src/r3d_gemm_w2a8.hip:21, tools/bench_w2a8.cpp:78-84) */
+ORC_API void orc_w2a8_group_sums(const int8_t* A, int64_t M, int64_t K, float* ASUM) {
+    const int64_t G = K / 128, mpad = (M + 15) / 16 * 16;
+    for (int64_t i = 0; i < G * mpad; ++i) ASUM[i] = 0.0f;
+    for (int64_t m = 0; m < M; ++m)
+        for (int64_t g = 0; g < G; ++g) {
+            float s = 0.0f;
+            for (int64_t k = g * 128; k < g * 128 + 128; ++k) s += (float)A[m * K + w2_step_pos(k)];
+            ASUM[g * mpad + m] = s;
+        }
+}
+
 /* ------------------------------------------------------------------ logit_rerank, joined e4m3 head
  * src/r3d_logit_rerank_e4m3.hip:22-39 of libr3d (its statement of libref's ref_logit_rerank): per row
  * m and candidate r with global id g, local = g - vocab_off; g < 0 or local outside [0, n_vocab) is

@@ -79,7 +79,7 @@ def test_schemas_entry_for_entry(plug):
 
 def test_rows_names_priorities_constraints(plug):
     rows = {r.name: r for r in plug.rows()}
-    want = {"logits_gemm_e4m3": 1000, "logit_rerank_e4m3": 1000, "gemm_nt_q_mxfp4": 1000, "gemm_nt_q_mxfp4mx8": 1000, "gemm_nt_q_fp8a8": 1000,
+    want = {"logits_gemm_e4m3": 1000, "logit_rerank_e4m3": 1000, "gemm_nt_q_w2a8_decode": 1100, "gemm_nt_q_mxfp4": 1000, "gemm_nt_q_mxfp4mx8": 1000, "gemm_nt_q_fp8a8": 1000,
             "gemm_nt_q_fp8a8_decode": 1100, "gemm_nt_q_mxfp4_decode": 1100,
             "gemm_nt_q_mxfp4_decode_q8x": 1200, "gemm_nt_q_gated_fp8a8": 1000,
             "quant_act_fp8_act": 1000, "gated_quant_fp8_act": 1000, "rmsnorm_quant_fp8": 1000,
@@ -102,6 +102,7 @@ def test_band_resolution(plug):
     assert name(M=8, group=32, dtype="mxfp4a8") == "gemm_nt_q_mxfp4_decode_q8x"
     assert name(M=16, group=32, dtype="mxfp4a8") == "gemm_nt_q_mxfp4"
     assert name(M=8192, group=32, dtype="mxfp4mx8") == "gemm_nt_q_mxfp4mx8"
+    assert plug.resolve("gemm_nt_q", dict(M=14, K=5120, group=128, dtype="w2a8")).name == "gemm_nt_q_w2a8_decode"   # no N at issue
     assert name(M=1, group=32, dtype="mxfp4mx8") == "gemm_nt_q_mxfp4mx8"
     assert name(M=4, group=128, dtype="fp8a8") == "gemm_nt_q_fp8a8_decode"
     assert name(M=9, group=128, dtype="fp8a8") == "gemm_nt_q_fp8a8"
@@ -154,7 +155,7 @@ def _rows_under(env):
     return set(out[0].split(",")), out[1], out[2]
 
 
-ALL = {"logits_gemm_e4m3", "logit_rerank_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_mxfp4mx8", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode",
+ALL = {"logits_gemm_e4m3", "logit_rerank_e4m3", "gemm_nt_q_w2a8_decode", "gemm_nt_q_mxfp4", "gemm_nt_q_mxfp4mx8", "gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode",
        "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_gated_fp8a8",
        "quant_act_fp8_act", "gated_quant_fp8_act", "rmsnorm_quant_fp8", "rowtopk_bf16", "sample_argmax_f32"}
 
@@ -167,7 +168,7 @@ ALL = {"logits_gemm_e4m3", "logit_rerank_e4m3", "gemm_nt_q_mxfp4", "gemm_nt_q_mx
     ({"R3D_NO_MXFP4": ""}, {"gemm_nt_q_mxfp4", "gemm_nt_q_mxfp4mx8", "gemm_nt_q_mxfp4_decode", "gemm_nt_q_mxfp4_decode_q8x"}, "-", "gemm_nt_q_fp8a8_decode"),
     ({"R3D_NO_FP8_DEC": "1"}, {"gemm_nt_q_fp8a8_decode"}, "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_fp8a8"),
     ({"R3D_NO_FP8A8": "1"}, {"gemm_nt_q_fp8a8", "gemm_nt_q_fp8a8_decode", "gemm_nt_q_gated_fp8a8"}, "gemm_nt_q_mxfp4_decode_q8x", "-"),
-    ({"R3D_NO_DFLASH": "1"}, {"logit_rerank_e4m3"}, "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_fp8a8_decode"),
+    ({"R3D_NO_DFLASH": "1"}, {"logit_rerank_e4m3", "gemm_nt_q_w2a8_decode"}, "gemm_nt_q_mxfp4_decode_q8x", "gemm_nt_q_fp8a8_decode"),
 ])
 def test_kill_switch_matrix(env, hidden, mx_row, f8_row):
     # levers act at registration: a hidden row is not enumerated and the band re-resolves
@@ -538,6 +539,119 @@ def test_layout_hooks_roundtrip_and_gates(plug):
                 _enc(roles=("scale", "codes")), _enc(transform=b"givens"),
                 _enc(dtypes=(abi.RAD_F8E4M3, abi.RAD_U8)), _enc(blocks=((1, 2), (128, 128)))):
         assert L.r3d_layout_head(None, 0, 1, C.byref(bad), sel, planes, 2, C.byref(lay)) == D
+
+
+def _w2_enc(zero_dt=abi.RAD_U8, scale_dt=abi.RAD_F16, codes_dt=abi.RAD_U2, scheme=b"affine", transform=b"",
+            roles=("codes", "scale", "zero"), group=128):
+    return _enc(roles=roles, dtypes=(codes_dt, scale_dt, zero_dt), scheme=scheme, transform=transform,
+                blocks=((1, 1), (1, group), (1, group)))
+
+
+def test_w2a8_layout_hooks_roundtrip_and_gates(plug):
+    """the w2a8 row's hooks (operand 3 = the joined scale + zero planes) against the reference's own hook
+    compiled host-only from src/r3d_gemm_w2a8.hip:1362-1401, gate for gate"""
+    from oracle import oracle as orc
+    L = plug.lib
+    Rw = orc.ref_w2a8_host()
+    N, K = 32, 512
+    G = K // 128
+    rng = np.random.default_rng(2)
+    scale = rng.integers(0, 0x3C00, (N, G)).astype(np.uint16)
+    zero = rng.integers(0, 256, (N, G), dtype=np.uint8)
+    planes = (abi.RadTensor * 2)(tensor_desc(scale.ctypes.data, abi.RAD_F16, scale.shape),
+                                 tensor_desc(zero.ctypes.data, abi.RAD_U8, zero.shape))
+    sel = (C.c_int * 2)(1, 2)
+    lay = abi.RadLayout()
+
+    def params(**kw):
+        items = [abi.RadParam(k.encode(), abi.RAD_PK_INT, v, 0, None, 0.0) for k, v in kw.items()]
+        return (abi.RadParam * max(1, len(items)))(*items), len(items)
+
+    def rc(enc, operand=3, n=2, pl=planes, se=sel, **kw):
+        kw = {**dict(N=N, K=K, group=128), **kw}
+        pa, npar = params(**{k: v for k, v in kw.items() if v is not None})
+        lay2 = abi.RadLayout()
+        got = L.r3d_layout_gemm_w2a8(pa, npar, operand, C.byref(enc), se, pl, n, C.byref(lay))
+        if Rw is not None:
+            assert Rw.ref_layout_gemm_w2a8(pa, npar, operand, C.byref(enc), se, pl, n, C.byref(lay2)) == got
+            if got == abi.RAD_OK:
+                assert lay2.bytes == lay.bytes
+        return got
+
+    enc = _w2_enc()
+    assert rc(enc) == abi.RAD_OK and lay.bytes > scale.nbytes + zero.nbytes
+    pa, npar = params(N=N, K=K, group=128)
+    dst = np.zeros(lay.bytes, np.uint8)
+    assert L.r3d_relayout_gemm_w2a8(pa, npar, 3, C.byref(enc), sel, planes, 2, C.c_void_p(dst.ctypes.data),
+                                    C.c_int64(dst.size)) == abi.RAD_OK
+    want = np.frombuffer(planes_blob([("scale", abi.RAD_F16, (1, 128), scale), ("zero", abi.RAD_U8, (1, 128), zero)]), np.uint8)
+    assert np.array_equal(dst, want)
+    s2, z2 = np.zeros_like(scale), np.zeros_like(zero)
+    back = (abi.RadTensor * 2)(tensor_desc(s2.ctypes.data, abi.RAD_F16, s2.shape), tensor_desc(z2.ctypes.data, abi.RAD_U8, z2.shape))
+    assert L.r3d_unrelayout_gemm_w2a8(pa, npar, 3, C.byref(enc), sel, C.c_void_p(dst.ctypes.data), C.c_int64(dst.size),
+                                      back, 2) == abi.RAD_OK
+    assert np.array_equal(s2, scale) and np.array_equal(z2, zero)
+    D = abi.RAD_E_DTYPE
+    assert rc(enc, operand=2) == U and rc(enc, n=1) == U                    # the codes are stored as they are
+    for bad in (_w2_enc(scheme=b"lattice"), _w2_enc(transform=b"givens"), _w2_enc(codes_dt=abi.RAD_U4),
+                _w2_enc(scale_dt=abi.RAD_BF16), _w2_enc(zero_dt=abi.RAD_U2), _w2_enc(group=64),
+                _w2_enc(roles=("codes", "zero", "scale"))):
+        assert rc(bad) == D
+    assert rc(_w2_enc(zero_dt=abi.RAD_U4)) == abi.RAD_OK
+    assert rc(enc, group=64) == D and rc(enc, K=500) == SH and rc(enc, N=None) == SH
+    assert rc(enc, N=N + 1) == SH                                           # planes of another geometry
+    two = _enc(roles=("scale", "zero"), dtypes=(abi.RAD_F16, abi.RAD_U8), blocks=((1, 128), (1, 128)))
+    assert rc(two, se=(C.c_int * 2)(0, 1)) == D                             # no codes plane in the encoding
+
+
+def test_w2a8_entry_refusals(plug):
+    """every refusal of the w2a8 row entry in the reference's order (src/r3d_gemm_w2a8.hip:964-1028, :1320-1342)"""
+    N, K, M = 32, 512, 3
+    G = K // 128
+    buf = np.zeros(1 << 16, np.uint8)
+    scale = np.zeros((N, G), np.uint16); zero = np.zeros((N, G), np.uint8)
+    good = np.frombuffer(planes_blob([("scale", abi.RAD_F16, (1, 128), scale), ("zero", abi.RAD_U8, (1, 128), zero)]), np.uint8).copy()
+    f = plug.entry("r3d_rad_gemm_nt_q_w2a8_decode")
+    D = abi.RAD_E_DTYPE
+
+    def rc(blob=good, **over):
+        t = dict(a=tensor_desc(buf.ctypes.data, abi.RAD_I8, [M, K]), a_scale=tensor_desc(buf.ctypes.data, abi.RAD_F32, [M, 1]),
+                 b=tensor_desc(buf.ctypes.data, abi.RAD_U2, [N, K]), b_scale=tensor_desc(blob.ctypes.data, abi.RAD_U8, [blob.size]),
+                 y=tensor_desc(buf.ctypes.data, abi.RAD_BF16, [M, N]), a_sum=tensor_desc(buf.ctypes.data, abi.RAD_F32, [G, 16]),
+                 b_ref=tensor_desc(None, abi.RAD_BF16, []))
+        p = dict(M=M, N=N, K=K, group=128, dtype="w2a8")
+        for k, v in over.items():
+            if k in t:
+                t[k] = v
+            elif v is None:
+                p.pop(k)
+            else:
+                p[k] = v
+        return f(C.byref(ArgPack(list(t.values()), p).args), None)
+
+    assert rc(a_sum=tensor_desc(None, abi.RAD_F32, [])) == U                     # the zero point needs the group sums
+    assert rc(b_ref=tensor_desc(buf.ctypes.data, abi.RAD_BF16, [N, K])) == U
+    assert rc(N=None) == SH and rc(y=tensor_desc(buf.ctypes.data, abi.RAD_BF16, [M, N - 1])) == SH
+    assert rc(dtype="mxfp4a8") == U and rc(pb1=1) == U
+    assert rc(group=64) == SH and rc(group=None) == SH and rc(K=None) == SH
+    assert rc(K=500, a=tensor_desc(buf.ctypes.data, abi.RAD_I8, [M, 500]), b=tensor_desc(buf.ctypes.data, abi.RAD_U2, [N, 500])) == U
+    assert rc(y=tensor_desc(buf.ctypes.data, abi.RAD_BF16, [17, N]), a=tensor_desc(buf.ctypes.data, abi.RAD_I8, [17, K])) == U   # M > 16
+    assert rc(N=40, y=tensor_desc(buf.ctypes.data, abi.RAD_BF16, [M, 40]), b=tensor_desc(buf.ctypes.data, abi.RAD_U2, [40, K])) == U   # N % 16
+    assert rc(a=tensor_desc(buf.ctypes.data, abi.RAD_U8, [M, K])) == U
+    assert rc(a=tensor_desc(buf.ctypes.data, abi.RAD_I8, [M - 1, K])) == SH
+    assert rc(a=tensor_desc(buf.ctypes.data, abi.RAD_I8, [M, K], [2 * K, 2])) == ST
+    assert rc(b=tensor_desc(buf.ctypes.data + 2, abi.RAD_U2, [N, K])) == U       # breaks the dword walk
+    assert rc(a_sum=tensor_desc(buf.ctypes.data, abi.RAD_F32, [G, 8])) == SH     # smaller than G x mpad
+    bad = good.copy(); bad[0] ^= 0xFF
+    assert rc(blob=bad) == D
+    bf = np.frombuffer(planes_blob([("scale", abi.RAD_BF16, (1, 128), scale), ("zero", abi.RAD_U8, (1, 128), zero)]), np.uint8).copy()
+    assert rc(blob=bf) == U
+    z2 = np.frombuffer(planes_blob([("scale", abi.RAD_F16, (1, 128), scale), ("zero", abi.RAD_U2, (1, 128), zero)]), np.uint8).copy()
+    assert rc(blob=z2) == U
+    g64 = np.frombuffer(planes_blob([("scale", abi.RAD_F16, (1, 64), scale), ("zero", abi.RAD_U8, (1, 128), zero)]), np.uint8).copy()
+    assert rc(blob=g64) == SH
+    wrongn = np.frombuffer(planes_blob([("scale", abi.RAD_F16, (1, 128), scale[:16]), ("zero", abi.RAD_U8, (1, 128), zero)]), np.uint8).copy()
+    assert rc(blob=wrongn) == SH
 
 
 def test_no_product_code_touches_the_oracle():
