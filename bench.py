@@ -424,7 +424,7 @@ def run_all(args):
         del calls, keep
         torch.cuda.empty_cache()
 
-    want = set(c.strip().upper() for c in args.cfg.split(",")) if args.cfg else {"C1", "C2", "C3", "C4", "C5", "ROWS"}
+    want = set(c.strip().upper() for c in args.cfg.split(",")) if args.cfg else {"C1", "C2", "C3", "C4", "C5", "ROWS", "W2A8"}
     if "C1" in want:
         decode_case("C1", "fp8a8", 1, 4096, 4096)
     if "C2" in want:
@@ -522,6 +522,48 @@ def run_all(args):
             val = torch.zeros((M, R), dtype=torch.float32, device=dev)
             pairs = torch.zeros((M, R, 2), dtype=torch.float32, device=dev)
             row_case("rowtopk_bf16", f"M={M} N={N} R={R}", M * N * 2, lambda i: ops.row_topk(ls[i], idx, val, pairs, R=R))
+        # the candidate rescoring row over the e4m3 head (each candidate reads its own row: 32 x 5120 bytes)
+        from libr3d_b200.plugin import planes_blob
+        NVr, Kr, R = 151936, 5120, 32
+        hc = torch.randint(0, 127, (NVr, Kr), dtype=torch.uint8, generator=torch.Generator().manual_seed(5)).numpy()
+        hs = np.full(((NVr + 127) // 128, Kr // 128), 0x3C00, np.uint16)       # f16 1.0
+        blob = torch.from_numpy(np.frombuffer(planes_blob([("codes", abi.RAD_F8E4M3, (1, 1), hc),
+                                                           ("scale", abi.RAD_F16, (128, 128), hs)]), np.uint8).copy()).to(dev)
+        del hc
+        for M in (1, 16):
+            xs = [torch.randn((M, Kr), device=dev, generator=g).to(torch.bfloat16) for _ in range(4)]
+            ids = [torch.randint(0, NVr, (M, R), dtype=torch.int32, device=dev, generator=g) for _ in range(4)]
+            idx = torch.zeros((M, R), dtype=torch.int32, device=dev)
+            val = torch.zeros((M, R), dtype=torch.float32, device=dev)
+            row_case("logit_rerank_e4m3", f"M={M} N={NVr} K={Kr} R={R}", M * R * Kr,
+                     lambda i: ops.logit_rerank(xs[i], blob, ids[i], idx, val, n_vocab=NVr, n_embd=Kr))
+        del blob
+        torch.cuda.empty_cache()
+    if "W2A8" in want:
+        # the draft head's 2-bit decode band (N = 248320 rows x K = 5120: 318 MB of codes a plane, two planes;
+        # --w2-rows shrinks N for a profiler capture)
+        from libr3d_b200.plugin import planes_blob
+        Nw, Kw = args.w2_rows, 5120
+        G = Kw // 128
+        sc16 = np.full((Nw, G), 0x1E00, np.uint16)
+        zp8 = np.ones((Nw, G), np.uint8)
+        wblob = torch.from_numpy(np.frombuffer(planes_blob([("scale", abi.RAD_F16, (1, 128), sc16),
+                                                            ("zero", abi.RAD_U8, (1, 128), zp8, G)]), np.uint8).copy()).to(dev)
+        wb = [torch.randint(0, 256, (Nw, Kw // 4), dtype=torch.uint8, device=dev, generator=g) for _ in range(2)]
+        for M in (1, 2, 4, 8, 16):
+            a8 = torch.randint(-127, 128, (M, Kw), dtype=torch.int8, device=dev, generator=g)
+            asc = torch.full((M,), 0.01, dtype=torch.float32, device=dev)
+            asum = torch.zeros((G, 16), dtype=torch.float32, device=dev)
+            asum[:, :M] = a8.view(M, G, 128).to(torch.float32).sum(-1).T
+            yw = torch.zeros((M, Nw), dtype=torch.bfloat16, device=dev)
+            calls = [lambda st, i=i: ops.gemm_w2a8(a8, asc, wb[i], wblob, yw, asum, N=Nw, K=Kw) for i in range(2)]
+            us = timed(calls, 10)
+            nbytes = Nw * Kw // 4 + Nw * G * 3 + M * Kw + M * Nw * 2
+            out.append({"cfg": "W2A8", "row": "gemm_nt_q_w2a8_decode", "shape": f"M={M} N={Nw} K={Kw}",
+                        "us_per_call": round(us, 2), "GBs": round(nbytes / us / 1e3, 1),
+                        "hbm_frac_of_measured": round(nbytes / us / 1e3 / peak, 3)})
+        del wb, wblob
+        torch.cuda.empty_cache()
     for r in out:
         sys.stderr.write(json.dumps(r) + "\n")
     print(json.dumps({"workload": "all", "n_gpus": 1, "peak_GBs": peak, "peak_source": "measured", "timed_as":
@@ -730,8 +772,9 @@ def main():
     ap.add_argument("--regions", type=int, default=5, help="how many times the K-step region is timed (median reported)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-sub", action="store_true", help="skip the sub-records (other row, plane sweep, C5)")
-    ap.add_argument("--cfg", default="", help="--workload all: comma list of configurations to run (C1..C5, ROWS), default all")
+    ap.add_argument("--cfg", default="", help="--workload all: comma list of configurations to run (C1..C5, ROWS, W2A8), default all")
     ap.add_argument("--tokens", type=int, default=8192, help="--workload all: M of the prefill configuration C4")
+    ap.add_argument("--w2-rows", type=int, default=248320, help="--workload all --cfg W2A8: rows of the 2-bit draft head")
     ap.add_argument("--gather", default="push", choices=["push", "nccl"],
                     help="N > 1: all-gather fused into the GEMV epilogue (push) or NCCL after it")
     ap.add_argument("--workload", default="c2", help="c2 (default, the headline), c5 (sharded LM head) or all (every configuration, one GPU)")

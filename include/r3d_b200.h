@@ -185,14 +185,17 @@ typedef struct R3dW2A8 {
     const void*  zero;      /* u8 [N, K/128], or u4 (two a byte, low nibble first) when zero_u4 */
     const float* a_sum;     /* f32 [K/128, mpad], group-major: the row's code sums per 128 of K */
     void*        y;         /* bf16 [M, N] */
-    int32_t      m, n, k, mpad, zero_u4, reserved;
+    int32_t      m, n, k, mpad, zero_u4;
+    int32_t      arm;       /* R3D_ARM_AUTO, or R3D_ARM_EXACT: the one-thread-per-row kernel whatever the alignment */
     int64_t      a_pitch, as_pitch, y_pitch;   /* elements */
     int64_t      b_pitch, zp_pitch;            /* bytes */
     int64_t      sc_pitch;                     /* f16 elements */
 } R3dW2A8;
 
-/* Replaces the kernel dispatch of w2_launch (src/r3d_gemm_w2a8.hip:1058-1315): one thread per weight
- * row, dp4a over byte-quads cut from the 2-bit plane, the oracle's flush per 128 of K; exact. */
+/* Replaces the kernel dispatch of w2_launch (src/r3d_gemm_w2a8.hip:1058-1315). 16-byte aligned operands
+ * (K >= 512): persistent CTAs stream 256-row tiles by TMA and form the exact group sums with integer
+ * mma.sync over byte-quads cut from the 2-bit plane; anything else: one thread per weight row with dp4a.
+ * Both apply the oracle's flush per 128 of K; exact, bit-identical to each other. */
 int r3d_b200_gemm_w2a8(const R3dW2A8* q, void* stream);
 
 typedef struct R3dLogits {

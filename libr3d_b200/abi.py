@@ -124,7 +124,7 @@ class R3dW2A8(C.Structure):
     _fields_ = [("a", C.c_void_p), ("a_scale", C.c_void_p), ("b", C.c_void_p), ("scale", C.c_void_p),
                 ("zero", C.c_void_p), ("a_sum", C.c_void_p), ("y", C.c_void_p),
                 ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("mpad", C.c_int32),
-                ("zero_u4", C.c_int32), ("reserved", C.c_int32),
+                ("zero_u4", C.c_int32), ("arm", C.c_int32),
                 ("a_pitch", C.c_int64), ("as_pitch", C.c_int64), ("y_pitch", C.c_int64),
                 ("b_pitch", C.c_int64), ("zp_pitch", C.c_int64), ("sc_pitch", C.c_int64)]
 

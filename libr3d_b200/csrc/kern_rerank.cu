@@ -13,11 +13,14 @@
  * The double chain is serial by definition, so the work is laid out for its latency, not for a
  * tensor core: one block of eight warps per row; the row's activations are widened to f32 once
  * into shared memory by the whole block; every warp serves four candidates at once, eight lanes
- * each: per step a lane fetches four consecutive codes of its candidate's head row (one 32-byte
- * sector per candidate, against the reference's one thread per candidate striding its own row),
- * forms the four exact products, and the segment's accumulator takes the 32 products of the step
- * in ascending k through width-8 shuffles -- the same adds in the same order, four chains per
- * FP64 instruction. Thread 0 runs the selection over shared memory.
+ * each: per 128-K block a lane fetches sixteen consecutive codes of its candidate's head row (one
+ * 128-byte line per candidate, against the reference's one thread per candidate striding its own
+ * row) with the loads of the next two blocks already in flight (a head row is touched once, so every
+ * load is a DRAM round trip: unhidden they were nine tenths of the kernel's time), forms the
+ * sixteen exact products, and the segment's accumulator takes the 128 products of the block in
+ * ascending k through width-8 shuffles -- the same adds in the same order, four chains per FP64
+ * instruction. Ragged K, unaligned heads and rows too wide for shared memory take 32-K steps of
+ * four codes a lane. Thread 0 runs the selection over shared memory.
  */
 #include "r3d_kernels.h"
 #include "r3d_numerics.cuh"
@@ -62,7 +65,42 @@ k_logit_rerank_e4m3(const uint8_t* __restrict__ x, int xdt, int64_t x_rs,
         const int64_t sbase = pad ? 0 : (local / br) * scale_rs;
         const bool al4 = ((((uintptr_t)codes) | (uintptr_t)code_rs) & 3) == 0;
         double acc = 0.0;
-        for (int k0 = 0; k0 < K; k0 += 32) {
+        int k0 = 0;
+        const bool al16 = ((((uintptr_t)codes) | (uintptr_t)code_rs) & 15) == 0;
+        if (x_in_smem && al16) {
+            /* whole 128-K blocks: a lane holds sixteen consecutive codes of its candidate (one 16-byte
+             * load; the segment reads one 128-byte line), the loads of the next two blocks are in flight
+             * while this block's 128 products are added -- in ascending k, as above */
+            const int nblk = K >> 7;
+            uint4 c1 = make_uint4(0, 0, 0, 0), c2 = c1;
+            float s1 = 0.f, s2 = 0.f;
+            if (!pad && nblk > 0) { c1 = *(const uint4*)(crow + 16 * j); s1 = ld_scale_any(scale, sbase, sdt); }
+            if (!pad && nblk > 1) { c2 = *(const uint4*)(crow + 128 + 16 * j); s2 = ld_scale_any(scale, sbase + 1, sdt); }
+            for (int b = 0; b < nblk; ++b) {
+                const uint4 c = c1;
+                const float s = s1;
+                c1 = c2; s1 = s2;
+                if (!pad && b + 2 < nblk) {
+                    c2 = *(const uint4*)(crow + (int64_t)(b + 2) * 128 + 16 * j);
+                    s2 = ld_scale_any(scale, sbase + b + 2, sdt);
+                }
+                const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
+                const float* xb = xs + (b << 7) + 16 * j;
+                double p[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float hv = __fmul_rn(e4m3_to_f32((uint8_t)(cw[i >> 2] >> (8 * (i & 3)))), s);
+                    p[i] = pad ? 0.0 : __dmul_rn((double)xb[i], (double)hv);
+                }
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj)
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        acc = __dadd_rn(acc, __shfl_sync(0xffffffffu, p[i], jj, 8));
+            }
+            k0 = nblk << 7;
+        }
+        for (; k0 < K; k0 += 32) {
             const int k = k0 + 4 * j;
             double p[4] = {0.0, 0.0, 0.0, 0.0};
             if (!pad && k < K) {

@@ -721,6 +721,8 @@ int tc_status() {
     v = tc_q8x_status();
     if (v) return v;
     v = tc_gemm2_status();
+    if (v) return v;
+    v = tc_w2a8_status();
     return v ? v : tc_gemm_status();
 }
 

@@ -327,6 +327,8 @@ k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
         const uint32_t tset = tlane + kSfCols + set * SB;
         const float* rec_t = rec_s + (size_t)(set * TPS) * n128 * 8;
         const f32x2 k_half = pk2(0.5f, 0.5f), k_four = pk2(4.0f, 4.0f), k_sixteen = pk2(16.0f, 16.0f);
+        const float nzf = P.m < 0 ? 1.0f : -0.0f;                   /* -0 the assembler cannot fold away */
+        const f32x2 k_nz = pk2(nzf, nzf);
         /* The walk is a sequence of steps of one 128-of-K unit (two K=64 slabs, four 32-groups), two
          * per stage. The tensor-memory loads of step i+1 are issued before step i is computed and
          * waited for after it, so their latency hides behind the float chains. What a step keeps of
@@ -406,7 +408,11 @@ k_tc_q8x(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
                         f32x2 v = mul2(PF[tl][h], h ? sg.y : sg.x);
                         v = mul2(v, as2);
                         v = mul2(v, h ? sc23 : sc01);
-                        c[h] = mul2(v, k_half);
+                        /* walk 1 adds the pair with a packed add: the halving is written as fma(v, 0.5, -0) so
+                         * that it is rounded alone (a packed multiply whose only use is a packed add is merged
+                         * into one fused multiply-add by the assembler; with a subnormal half that is another
+                         * rounding than the chain's) */
+                        c[h] = WALK ? fma2(v, k_half, k_nz) : mul2(v, k_half);
                     }
                     if (WALK == 0) {
                         float c0, c1, c2, c3;

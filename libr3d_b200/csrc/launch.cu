@@ -184,7 +184,7 @@ extern "C" int r3d_b200_gemm_mxfp4mx8(const R3dGemmQ* q, void* stream) {
 
 extern "C" int r3d_b200_gemm_w2a8(const R3dW2A8* q, void* stream) {
     if (!q || !device_is_sm100()) return RAD_E_UNSUPPORTED;
-    debug_arm("w2a8", "dp4a row walk", q->m);
+    debug_arm("w2a8", "integer mma tiles or dp4a row walk", q->m);
     return launch_gemm_w2a8(*q, (cudaStream_t)stream);
 }
 

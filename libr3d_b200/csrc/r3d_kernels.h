@@ -92,6 +92,7 @@ int q8x_gemv(const R3dGemmQ& p, const int8_t* x8, const float* sg, int walk, cud
 bool tc_q8x_ok(const R3dGemmQ& p);
 int  tc_q8x(const R3dGemmQ& p, int8_t* x8, float* sg, int walk, cudaStream_t st);
 int  tc_q8x_status();
+int  tc_w2a8_status();
 /* requantise + dot, on the tensor core when the operands allow it, else the dp4a kernels */
 int  q8x_run(const R3dGemmQ& p, int8_t* x8, float* sg, int walk, cudaStream_t st);
 
