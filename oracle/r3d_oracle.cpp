@@ -10,13 +10,19 @@
  * dependency that libr3d does not vendor; the citations below are libr3d's own scalar
  * restatements of it, which is what its unit tools grade its kernels with.
  *
- * Pinning: oracle/ref_pin.cpp compiles the one header of the reference that is plain
- * C++ (src/r3d_mxfp4_q8x.h) and tests/test_oracle_pin.py checks this file's tables against
- * it; the remaining rules are pinned by the known-answer cases the reference's tools hold
- * (analytic unit fixture, decoder spot values, fixture generators).
+ * Pinning: oracle/Makefile compiles the reference's own sources of this path from where
+ * they lie (src/r3d_mxfp4_q8x.h on the CPU; the band, norm, logits, fp8a8, mxfp4 and
+ * rerank .hip files for the GPU through oracle/hipstub/; the w2a8 layout hooks host-only)
+ * into oracle/_ref/. tests/test_oracle_codecs.py checks this file's tables, decoders and
+ * e4m3 encoder against that compiled code over all codes and rounding midpoints;
+ * tests/test_gpu_ref_band.py, tests/test_gpu_band_rows.py and tests/test_gpu_rerank.py run
+ * the reference's kernels beside this file's rules; tests/test_oracle_gemm.py holds the
+ * known-answer cases of the reference's tools (analytic unit fixture, the probe tool's
+ * srand(777) fixture, decoder spot values) and an independent numpy walk of each rule.
  * Extensions the reference has no row or test for -- the mxfp4 LM head, the OCP-MX
- * activation quantiser, fp32 per-channel / per-token scale grids -- are PARITY UNPINNED:
- * the rule is fixed by this file alone.
+ * activation quantiser and the mxfp4mx8 product, fp32 per-channel / per-token scale grids
+ * -- are PARITY UNPINNED: the rule is fixed by this file alone. The w2a8 rule follows the
+ * reference's written transcription (src/r3d_gemm_w2a8.hip:32-51); its kernels are not run.
  *
  * Build: g++ -O3 -std=c++17 -fopenmp -ffp-contract=off (no -ffast-math): mul and add stay
  * separate roundings except where fmaf is written, as the reference builds with

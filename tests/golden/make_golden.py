@@ -1,9 +1,11 @@
 """Writes the golden input/output vectors under tests/golden/ (small .npz files).
 
-The reference's kernels are HIP and its arbiter (radiance libref) is not shipped with it, so
-no output of the reference itself can be produced in this environment. These vectors are
-therefore outputs of the CPU restatement (oracle/) on (a) the reference tools' own seeded
-fixtures and (b) small draws of the benchmark distributions. They freeze the oracle: a later
+The reference's arbiter (radiance libref) is not shipped with it, and its kernels run only on a
+GPU (they are HIP sources, compiled for the B200 through stand-in headers by oracle/Makefile and
+run beside the oracle in the -m gpu tests), so nothing of the reference itself can be executed in
+the GPU-less container these vectors are made in. They are therefore outputs of the CPU
+restatement (oracle/) on (a) the reference tools' own seeded fixtures and (b) small draws of the
+benchmark distributions. They freeze the oracle: a later
 edit that changes any output byte fails tests/test_oracle_gemm.py::test_golden_vectors, and
 the GPU tests use the same files where the reference tree is absent.
 
