@@ -522,6 +522,26 @@ def run_all(args):
             val = torch.zeros((M, R), dtype=torch.float32, device=dev)
             pairs = torch.zeros((M, R, 2), dtype=torch.float32, device=dev)
             row_case("rowtopk_bf16", f"M={M} N={N} R={R}", M * N * 2, lambda i: ops.row_topk(ls[i], idx, val, pairs, R=R))
+        # gemm_nt_q_gated @ fp8a8: the gate_up projection (2n = 27648 rows, K = 5120) with the gated quantiser
+        # closing the call; bytes = the weight stream + operands + codes and scales out
+        Kg, Ng = 5120, 27648
+        wg = [(torch.randint(0, 127, (Ng, Kg), dtype=torch.uint8, device=dev, generator=g),
+               (torch.rand((Ng // 128, Kg // 128), device=dev, generator=g) * 0.01 + 0.001).to(torch.bfloat16)) for _ in range(3)]
+        for M in (1, 4, 8, 16):
+            xg = torch.randn((M, Kg), device=dev, generator=g).to(torch.bfloat16)
+            Ag, ASg = ops.quant_act_fp8(xg, 128)
+            qg = torch.zeros((M, Ng // 2), dtype=torch.uint8, device=dev)
+            sg = torch.zeros((M, Ng // 2 // 128), dtype=torch.float32, device=dev)
+            scr = torch.empty(64 * Ng * 2, dtype=torch.uint8, device=dev)
+            calls = [lambda st, i=i: ops.gemm_nt_q_gated(Ag, ASg, wg[i][0], wg[i][1], qg, sg, N=Ng, K=Kg, scratch=scr)
+                     for i in range(3)]
+            us = timed(calls, 30)
+            nbytes = Ng * Kg + (Ng // 128) * (Kg // 128) * 2 + M * (Kg + Kg // 128 * 4) + M * (Ng // 2) + M * (Ng // 2 // 128) * 4
+            out.append({"cfg": "ROWS", "row": "gemm_nt_q_gated_fp8a8", "shape": f"M={M} 2n={Ng} K={Kg}",
+                        "us_per_call": round(us, 2), "GBs": round(nbytes / us / 1e3, 1),
+                        "hbm_frac_of_measured": round(nbytes / us / 1e3 / peak, 3)})
+        del wg
+        torch.cuda.empty_cache()
         # the candidate rescoring row over the e4m3 head (each candidate reads its own row: 32 x 5120 bytes)
         from libr3d_b200.plugin import planes_blob
         NVr, Kr, R = 151936, 5120, 32

@@ -192,6 +192,15 @@ typedef struct R3dW2A8 {
     int64_t      sc_pitch;                     /* f16 elements */
 } R3dW2A8;
 
+/* gemm_nt_q_gated @ fp8a8 as one launch (replaces the fused kernels of src/r3d_gemm_fp8a8.hip:700-825 and
+ * their dispatch :1167-1253): the decode band over the [2n, K] gate_up weight with the gated quantiser
+ * (silu or sigmoid of the gate times up -> bf16 -> group amax -> e4m3) as the kernel's epilogue; q->n = 2n,
+ * q->y unused; codes e4m3 [M, n], scale f32 [M, n/128], ob optional gated product (bf16 | f32).
+ * Returns RAD_E_UNSUPPORTED for shapes it does not serve byte-identically to r3d_b200_gemm_fp8a8 followed by
+ * r3d_b200_gated_quant_fp8 (M > 64, n not a multiple of 128, projections narrow enough that K is split). */
+int r3d_b200_gemm_fp8a8_gated(const R3dGemmQ* q, void* codes, int64_t q_pitch, float* scale, int64_t s_pitch,
+                              void* ob, int32_t ob_dtype, int64_t ob_pitch, int32_t silu, void* stream);
+
 /* Replaces the kernel dispatch of w2_launch (src/r3d_gemm_w2a8.hip:1058-1315). 16-byte aligned operands
  * (K >= 512): persistent CTAs stream 256-row tiles by TMA and form the exact group sums with integer
  * mma.sync over byte-quads cut from the 2-bit plane; anything else: one thread per weight row with dp4a.

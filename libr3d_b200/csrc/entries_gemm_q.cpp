@@ -335,7 +335,9 @@ int r3d_rad_gemm_nt_q_mxfp4_decode_q8x(const RadArgs* a, RadStream s) {
  * q (e4m3 [M, n]), scale (f32 [M, n/group]), out_bf16 (optional, bf16 or f32), a_sum (refused). The
  * [2n, K] gate_up weight's product lands as bf16 [M, 2n] in the launch scratch, then the gated
  * quantiser reads it: byte-identical to gemm_nt_q followed by gated_quant_fp8, because it is that
- * pair. M = numel(q) / n; `act` is required; the arena (64 * N * 2 bytes, the scratch hook) is
+ * pair. Wide projections (no K split, n a multiple of 128, group 128) at M <= 8 run as ONE launch instead: the
+ * tcgen05 decode kernel takes a gate tile and its up tile in a cluster of two and closes with the
+ * quantiser in its epilogue -- the same accumulation and the same statements, so the same bytes. M = numel(q) / n; `act` is required; the arena (64 * N * 2 bytes, the scratch hook) is
  * checked, never overrun. */
 int r3d_rad_gemm_nt_q_gated_fp8(const RadArgs* a, RadStream s) {
     static const bool off = env_present("R3D_NO_FP8A8");
@@ -381,6 +383,16 @@ int r3d_rad_gemm_nt_q_gated_fp8(const RadArgs* a, RadStream s) {
     if (!a->scratch || a->scratch_bytes < need) return RAD_E_UNSUPPORTED;
     if (!inner_contiguous(Q) || !inner_contiguous(SC) || (OB && !inner_contiguous(OB))) return RAD_E_STRIDE;
 
+    /* one launch where the fused kernel gives the pair's bytes (group 128 = one gate tile a quantiser group)
+     * and is the faster of the two: up to eight tokens (measured at 2n = 27648, K = 5120: 26.1 / 27.6 / 29.4 us
+     * against 29.1 / 29.6 / 30.4 for M = 1 / 4 / 8; at sixteen tokens the exponentials in the kernel's tail
+     * cost more than the second launch saves, 33.3 against 32.2); the pair otherwise */
+    if (g == 128 && M <= 8) {
+        const int rf = r3d_b200_gemm_fp8a8_gated(&q, Q->data, row_pitch(Q, n), (float*)SC->data, row_pitch(SC, ngrp),
+                                                 OB ? OB->data : nullptr, OB ? (int32_t)OB->dtype : RAD_BF16,
+                                                 OB ? row_pitch(OB, n) : 0, silu, (void*)s);
+        if (rf != RAD_E_UNSUPPORTED) return rf;
+    }
     const int rg = r3d_b200_gemm_fp8a8(&q, (void*)s);
     if (rg != RAD_OK) return rg;
     return r3d_b200_gated_quant_fp8(a->scratch, N, Q->data, row_pitch(Q, n), (float*)SC->data, row_pitch(SC, ngrp),

@@ -58,6 +58,13 @@ struct TcParams {
     int as_cols, ws_cols, rblk, ws_dtype;
     int ksplit;                                    /* CTAs per cluster = K shares per row tile */
     PushCfg push;                                  /* world > 0: store into every rank's gathered buffer */
+    /* gemm_nt_q_gated: the weight is [2 n_half, K], gate rows first. A cluster of two CTAs takes gate tile g
+     * and up tile g over the whole K; the gate CTA closes the call with the gated quantiser
+     * (src/r3d_gemm_fp8a8.hip:700-825 of libr3d) instead of storing y */
+    int gated, gsilu, gob_dtype;
+    uint8_t* gq; int64_t gq_pitch;                 /* e4m3 codes [M, n_half] */
+    float* gs; int64_t gs_pitch;                   /* f32 scale [M, n_half / 128] */
+    void* gob; int64_t gob_pitch;                  /* optional gated product, bf16 or f32 */
 };
 
 using namespace tcdev;
@@ -66,8 +73,8 @@ using namespace tcdev;
  * epilogue actually reads and stores (M rounded up to 1, 2, 4, 8, 16, ...): the TMEM columns
  * of padding tokens are never touched. The CTAs of a cluster split K between them and the
  * leader adds the partial sums through distributed shared memory, in rank order. */
-template <int FMT, int NTOK, int ML, int kTcStages, int LG>
-__global__ void __launch_bounds__(kTcThreads)
+template <int FMT, int NTOK, int ML, int kTcStages, int LG, int GATED>
+__global__ void __launch_bounds__(kTcThreads, (GATED && ML <= 32) ? 2 : 1)
 k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
             const TcParams P) {
     constexpr int kBBytes = NTOK * kStageK;
@@ -96,10 +103,11 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ks = P.ksplit;
     const int crank = ks > 1 ? (int)cluster_rank() : 0;
-    const int r0 = (blockIdx.x / ks) * kTileRows;
     const int n128 = P.k / kStageK;
-    const int it0 = (int)((int64_t)n128 * crank / ks);             /* this CTA's K stages */
-    const int nk = (int)((int64_t)n128 * (crank + 1) / ks) - it0;
+    /* gated: cluster rank 0 = gate tile, rank 1 = the up tile n_half rows below, both over all of K */
+    const int r0 = GATED ? (int)(blockIdx.x / 2) * kTileRows + (crank ? P.n / 2 : 0) : (blockIdx.x / ks) * kTileRows;
+    const int it0 = GATED ? 0 : (int)((int64_t)n128 * crank / ks);    /* this CTA's K stages */
+    const int nk = GATED ? n128 : (int)((int64_t)n128 * (crank + 1) / ks) - it0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTcStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&prep[s], 4); }
@@ -281,25 +289,80 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                 }
             }
         }
-        if (ks > 1 && crank != 0) {
+        if (ks > 1 && (crank != 0 || GATED)) {
             /* every stage of this CTA has been consumed: the stage ring is free to carry the
-             * partial sums to the leader */
+             * partial sums to the leader (gated: each CTA's bf16-rounded outputs to its partner) */
             float* red = (float*)smem;
 #pragma unroll
-            for (int t = 0; t < ML; ++t) red[t * kTileRows + q * 32 + lane] = alive ? acc[t] : __int_as_float(0x7fc00000);
+            for (int t = 0; t < ML; ++t)
+                red[t * kTileRows + q * 32 + lane] = !alive ? __int_as_float(0x7fc00000)
+                                                     : GATED ? bf16_to_f32(f32_to_bf16(acc[t])) : acc[t];
         }
     }
 
     if (ks > 1) {
         cluster_sync_all();                                   /* partial sums are in place */
-        if (warp >= 2 && crank == 0) {
+        if (!GATED && warp >= 2 && crank == 0) {
             const float* red = (const float*)smem;
             for (int r = 1; r < ks; ++r)
 #pragma unroll
                 for (int t = 0; t < ML; ++t) acc[t] += ld_peer_f32(red + t * kTileRows + q * 32 + lane, (uint32_t)r);
         }
+        if (GATED && warp >= 2) {
+            /* The gated quantiser over this pair's 128 columns of n (one quantiser group), every statement as
+             * k_gated_quant_fp8 has it: the band's outputs rounded to bf16, h = bf16((silu ? gt*sg : sg) * up)
+             * with sg through a double-precision exp, the group's amax (NaN never wins), scale = amax / 448
+             * (1 when amax = 0), saturating RTNE e4m3 codes of h / scale. Thread = column of n. The two CTAs
+             * share the tokens (even slots: the gate CTA, odd slots: the up CTA; each reads the other half of
+             * its operands from its partner's shared memory): the exponentials are the cost of this tail. */
+            const float* red = (const float*)smem;
+            float* amax_s = (float*)smem + ML * kTileRows;      /* own stage ring, past the exported values */
+            const int col = (int)(blockIdx.x / 2) * kTileRows + q * 32 + lane;
+            float other[(ML + 1) / 2];
+#pragma unroll
+            for (int t = 0; t < ML; ++t)
+                if ((t & 1) == crank) other[t >> 1] = ld_peer_f32(red + t * kTileRows + q * 32 + lane, (uint32_t)(crank ^ 1));
+#pragma unroll
+            for (int t = 0; t < ML; ++t) {
+                if ((t & 1) != crank) continue;
+                const float mine = bf16_to_f32(f32_to_bf16(acc[t]));
+                const float gt = crank ? other[t >> 1] : mine;
+                const float up = crank ? mine : other[t >> 1];
+                const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, (float)exp((double)(-gt))));
+                const float a = P.gsilu ? __fmul_rn(gt, sg) : sg;
+                const float h = bf16_to_f32(f32_to_bf16(__fmul_rn(a, up)));
+                acc[t] = h;
+                float mx = fabsf(h);
+                if (!(mx > 0.0f)) mx = 0.0f;                    /* NaN and zero start the maximum at 0 */
+                for (int off = 16; off; off >>= 1) {
+                    const float o = __shfl_xor_sync(0xffffffffu, mx, off);
+                    if (o > mx) mx = o;
+                }
+                if (lane == 0) amax_s[q * ML + t] = mx;
+            }
+            asm volatile("bar.sync 3, 128;" ::: "memory");
+            const int grp = (int)(blockIdx.x / 2);
+#pragma unroll
+            for (int t = 0; t < ML; ++t) {
+                if ((t & 1) != crank || t >= P.mlive || !alive) continue;
+                float r = amax_s[t];
+                for (int w = 1; w < 4; ++w) if (amax_s[w * ML + t] > r) r = amax_s[w * ML + t];
+                const float sc = r > 0.0f ? __fmul_rn(r, 1.0f / 448.0f) : 1.0f;
+                if (q == 0 && lane == 0) P.gs[(int64_t)t * P.gs_pitch + grp] = sc;
+                const float inv = __fdiv_rn(1.0f, sc);
+                const float h = acc[t];
+                if (P.gob) {
+                    if (P.gob_dtype == RAD_F32) ((float*)P.gob)[(int64_t)t * P.gob_pitch + col] = h;
+                    else ((uint16_t*)P.gob)[(int64_t)t * P.gob_pitch + col] = f32_to_bf16(h);
+                }
+                float c = __fmul_rn(h, inv);
+                if (c > 448.0f) c = 448.0f;
+                if (c < -448.0f) c = -448.0f;
+                P.gq[(int64_t)t * P.gq_pitch + col] = f32_to_e4m3(c);
+            }
+        }
     }
-    if (warp >= 2 && crank == 0 && alive && row < P.n) {
+    if (!GATED && warp >= 2 && crank == 0 && alive && row < P.n) {
         if (LG) {
             /* activation rows [0, ML/2) carry the leading piece of each token and rows
              * [ML/2, ML) the residual piece: their sums are the token's logit */
@@ -408,7 +471,7 @@ const CUtensorMap* tensor_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_
 
 int sm_count();
 
-template <int FMT, int NTOK, int ML, int kTcStages, int LG>
+template <int FMT, int NTOK, int ML, int kTcStages, int LG, int GATED>
 int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaStream_t st) {
     const size_t smem = 1024 + (size_t)kTcStages * (kABytes + NTOK * kStageK) +
                         (3 * kTcStages + 8) * sizeof(uint64_t) + 16 +
@@ -419,10 +482,10 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
     if (adev < 0) return RAD_E_DEVICE;
     size_t& attr_set = attr_set_dev[adev];
     if (smem > attr_set) {
-        if (cudaFuncSetAttribute(k_tc_decode<FMT, NTOK, ML, kTcStages, LG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(k_tc_decode<FMT, NTOK, ML, kTcStages, LG, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) return RAD_E_DEVICE;
         /* ask for the largest shared-memory carve-out so that two CTAs fit on an SM */
-        (void)cudaFuncSetAttribute(k_tc_decode<FMT, NTOK, ML, kTcStages, LG>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        (void)cudaFuncSetAttribute(k_tc_decode<FMT, NTOK, ML, kTcStages, LG, GATED>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                    (int)cudaSharedmemCarveoutMaxShared);
         attr_set = smem;
     }
@@ -439,9 +502,11 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
     if (ks > 8) ks = 8;
     if (ks > P.k / kStageK) ks = P.k / kStageK;
     if (ks < 1) ks = 1;
+    int grid = tiles * ks;
+    if (GATED) { ks = 2; grid = tiles; }               /* tiles = gate tiles + up tiles: one cluster a pair */
     P.ksplit = ks;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned)(tiles * ks));
+    cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kTcThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -452,21 +517,21 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
     at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = tc_pdl_on() ? 2 : 1;
     count_launch();
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_decode<FMT, NTOK, ML, kTcStages, LG>, *tw, *ta, P);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_decode<FMT, NTOK, ML, kTcStages, LG, GATED>, *tw, *ta, P);
     return e == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
 }
 
-template <int FMT, int NTOK, int ML, int LG = 0>
+template <int FMT, int NTOK, int ML, int LG = 0, int GATED = 0>
 int launch_tc(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaStream_t st) {
     /* the deepest ring that still lets two CTAs share an SM (233472 bytes of shared memory,
      * 1 KiB of it reserved per CTA): two CTAs' streams together are what saturates HBM */
     const size_t fixed = 1024 + (3 * 6 + 8) * sizeof(uint64_t) + 16 + (size_t)(P.k / kStageK) * NTOK * sizeof(float);
     const size_t stage = kABytes + NTOK * kStageK;
     const size_t half = 233472 / 2 - 1024;
-    if (fixed + 6 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 6, LG>(tw, ta, P, st);
-    if (fixed + 4 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 4, LG>(tw, ta, P, st);
-    if (fixed + 3 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 3, LG>(tw, ta, P, st);
-    return launch_tc_s<FMT, NTOK, ML, 6, LG>(tw, ta, P, st);          /* one CTA per SM */
+    if (fixed + 6 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 6, LG, GATED>(tw, ta, P, st);
+    if (fixed + 4 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 4, LG, GATED>(tw, ta, P, st);
+    if (fixed + 3 * stage <= half) return launch_tc_s<FMT, NTOK, ML, 3, LG, GATED>(tw, ta, P, st);
+    return launch_tc_s<FMT, NTOK, ML, 6, LG, GATED>(tw, ta, P, st);          /* one CTA per SM */
 }
 
 int sm_count() {
@@ -566,15 +631,15 @@ bool lg_scratch(LgScratch* out) {
     return true;
 }
 
-template <int FMT, int NTOK>
+template <int FMT, int NTOK, int GATED = 0>
 int launch_tc_ml(const CUtensorMap* tw, const CUtensorMap* ta, const TcParams& P, cudaStream_t st) {
     if (NTOK == 16) {
-        if (P.m <= 1) return launch_tc<FMT, 16, 1>(tw, ta, P, st);
-        if (P.m <= 2) return launch_tc<FMT, 16, 2>(tw, ta, P, st);
-        if (P.m <= 4) return launch_tc<FMT, 16, 4>(tw, ta, P, st);
-        if (P.m <= 8) return launch_tc<FMT, 16, 8>(tw, ta, P, st);
+        if (P.m <= 1) return launch_tc<FMT, 16, 1, 0, GATED>(tw, ta, P, st);
+        if (P.m <= 2) return launch_tc<FMT, 16, 2, 0, GATED>(tw, ta, P, st);
+        if (P.m <= 4) return launch_tc<FMT, 16, 4, 0, GATED>(tw, ta, P, st);
+        if (P.m <= 8) return launch_tc<FMT, 16, 8, 0, GATED>(tw, ta, P, st);
     }
-    return launch_tc<FMT, NTOK, NTOK>(tw, ta, P, st);
+    return launch_tc<FMT, NTOK, NTOK, 0, GATED>(tw, ta, P, st);
 }
 
 bool al(const void* p, int a) { return (((uintptr_t)p) & (uintptr_t)(a - 1)) == 0; }
@@ -608,6 +673,36 @@ int tc_fp8a8(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push) {
     if (ntok == 16) return launch_tc_ml<TC_FP8, 16>(tw, ta, P, st);
     if (ntok == 32) return launch_tc_ml<TC_FP8, 32>(tw, ta, P, st);
     return launch_tc_ml<TC_FP8, 64>(tw, ta, P, st);
+}
+
+/* gemm_nt_q_gated in one launch: served when the plain band would run the same accumulation (one CTA a
+ * row tile over the whole K: enough tiles that K is not split), so that the result stays byte-identical to
+ * the band followed by the quantiser; n_half a multiple of 128 = one quantiser group a gate tile */
+bool tc_fp8a8_gated_ok(const R3dGemmQ& p) {
+    static const int forced = [] { const char* e = getenv("R3D_TC_KSPLIT"); return e ? atoi(e) : 0; }();
+    const int tiles = (p.n + kTileRows - 1) / kTileRows;
+    return tc_fp8a8_ok(p) && (p.n % (2 * kTileRows)) == 0 && forced <= 1 && (5 * sm_count() / 3) / tiles < 2;
+}
+
+int tc_fp8a8_gated(const R3dGemmQ& p, const GatedOut& g, cudaStream_t st) {
+    const int ntok = p.m <= 16 ? 16 : p.m <= 32 ? 32 : 64;
+    const CUtensorMap* tw = tensor_map(p.b, (uint64_t)p.k, (uint64_t)p.n, (uint64_t)p.b_pitch,
+                                       CU_TENSOR_MAP_DATA_TYPE_UINT8, kTileRows);
+    const CUtensorMap* ta = tensor_map(p.a, (uint64_t)p.k, (uint64_t)p.m, (uint64_t)p.a_pitch,
+                                       CU_TENSOR_MAP_DATA_TYPE_UINT8, (uint32_t)ntok);
+    if (!tw || !ta) return RAD_E_UNSUPPORTED;
+    TcParams P{};
+    P.ws = (const uint8_t*)p.b_scale; P.ws_pitch = p.bs_pitch;
+    P.as = p.a_scale; P.as_pitch = p.as_pitch;
+    P.y = nullptr; P.y_pitch = 0; P.y_dtype = RAD_BF16;
+    P.m = p.m; P.mlive = p.m; P.n = p.n; P.k = p.k;
+    P.as_cols = p.as_cols; P.ws_cols = p.bs_cols; P.rblk = p.rblk; P.ws_dtype = p.bs_dtype;
+    P.gated = 1; P.gsilu = g.silu; P.gob_dtype = g.ob_dtype;
+    P.gq = (uint8_t*)g.q; P.gq_pitch = g.q_pitch; P.gs = g.scale; P.gs_pitch = g.s_pitch;
+    P.gob = g.ob; P.gob_pitch = g.ob_pitch;
+    if (ntok == 16) return launch_tc_ml<TC_FP8, 16, 1>(tw, ta, P, st);
+    if (ntok == 32) return launch_tc_ml<TC_FP8, 32, 1>(tw, ta, P, st);
+    return launch_tc_ml<TC_FP8, 64, 1>(tw, ta, P, st);
 }
 
 int tc_mxfp4a8(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push) {
@@ -723,6 +818,8 @@ int tc_status() {
     v = tc_gemm2_status();
     if (v) return v;
     v = tc_w2a8_status();
+    if (v) return v;
+    v = rerank_status();
     return v ? v : tc_gemm_status();
 }
 

@@ -140,6 +140,22 @@ extern "C" int r3d_b200_gemm_fp8a8(const R3dGemmQ* q, void* stream) {
     return RAD_E_UNSUPPORTED;
 }
 
+/* gemm_nt_q_gated @ fp8a8 in one launch: the band with the gated quantiser as its epilogue. q->y is not
+ * used. RAD_E_UNSUPPORTED when the shape is not one the fused kernel serves byte-identically to the
+ * band followed by r3d_b200_gated_quant_fp8 (the caller then runs that pair). */
+extern "C" int r3d_b200_gemm_fp8a8_gated(const R3dGemmQ* q, void* codes, int64_t q_pitch, float* scale,
+                                         int64_t s_pitch, void* ob, int32_t ob_dtype, int64_t ob_pitch,
+                                         int32_t silu, void* stream) {
+    if (!q || !codes || !scale || !device_is_sm100()) return RAD_E_UNSUPPORTED;
+    if (ob && ob_dtype != RAD_BF16 && ob_dtype != RAD_F32) return RAD_E_DTYPE;
+    static const bool off = [] { const char* e = getenv("R3D_GATED_COMPOSED"); return e && *e && *e != '0'; }();
+    if (off || q->m > 64 || (q->arm != R3D_ARM_AUTO && q->arm != R3D_ARM_TILE) || !tc_fp8a8_gated_ok(*q))
+        return RAD_E_UNSUPPORTED;
+    debug_arm("fp8a8", "tcgen05 with the gated quantiser as its epilogue", q->m);
+    const GatedOut g{codes, q_pitch, scale, s_pitch, ob, ob_dtype, ob_pitch, silu};
+    return tc_fp8a8_gated(*q, g, (cudaStream_t)stream);
+}
+
 extern "C" int r3d_b200_gemm_mxfp4a8(const R3dGemmQ* q, void* stream) {
     if (!q || !device_is_sm100()) return RAD_E_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;

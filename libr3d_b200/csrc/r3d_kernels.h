@@ -80,6 +80,10 @@ int  tc_gemm_ws_fp8a8(const R3dGemmQ& p, cudaStream_t st);
  * [256 x 192] per pair */
 bool tc_gemm_mx_ok(const R3dGemmQ& p);
 int  tc_gemm_mx(const R3dGemmQ& p, cudaStream_t st);
+/* outputs of the gated quantiser when it runs as the epilogue of the fp8a8 decode kernel */
+struct GatedOut { void* q; int64_t q_pitch; float* scale; int64_t s_pitch; void* ob; int ob_dtype; int64_t ob_pitch; int silu; };
+bool tc_fp8a8_gated_ok(const R3dGemmQ& p);
+int  tc_fp8a8_gated(const R3dGemmQ& p, const GatedOut& g, cudaStream_t st);
 int  tc_gemm2_status();
 int  tc_status();                      /* 0, or the code of a bounded wait that expired */
 
@@ -93,6 +97,7 @@ bool tc_q8x_ok(const R3dGemmQ& p);
 int  tc_q8x(const R3dGemmQ& p, int8_t* x8, float* sg, int walk, cudaStream_t st);
 int  tc_q8x_status();
 int  tc_w2a8_status();
+int  rerank_status();
 /* requantise + dot, on the tensor core when the operands allow it, else the dp4a kernels */
 int  q8x_run(const R3dGemmQ& p, int8_t* x8, float* sg, int walk, cudaStream_t st);
 

@@ -32,6 +32,7 @@ EXPORTS = [
     "r3d_rad_gemm_nt_q_mx8", "r3d_b200_mma_peak", "r3d_rad_logit_rerank_e4m3", "r3d_b200_forget_head",
     "r3d_rad_gemm_nt_q_w2a8_decode", "r3d_layout_gemm_w2a8", "r3d_relayout_gemm_w2a8", "r3d_unrelayout_gemm_w2a8",
     "r3d_b200_gemm_w2a8",
+    "r3d_b200_gemm_fp8a8_gated",
     "r3d_b200_logits", "r3d_b200_quant_act_fp8", "r3d_b200_pick_arm_fp8a8",
     "r3d_b200_pick_arm_mxfp4a8", "r3d_b200_launch_count", "r3d_b200_stream_status",
     "r3d_b200_gather_create", "r3d_b200_gather_connect", "r3d_b200_gather_buffer", "r3d_b200_gather_wait",

@@ -85,3 +85,64 @@ def test_fused_row_refusals():
     ops.gemm_nt_q_gated(t["A"], t["AS"], t["B"], t["BS"].view(torch.bfloat16), q, s, N=N, K=K, scratch=exact)
     torch.cuda.synchronize()
     assert int(torch.count_nonzero(q)) > 0
+
+
+def _q_struct(t, M, N, K, y_ptr=0):
+    q = abi.R3dGemmQ()
+    q.a, q.a_scale, q.b, q.b_scale, q.y = t["A"].data_ptr(), t["AS"].data_ptr(), t["B"].data_ptr(), t["BS"].data_ptr(), y_ptr
+    q.m, q.n, q.k, q.as_cols = M, N, K, K // 128
+    q.a_pitch, q.y_pitch, q.as_pitch, q.arm = K, N, K // 128, abi.R3D_ARM_AUTO
+    q.bs_cols, q.rblk, q.bs_dtype, q.b_pitch, q.bs_pitch = K // 128, 128, abi.RAD_BF16, K, K // 128
+    return q
+
+
+@pytest.mark.parametrize("M,N,K,act", [(1, 16384, 512, "silu"), (5, 27648, 640, "sigmoid"), (16, 27648, 5120, "silu"),
+                                       (33, 16384, 1024, "silu"), (64, 16384, 384, "sigmoid")])
+def test_wide_projections_run_as_one_launch_with_the_pair_s_bytes(M, N, K, act):
+    """Projections wide enough that the band does not split K are served by the decode kernel with the gated
+    quantiser as its epilogue (a gate tile and its up tile in a cluster of two): the launch-layer entry takes
+    the call, and codes, scales and the gated product are the bytes of the band followed by the quantiser."""
+    case = gen.case_fp8(900 + M, M, N, K, "ref128")
+    t = {k: gu.dev(case[k]) for k in ("A", "AS", "B", "BS")}
+    n = N // 2
+    y = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_nt_q(t["A"], t["AS"], t["B"], t["BS"].view(torch.bfloat16), y, dtype="fp8a8", N=N, K=K)
+    torch.cuda.synchronize()
+    ybits = y.view(torch.int16).cpu().numpy().view(np.uint16)
+    want_q, want_s, want_ob = orc.gated_quant_fp8(ybits, 128, act == "silu", want_ob=True)
+    # the row
+    q = torch.zeros((M, n), dtype=torch.uint8, device="cuda")
+    s = torch.zeros((M, n // 128), dtype=torch.float32, device="cuda")
+    ob = torch.zeros((M, n), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_nt_q_gated(t["A"], t["AS"], t["B"], t["BS"].view(torch.bfloat16), q, s, N=N, K=K, act=act, out=ob)
+    torch.cuda.synchronize()
+    assert np.array_equal(q.cpu().numpy(), want_q)
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), want_s.view(np.uint32))
+    assert np.array_equal(ob.view(torch.int16).cpu().numpy().view(np.uint16), want_ob)
+    # the one-launch entry itself, guard bands around its outputs, f32 product
+    P = ops.plugin()
+    gq, gs, gob = gu.GuardedOut((M, n), np.uint8), gu.GuardedOut((M, n // 128), np.float32), gu.GuardedOut((M, n), np.float32)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    qs = _q_struct(t, M, N, K)
+    rc = P.lib.r3d_b200_gemm_fp8a8_gated(C.byref(qs), C.c_void_p(gq.ptr), C.c_int64(n), C.c_void_p(gs.ptr), C.c_int64(n // 128),
+                                         C.c_void_p(gob.ptr), C.c_int32(abi.RAD_F32), C.c_int64(n), C.c_int32(act == "silu"), st)
+    assert rc == abi.RAD_OK
+    assert np.array_equal(gq.get(), want_q)
+    assert np.array_equal(gs.get().view(np.uint32), want_s.view(np.uint32))
+    assert np.array_equal(gen.f32_to_bf16_bits(gob.get()), want_ob)
+    assert P.lib.r3d_b200_stream_status() == 0
+
+
+def test_narrow_projections_stay_on_the_pair():
+    """where the band splits K between the CTAs of a cluster the one-launch entry declines (its accumulation
+    would differ from the band's) and the row runs the pair"""
+    M, N, K = 4, 1024, 512
+    case = gen.case_fp8(2, M, N, K, "ref128")
+    t = {k: gu.dev(case[k]) for k in ("A", "AS", "B", "BS")}
+    P = ops.plugin()
+    n = N // 2
+    gq, gs = gu.GuardedOut((M, n), np.uint8), gu.GuardedOut((M, n // 128), np.float32)
+    qs = _q_struct(t, M, N, K)
+    rc = P.lib.r3d_b200_gemm_fp8a8_gated(C.byref(qs), C.c_void_p(gq.ptr), C.c_int64(n), C.c_void_p(gs.ptr), C.c_int64(n // 128),
+                                         None, C.c_int32(abi.RAD_BF16), C.c_int64(0), C.c_int32(1), None)
+    assert rc == abi.RAD_E_UNSUPPORTED

@@ -108,3 +108,25 @@ def test_logit_rerank_against_the_reference_kernel(M, N, K, R, br, sdt, off):
     finally:
         torch.cuda.synchronize()
         Rf.ref_rerank_free(mem)
+
+
+@pytest.mark.parametrize("nan", [False, True])
+def test_logit_rerank_duplicate_ids_and_nan_scores(nan):
+    """The same id twice in a row's list (equal value, equal id: the earlier slot is picked first) and, in the
+    second case, a head row holding a NaN code: its score is NaN and the selection's comparisons with it are
+    all false, which makes the outcome depend on the slot order exactly as the reference's loop does."""
+    M, N, K, R = 3, 700, 1280, 16
+    c, ids = _case(5, M, N, K, R, 128, 0, 0, pads=True, ties=True)
+    ids[:, 9] = ids[:, 6]
+    ids[1, 0] = ids[1, 12]
+    if nan:
+        c["codes"][ids[0, 7], 100] = 0x7F
+        c["codes"][ids[2, 0], 3] = 0xFF
+    want_i, want_v, want_p = orc.logit_rerank_e4m3(c["X"], c["codes"], c["scale"], 0, 128, ids, 0)
+    got_i, got_v, got_p = _run(c, ids, N, K, 0)
+    assert np.array_equal(got_i, want_i)
+    same = lambda a, b: ((a.view(np.uint32) == b.view(np.uint32)) | (np.isnan(a) & np.isnan(b))).all()
+    assert same(got_v, want_v)                                  # a NaN's sign and payload are not part of the contract
+    assert np.array_equal(np.ascontiguousarray(got_p[..., 0]).view(np.uint32), np.ascontiguousarray(want_p[..., 0]).view(np.uint32))
+    assert same(np.ascontiguousarray(got_p[..., 1]), np.ascontiguousarray(want_p[..., 1]))
+    assert np.isnan(want_v).any() == nan
