@@ -51,6 +51,11 @@ int r3d_rad_rmsnorm_quant_fp8(const RadArgs* a, RadStream s);
  * (int32 id, f32 value) plane a sharded head gathers instead of its logits. Replaces
  * r3d_rad_row_topk (src/r3d_more.hip:179-236, :438-476). */
 int r3d_rad_row_topk(const RadArgs* a, RadStream s);
+/* scratch hooks of row_topk and sample_argmax (no reference counterpart: the reference's rows re-read the row
+ * from one block and need no arena): bytes of the tournament's two survivor planes. With the arena in
+ * RadArgs.scratch the rows allocate nothing; without one they fall back to planes of their own. */
+int64_t r3d_rad_row_topk_scratch(const RadArgs* a);
+int64_t r3d_rad_sample_argmax_scratch(const RadArgs* a);
 /* sample_argmax (logits, params, token): greedy decode over f32 logits, ties to the lower token
  * id; `params` is not read. Replaces r3d_rad_sample_argmax (src/r3d_sample.hip:166-173, :607-623). */
 int r3d_rad_sample_argmax(const RadArgs* a, RadStream s);

@@ -173,7 +173,20 @@ extern "C" int r3d_rad_row_topk(const RadArgs* a, RadStream s) {
     if (!device_is_sm100()) return RAD_E_UNSUPPORTED;
     return launch_row_topk(x->data, (int)x->dtype, xp, (int32_t*)idx->data, ip, (float*)val->data, vp,
                            pairs ? (float*)pairs->data : nullptr, pp, (int)M, (int)N, (int)R, off,
-                           (cudaStream_t)(uintptr_t)s);
+                           (cudaStream_t)(uintptr_t)s, a->scratch, a->scratch_bytes);
+}
+
+/* the launch arena of row_topk: the tournament's two survivor planes (src/r3d_more.hip's row needs none: it
+ * re-reads the row R times from one block instead). With the arena the row allocates nothing; without one
+ * it falls back to planes of its own, allocated on first use. */
+extern "C" int64_t r3d_rad_row_topk_scratch(const RadArgs* a) {
+    const RadTensor* x = rad_arg_in(a, 0);
+    const int64_t N = int_param(a, "N", x && x->rank >= 2 ? x->shape[1] : 0);
+    const int64_t R = int_param(a, "R", 1);
+    if (N <= 0 || N > kMaxExtent || R <= 0 || R > 32) return 0;
+    /* M from the operand when it is there, else the query's M (an upper bound is what an arena wants) */
+    const int64_t M = x ? rad_tensor_numel(x) / N : int_param(a, "M", 0);
+    return M > 0 && M <= 0xffff ? r3d::row_topk_scratch_bytes(M, N, R) : 0;
 }
 
 /* Greedy sampling: token[m] = the column of the row's largest logit, ties to the lower token id --
@@ -193,5 +206,14 @@ extern "C" int r3d_rad_sample_argmax(const RadArgs* a, RadStream s) {
     if (lg->rank != 2 || lg->shape[1] != nv || lg->stride[1] != 1) return RAD_E_STRIDE;
     if (!device_is_sm100()) return RAD_E_UNSUPPORTED;
     return launch_row_topk(lg->data, RAD_F32, lg->stride[0], (int32_t*)tok->data, 1, nullptr, 0, nullptr, 0, (int)M,
-                           (int)nv, 1, 0, (cudaStream_t)(uintptr_t)s);
+                           (int)nv, 1, 0, (cudaStream_t)(uintptr_t)s, a->scratch, a->scratch_bytes);
+}
+
+extern "C" int64_t r3d_rad_sample_argmax_scratch(const RadArgs* a) {
+    const RadTensor* lg = rad_arg_in(a, 0);
+    long long nv = 0;
+    if (!rad_args_geti(a, "n_vocab", &nv) || nv <= 0) nv = lg && lg->rank >= 2 ? lg->shape[1] : 0;
+    if (nv <= 0 || nv > kMaxExtent) return 0;
+    const int64_t M = lg ? rad_tensor_numel(lg) / nv : int_param(a, "M", 0);
+    return M > 0 && M <= 0xffff ? r3d::row_topk_scratch_bytes(M, nv, 1) : 0;
 }

@@ -154,13 +154,29 @@ Survivors* survivors(size_t items) {
 
 } /* namespace */
 
+/* bytes of the two survivor planes a call needs (0 when the row fits one tile): what the rows' scratch
+ * hooks ask the engine for */
+int64_t row_topk_scratch_bytes(int64_t M, int64_t N, int64_t R) {
+    const int64_t tiles0 = (N + kTile - 1) / kTile;
+    return tiles0 > 1 ? 2 * M * tiles0 * R * (int64_t)sizeof(unsigned long long) : 0;
+}
+
 int launch_row_topk(const void* x, int x_dtype, int64_t x_pitch, int32_t* idx, int64_t idx_pitch, float* val,
                     int64_t val_pitch, float* pairs, int64_t pairs_pitch, int M, int N, int R, int64_t off,
-                    cudaStream_t st) {
+                    cudaStream_t st, void* scratch, int64_t scratch_bytes) {
     const int tiles0 = (N + kTile - 1) / kTile;
     Survivors* S = nullptr;
+    Survivors arena{};
     if (tiles0 > 1) {
-        S = survivors((size_t)M * tiles0 * R);
+        /* the launch arena when the engine provides one (the rows declare a scratch hook: nothing is
+         * allocated then); the plugin's own planes otherwise, grown on first use */
+        const size_t items = (size_t)M * tiles0 * R;
+        if (scratch && scratch_bytes >= row_topk_scratch_bytes(M, N, R) && (((uintptr_t)scratch) & 7) == 0) {
+            arena.k[0] = (unsigned long long*)scratch; arena.k[1] = arena.k[0] + items; arena.items = items;
+            S = &arena;
+        } else {
+            S = survivors(items);
+        }
         if (!S) return RAD_E_DEVICE;
     }
     TopkPass P{};

@@ -35,7 +35,8 @@ int launch_rmsnorm_quant_fp8(const void* x, int64_t x_pitch, void* res, int64_t 
 /* exact per-row top-R (kern_topk.cu); pitches in elements (pairs: floats); val and pairs may be null */
 int launch_row_topk(const void* x, int x_dtype, int64_t x_pitch, int32_t* idx, int64_t idx_pitch, float* val,
                     int64_t val_pitch, float* pairs, int64_t pairs_pitch, int M, int N, int R, int64_t off,
-                    cudaStream_t st);
+                    cudaStream_t st, void* scratch = nullptr, int64_t scratch_bytes = 0);
+int64_t row_topk_scratch_bytes(int64_t M, int64_t N, int64_t R);
 
 /* logit_rerank over the joined e4m3 head (kern_rerank.cu): pitches in elements; pairs may be null */
 int launch_logit_rerank_e4m3(const void* x, int xdt, int64_t x_rs, const void* codes, int64_t code_rs,

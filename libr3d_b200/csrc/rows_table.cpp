@@ -211,6 +211,11 @@ enum { kPrioPlain = 1000, kPrioDecode = 1100, kPrioQ8x = 1200 };
     { name, op, family, summary, shapes, dtypes, RAD_DOMAIN_DEVICE, prio, cons,          \
       COUNT_OF(cons), nullptr, 0, nullptr, nullptr, nullptr, launch, nullptr, nullptr,    \
       nullptr, nullptr, nullptr, nullptr }
+/* the same with a scratch hook (the launch arena the engine provides) */
+#define ROW_S(name, op, family, summary, shapes, dtypes, prio, cons, launch, scratch)    \
+    { name, op, family, summary, shapes, dtypes, RAD_DOMAIN_DEVICE, prio, cons,          \
+      COUNT_OF(cons), nullptr, 0, nullptr, nullptr, nullptr, launch, scratch, nullptr,    \
+      nullptr, nullptr, nullptr, nullptr }
 
 const RadKernelInfo kRows[] = {
     { "logits_gemm_e4m3", "logits_gemm", "vocab",
@@ -331,20 +336,20 @@ const RadKernelInfo kRows[] = {
         kPrioPlain, kCRmsQuant, r3d_rad_rmsnorm_quant_fp8),
 
     /* the consumer behind the column-sharded LM head (src/r3d_rows.cpp:2084-2091) */
-    ROW("rowtopk_bf16", "row_topk", "select",
+    ROW_S("rowtopk_bf16", "row_topk", "select",
         "exact per-row top-R of a bf16 matrix, descending, ties to the lower column: a tournament "
         "of 512-item warp tiles held in registers, repeated over the survivors",
         "any M, N a multiple of 8, R <= 32",
         "bf16 in, f32 values + i32 columns out, optional f32 pairs plane",
-        kPrioPlain, kCRowTopk, r3d_rad_row_topk),
+        kPrioPlain, kCRowTopk, r3d_rad_row_topk, r3d_rad_row_topk_scratch),
 
     /* greedy decode directly behind logits_gemm's f32 logits (src/r3d_rows.cpp:1791-1798) */
-    ROW("sample_argmax_f32", "sample_argmax", "sample",
+    ROW_S("sample_argmax_f32", "sample_argmax", "sample",
         "greedy, ties to the lower token id: the top-1 of the (value descending, id ascending) "
         "tournament that row_topk runs, so greedy and top-1 agree",
         "any vocabulary",
         "f32 logits, i32 token; the parameter blob is not read",
-        kPrioPlain, kCArgmax, r3d_rad_sample_argmax),
+        kPrioPlain, kCArgmax, r3d_rad_sample_argmax, r3d_rad_sample_argmax_scratch),
 };
 
 /* ------------------------------------------------------------------ registration gate */

@@ -186,12 +186,31 @@ def _act_dt(t: torch.Tensor) -> tuple[int, str]:
     return (abi.RAD_F32, "f32") if t.dtype == torch.float32 else (abi.RAD_BF16, "bf16")
 
 
-def _issue(op: str, query: dict, tensors: list) -> Row:
+_ARENA: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _arena(nbytes: int, device: torch.device) -> torch.Tensor:
+    """the launch arena an engine hands a row whose scratch hook asks for one: kept per device, grown only"""
+    key = (device.index or 0, 0)
+    t = _ARENA.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _ARENA[key] = t
+    return t
+
+
+def _issue(op: str, query: dict, tensors: list, scratch_hook=None, device: torch.device | None = None) -> Row:
     P = plugin()
     r = P.resolve(op, query)
     if r is None:
         raise RuntimeError(f"no row serves {op} {query}")
-    rc = P.launch_row(r, ArgPack(tensors, query), _stream())
+    pack = ArgPack(tensors, query)
+    if scratch_hook is not None and device is not None:
+        need = int(scratch_hook(pack.args))
+        if need > 0:
+            arena = _arena(need, device)
+            pack = ArgPack(tensors, query, scratch=arena.data_ptr(), scratch_bytes=arena.numel())
+    rc = P.launch_row(r, pack, _stream())
     if rc != abi.RAD_OK:
         raise RowRefused(r.name, rc)
     return r
@@ -232,14 +251,16 @@ def rmsnorm_quant_fp8(x: torch.Tensor, w: torch.Tensor, q: torch.Tensor, scale: 
 
 
 def row_topk(x: torch.Tensor, idx: torch.Tensor, val: torch.Tensor, pairs: torch.Tensor | None = None, *,
-             R: int, vocab_off: int | None = None) -> Row:
+             R: int, vocab_off: int | None = None, arena: bool = True) -> Row:
     """The row_topk op through its row: x [M, N] bf16 -> idx i32 [M, R], val f32 [M, R] and, when given,
-    pairs f32 [M, R, 2] holding (bits of the int32 id, value)."""
+    pairs f32 [M, R, 2] holding (bits of the int32 id, value). `arena`: hand the row the launch arena its
+    scratch hook asks for (as an engine does); without it the row uses planes of its own."""
     query = dict(M=x.shape[0], N=x.shape[-1], R=R, dtype="bf16")
     if vocab_off is not None:
         query["vocab_off"] = int(vocab_off)
     return _issue("row_topk", query, [_desc(x, abi.RAD_BF16), _desc(idx, abi.RAD_I32), _desc(val, abi.RAD_F32),
-                                      _desc(pairs, abi.RAD_F32)])
+                                      _desc(pairs, abi.RAD_F32)],
+                  plugin().lib.r3d_rad_row_topk_scratch if arena else None, x.device)
 
 
 def sample_argmax(logits: torch.Tensor, token: torch.Tensor, params: torch.Tensor | None = None) -> Row:
@@ -247,7 +268,8 @@ def sample_argmax(logits: torch.Tensor, token: torch.Tensor, params: torch.Tenso
     lower id). `params` is the engine's per-row parameter blob; the row does not read it."""
     query = dict(M=logits.shape[0], n_vocab=logits.shape[1])
     return _issue("sample_argmax", query, [_desc(logits, abi.RAD_F32), _desc(params, abi.RAD_U8),
-                                           _desc(token, abi.RAD_I32)])
+                                           _desc(token, abi.RAD_I32)],
+                  plugin().lib.r3d_rad_sample_argmax_scratch, logits.device)
 
 
 class BoundGemm:

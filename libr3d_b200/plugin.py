@@ -24,6 +24,7 @@ EXPORTS = [
     "r3d_rad_gemm_nt_q_fp8", "r3d_rad_gemm_nt_q_fp8_decode", "r3d_rad_gemm_nt_q",
     "r3d_rad_gemm_nt_q_mxfp4_decode", "r3d_rad_gemm_nt_q_mxfp4_decode_q8x",
     "r3d_rad_gemm_nt_q_gated_fp8", "r3d_rad_gemm_nt_q_gated_fp8_scratch", "r3d_b200_gated_quant_fp8",
+    "r3d_rad_row_topk_scratch", "r3d_rad_sample_argmax_scratch",
     "r3d_rad_quant_act_fp8", "r3d_rad_gated_quant_fp8", "r3d_rad_rmsnorm_quant_fp8", "r3d_rad_row_topk", "r3d_rad_sample_argmax",
     "r3d_mxfp4_q8x_off", "r3d_rad_logits_gemm_e4m3", "r3d_layout_head", "r3d_relayout_head",
     "r3d_unrelayout_head",
@@ -50,6 +51,7 @@ class Row:
     constraints: list[tuple[str, int, int, str | None]]
     launch: int
     has_layout: bool
+    has_scratch: bool = False
 
 
 def _holds(c: tuple[str, int, int, str | None], query: dict[str, Any]) -> bool:
@@ -102,6 +104,9 @@ class Plugin:
         L.r3d_b200_logits.argtypes = [C.POINTER(abi.R3dLogits), C.c_void_p]
         L.r3d_rad_gemm_nt_q_gated_fp8_scratch.restype = C.c_int64
         L.r3d_rad_gemm_nt_q_gated_fp8_scratch.argtypes = [C.POINTER(abi.RadArgs)]
+        for hook in (L.r3d_rad_row_topk_scratch, L.r3d_rad_sample_argmax_scratch):
+            hook.restype = C.c_int64
+            hook.argtypes = [C.POINTER(abi.RadArgs)]
         L.r3d_b200_gated_quant_fp8.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
                                                C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
                                                C.c_int32, C.c_void_p]
@@ -151,7 +156,7 @@ class Plugin:
                      r.constraints[j].sval.decode() if r.constraints[j].sval else None)
                     for j in range(r.n_constraints)]
             out.append(Row(r.name.decode(), r.op.decode(), r.priority, r.domain, cons,
-                           r.launch or 0, bool(r.layout)))
+                           r.launch or 0, bool(r.layout), bool(r.scratch)))
         return out
 
     def resolve(self, op: str, query: dict[str, Any]) -> Row | None:

@@ -240,3 +240,35 @@ def test_greedy_decode_tail_logits_then_argmax():
     ops.sample_argmax(ld, tok)
     torch.cuda.synchronize()
     assert np.array_equal(tok.cpu().numpy(), orc.sample_argmax(got))
+
+
+def test_row_topk_with_the_launch_arena_allocates_nothing_and_agrees():
+    """With the arena its scratch hook asks for, the row's first call at a new size leaves the device's free
+    memory where it was (the survivor planes live in the arena); without the arena it falls back to planes of
+    its own. Both give the same picks."""
+    M, N, R = 3, 40000, 32
+    rng = np.random.default_rng(12)
+    x = gen.f32_to_bf16_bits(rng.standard_normal((M, N)).astype(np.float32))
+    xd = gu.dev(x).view(torch.bfloat16)
+    outs = []
+    for arena in (True, False):
+        idx = torch.zeros((M, R), dtype=torch.int32, device="cuda")
+        val = torch.zeros((M, R), dtype=torch.float32, device="cuda")
+        if arena:
+            ops.row_topk(xd, idx, val, None, R=R)                     # the arena itself is created here
+            torch.cuda.synchronize()
+            free0 = torch.cuda.mem_get_info()[0]
+            xs = gu.dev(gen.f32_to_bf16_bits(rng.standard_normal((5, N)).astype(np.float32))).view(torch.bfloat16)
+            i5 = torch.zeros((5, R), dtype=torch.int32, device="cuda")
+            v5 = torch.zeros((5, R), dtype=torch.float32, device="cuda")
+            torch.cuda.synchronize()
+            free1 = torch.cuda.mem_get_info()[0]
+            ops.row_topk(xs, i5, v5, None, R=R)                        # more survivors than any call before
+            torch.cuda.synchronize()
+            assert torch.cuda.mem_get_info()[0] == free1 <= free0
+        ops.row_topk(xd, idx, val, None, R=R, arena=arena)
+        torch.cuda.synchronize()
+        outs.append((idx.cpu().numpy(), val.cpu().numpy()))
+    want_i, want_v = orc.row_topk(x, R, 0)
+    for gi, gv in outs:
+        assert np.array_equal(gi, want_i) and np.array_equal(gv.view(np.uint32), want_v.view(np.uint32))
