@@ -145,9 +145,9 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "C2 mxfp4a8 decode GEMV, M in {1,2,4}, K=5120, N=27648 per GPU", "sample": sample,
-                   "host_threads": threads},
-        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": {"workload": "C2 mxfp4a8 decode GEMV, M in {1,2,4}, K=5120, N=27648 per GPU"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample,
+                         "host_threads": threads},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "reference_gpu": ref_gpu,
     }))

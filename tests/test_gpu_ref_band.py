@@ -164,6 +164,9 @@ def test_gemm_arms_against_the_reference_kernels(kind, entry, M, N, K):
     assert (d <= 2).mean() > 0.999, ("this library vs reference", float((d <= 2).mean()), int(d.max()))
 
 
+_IMMORTAL_WEIGHTS: list = []
+
+
 @pytest.mark.parametrize("M", [1, 2, 4, 8])
 def test_q8x_arm_against_the_reference_q8x_row(M):
     """The reference's int8-per-32 decode row (its repacked plane, requantiser and dot4 / lane-map
@@ -175,6 +178,10 @@ def test_q8x_arm_against_the_reference_q8x_row(M):
     N, K = 640, 2048
     case = gen.case_mxfp4(7100 + M, M, N, K)
     t = {k: gu.dev(case[k]) for k in ("A", "AS", "B", "BS")}
+    # The reference row remembers the int8 plane it repacked by the weight's device address and treats
+    # weights as immortal (src/r3d_gemm_mxfp4.hip:1879-1880): a weight freed here could hand its address to
+    # the next case's weight, which the reference would then serve with this case's plane.
+    _IMMORTAL_WEIGHTS.append((t["B"], t["BS"]))
     y_ref = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
     pack = _gemm_pack(t, "mxfp4a8", M, N, K, y_ref)
     assert R.ref_mxfp4_gemm_nt_q_decode_q8x(C.byref(pack.args), None) == 0
