@@ -471,6 +471,26 @@ const CUtensorMap* tensor_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_
 
 int sm_count();
 
+/* K shares per row tile (the CTAs of one cluster; never more shares than whole stages). Measured over 16
+ * to 216 row tiles (M = 1..16, K = 4096..13824): the best share count keeps the grid near 190-250 CTAs
+ * and never past five shares -- more CTAs than the device holds at once (two per SM) wait for a second
+ * wave (tiles * shares of 298 ran up to 70 % slower), and six to eight shares cost more in the reduction
+ * than they stream. 124 to 148 tiles (one CTA per SM, half the device's slots idle: the slab of a head
+ * sharded eight ways) take two shares, 296 CTAs at most (measured on 148 tiles x 5120: 21.5 -> 19.7 us).
+ * Splitting off the few tiles past a whole number of waves into a second grid with five shares was
+ * measured and dropped (297 tiles: 41.9 -> 41.0 us; the full head 119 -> 125 us: the remainder already
+ * overlaps the last wave and the next call's prefetch). */
+int k_shares(int tiles, int n128, int ctas_per_sm) {
+    static const int forced = [] { const char* e = getenv("R3D_TC_KSPLIT"); return e ? atoi(e) : 0; }();
+    const int sms = sm_count();
+    int ks = forced > 0 ? forced : (5 * sms / 3) / (tiles > 0 ? tiles : 1);
+    if (forced <= 0 && ks > 5) ks = 5;
+    if (forced <= 0 && ks == 1 && tiles <= sms && ctas_per_sm >= 2) ks = 2;
+    if (ks > 8) ks = 8;
+    if (ks > n128) ks = n128;
+    return ks < 1 ? 1 : ks;
+}
+
 template <int FMT, int NTOK, int ML, int kTcStages, int LG, int GATED>
 int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaStream_t st) {
     const size_t smem = 1024 + (size_t)kTcStages * (kABytes + NTOK * kStageK) +
@@ -489,24 +509,12 @@ int launch_tc_s(const CUtensorMap* tw, const CUtensorMap* ta, TcParams P, cudaSt
                                    (int)cudaSharedmemCarveoutMaxShared);
         attr_set = smem;
     }
-    /* K shares per row tile (CTAs of one cluster): never more shares than whole stages, at most 8
-     * (portable cluster) */
     const int tiles = (P.n + kTileRows - 1) / kTileRows;
-    static const int forced = [] { const char* e = getenv("R3D_TC_KSPLIT"); return e ? atoi(e) : 0; }();
-    /* measured over 16 to 216 row tiles (M = 1..16, K = 4096..13824): the best share count keeps
-     * the grid near 190-250 CTAs and never past five shares -- tiles * shares of 288 and more ran up
-     * to 70 % slower (a cluster must sit inside one GPC, so the last clusters of such a grid wait
-     * for a second wave), and six to eight shares cost more in the reduction than they stream */
-    int ks = forced > 0 ? forced : (5 * sm_count() / 3) / (tiles > 0 ? tiles : 1);
-    if (forced <= 0 && ks > 5) ks = 5;
-    if (ks > 8) ks = 8;
-    if (ks > P.k / kStageK) ks = P.k / kStageK;
-    if (ks < 1) ks = 1;
-    int grid = tiles * ks;
-    if (GATED) { ks = 2; grid = tiles; }               /* tiles = gate tiles + up tiles: one cluster a pair */
+    /* gated: tiles = gate tiles + up tiles, one cluster a pair */
+    const int ks = GATED ? 2 : k_shares(tiles, P.k / kStageK, 2 * smem + 2048 <= 233472 ? 2 : 1);
     P.ksplit = ks;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned)grid);
+    cfg.gridDim = dim3((unsigned)(GATED ? tiles : tiles * ks));
     cfg.blockDim = dim3(kTcThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -679,9 +687,8 @@ int tc_fp8a8(const R3dGemmQ& p, cudaStream_t st, const PushCfg* push) {
  * row tile over the whole K: enough tiles that K is not split), so that the result stays byte-identical to
  * the band followed by the quantiser; n_half a multiple of 128 = one quantiser group a gate tile */
 bool tc_fp8a8_gated_ok(const R3dGemmQ& p) {
-    static const int forced = [] { const char* e = getenv("R3D_TC_KSPLIT"); return e ? atoi(e) : 0; }();
     const int tiles = (p.n + kTileRows - 1) / kTileRows;
-    return tc_fp8a8_ok(p) && (p.n % (2 * kTileRows)) == 0 && forced <= 1 && (5 * sm_count() / 3) / tiles < 2;
+    return tc_fp8a8_ok(p) && (p.n % (2 * kTileRows)) == 0 && k_shares(tiles, p.k / kStageK, 2) == 1;
 }
 
 int tc_fp8a8_gated(const R3dGemmQ& p, const GatedOut& g, cudaStream_t st) {

@@ -96,8 +96,8 @@ def _q_struct(t, M, N, K, y_ptr=0):
     return q
 
 
-@pytest.mark.parametrize("M,N,K,act", [(1, 16384, 512, "silu"), (5, 27648, 640, "sigmoid"), (16, 27648, 5120, "silu"),
-                                       (33, 16384, 1024, "silu"), (64, 16384, 384, "sigmoid")])
+@pytest.mark.parametrize("M,N,K,act", [(1, 19200, 512, "silu"), (5, 27648, 640, "sigmoid"), (16, 27648, 5120, "silu"),
+                                       (33, 19200, 1024, "silu"), (64, 19200, 384, "sigmoid")])
 def test_wide_projections_run_as_one_launch_with_the_pair_s_bytes(M, N, K, act):
     """Projections wide enough that the band does not split K are served by the decode kernel with the gated
     quantiser as its epilogue (a gate tile and its up tile in a cluster of two): the launch-layer entry takes
