@@ -96,7 +96,8 @@ def _q_struct(t, M, N, K, y_ptr=0):
     return q
 
 
-@pytest.mark.parametrize("M,N,K,act", [(1, 19200, 512, "silu"), (5, 27648, 640, "sigmoid"), (16, 27648, 5120, "silu"),
+@pytest.mark.parametrize("M,N,K,act", [(1, 19200, 512, "silu"), (2, 27648, 1024, "silu"), (4, 19200, 640, "sigmoid"),
+                                       (5, 27648, 640, "sigmoid"), (8, 19200, 256, "silu"), (16, 27648, 5120, "silu"),
                                        (33, 19200, 1024, "silu"), (64, 19200, 384, "sigmoid")])
 def test_wide_projections_run_as_one_launch_with_the_pair_s_bytes(M, N, K, act):
     """Projections wide enough that the band does not split K are served by the decode kernel with the gated
