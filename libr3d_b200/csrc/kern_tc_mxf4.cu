@@ -111,6 +111,22 @@ constexpr size_t smem_fixed() {
 
 /* NP: piece rows on the MMA's N axis (12 per token, padded to 16 / 32 / 48 / 96); MT: tokens
  * (1, 2, 4, 8: M rounds up, rows past M are zero-filled by the tensor map and never stored). */
+/* two f32 in one 64-bit register pair and the packed fused multiply-add on them (each half an IEEE
+ * fma): the twelve piece columns of a (token, group) are folded two at a time */
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) {
+    f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r;
+}
+__device__ __forceinline__ void upk2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r;
+}
+
 template <int NP, int MT, int kStages, bool SR>
 __global__ void __launch_bounds__(SR ? kThreadsSR : kThreads)
 k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
@@ -294,9 +310,25 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
             as_s[i] = t < P.m ? __ldg(P.as + (int64_t)t * P.as_pitch + c) : 0.0f;
         }
         asm volatile("bar.sync 3, 128;" ::: "memory");
-        float wj[kPieces];
+        f32x2 wj2[kPieces / 2];
 #pragma unroll
-        for (int j = 0; j < kPieces; ++j) wj[j] = piece_scale(j);
+        for (int j = 0; j < kPieces / 2; ++j) wj2[j] = pk2(piece_scale(2 * j), piece_scale(2 * j + 1));
+        /* the window-weighted sum of a (token, group)'s twelve piece columns, two columns an instruction */
+        auto fold = [&](const float* c) -> float {
+            if (MT <= 2) {
+                /* one and two tokens: the scalar chain (measured: the packed form costs M = 2 a microsecond) */
+                float v = c[0] * piece_scale(0);
+#pragma unroll
+                for (int j = 1; j < kPieces; ++j) v = fmaf(c[j], piece_scale(j), v);
+                return v;
+            }
+            f32x2 v = mul2(pk2(c[0], c[1]), wj2[0]);
+#pragma unroll
+            for (int j = 1; j < kPieces / 2; ++j) v = fma2(pk2(c[2 * j], c[2 * j + 1]), wj2[j], v);
+            float lo, hi;
+            upk2(v, lo, hi);
+            return lo + hi;
+        };
         for (int it = 0; it < nk && alive; ++it) {
             if (!SR && it + LEAD < nk) { alive = prepare(it + LEAD); if (!alive) break; }
             const int ab = it % kBufs;
@@ -323,12 +355,7 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 #pragma unroll
                 for (int t = 0; t < MT; ++t) {
 #pragma unroll
-                    for (int g = 0; g < 2; ++g) {
-                        float v = c[g][t * kPieces] * wj[0];
-#pragma unroll
-                        for (int j = 1; j < kPieces; ++j) v = fmaf(c[g][t * kPieces + j], wj[j], v);
-                        acc[t] += v * sa[g * MT + t];
-                    }
+                    for (int g = 0; g < 2; ++g) acc[t] += fold(c[g] + t * kPieces) * sa[g * MT + t];
                 }
             } else {
 #pragma unroll
@@ -345,12 +372,7 @@ k_tc_mxf4(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                         if (lane == 0) mbar_arrive(&acc_empty[ab]);
                     }
 #pragma unroll
-                    for (int t = 0; t < MT; ++t) {
-                        float v = c[t * kPieces] * wj[0];
-#pragma unroll
-                        for (int j = 1; j < kPieces; ++j) v = fmaf(c[t * kPieces + j], wj[j], v);
-                        acc[t] += v * sa[g * MT + t];
-                    }
+                    for (int t = 0; t < MT; ++t) acc[t] += fold(c + t * kPieces) * sa[g * MT + t];
                 }
             }
         }

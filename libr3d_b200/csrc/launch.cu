@@ -77,7 +77,8 @@ static int auto_arm_fp8a8(const R3dGemmQ& q) {
 static int auto_arm_mxfp4a8(const R3dGemmQ& q) {
     static const bool pack_off = [] { const char* e = getenv("R3D_NO_PACK"); return e && *e && *e != '0'; }();
     /* measured: above M = 4 the packed kernel's single accumulator buffer loses to the unpacking kernel */
-    if (!pack_off && q.m <= 4 && tc_mxf4_ok(q)) return R3D_ARM_PACK;
+    static const int pack_max = [] { const char* e = getenv("R3D_PACK_MAXM"); const int v = e ? atoi(e) : 0; return v >= 1 && v <= 8 ? v : 4; }();
+    if (!pack_off && q.m <= pack_max && tc_mxf4_ok(q)) return R3D_ARM_PACK;
     R3dGemmQ probe = q; if (probe.m > 32) probe.m = 32;
     if (tc_mxfp4a8_ok(probe)) return R3D_ARM_TILE;
     probe = q; if (probe.m > 64) probe.m = 64;
