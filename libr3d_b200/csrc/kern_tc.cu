@@ -125,9 +125,31 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     } else if (warp >= 2) {
         dep_wait();                        /* activation scales are the previous kernel's output */
-        for (int i = threadIdx.x - 64; i < n128 * NTOK; i += 128) {
-            const int g = i / NTOK, t = i - g * NTOK;
-            as_s[i] = t < P.m ? __ldg(P.as + (int64_t)t * P.as_pitch + scale_col(g, P.as_cols, n128)) : 0.0f;
+        /* This staging sits between the previous kernel's end and this kernel's first flush: thread = 128-K
+         * group, the live tokens' scales along their rows (coalesced), eight loads in flight a thread (one
+         * load a turn of a loop cost a microsecond on 4096 x 4096 and 3.6 us at K = 13824, sixteen tokens). */
+        const int et = threadIdx.x - 64;
+        const int gend = it0 + nk;                     /* this CTA's K share */
+        /* few groups (a K share of a cluster, a short K): the 128 threads split the tokens between them too */
+        const int parts = nk <= 32 ? 4 : nk <= 64 ? 2 : 1;
+        const int lanes = 128 / parts, part = et / lanes, gl = et - part * lanes;
+        const int tpp = NTOK / parts;                  /* tokens a part: NTOK is 16, 32 or 64 */
+        for (int g0 = it0; g0 < gend; g0 += lanes) {
+            const int g = g0 + gl;
+            const int col = g < gend ? scale_col(g, P.as_cols, n128) : 0;
+            for (int tb = 0; tb < tpp; tb += 8) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int t = part * tpp + tb + u;
+                    v[u] = (g < gend && tb + u < tpp && t < P.m) ? __ldg(P.as + (int64_t)t * P.as_pitch + col) : 0.0f;
+                }
+                if (g < gend) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (tb + u < tpp) as_s[g * NTOK + part * tpp + tb + u] = v[u];
+                }
+            }
         }
     }
     if (warp >= 1) {
