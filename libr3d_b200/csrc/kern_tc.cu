@@ -326,7 +326,26 @@ k_tc_decode(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         cluster_sync_all();                                   /* partial sums are in place */
         if (!GATED && warp >= 2 && crank == 0) {
             const float* red = (const float*)smem;
-            for (int r = 1; r < ks; ++r)
+            int r = 1;
+            if (ML <= 16) {
+                /* up to four peers' partial sums are requested together (a remote read is a few hundred
+                 * nanoseconds; one peer after the other cost the small shapes most of a microsecond) and
+                 * added in rank order */
+                float pr[4][ML];
+#pragma unroll
+                for (int p = 0; p < 4; ++p)
+#pragma unroll
+                    for (int t = 0; t < ML; ++t)
+                        pr[p][t] = p + 1 < ks ? ld_peer_f32(red + t * kTileRows + q * 32 + lane, (uint32_t)(p + 1)) : 0.0f;
+#pragma unroll
+                for (int p = 0; p < 4; ++p)
+                    if (p + 1 < ks) {
+#pragma unroll
+                        for (int t = 0; t < ML; ++t) acc[t] += pr[p][t];
+                    }
+                r = 5;
+            }
+            for (; r < ks; ++r)
 #pragma unroll
                 for (int t = 0; t < ML; ++t) acc[t] += ld_peer_f32(red + t * kTileRows + q * 32 + lane, (uint32_t)r);
         }
