@@ -5,9 +5,10 @@
  * into the gathered [M, world * n_pad] buffer of every rank (its own included) through peer
  * mappings of those buffers (plain st.global over NVLink; no remote loads). The kernel does not
  * signal: the kernel that follows it in the stream (k_gather_wait) starts when the GEMV grid has
- * completed, publishes this rank's call count to every rank's flag array behind one system-scope
- * fence, and then waits (bounded) until every rank's count has reached its own. Ranks issue the
- * same sequence of calls, so the counts agree without host traffic and survive graph replay.
+ * completed, publishes this rank's call count to every rank's flag array by release stores at
+ * system scope, and then waits (bounded, acquire loads) until every rank's count has reached
+ * its own. Ranks issue the same sequence of calls, so the counts agree without host traffic and
+ * survive graph replay.
  * (Signalling from the GEMV itself needs a fence per CTA, which queues behind the weight
  * stream: measured +4.5 to +17 us per call depending on where the fences sit.) */
 #pragma once
