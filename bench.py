@@ -975,89 +975,165 @@ def main():
 
     # ---- end to end: host activations in, host outputs back, through the declared ops
     # every step: ONE copy of the packed activations (codes + scales of the three calls) from
-    # pinned host memory, three issues, ONE copy of the packed outputs back, then a host wait
+    # pinned host memory, three issues, ONE copy of the packed outputs back to pinned host memory.
+    # Device and host buffers are doubled (step i uses set i % 2) so that a recorded pass can run
+    # the copies of one step beside the kernels of its neighbours; the kernels themselves stay on
+    # one stream in step order (the library's activation scratch and the ranks' call counts need it).
     in_bytes = sum(acts[m][0].numel() + acts[m][1].numel() * 4 for m in MS)
     h_in = torch.empty(in_bytes, dtype=torch.uint8).pin_memory()
-    d_in = torch.empty(in_bytes, dtype=torch.uint8, device=dev)
-    d_out = torch.empty((sum(MS), N_DIM), dtype=torch.bfloat16, device=dev)
-    h_out = torch.empty((sum(MS), N_DIM), dtype=torch.bfloat16).pin_memory()
+    d_ins = [torch.empty(in_bytes, dtype=torch.uint8, device=dev) for _ in range(2)]
+    d_outs = [torch.empty((sum(MS), N_DIM), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    h_outs = [torch.empty((sum(MS), N_DIM), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     e2e_ops, e2e_out, off, row_at = {}, {}, 0, 0
     for m in MS:
         na, ns = acts[m][0].numel(), acts[m][1].numel() * 4
         h_in[off:off + na].copy_(acts[m][0].flatten().cpu())
         h_in[off + na:off + na + ns].copy_(acts[m][1].flatten().view(torch.uint8).cpu())
-        a_v = d_in[off:off + na].view(m, K_DIM)
-        s_v = d_in[off + na:off + na + ns].view(torch.float32).view(m, K_DIM // 128)
-        e2e_out[m] = d_out[row_at:row_at + m]
-        for p in range(rot):
-            e2e_ops[m, p] = (shard.PushedGemm(pg, a_v, s_v, planes[p][0], planes[p][1], dtype="mxfp4a8", M=m,
-                                              n_local=N_DIM, n_pad=N_DIM, K=K_DIM, scratch=e2e_out[m]) if push else
-                             ops.BoundGemm(a_v, s_v, planes[p][0], planes[p][1], e2e_out[m],
-                                           dtype="mxfp4a8", N=N_DIM, K=K_DIM, row=args.row))
+        for bset in range(2):
+            a_v = d_ins[bset][off:off + na].view(m, K_DIM)
+            s_v = d_ins[bset][off + na:off + na + ns].view(torch.float32).view(m, K_DIM // 128)
+            e2e_out[m, bset] = d_outs[bset][row_at:row_at + m]
+            for p in range(rot):
+                e2e_ops[m, p, bset] = (shard.PushedGemm(pg, a_v, s_v, planes[p][0], planes[p][1], dtype="mxfp4a8", M=m,
+                                                        n_local=N_DIM, n_pad=N_DIM, K=K_DIM, scratch=e2e_out[m, bset]) if push else
+                                       ops.BoundGemm(a_v, s_v, planes[p][0], planes[p][1], e2e_out[m, bset],
+                                                     dtype="mxfp4a8", N=N_DIM, K=K_DIM, row=args.row))
         off += na + ns
         row_at += m
-    h2d, d2h = in_bytes, h_out.numel() * 2
+    h2d, d2h = in_bytes, h_outs[0].numel() * 2
 
-    def step_e2e_body(i: int):
-        d_in.copy_(h_in, non_blocking=True)
+    def rows_e2e(i: int):
+        """the row issues of step i on the current stream (buffer set i % 2, plane i % rot)"""
+        bset = i % 2
         if push:
             # every rank ends up with the full [m, world * N] result in its slot; the host reads
             # back this rank's own columns of it (the same bytes per rank as at N = 1)
             for m in MS:
-                e2e_ops[m, i % rot].issue(i % 2)
-                e2e_out[m].copy_(e2e_ops[m, i % rot].result(i % 2)[:, rank * N_DIM:(rank + 1) * N_DIM])
+                e2e_ops[m, i % rot, bset].issue(i % 2)
+                e2e_out[m, bset].copy_(e2e_ops[m, i % rot, bset].result(i % 2)[:, rank * N_DIM:(rank + 1) * N_DIM])
         else:
             for m in MS:
-                e2e_ops[m, i % rot].issue()
+                e2e_ops[m, i % rot, bset].issue()
             if world > 1:
                 for m in MS:
-                    dist.all_gather_into_tensor(gathered[m], e2e_out[m])
-        h_out.copy_(d_out, non_blocking=True)
+                    dist.all_gather_into_tensor(gathered[m], e2e_out[m, bset])
 
-    # The engine records a pass once and replays it: the copies in, the row issues and the copy out
-    # of one step are recorded per weight plane (the rows are called during the recording) and each
-    # timed step replays its recording and waits for it on the host. If recording is not possible
-    # (the NCCL-gather form), the step is issued directly.
-    e2e_graphs, e2e_how = None, "direct issue per step"
+    def step_e2e_body(i: int):
+        """copy in, the row issues, copy out of step i, all on the current stream"""
+        d_ins[i % 2].copy_(h_in, non_blocking=True)
+        rows_e2e(i)
+        h_outs[i % 2].copy_(d_outs[i % 2], non_blocking=True)
+
+    e2e_period = rot if rot % 2 == 0 else 2 * rot          # (plane, buffer set) pairs repeat with this period
+    s_k, s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+
+    def pass_e2e_body():
+        """one pass of e2e_period steps on the current stream (s_k) with the copies forked to s_in and
+        s_out: step i's copy-in waits only for step i - 2's rows (its buffer set is free), its rows for
+        that copy and for step i - 2's copy-out, its copy-out for its rows"""
+        ev_k, ev_out = {}, {}
+        s_in.wait_stream(s_k)
+        s_out.wait_stream(s_k)
+        for i in range(e2e_period):
+            bset = i % 2
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(ev_k[i - 2])
+                d_ins[bset].copy_(h_in, non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record()
+            s_k.wait_event(ev_in)
+            if i >= 2:
+                s_k.wait_event(ev_out[i - 2])
+            rows_e2e(i)
+            ev_k[i] = torch.cuda.Event()
+            ev_k[i].record()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_k[i])
+                h_outs[bset].copy_(d_outs[bset], non_blocking=True)
+                ev_out[i] = torch.cuda.Event()
+                ev_out[i].record()
+        s_k.wait_stream(s_in)
+        s_k.wait_stream(s_out)
+
+    # The engine records a pass once and replays it. Two forms are timed. "serial": the copy in, the
+    # row issues and the copy out of one step are one recording per (weight plane, buffer set); the
+    # host waits for step i before it issues step i + 1. "pipelined": one recording holds a pass of
+    # e2e_period steps with the copies forked as above; the host waits once per pass. If recording
+    # is not possible (the NCCL-gather form), both are issued directly.
+    e2e_graphs, e2e_pass, e2e_how = None, None, "direct issue"
+    s_k.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s_k):
+        for i in range(2):
+            step_e2e_body(i)
+        pass_e2e_body()
+    torch.cuda.synchronize()
     if recordable:
         try:
-            for i in range(2):
-                step_e2e_body(i)
-            torch.cuda.synchronize()
-            cap = torch.cuda.Stream()
-            cap.wait_stream(torch.cuda.current_stream())
             e2e_graphs = []
-            with torch.cuda.stream(cap):
-                for i in range(rot):
+            with torch.cuda.stream(s_k):
+                for i in range(e2e_period):
                     gph = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(gph, stream=cap):
+                    with torch.cuda.graph(gph, stream=s_k):
                         step_e2e_body(i)
                     e2e_graphs.append(gph)
-            torch.cuda.current_stream().wait_stream(cap)
+                e2e_pass = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(e2e_pass, stream=s_k):
+                    pass_e2e_body()
             torch.cuda.synchronize()
-            e2e_how = "replay of a recorded step (copy in, row issues, copy out), host wait per step"
+            e2e_how = "replay of recordings"
         except Exception as ex:                          # noqa: BLE001 - fall back to direct issue, and say so
             sys.stderr.write(f"bench: end-to-end step not recordable ({type(ex).__name__}: {ex}); issuing directly\n")
-            e2e_graphs = None
+            e2e_graphs, e2e_pass = None, None
             torch.cuda.synchronize()
 
-    def step_e2e(i: int):
-        if e2e_graphs is not None:
-            e2e_graphs[i % rot].replay()
-        else:
-            step_e2e_body(i)
-        torch.cuda.current_stream().synchronize()          # the caller reads the step's result
+    def run_serial(n: int):
+        with torch.cuda.stream(s_k):
+            for i in range(n):
+                if e2e_graphs is not None:
+                    e2e_graphs[i % e2e_period].replay()
+                else:
+                    step_e2e_body(i)
+                s_k.synchronize()                          # the caller reads the step's result
 
-    e2e_steps = min(args.steps, 200)
-    for i in range(3):
-        step_e2e(i)
-    ms_e_list = _timed(lambda: [step_e2e(i) for i in range(e2e_steps)], 3, fence)
-    if world > 1:
-        t = torch.tensor(ms_e_list, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_e_list = [float(v) for v in t.tolist()]
-    ms_e = statistics.median(ms_e_list)
-    e2e = STEP_BYTES * e2e_steps * world / (ms_e * 1e-3) / 1e9
+    def run_pipelined(n: int):
+        with torch.cuda.stream(s_k):
+            for _ in range(n // e2e_period):
+                if e2e_pass is not None:
+                    e2e_pass.replay()
+                else:
+                    pass_e2e_body()
+                s_k.synchronize()                          # the caller reads the pass's results
+
+    e2e_steps = max(e2e_period, min(args.steps, 200) // e2e_period * e2e_period)
+    run_serial(4)
+    run_pipelined(e2e_period)
+
+    def e2e_of(run):
+        lst = _timed(lambda: run(e2e_steps), 3, fence)
+        if world > 1:
+            t = torch.tensor(lst, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            lst = [float(v) for v in t.tolist()]
+        return STEP_BYTES * e2e_steps * world / (statistics.median(lst) * 1e-3) / 1e9, lst
+
+    e2e_serial, _ = e2e_of(run_serial)
+    e2e, ms_e_list = e2e_of(run_pipelined)
+    # what the last two steps of the last pass left in host memory == the same calls issued alone
+    torch.cuda.synchronize()
+    for i in (e2e_period - 2, e2e_period - 1):
+        row_at = 0
+        for m in MS:
+            if push:
+                pushed[m, i % rot].issue(i % 2)
+                ref = pushed[m, i % rot].result(i % 2)[:, rank * N_DIM:(rank + 1) * N_DIM]
+            else:
+                ops_[args.row, m, i % rot].issue()
+                ref = outs[m]
+            torch.cuda.synchronize()
+            got = h_outs[i % 2][row_at:row_at + m]
+            assert torch.equal(ref.cpu().view(torch.int16), got.view(torch.int16)), f"end-to-end result differs (step {i}, M={m})"
+            row_at += m
 
     if not args.no_sub:
         if pg is not None and push:
@@ -1105,8 +1181,13 @@ def main():
                                     else "k_tc_mxf4<NP,MT> (one per call, after its k_mxf4_split)"),
                          "bytes_per_launch": STEP_BYTES / 3,
                          "us_per_launch": per_launch_s * 1e6},
-            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "timed_as": e2e_how,
-                    "steps": e2e_steps, "regions": len(ms_e_list)},
+            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "timed_as": e2e_how + f": a pass of {e2e_period} steps, each step's copy-in and copy-out on side "
+                                          "streams beside its neighbours' kernels (two buffer sets), the host waits once per pass",
+                    "serial": {"value": e2e_serial, "unit": "GB/s",
+                               "timed_as": "copy in, rows, copy out on one stream; the host waits for step i before issuing step i + 1"},
+                    "steps": e2e_steps, "regions": len(ms_e_list),
+                    "checked": "host results of the last pass bit-equal to the same calls issued alone"},
             "gpu_launches": int(launches),
             "clocks": clk.summary(),
         }
