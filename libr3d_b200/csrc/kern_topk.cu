@@ -3,13 +3,15 @@
  * one block per row and re-reads the row R times).
  *
  * Here the selection is a tournament, because it serves the column-sharded LM head, whose rows are
- * 19 to 152 thousand columns wide at M = 1..16: a pass gives every warp a tile of 512 items held in
+ * 19 to 152 thousand columns wide at M = 1..16. A pass gives every warp a tile of 512 items held in
  * registers (16 per lane, sorted once by each lane) and takes the tile's top R with one warp-wide
- * integer maximum and one vote per pick -- no shared memory, no block barrier -- and passes repeat over the
- * survivors (tiles * R of them) until one tile is left; that last pass writes idx / val / pairs with `vocab_off` added. The order is total on everything
- * but NaN, so the survivors of the survivors are exactly the R the reference's rounds pick; a slot
- * that cannot be filled reports (-1, -inf) as there. A NaN's place is unspecified (in the reference
- * it depends on which thread meets it first).
+ * integer maximum and one vote per pick; the eight warps of a block leave their picks in shared
+ * memory and the block's first warp plays the same tournament over those (at most 256 items), so a
+ * block of 4096 items hands on R survivors. Passes repeat over the survivors until one block is
+ * left (151936 columns: two launches); that last pass writes idx / val / pairs with `vocab_off`
+ * added. The order is total on everything but NaN, so the survivors of the survivors are exactly
+ * the R the reference's rounds pick; a slot that cannot be filled reports (-1, -inf) as there. A
+ * NaN's place is unspecified (in the reference it depends on which thread meets it first).
  */
 #include <cmath>
 #include "r3d_kernels.h"
@@ -23,7 +25,9 @@ namespace {
 
 constexpr int kTile = 512;            /* items per warp */
 constexpr int kPer = kTile / 32;      /* items per lane */
-constexpr int kWarps = 4;             /* warps (tiles) per block */
+constexpr int kWarps = 8;             /* warps (tiles) per block */
+constexpr int kBlockItems = kTile * kWarps;
+constexpr int kMergePer = kWarps * 32 / 32;   /* items per lane in the block's merge: kWarps * R <= 256 */
 
 /* An item is one 64-bit key whose unsigned order is the selection order: the high word is the
  * value mapped monotonically onto unsigned integers (-0 first folded onto +0, which the rule
@@ -52,31 +56,15 @@ __device__ __forceinline__ float load_x(const TopkPass& P, int64_t m, int e) {
                                 : bf16_to_f32(((const uint16_t*)P.x)[m * P.x_pitch + e]);
 }
 
-template <bool FIRST>
-__global__ __launch_bounds__(kWarps * 32) void k_topk_pass(const TopkPass P) {
-    const int lane = threadIdx.x & 31;
-    const int tile = blockIdx.x * kWarps + (threadIdx.x >> 5);
-    const int64_t m = blockIdx.y;
-    const int base = tile * kTile;
-    /* passes are launched with programmatic stream serialisation: the next pass may take its
-     * place on the machine now, and this one reads nothing before its predecessor has finished */
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (base >= P.n) return;                          /* whole warp: no warp-wide step is left behind */
-    unsigned long long k[kPer];
+/* each lane sorts its NP keys, largest first (bitonic network, every index a constant) */
+template <int NP>
+__device__ __forceinline__ void sort_desc(unsigned long long (&k)[NP]) {
 #pragma unroll
-    for (int j = 0; j < kPer; ++j) {
-        const int e = base + lane * kPer + j;            /* a lane owns 16 neighbouring items */
-        k[j] = 0ull;
-        if (e < P.n) k[j] = FIRST ? key_of(load_x(P, m, e), e) : P.ck[m * P.c_pitch + e];
-    }
-    /* each lane sorts its 16 keys, largest first (bitonic network, every index a constant) */
-#pragma unroll
-    for (int kk = 2; kk <= kPer; kk <<= 1)
+    for (int kk = 2; kk <= NP; kk <<= 1)
 #pragma unroll
         for (int jj = kk >> 1; jj > 0; jj >>= 1)
 #pragma unroll
-            for (int i = 0; i < kPer; ++i) {
+            for (int i = 0; i < NP; ++i) {
                 const int l = i ^ jj;
                 if (l > i) {
                     const bool desc = (i & kk) == 0;
@@ -86,39 +74,89 @@ __global__ __launch_bounds__(kWarps * 32) void k_topk_pass(const TopkPass P) {
                     k[l] = sw ? a : b;
                 }
             }
-    /* the sorted lists go to shared memory ([item][lane]: no bank conflicts); a lane keeps only its
-     * head in a register and fetches the next item when it wins */
-    __shared__ unsigned long long s_k[kWarps][kPer][32];
-    __shared__ int s_col[kWarps][32];
-    const int wib = threadIdx.x >> 5;
+}
+
+/* One warp's tournament over 32 sorted lists of NP keys. The lists go to shared memory ([item][lane]:
+ * no bank conflicts); a lane keeps only its head in a register and fetches the next item when it
+ * wins. R rounds: the largest head value of the warp (one warp-wide integer maximum); of the lanes
+ * that hold it the lowest wins (one vote), because items lie in the warp's range in ascending column
+ * order wherever their values are equal -- in the rows themselves by construction, among a block's
+ * picks because its warps cover ascending column ranges and each lists equal values in ascending
+ * column, and among survivors because blocks do the same. The winner (lane 0 when nothing is left)
+ * hands the pick to emit(r, ok, key) and pops it. */
+template <int NP, typename Emit>
+__device__ __forceinline__ void tournament(unsigned long long (&k)[NP], unsigned long long (*sk)[32],
+                                           const int lane, const int R, Emit emit) {
 #pragma unroll
-    for (int j = 0; j < kPer; ++j) s_k[wib][j][lane] = k[j];
+    for (int j = 0; j < NP; ++j) sk[j][lane] = k[j];
     unsigned long long head = k[0];
     int h = 0;
-    /* R rounds: the largest head value of the warp (one warp-wide integer maximum); of the lanes
-     * that hold it the lowest wins (one vote), because items lie in the tile in ascending column
-     * order wherever their values are equal -- in the rows themselves by construction, and among
-     * survivors because tiles cover ascending column ranges and each tile lists equal values in
-     * ascending column. The winner records the pick and pops it. */
-    for (int r = 0; r < P.R; ++r) {
+    for (int r = 0; r < R; ++r) {
         const uint32_t hi = (uint32_t)(head >> 32);
         const uint32_t vmax = __reduce_max_sync(0xffffffffu, hi);
         const bool ok = vmax != 0u;
         const uint32_t holders = __ballot_sync(0xffffffffu, ok && hi == vmax);
         if (ok ? lane == __ffs(holders) - 1 : lane == 0) {
-            if (P.last) s_col[wib][r] = ok ? (int)(0xffffffffu - (uint32_t)head) : -1;
-            else P.ok[m * P.o_pitch + (int64_t)tile * P.R + r] = ok ? head : 0ull;
+            emit(r, ok, head);
             if (ok) {
                 ++h;
-                head = h < kPer ? s_k[wib][h][lane] : 0ull;
+                head = h < NP ? sk[h][lane] : 0ull;
             }
         }
+    }
+}
+
+template <bool FIRST>
+__global__ __launch_bounds__(kWarps * 32) void k_topk_pass(const TopkPass P) {
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int64_t m = blockIdx.y;
+    const int block0 = blockIdx.x * kBlockItems;
+    const int base = block0 + wib * kTile;
+    /* passes are launched with programmatic stream serialisation: the next pass may take its
+     * place on the machine now, and this one reads nothing before its predecessor has finished */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ unsigned long long s_k[kWarps][kPer][32];
+    __shared__ unsigned long long s_pick[kWarps * 32];          /* [warp][r], R apart */
+    __shared__ int s_col[32];
+    /* a block whose items fit one warp's tile needs no merge: that warp's picks are the block's */
+    const bool one_tile = P.n - block0 <= kTile;
+    if (one_tile && wib != 0) return;
+    auto hand_on = [&](int r, bool ok, unsigned long long key) {
+        if (P.last) s_col[r] = ok ? (int)(0xffffffffu - (uint32_t)key) : -1;
+        else P.ok[m * P.o_pitch + (int64_t)blockIdx.x * P.R + r] = ok ? key : 0ull;
+    };
+    {
+        unsigned long long k[kPer];
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+            const int e = base + lane * kPer + j;            /* a lane owns 16 neighbouring items */
+            k[j] = 0ull;
+            if (e < P.n) k[j] = FIRST ? key_of(load_x(P, m, e), e) : P.ck[m * P.c_pitch + e];
+        }
+        sort_desc<kPer>(k);
+        if (one_tile) tournament<kPer>(k, s_k[0], lane, P.R, hand_on);
+        else tournament<kPer>(k, s_k[wib], lane, P.R,
+                              [&](int r, bool ok, unsigned long long key) { s_pick[wib * P.R + r] = ok ? key : 0ull; });
+    }
+    if (!one_tile) {
+        __syncthreads();
+        if (wib != 0) return;
+        /* the block's first warp merges the warps' picks: a lane owns kMergePer neighbouring items */
+        unsigned long long q[kMergePer];
+#pragma unroll
+        for (int j = 0; j < kMergePer; ++j) {
+            const int e = lane * kMergePer + j;
+            q[j] = e < kWarps * P.R ? s_pick[e] : 0ull;
+        }
+        sort_desc<kMergePer>(q);
+        tournament<kMergePer>(q, s_k[0], lane, P.R, hand_on);
     }
     if (P.last) {
         /* lane r writes pick r; the value is re-read from the row (a zero keeps its sign) */
         __syncwarp();
         if (lane < P.R) {
-            const int col = s_col[wib][lane];
+            const int col = s_col[lane];
             const int32_t out_col = col >= 0 ? (int32_t)(col + P.off) : -1;
             const float out_val = (col >= 0 && (P.val || P.pairs)) ? load_x(P, m, col) : -INFINITY;
             P.idx[m * P.idx_pitch + lane] = out_col;
@@ -154,17 +192,17 @@ Survivors* survivors(size_t items) {
 
 } /* namespace */
 
-/* bytes of the two survivor planes a call needs (0 when the row fits one tile): what the rows' scratch
+/* bytes of the two survivor planes a call needs (0 when the row fits one block): what the rows' scratch
  * hooks ask the engine for */
 int64_t row_topk_scratch_bytes(int64_t M, int64_t N, int64_t R) {
-    const int64_t tiles0 = (N + kTile - 1) / kTile;
+    const int64_t tiles0 = (N + kBlockItems - 1) / kBlockItems;
     return tiles0 > 1 ? 2 * M * tiles0 * R * (int64_t)sizeof(unsigned long long) : 0;
 }
 
 int launch_row_topk(const void* x, int x_dtype, int64_t x_pitch, int32_t* idx, int64_t idx_pitch, float* val,
                     int64_t val_pitch, float* pairs, int64_t pairs_pitch, int M, int N, int R, int64_t off,
                     cudaStream_t st, void* scratch, int64_t scratch_bytes) {
-    const int tiles0 = (N + kTile - 1) / kTile;
+    const int tiles0 = (N + kBlockItems - 1) / kBlockItems;          /* blocks of the first pass */
     Survivors* S = nullptr;
     Survivors arena{};
     if (tiles0 > 1) {
@@ -187,7 +225,7 @@ int launch_row_topk(const void* x, int x_dtype, int64_t x_pitch, int32_t* idx, i
     for (;;) {
         P.n = n; P.last = tiles == 1;
         if (!P.last) { P.ok = S->k[pass & 1]; P.o_pitch = (int64_t)tiles * R; }
-        const dim3 grid((unsigned)((tiles + kWarps - 1) / kWarps), (unsigned)M);
+        const dim3 grid((unsigned)tiles, (unsigned)M);
         count_launch();
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = grid; cfg.blockDim = dim3(kWarps * 32); cfg.stream = st;
@@ -201,7 +239,7 @@ int launch_row_topk(const void* x, int x_dtype, int64_t x_pitch, int32_t* idx, i
         if (P.last) break;
         P.ck = P.ok; P.c_pitch = P.o_pitch;
         n = tiles * R;
-        tiles = (n + kTile - 1) / kTile;
+        tiles = (n + kBlockItems - 1) / kBlockItems;
         ++pass;
     }
     return RAD_OK;

@@ -136,7 +136,11 @@ def test_rmsnorm_quant_row_against_the_reference_kernel(M, n, with_res):
 
 @pytest.mark.parametrize("M,N,R,off,with_pairs", [(1, 151936, 32, 0, True), (4, 19072, 8, 132864, True),
                                                    (16, 19072, 1, 19072, False), (3, 8, 32, 5, True),
-                                                   (2, 512, 32, 0, False), (5, 1000, 7, 0, True)])
+                                                   (2, 512, 32, 0, False), (5, 1000, 7, 0, True),
+                                                   # a second block of eight items; a block whose last warp is partly
+                                                   # filled; two full blocks; three passes (more than 4096 survivors)
+                                                   (2, 4104, 32, 0, True), (1, 4616, 5, 3, False),
+                                                   (2, 8192, 32, 0, False), (1, 600000, 32, 0, True)])
 def test_row_topk_row_against_oracle(M, N, R, off, with_pairs):
     """Exact top-R with ties: the values are drawn from few distinct bf16 numbers so every row holds
     many equal candidates, plus +-inf and signed zeros; slots past the row's width are (-1, -inf)."""

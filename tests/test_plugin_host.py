@@ -664,11 +664,11 @@ def test_no_product_code_touches_the_oracle():
 
 
 def test_topk_rows_declare_a_launch_arena(plug):
-    """row_topk and sample_argmax carry a scratch hook: two survivor planes of M * ceil(N / 512) * R 64-bit keys
-    (nothing when the row fits one tile), computed from the query when the operands are not there yet"""
+    """row_topk and sample_argmax carry a scratch hook: two survivor planes of M * ceil(N / 4096) * R 64-bit keys
+    (nothing when the row fits one block of the selection kernel), computed from the query when the operands are not there yet"""
     rows = {r.name: r for r in plug.rows()}
     assert rows["rowtopk_bf16"].has_scratch and rows["sample_argmax_f32"].has_scratch
     q = ArgPack([], dict(M=4, N=151936, R=32, dtype="bf16"))
-    assert plug.lib.r3d_rad_row_topk_scratch(q.args) == 2 * 4 * 297 * 32 * 8
-    assert plug.lib.r3d_rad_row_topk_scratch(ArgPack([], dict(M=4, N=512, R=8, dtype="bf16")).args) == 0
-    assert plug.lib.r3d_rad_sample_argmax_scratch(ArgPack([], dict(M=2, n_vocab=151936)).args) == 2 * 2 * 297 * 8
+    assert plug.lib.r3d_rad_row_topk_scratch(q.args) == 2 * 4 * 38 * 32 * 8
+    assert plug.lib.r3d_rad_row_topk_scratch(ArgPack([], dict(M=4, N=4096, R=8, dtype="bf16")).args) == 0
+    assert plug.lib.r3d_rad_sample_argmax_scratch(ArgPack([], dict(M=2, n_vocab=151936)).args) == 2 * 2 * 38 * 8
