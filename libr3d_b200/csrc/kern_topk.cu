@@ -5,9 +5,9 @@
  * Here the selection is a tournament, because it serves the column-sharded LM head, whose rows are
  * 19 to 152 thousand columns wide at M = 1..16. A pass gives every warp a tile of 512 items held in
  * registers (16 per lane, sorted once by each lane) and takes the tile's top R with one warp-wide
- * integer maximum and one vote per pick; the eight warps of a block leave their picks in shared
- * memory and the block's first warp plays the same tournament over those (at most 256 items), so a
- * block of 4096 items hands on R survivors. Passes repeat over the survivors until one block is
+ * integer maximum and one vote per pick; the eight warps of a block leave their picks, largest
+ * first, in shared memory and merge them pairwise in three steps (a bitonic half-cleaner and five
+ * compare-exchange steps across the lanes per merge), so a block of 4096 items hands on R survivors. Passes repeat over the survivors until one block is
  * left (151936 columns: two launches); that last pass writes idx / val / pairs with `vocab_off`
  * added. The order is total on everything but NaN, so the survivors of the survivors are exactly
  * the R the reference's rounds pick; a slot that cannot be filled reports (-1, -inf) as there. A
@@ -27,7 +27,7 @@ constexpr int kTile = 512;            /* items per warp */
 constexpr int kPer = kTile / 32;      /* items per lane */
 constexpr int kWarps = 8;             /* warps (tiles) per block */
 constexpr int kBlockItems = kTile * kWarps;
-constexpr int kMergePer = kWarps * 32 / 32;   /* items per lane in the block's merge: kWarps * R <= 256 */
+static_assert(kWarps == 8, "the block's merge is three pairwise steps");
 
 /* An item is one 64-bit key whose unsigned order is the selection order: the high word is the
  * value mapped monotonically onto unsigned integers (-0 first folded onto +0, which the rule
@@ -117,7 +117,8 @@ __global__ __launch_bounds__(kWarps * 32) void k_topk_pass(const TopkPass P) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ unsigned long long s_k[kWarps][kPer][32];
-    __shared__ unsigned long long s_pick[kWarps * 32];          /* [warp][r], R apart */
+    __shared__ unsigned long long s_pick[kWarps][32];           /* a warp's picks, largest first, zeros behind */
+    __shared__ unsigned long long s_m1[kWarps / 2][32], s_m2[kWarps / 4][32];
     __shared__ int s_col[32];
     /* a block whose items fit one warp's tile needs no merge: that warp's picks are the block's */
     const bool one_tile = P.n - block0 <= kTile;
@@ -135,22 +136,39 @@ __global__ __launch_bounds__(kWarps * 32) void k_topk_pass(const TopkPass P) {
             if (e < P.n) k[j] = FIRST ? key_of(load_x(P, m, e), e) : P.ck[m * P.c_pitch + e];
         }
         sort_desc<kPer>(k);
-        if (one_tile) tournament<kPer>(k, s_k[0], lane, P.R, hand_on);
-        else tournament<kPer>(k, s_k[wib], lane, P.R,
-                              [&](int r, bool ok, unsigned long long key) { s_pick[wib * P.R + r] = ok ? key : 0ull; });
+        if (one_tile) {
+            tournament<kPer>(k, s_k[0], lane, P.R, hand_on);
+        } else {
+            s_pick[wib][lane] = 0ull;
+            __syncwarp();
+            tournament<kPer>(k, s_k[wib], lane, P.R,
+                             [&](int r, bool ok, unsigned long long key) { s_pick[wib][r] = ok ? key : 0ull; });
+        }
     }
     if (!one_tile) {
+        /* the eight sorted lists merge pairwise in three steps. Keys are distinct (the column is
+         * part of the key), so plain 64-bit comparisons give the selection order. Two lists of 32,
+         * largest first: max(X[i], Y[31 - i]) over i holds the 32 largest of both as a bitonic
+         * sequence, which five compare-exchange steps across the lanes sort. */
+        auto merge2 = [&](const unsigned long long* x, const unsigned long long* y) {
+            const unsigned long long a = x[lane], b = y[31 - lane];
+            unsigned long long z = a > b ? a : b;
+#pragma unroll
+            for (int s2 = 16; s2; s2 >>= 1) {
+                const unsigned long long o = __shfl_xor_sync(0xffffffffu, z, s2);
+                const bool up = (lane & s2) == 0;           /* the lower lane of a pair keeps the larger key */
+                z = (up == (z > o)) ? z : o;
+            }
+            return z;
+        };
+        __syncthreads();
+        if (wib < kWarps / 2) s_m1[wib][lane] = merge2(s_pick[2 * wib], s_pick[2 * wib + 1]);
+        __syncthreads();
+        if (wib < kWarps / 4) s_m2[wib][lane] = merge2(s_m1[2 * wib], s_m1[2 * wib + 1]);
         __syncthreads();
         if (wib != 0) return;
-        /* the block's first warp merges the warps' picks: a lane owns kMergePer neighbouring items */
-        unsigned long long q[kMergePer];
-#pragma unroll
-        for (int j = 0; j < kMergePer; ++j) {
-            const int e = lane * kMergePer + j;
-            q[j] = e < kWarps * P.R ? s_pick[e] : 0ull;
-        }
-        sort_desc<kMergePer>(q);
-        tournament<kMergePer>(q, s_k[0], lane, P.R, hand_on);
+        const unsigned long long z = merge2(s_m2[0], s_m2[1]);
+        if (lane < P.R) hand_on(lane, z != 0ull, z);
     }
     if (P.last) {
         /* lane r writes pick r; the value is re-read from the row (a zero keeps its sign) */
