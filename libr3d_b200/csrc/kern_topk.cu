@@ -89,20 +89,22 @@ __device__ __forceinline__ void tournament(unsigned long long (&k)[NP], unsigned
                                            const int lane, const int R, Emit emit) {
 #pragma unroll
     for (int j = 0; j < NP; ++j) sk[j][lane] = k[j];
-    unsigned long long head = k[0];
+    /* head and its successor live in registers and the round has no branch around the pop: a win
+     * moves the successor up and asks shared memory for the one after, off the critical path */
+    unsigned long long head = k[0], next = NP > 1 ? k[1] : 0ull;
     int h = 0;
     for (int r = 0; r < R; ++r) {
         const uint32_t hi = (uint32_t)(head >> 32);
         const uint32_t vmax = __reduce_max_sync(0xffffffffu, hi);
         const bool ok = vmax != 0u;
         const uint32_t holders = __ballot_sync(0xffffffffu, ok && hi == vmax);
-        if (ok ? lane == __ffs(holders) - 1 : lane == 0) {
-            emit(r, ok, head);
-            if (ok) {
-                ++h;
-                head = h < NP ? sk[h][lane] : 0ull;
-            }
-        }
+        const bool win = lane == (ok ? __ffs(holders) - 1 : 0);
+        if (win) emit(r, ok, head);
+        const bool pop = win && ok;
+        h += pop ? 1 : 0;
+        const unsigned long long after = sk[h + 1 < NP ? h + 1 : NP - 1][lane];
+        head = pop ? next : head;
+        next = pop ? (h + 1 < NP ? after : 0ull) : next;
     }
 }
 
