@@ -11,20 +11,23 @@
  * the optional (id bits, value) pairs plane written in that order.
  *
  * The double chain is serial by definition, so the work is laid out for its latency, not for a
- * tensor core: one block of eight warps per row; the row's activations are widened to f32 once
- * into shared memory by the whole block; every warp serves four candidates at once, eight lanes
- * each: per 128-K block a lane fetches sixteen consecutive codes of its candidate's head row (one
- * 128-byte line per candidate, against the reference's one thread per candidate striding its own
- * row) with the loads of the next two blocks already in flight (a head row is touched once, so every
- * load is a DRAM round trip: unhidden they were nine tenths of the kernel's time), forms the
- * sixteen exact products, and the segment's accumulator takes the 128 products of the block in
- * ascending k through width-8 shuffles -- the same adds in the same order, four chains per FP64
- * instruction. Ragged K, unaligned heads and rows too wide for shared memory take 32-K steps of
- * four codes a lane. Thread 0 runs the selection over shared memory.
+ * tensor core. Two kernels:
+ *   k_logit_rerank_chain (whole 128-K blocks, 16-byte aligned head rows, K up to about 12,000): one
+ *     warp carries all the row's chains, lane = candidate, one FP64 add instruction for up to 32
+ *     chains; sixteen producer warps form the exact products ahead of it in shared memory (see the
+ *     kernel's own comment).
+ *   k_logit_rerank_e4m3 (everything else): one block of eight warps per row; every warp serves four
+ *     candidates at once, eight lanes each: per 128-K block a lane fetches sixteen consecutive codes
+ *     of its candidate's head row, forms the sixteen exact products, and the segment's accumulator
+ *     takes the 128 products of the block in ascending k through width-8 shuffles -- the same adds
+ *     in the same order, four chains per FP64 instruction. Ragged K, unaligned heads and rows too
+ *     wide for shared memory take 32-K steps of four codes a lane.
+ * The selection runs in one warp over shared memory.
  */
 #include "r3d_kernels.h"
 #include "r3d_numerics.cuh"
 #include <cmath>
+#include <cstdlib>
 
 namespace r3d { __device__ int g_rr_status = 0; }
 #define R3D_TC_STATUS_WORD ::r3d::g_rr_status
@@ -36,10 +39,74 @@ namespace {
 constexpr int kMaxR = 32;
 constexpr int kWarps = 8;
 
+/* the same in two halves, so that a load issued ahead is not waited for before its value is needed */
+__device__ __forceinline__ uint32_t ld_scale_raw(const void* base, int64_t idx, int dt) {
+    return dt == RAD_F32 ? ((const uint32_t*)base)[idx] : (uint32_t)((const uint16_t*)base)[idx];
+}
+__device__ __forceinline__ float scale_of_raw(uint32_t raw, int dt) {
+    if (dt == RAD_F32) return __uint_as_float(raw);
+    if (dt == RAD_F16) return f16_to_f32((uint16_t)raw);
+    return bf16_to_f32((uint16_t)raw);
+}
+
 __device__ __forceinline__ float ld_scale_any(const void* base, int64_t idx, int dt) {
     if (dt == RAD_F32) return ((const float*)base)[idx];
     if (dt == RAD_F16) return f16_to_f32(((const uint16_t*)base)[idx]);
     return bf16_to_f32(((const uint16_t*)base)[idx]);
+}
+
+/* The R rounds of selection, run by one whole warp over the candidates' ids and scores in shared
+ * memory. Without NaN scores the selection's order is a total order (value descending, lower id first,
+ * earlier slot first; pads last), so a candidate's place is the count of candidates ahead of it; with a
+ * NaN score lane 0 plays the rounds one after the other, as the reference does. */
+__device__ __forceinline__ void rerank_select(const int lane, const int32_t* sid, const float* ssc, const int R,
+                                              const int64_t m, int32_t* __restrict__ idx, const int64_t idx_rs,
+                                              float* __restrict__ val, const int64_t val_rs, float* __restrict__ pairs) {
+    const bool mine = lane < R && sid[lane] >= 0;
+    const float sv = lane < R ? ssc[lane] : 0.0f;
+    const unsigned any_nan = __ballot_sync(0xffffffffu, mine && sv != sv);
+    const unsigned livem = __ballot_sync(0xffffffffu, mine);
+    if (any_nan == 0u) {
+        if (mine) {
+            int ahead = 0;
+            const int32_t id = sid[lane];
+            for (int c = 0; c < R; ++c) {
+                if (!((livem >> c) & 1u) || c == lane) continue;
+                const float so = ssc[c];
+                const int32_t io = sid[c];
+                ahead += (so > sv || (so == sv && (io < id || (io == id && c < lane)))) ? 1 : 0;
+            }
+            idx[m * idx_rs + ahead] = id;
+            val[m * val_rs + ahead] = sv;
+            if (pairs) { float* p = pairs + (m * R + ahead) * 2; p[0] = __int_as_float(id); p[1] = sv; }
+        }
+        const int nl = __popc(livem);
+        if (lane < R && lane >= nl) {
+            idx[m * idx_rs + lane] = -1;
+            val[m * val_rs + lane] = -INFINITY;
+            if (pairs) { float* p = pairs + (m * R + lane) * 2; p[0] = __int_as_float(-1); p[1] = -INFINITY; }
+        }
+        return;
+    }
+    if (lane != 0) return;
+    uint32_t used = 0u;
+    for (int o = 0; o < R; ++o) {
+        int best = -1;
+        for (int c = 0; c < R; ++c) {
+            if (((used >> c) & 1u) || sid[c] < 0) continue;
+            if (best < 0 || ssc[c] > ssc[best] || (ssc[c] == ssc[best] && sid[c] < sid[best])) best = c;
+        }
+        const int32_t oid = best >= 0 ? sid[best] : -1;
+        const float ov = best >= 0 ? ssc[best] : -INFINITY;
+        if (best >= 0) used |= 1u << best;
+        idx[m * idx_rs + o] = oid;
+        val[m * val_rs + o] = ov;
+        if (pairs) {
+            float* p = pairs + (m * R + o) * 2;
+            p[0] = __int_as_float(oid);
+            p[1] = ov;
+        }
+    }
 }
 
 __global__ void __launch_bounds__(32 * kWarps)
@@ -194,57 +261,169 @@ k_logit_rerank_e4m3(const uint8_t* __restrict__ x, int xdt, int64_t x_rs,
         }
     }
     __syncthreads();
-    if (warp == 0) {
-        /* without NaN scores the selection's order is a total order (value descending, lower id first,
-         * earlier slot first; pads last), so a candidate's place is the count of candidates ahead of it */
-        const bool mine = lane < R && sid[lane] >= 0;
-        const float sv = lane < R ? ssc[lane] : 0.0f;
-        const unsigned any_nan = __ballot_sync(0xffffffffu, mine && sv != sv);
-        const unsigned livem = __ballot_sync(0xffffffffu, mine);
-        if (any_nan == 0u) {
-            if (mine) {
-                int ahead = 0;
-                const int32_t id = sid[lane];
-                for (int c = 0; c < R; ++c) {
-                    if (!((livem >> c) & 1u) || c == lane) continue;
-                    const float so = ssc[c];
-                    const int32_t io = sid[c];
-                    ahead += (so > sv || (so == sv && (io < id || (io == id && c < lane)))) ? 1 : 0;
-                }
-                idx[m * idx_rs + ahead] = id;
-                val[m * val_rs + ahead] = sv;
-                if (pairs) { float* p = pairs + (m * R + ahead) * 2; p[0] = __int_as_float(id); p[1] = sv; }
-            }
-            const int nl = __popc(livem);
-            if (lane < R && lane >= nl) {
-                idx[m * idx_rs + lane] = -1;
-                val[m * val_rs + lane] = -INFINITY;
-                if (pairs) { float* p = pairs + (m * R + lane) * 2; p[0] = __int_as_float(-1); p[1] = -INFINITY; }
-            }
-            return;
-        }
-    }
+    if (warp == 0) rerank_select(lane, sid, ssc, R, m, idx, idx_rs, val, val_rs, pairs);
+}
+/* two e4m3 codes -> two f32 by the conversion instruction (e4m3 -> f16 is exact for every code, zeros
+ * keep their sign, S.1111.111 becomes a NaN), then f16 -> f32 */
+__device__ __forceinline__ void e4m3x2_to_f32(uint16_t two, float& lo, float& hi) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(two));
+    asm("cvt.f32.f16 %0, %1;" : "=f"(lo) : "h"((uint16_t)(h2 & 0xffffu)));
+    asm("cvt.f32.f16 %0, %1;" : "=f"(hi) : "h"((uint16_t)(h2 >> 16)));
+}
+
+/* ---- the chain form: whole 128-K blocks, 16-byte aligned head rows.
+ * Warp 0 carries all the row's chains at once, lane = candidate: one FP64 add instruction advances
+ * up to 32 chains, fed from shared memory, so a row costs K dependent adds (8 cycles each) and no
+ * shuffle sits in the chain. Sixteen producer warps form the exact products up to four 128-K chunks
+ * ahead, lane = candidate again: four warps a chunk, each a 32-column quarter of it (one whole
+ * 32-byte sector of the candidate's head row per lane; 8-byte pieces of a sector per warp measured
+ * twice as slow: nine tenths of the issue stalls were waits for those loads), written as
+ * [k][candidate] doubles, which both sides touch without bank conflicts. A ring of four chunk
+ * buffers with a full and an empty barrier each couples the two sides; every wait is bounded. */
+constexpr int kChainWarps = 17;
+constexpr int kChunkK = 128;
+constexpr int kChainBufs = 4;
+constexpr int kChunkDoubles = kChunkK * kMaxR;
+
+__global__ void __launch_bounds__(32 * kChainWarps)
+k_logit_rerank_chain(const uint8_t* __restrict__ x, int xdt, int64_t x_rs,
+                     const uint8_t* __restrict__ codes, int64_t code_rs,
+                     const void* __restrict__ scale, int64_t scale_rs, int br, int sdt,
+                     const int32_t* __restrict__ in, int64_t in_rs,
+                     int32_t* __restrict__ idx, int64_t idx_rs, float* __restrict__ val, int64_t val_rs,
+                     float* __restrict__ pairs, int R, int K, int64_t NV, int64_t voff) {
+    extern __shared__ __align__(16) uint8_t chain_smem[];
+    double* p_s = (double*)chain_smem;                               /* [kChainBufs][128][32] */
+    double* xs = p_s + kChainBufs * kChunkDoubles;                   /* [K], the activation row widened once */
+    uint64_t* full = (uint64_t*)(xs + K);
+    uint64_t* empty = full + kChainBufs;
+    __shared__ int32_t sid[kMaxR];
+    __shared__ float ssc[kMaxR];
+    const int64_t m = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        uint32_t used = 0u;
-        for (int o = 0; o < R; ++o) {
-            int best = -1;
-            for (int c = 0; c < R; ++c) {
-                if (((used >> c) & 1u) || sid[c] < 0) continue;
-                if (best < 0 || ssc[c] > ssc[best] || (ssc[c] == ssc[best] && sid[c] < sid[best])) best = c;
+        for (int b = 0; b < kChainBufs; ++b) { tcdev::mbar_init(&full[b], 4); tcdev::mbar_init(&empty[b], 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int k = threadIdx.x; k < K; k += blockDim.x)
+        xs[k] = (double)(xdt == RAD_F32 ? ((const float*)x)[m * x_rs + k] : bf16_to_f32(((const uint16_t*)x)[m * x_rs + k]));
+    __syncthreads();
+    const int64_t g = lane < R ? (int64_t)in[m * in_rs + lane] : -1;
+    const int64_t local = g - voff;
+    const bool pad = lane >= R || g < 0 || local < 0 || local >= NV;
+    const int nchunk = K >> 7;
+    if (warp == 0) {
+        double acc = 0.0;
+        /* sixteen products are fetched while the sixteen before them are added, across chunk borders
+         * too: the wait for the next chunk and the fetch of its first sixteen sit before the last
+         * sixteen adds of this one. The empty asm statements keep the compiler from sinking a fetch
+         * down to its add, which would put the shared-memory latency into the chain. */
+        double v[16], u[16];
+        bool alive = nchunk > 0 ? __all_sync(0xffffffffu, tcdev::mbar_wait(&full[0], 0u, 52)) : true;
+        if (alive && nchunk > 0) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = p_s[i * kMaxR + lane];
+        }
+        for (int c = 0; c < nchunk && alive; ++c) {
+            const int buf = c % kChainBufs;
+            const double* pb = p_s + buf * kChunkDoubles + lane;
+#pragma unroll 1
+            for (int k0 = 0; k0 < kChunkK - 32; k0 += 32) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) u[i] = pb[(k0 + 16 + i) * kMaxR];
+                asm volatile("" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc = __dadd_rn(acc, v[i]);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = pb[(k0 + 32 + i) * kMaxR];
+                asm volatile("" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc = __dadd_rn(acc, u[i]);
             }
-            const int32_t oid = best >= 0 ? sid[best] : -1;
-            const float ov = best >= 0 ? ssc[best] : -INFINITY;
-            if (best >= 0) used |= 1u << best;
-            idx[m * idx_rs + o] = oid;
-            val[m * val_rs + o] = ov;
-            if (pairs) {
-                float* p = pairs + (m * R + o) * 2;
-                p[0] = __int_as_float(oid);
-                p[1] = ov;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) u[i] = pb[(kChunkK - 16 + i) * kMaxR];
+            asm volatile("" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc = __dadd_rn(acc, v[i]);
+            if (c + 1 < nchunk) {
+                const int nb = (c + 1) % kChainBufs;
+                /* the warp leaves the loop as one: a lane that gave up takes the others with it */
+                alive = __all_sync(0xffffffffu, tcdev::mbar_wait(&full[nb], (uint32_t)(((c + 1) / kChainBufs) & 1), 52));
+                if (alive) {
+                    const double* pn = p_s + nb * kChunkDoubles + lane;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = pn[i * kMaxR];
+                }
+            }
+            asm volatile("" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc = __dadd_rn(acc, u[i]);
+            __syncwarp();
+            if (lane == 0) tcdev::mbar_arrive(&empty[buf]);
+        }
+        if (!alive) acc = __longlong_as_double(0x7ff8000000000000ll);     /* a wait ran out: NaN, status word set */
+        if (lane < R) {
+            sid[lane] = pad ? -1 : (int32_t)g;
+            ssc[lane] = pad ? -INFINITY : (float)acc;
+        }
+        __syncwarp();
+        rerank_select(lane, sid, ssc, R, m, idx, idx_rs, val, val_rs, pairs);
+    } else {
+        /* producer warp w serves the chunks c = grp, grp + 4, ... (grp = w / 4: always ring buffer grp) and
+         * in them the columns [32 sec, 32 sec + 32) (sec = w % 4): a lane reads one whole 32-byte sector of
+         * its candidate's head row per chunk, so no fetched byte is dropped. The codes and the scale of its
+         * next chunk but one are already in registers; the loop is unrolled by two so that a slot is
+         * refilled in place (a register move would wait for the load). */
+        const int w = warp - 1, grp = w >> 2, sec = w & 3;
+        const uint8_t* crow = codes + (pad ? 0 : local) * code_rs + 32 * sec;
+        const int64_t sbase = pad ? 0 : (local / br) * scale_rs;
+        constexpr int kAhead = 2;
+        uint4 ca[kAhead], cb2[kAhead];
+        uint32_t sq[kAhead];
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            const int c = grp + kChainBufs * u;
+            ca[u] = make_uint4(0u, 0u, 0u, 0u); cb2[u] = ca[u]; sq[u] = 0u;
+            if (c < nchunk) {
+                ca[u] = *(const uint4*)(crow + (int64_t)c * kChunkK);
+                cb2[u] = *(const uint4*)(crow + (int64_t)c * kChunkK + 16);
+                sq[u] = ld_scale_raw(scale, sbase + c, sdt);
+            }
+        }
+        bool alive = true;
+        double* pb = p_s + grp * kChunkDoubles + (32 * sec) * kMaxR + lane;
+        for (int j0 = 0; alive; j0 += kAhead) {
+            if (grp + kChainBufs * j0 >= nchunk) break;
+#pragma unroll
+            for (int u = 0; u < kAhead; ++u) {
+                const int j = j0 + u, c = grp + kChainBufs * j;
+                if (c >= nchunk || !alive) break;
+                if (j >= 1) alive = __all_sync(0xffffffffu, tcdev::mbar_wait(&empty[grp], (uint32_t)((j - 1) & 1), 53));
+                if (!alive) break;
+                const double* xb = xs + c * kChunkK + 32 * sec;
+                const uint32_t cw[8] = {ca[u].x, ca[u].y, ca[u].z, ca[u].w, cb2[u].x, cb2[u].y, cb2[u].z, cb2[u].w};
+                const float s0 = scale_of_raw(sq[u], sdt);
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float lo, hi;
+                    e4m3x2_to_f32((uint16_t)(cw[i >> 2] >> (8 * (i & 3))), lo, hi);
+                    pb[i * kMaxR] = pad ? 0.0 : __dmul_rn(xb[i], (double)__fmul_rn(lo, s0));
+                    pb[(i + 1) * kMaxR] = pad ? 0.0 : __dmul_rn(xb[i + 1], (double)__fmul_rn(hi, s0));
+                }
+                __syncwarp();
+                if (lane == 0) tcdev::mbar_arrive(&full[grp]);
+                const int cn = c + kChainBufs * kAhead;
+                if (cn < nchunk) {
+                    ca[u] = *(const uint4*)(crow + (int64_t)cn * kChunkK);
+                    cb2[u] = *(const uint4*)(crow + (int64_t)cn * kChunkK + 16);
+                    sq[u] = ld_scale_raw(scale, sbase + cn, sdt);
+                }
             }
         }
     }
 }
+
 } /* namespace */
 
 int launch_logit_rerank_e4m3(const void* x, int xdt, int64_t x_rs, const void* codes, int64_t code_rs,
@@ -258,6 +437,25 @@ int launch_logit_rerank_e4m3(const void* x, int xdt, int64_t x_rs, const void* c
     const size_t nblk = (size_t)(K >> 7);
     const size_t full = want + (size_t)kMaxR * K + (kMaxR * nblk + 2) * sizeof(float) + 16;
     const bool al16 = ((((uintptr_t)codes) | (uintptr_t)code_rs) & 15) == 0;
+    /* the chain form: whole 128-K blocks, 16-byte aligned head rows, four chunk buffers + the row in shared memory */
+    static const bool chain_off = [] { const char* e = getenv("R3D_RERANK_NO_CHAIN"); return e && *e && *e != '0'; }();
+    const size_t chain_smem = (size_t)kChainBufs * kChunkDoubles * sizeof(double) + 2 * want + 2 * kChainBufs * sizeof(uint64_t);
+    const bool al16c = ((((uintptr_t)codes) | (uintptr_t)code_rs) & 15) == 0;
+    if (!chain_off && al16c && K >= 128 && (K & 127) == 0 && chain_smem <= 227 * 1024) {
+        const int dev = tc_device();
+        if (dev < 0) return RAD_E_DEVICE;
+        static size_t chain_attr[kTcMaxDevices] = {};
+        if (chain_smem > chain_attr[dev]) {
+            if (cudaFuncSetAttribute(k_logit_rerank_chain, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)chain_smem) != cudaSuccess)
+                return RAD_E_DEVICE;
+            chain_attr[dev] = chain_smem;
+        }
+        count_launch();
+        k_logit_rerank_chain<<<(unsigned)M, 32 * kChainWarps, chain_smem, st>>>(
+            (const uint8_t*)x, xdt, x_rs, (const uint8_t*)codes, code_rs, scale, scale_rs, br, sdt, in, in_rs, idx, idx_rs,
+            val, val_rs, pairs, R, K, NV, voff);
+        return cudaGetLastError() == cudaSuccess ? RAD_OK : RAD_E_DEVICE;
+    }
     int mode = want <= 48 * 1024 ? 1 : 0;               /* larger rows are read through the caches */
     size_t smem = mode ? want : 0;
     if (al16 && K >= 128 && (K & 127) == 0 && full <= 227 * 1024) { mode = 2; smem = full; }
