@@ -903,16 +903,21 @@ def main():
         graph = _record(lambda i: step(i, row, nrot), nrot)
         per_replay = P.lib.r3d_b200_launch_count() - lc
         replays, rem = divmod(steps, nrot)
+        lc = P.lib.r3d_b200_launch_count()
+        graph_rem = _record(lambda i: step(i, row, nrot), rem) if rem else None      # the last, shorter pass
+        per_rem = P.lib.r3d_b200_launch_count() - lc
         for _ in range(3):
             graph.replay()
+        if graph_rem is not None:
+            graph_rem.replay()
 
         def run():
             for _ in range(replays):
                 graph.replay()
-            for i in range(rem):
-                step(i, row, nrot)
-        run.keep = graph
-        return run, per_replay * replays
+            if graph_rem is not None:
+                graph_rem.replay()
+        run.keep = (graph, graph_rem)
+        return run, per_replay * replays + per_rem
 
     # ---- device-timed region: exactly `steps` steps, timed `regions` times; the median is the value
     run_main, graph_launches = region_runner(args.row, rot, args.steps)
